@@ -1,0 +1,138 @@
+"""Pins the CPU oracle (numpy restatement and torch port) against vectors
+produced by the reference's own HyenaInferenceEngine / hyena_ops references."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import hyena_oracle as O
+from oracle import torch_port as TP
+
+TOL = {"f32": 2e-6, "bf16": 2.5e-3}   # bf16: single-ulp flips where fp32 sums differ in the last bit
+DT = {"f32": torch.float32, "bf16": torch.bfloat16}
+
+
+def close(a, b, io, scale=1.0):
+    assert a.shape == b.shape, (a.shape, b.shape)
+    err = O.rel_l2(a, b)
+    assert err <= TOL[io] * scale, err
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("L", [1, 2, 50])
+@pytest.mark.parametrize("tag", ["nobias", "bias"])
+def test_featurizer(golden, io, L, tag):
+    k = f"feat_{io}_L{L}_{tag}"
+    u, w, b = golden[k + "_u"], golden[k + "_w"], golden[k + "_b"]
+    z, st = O.featurizer(u, w, b if tag == "bias" else None, io=io)
+    close(z, golden[k + "_z"], io)
+    assert np.array_equal(st.astype(np.float32), golden[k + "_state"])
+    zt, stt = TP.featurizer(torch.from_numpy(u).to(DT[io]), torch.from_numpy(w).to(DT[io]),
+                            torch.from_numpy(b).to(DT[io]) if tag == "bias" else None)
+    assert np.array_equal(zt.float().numpy(), golden[k + "_z"])
+    assert np.array_equal(stt.float().numpy(), golden[k + "_state"])
+
+
+GCG = [(7, 50, "split"), (7, 4, "split"), (4, 33, "interleaved"), (128, 300, "split"),
+       (128, 100, "interleaved"), (7, 40, "column_split"), (128, 200, "column_split")]
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("K,L,layout", GCG)
+def test_gate_conv_gate(golden, io, K, L, layout):
+    k = f"gcg_{io}_K{K}_L{L}_{layout}"
+    z, h, Dp = golden[k + "_z"], golden[k + "_h"], golden[k + "_D"]
+    flip = layout == "column_split"
+    y, st = O.gate_conv_gate(z, h, Dp if K >= 128 else None, 32, K, io=io, layout=layout, num_heads=4,
+                             flip_x1x2=flip, gated_bias=K >= 128)
+    close(y, golden[k + "_y"], io, scale=5.0 if K >= 128 else 1.0)  # reference MR goes through an fp32 FFT
+    assert np.array_equal(st.astype(np.float32), golden[k + "_state"])
+    yt, stt = TP.gate_conv_gate(torch.from_numpy(z).to(DT[io]), torch.from_numpy(h).to(DT[io]),
+                                torch.from_numpy(Dp).to(DT[io]) if K >= 128 else None, 32, K, layout=layout,
+                                num_heads=4, flip=flip, gated_bias=K >= 128)
+    close(yt.float().numpy(), golden[k + "_y"], io, scale=0.5)
+    assert np.array_equal(stt.float().numpy(), golden[k + "_state"])
+    # the "fp32 reference" (no intermediate rounding) stays within the bf16 budget of the mirrored path
+    y32, _ = O.gate_conv_gate(z, h, Dp if K >= 128 else None, 32, K, io=io, layout=layout, num_heads=4,
+                              flip_x1x2=flip, gated_bias=K >= 128, mirror=False)
+    assert O.rel_l2(y32, golden[k + "_y"]) <= (4e-3 if io == "bf16" else 1e-5)
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("L,layout", [(200, "split"), (64, "interleaved")])
+def test_long_conv(golden, io, L, layout):
+    k = f"iir_{io}_L{L}_{layout}"
+    z, lp, R, Dp = golden[k + "_z"], golden[k + "_lp"], golden[k + "_R"], golden[k + "_D"]
+    h = O.modal_filter(lp, R, L)
+    assert O.rel_l2(h, golden[k + "_h"][0]) < 1e-6
+    y, kv = O.long_conv_gate(z, h, Dp, 16, io=io, layout=layout)
+    close(y, golden[k + "_y"], io, scale=5.0)
+    st = O.modal_state(kv, lp)
+    assert O.rel_l2(st, golden[k + "_state"]) < 2e-5   # reference state comes out of a complex64 FFT pair
+    yt, stt = TP.long_conv_gate(torch.from_numpy(z).to(DT[io]), torch.from_numpy(golden[k + "_h"][0]),
+                                torch.from_numpy(Dp).to(DT[io]), 16, layout=layout,
+                                log_poles_d=torch.from_numpy(lp))
+    close(yt.float().numpy(), golden[k + "_y"], io, scale=0.5)
+    assert O.rel_l2(stt.numpy(), golden[k + "_state"]) < 1e-6
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("K,c0,flip,gb", [(3, 2, False, False), (3, 1, False, False), (7, 6, False, False),
+                                          (7, 3, False, False), (128, 127, True, True), (128, 20, True, True)])
+def test_step_fir(golden, io, K, c0, flip, gb):
+    k = f"stepfir_{io}_K{K}_c{c0}"
+    w = golden[k + "_w"]
+    b = golden[k + "_b"] if gb else None
+    st = golden[k + "_state0"]
+    stt = torch.from_numpy(st).to(DT[io])
+    for i in range(3):
+        u = golden[f"{k}_u{i}"]
+        y, st = O.step_fir(u, st, w, bias=b, gated_bias=gb, flip_filter=flip, io=io)
+        close(y, golden[f"{k}_y{i}"], io)
+        assert st.shape == golden[f"{k}_state{i + 1}"].shape
+        assert np.array_equal(st, golden[f"{k}_state{i + 1}"])
+        yt, stt = TP.step_fir(torch.from_numpy(u).to(DT[io]), stt, torch.from_numpy(w).to(DT[io]),
+                              bias=None if b is None else torch.from_numpy(b).to(DT[io]), gated_bias=gb,
+                              flip_filter=flip)
+        assert np.array_equal(stt.numpy(), golden[f"{k}_state{i + 1}"])
+        close(yt.float().numpy(), golden[f"{k}_y{i}"], io)
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+def test_step_iir(golden, io):
+    k = f"stepiir_{io}"
+    lp, R, Dp, st = golden[k + "_lp"], golden[k + "_R"], golden[k + "_D"], golden[k + "_state0"]
+    for i in range(3):
+        y, st = O.step_iir(golden[f"{k}_x2{i}"], golden[f"{k}_x1{i}"], golden[f"{k}_v{i}"], Dp, R, lp, st)
+        # the reference multiplies x1*v in the I/O dtype first; allow that one rounding
+        assert O.rel_l2(y, golden[f"{k}_y{i}"]) <= (3e-3 if io == "bf16" else 2e-6)
+        assert O.rel_l2(st, golden[f"{k}_state{i + 1}"]) <= (3e-3 if io == "bf16" else 2e-6)
+
+
+@pytest.mark.parametrize("K", [7, 128])
+def test_prefill_decode_continuity(golden, K):
+    """The state left by prefill, fed to one decode step, reproduces position L of a
+    prefill over L+1 tokens -- in the reference's vectors and in the oracle."""
+    k = f"cont_K{K}"
+    z, h, Dp = golden[k + "_z"], golden[k + "_h"], golden[k + "_D"]
+    assert O.rel_l2(golden[k + "_ystep"], golden[k + "_yfull_last"]) < 1e-5
+    D, L = 32, z.shape[-1] - 1
+    _, st = O.gate_conv_gate(z[..., :L], h, Dp if K >= 128 else None, D, K, gated_bias=K >= 128)
+    assert np.array_equal(st.astype(np.float32), golden[k + "_state"])
+    q, kk, v = O.select_qkv(z[..., L].astype(np.float64), D)
+    y, st2 = O.step_fir(kk * v, st, O.expand_groups(h, D), bias=Dp if K >= 128 else None,
+                        gated_bias=K >= 128, flip_filter=K >= 128)
+    assert O.rel_l2(y * q, golden[k + "_yfull_last"]) < 1e-5
+    assert np.array_equal(st2, golden[k + "_state2"])
+
+
+@pytest.mark.parametrize("hl", [4, 32, 128])
+def test_hyena_ops_layout(golden, hl):
+    k = f"ops_hl{hl}"
+    y = O.gcg_blgdg(golden[k + "_x"], golden[k + "_B"], golden[k + "_C"], golden[k + "_h"])
+    assert O.rel_l2(y, golden[k + "_y"]) < 2e-6
+    assert O.rel_l2(y, golden[k + "_y_chunked"]) < 2e-6
+    h = golden[k + "_h"]
+    for g in range(h.shape[0]):
+        T, Th = O.toeplitz_pair(h[g, 0, ::-1], 128)
+        assert np.array_equal(T.astype(np.float32), golden[k + "_T"][g])
+        assert np.array_equal(Th.astype(np.float32), golden[k + "_That"][g])
