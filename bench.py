@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Benchmark of the Hyena convolution hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload mr|se|li|decode]
+
+Default workload: Hyena-MR grouped causal FIR prefill, B=4, L=8192, D=4096, bf16 I/O with fp32
+accumulation, 128-tap filters shared by groups of 16 channels, featurizer and gates fused
+(seeded synthetic data).  A step is one pass of the fused block over the whole batch.  With N > 1
+every rank owns one 4096-channel shard of a hidden dimension of 4096*N (channels are independent,
+so there is no collective on the data path) and `value` adds up the tokens of all shards.
+
+Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM; `e2e` goes
+through the public API with pinned host buffers, host<->device copies inside the timed region.
+`--impl reference` times the reference's CPU path (torch F.conv1d / torch.fft restated in
+oracle/torch_port.py) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, L, D, G, K, io, description)
+    "mr": dict(B=4, L=8192, D=4096, G=256, K=128, io="bf16", seed=1,
+               name="hyena_mr_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + 128-tap grouped FIR + gate)"),
+    "se": dict(B=4, L=8192, D=4096, G=256, K=7, io="bf16", seed=1,
+               name="hyena_se_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + 7-tap grouped FIR + gate)"),
+    "li": dict(B=1, L=131072, D=4096, G=256, K=0, io="bf16", seed=2,
+               name="hyena_li_prefill B=1 L=131072 D=4096 bf16 (featurizer3 + gate + 16-pole modal filter + gate)"),
+}
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_inputs(w, device, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(w["seed"])
+    B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
+    p = {}
+    # generated in slices to bound host memory; values ~ N(0, 1)
+    p["u"] = torch.empty(B, L, 3 * D, dtype=dtype)
+    for b in range(B):
+        p["u"][b] = torch.randn(L, 3 * D, generator=g).to(dtype)
+    p["w3"] = (torch.randn(3 * D, 1, 3, generator=g) / 3 ** 0.5).to(dtype)
+    if K > 0:
+        wt = torch.randn(G, 1, K, generator=g) / K ** 0.5
+        if K >= 128:
+            alpha = 0.01 + 0.09 * torch.rand(G, 1, 1, generator=g)
+            wt = wt * torch.exp(-alpha * torch.arange(K)[None, None])
+        p["h"] = wt.to(dtype)
+        p["Dp"] = torch.zeros(D, dtype=dtype) if K >= 128 else None
+    else:
+        p["log_poles"] = torch.log(0.9 + 0.099 * torch.rand(G, 16, generator=g))[..., None]
+        p["theta"] = torch.pi * torch.rand(G, 16, generator=g)
+        p["residues"] = torch.randn(G, 16, generator=g)
+        p["res_im"] = torch.randn(G, 16, generator=g)
+        p["Dp"] = torch.randn(D, generator=g).to(dtype)
+    return p
+
+
+def run_block(name, pc, u=None):
+    """One step through the public API; returns y [B, L, D]."""
+    from vortex_b200 import hyena_ops
+    u = pc["u"] if u is None else u
+    if name == "mr":
+        return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"])[0]
+    if name == "se":
+        return hyena_ops.hyena_se_fwd(u, pc["w3"], None, pc["h"])[0]
+    return hyena_ops.hyena_li_fwd(u, pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"], theta=pc["theta"],
+                                  res_im=pc["res_im"])[0]
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def cpu_baseline(name, w, steps=1):
+    """The reference's CPU path (oracle/torch_port.py) on a bounded channel slice, scaled to the full width."""
+    from oracle import torch_port as TP
+    torch.manual_seed(0)
+    Ds = {"mr": 256, "se": 256, "li": 64}[name]
+    B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
+    Gs = max(1, G * Ds // D)
+    dt = torch.bfloat16
+    u = torch.randn(B, L, 3 * Ds).to(dt)
+    w3 = (torch.randn(3 * Ds, 1, 3) / 3 ** 0.5).to(dt)
+    if K > 0:
+        h = (torch.randn(Gs, 1, K) / K ** 0.5).to(dt)
+        Dp = torch.zeros(Ds, dtype=dt)
+
+        def step():
+            z, _ = TP.featurizer(u, w3)
+            return TP.gate_conv_gate(z, h, Dp if K >= 128 else None, Ds, K, layout="interleaved", gated_bias=K >= 128)[0]
+    else:
+        lp = torch.log(0.9 + 0.099 * torch.rand(Ds, 16, 1))
+        R = torch.randn(Ds, 16)
+        Dp = torch.randn(Ds).to(dt)
+
+        def step():
+            z, _ = TP.featurizer(u, w3)
+            hh = TP.modal_filter(lp, R, L)
+            return TP.long_conv_gate(z, hh, Dp, Ds, layout="interleaved")[0]
+    step()
+    best = float("inf")
+    t_all = time.perf_counter()
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        step()
+        best = min(best, time.perf_counter() - t0)
+        if time.perf_counter() - t_all > 25:
+            break
+    full = best * (D / Ds)
+    return {"value": B * L / full, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{Ds} of {D} channels (B={B}, L={L}), best of up to {steps} passes, scaled by {D // Ds}x; "
+                      f"torch {torch.__version__} F.conv1d/torch.fft on {os.cpu_count()} host cpus"}, best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mr", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
+    w = WORKLOADS[a.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    tokens = w["B"] * w["L"]
+    config = {"workload": w["name"], "seed": w["seed"], "qkv_layout": "interleaved",
+              "sharding": f"channel: each of {world} rank(s) owns {w['D']} hidden channels, no collective",
+              "l2": "inputs (805 MB per step at the default workload) are larger than the 126 MB L2"}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        cb, best = cpu_baseline(a.workload, w, steps=max(1, a.steps))
+        line = {"impl": "reference", "metric": "hyena_prefill_throughput", "value": cb["value"], "unit": "tok/s",
+                "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": best * 1e3 * (w["D"] / 256),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": config, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    p = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), dev)
+    pc = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
+    from vortex_b200 import ops
+
+    for _ in range(a.warmup):
+        y = run_block(a.workload, pc)
+    ops.device_status()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as cs:
+        barrier()
+        ev0.record()
+        for _ in range(a.steps):
+            y = run_block(a.workload, pc)
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / a.steps
+    value = world * tokens / (ms_step * 1e-3)
+
+    # ---- end to end: pinned host input -> device -> kernel -> pinned host output, every step
+    e2e = None
+    if not a.no_e2e:
+        hu = p["u"].pin_memory()
+        hy = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+        du = torch.empty_like(pc["u"])
+        for _ in range(2):
+            du.copy_(hu, non_blocking=True)
+            hy.copy_(run_block(a.workload, pc, du), non_blocking=True)
+        barrier()
+        n_e2e = max(3, min(a.steps, 10))
+        ev0.record()
+        for _ in range(n_e2e):
+            du.copy_(hu, non_blocking=True)
+            hy.copy_(run_block(a.workload, pc, du), non_blocking=True)
+        ev1.record()
+        barrier()
+        ms_e = ev0.elapsed_time(ev1)
+        if dist is not None:
+            t = torch.tensor([ms_e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e = float(t.item())
+        e2e = {"value": world * tokens / (ms_e / n_e2e * 1e-3), "unit": "tok/s",
+               "h2d_bytes_per_step": hu.numel() * hu.element_size(), "d2h_bytes_per_step": hy.numel() * hy.element_size(),
+               "steps": n_e2e}
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = _peaks()
+    algo_bytes = 8 * w["B"] * w["D"] * w["L"]          # 3 reads + 1 write of 2-byte elements per channel and token
+    launches_per_step = LAUNCHES.get(a.workload, 1)
+    achieved = algo_bytes / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": "hyena_prefill_throughput", "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
+        "gpu_launches": launches_per_step * a.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC.get(a.workload), "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": algo_bytes,
+                     "note": "achieved = algorithmic bytes / (timed region / steps); one step = "
+                             f"{launches_per_step} kernel launch(es)"},
+        "e2e": e2e,
+    }
+    if not a.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(a.workload, w, steps=3)[0]
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# kernel launches of ours per step of each workload (no cache outputs requested)
+LAUNCHES = {"mr": 2, "se": 1, "li": 4}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (None until captured)
+NCU_TRAFFIC = {"mr": None, "se": None, "li": None}
+
+if __name__ == "__main__":
+    main()

@@ -160,7 +160,7 @@ def featurizer(u_blc, w, bias=None, io="f32", padding_mask=None, mirror=True):
 
 def gate_conv_gate(z_pre, h, bias, D, fir_length, io="f32", layout="split",
                    num_heads=1, flip_x1x2=False, gated_bias=False,
-                   padding_mask=None, mirror=True):
+                   padding_mask=None, mirror=True, round_input=True):
     """engine.parallel_fir(gate=True, dim_last=False)  (engine.py:150-159,
     174-232, 255-258; caller model.py:271-291).
 
@@ -168,8 +168,10 @@ def gate_conv_gate(z_pre, h, bias, D, fir_length, io="f32", layout="split",
     state kv[..., -(K-1):] (engine.py:256).  K < 128 is the cross-correlation
     path; K >= 128 the FFT/convolution path, where `bias` is the per-channel
     skip and is always applied as bias * kv (engine.py:78).
+    round_input=False keeps z_pre wide (used when the featurizer output is an
+    intermediate of a fused evaluation rather than a materialised tensor).
     """
-    z = round_io(z_pre, io)
+    z = round_io(z_pre, io) if round_input else np.asarray(z_pre, dtype=np.float64)
     q, k, v = select_qkv(z, D, layout, num_heads, flip_x1x2)
     kv = _maybe(k * v, io, mirror)
     hd = expand_groups(h, D)
@@ -357,5 +359,6 @@ def hyena_fused(u_blc, w3, h, bias, D, fir_length, io="f32", layout="interleaved
     state [B, 3D, 2], inner state [B, D, K-1]."""
     z, st0 = featurizer(u_blc, w3, None, io, None, mirror)
     y, st1 = gate_conv_gate(z, h, bias, D, fir_length, io, layout, num_heads,
-                            flip_x1x2, gated_bias=fir_length >= 128, mirror=mirror)
+                            flip_x1x2, gated_bias=fir_length >= 128, mirror=mirror,
+                            round_input=mirror)
     return y.transpose(0, 2, 1), st0, st1

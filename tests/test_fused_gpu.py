@@ -1,0 +1,154 @@
+"""GPU parity of the fused channel-last entry points (hyena_se_fwd / hyena_mr_fwd / hyena_li_fwd and the
+one-launch decode layer) against the CPU oracle, plus size-independent properties at full benchmark size."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import DT, TOL, cuda, make_block, rel_l2, to_np
+from oracle import hyena_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle(p, D, K, io, layout, heads=1, flip=False, mirror=False):
+    return O.hyena_fused(to_np(p["u"]), to_np(p["w3"]), to_np(p["h"]), None if p["Dp"] is None else to_np(p["Dp"]),
+                         D, K, io=io, layout=layout, num_heads=heads, flip_x1x2=flip, mirror=mirror)
+
+
+def _fused(pc, K, layout, heads=1, flip=False, want_state=True):
+    from vortex_b200 import hyena_ops
+    if K >= 128:
+        return hyena_ops.hyena_mr_fwd(pc["u"], pc["w3"], None, pc["h"], pc["Dp"], layout=layout, num_heads=heads,
+                                      flip=flip, want_state=want_state)
+    return hyena_ops.hyena_se_fwd(pc["u"], pc["w3"], None, pc["h"], layout=layout, num_heads=heads, flip=flip,
+                                  want_state=want_state)
+
+
+SE_CASES = [
+    ("f32", 1, 2048, 768, 48, 7, "split", 1, False),         # configuration 1, full size
+    ("bf16", 2, 1000, 256, 16, 7, "interleaved", 1, False),
+    ("bf16", 1, 333, 200, 25, 7, "interleaved", 1, True),    # D not a multiple of the 64-channel slab, odd groups
+    ("f16", 2, 77, 128, 8, 4, "interleaved", 1, False),
+    ("f32", 1, 5, 64, 4, 7, "interleaved", 1, False),        # L < K-1
+    ("f32", 2, 1, 64, 4, 7, "split", 1, False),              # single token
+    ("bf16", 1, 600, 256, 16, 7, "column_split", 2, True),
+    ("f32", 1, 129, 128, 128, 16, "split", 1, False),        # longest CUDA-core filter, per-channel taps
+]
+
+
+@pytest.mark.parametrize("io,B,L,D,G,K,layout,heads,flip", SE_CASES)
+def test_fused_se_vs_oracle(io, B, L, D, G, K, layout, heads, flip):
+    from vortex_b200 import ops
+    p = make_block(31, B, L, D, G, K, io)
+    ref, fs_ref, st_ref = _oracle(p, D, K, io, layout, heads, flip)
+    y, fs, st = _fused(cuda(p), K, layout, heads, flip)
+    ops.device_status()
+    assert y.shape == (B, L, D) and y.dtype == DT[io]
+    assert rel_l2(y, ref) <= TOL[io]
+    assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))     # copy of the last inputs: bit-exact
+    assert st.shape == st_ref.shape
+    assert rel_l2(st, st_ref) <= (1e-6 if io == "f32" else 2.5e-3)   # k*v rounded once to the I/O dtype
+
+
+def test_fused_se_exact_on_integers():
+    """Small-integer data makes every intermediate exact: fused output and caches equal the oracle bit
+    for bit, for every q/k/v layout -- pins the channel maps, tap order, halo handling and cache indexing."""
+    g = torch.Generator().manual_seed(5)
+    B, L, D, G, K = 2, 700, 128, 8, 7
+    u = torch.randint(-2, 3, (B, L, 3 * D), generator=g).float()
+    w3 = torch.randint(-1, 2, (3 * D, 1, 3), generator=g).float()
+    h = torch.randint(-1, 2, (G, 1, K), generator=g).float()
+    p = {"u": u, "w3": w3, "h": h, "Dp": None}
+    for layout, heads, flip in (("split", 1, False), ("interleaved", 1, False), ("interleaved", 1, True),
+                                ("column_split", 2, False)):
+        ref, fs_ref, st_ref = _oracle(p, D, K, "f32", layout, heads, flip, mirror=True)
+        y, fs, st = _fused(cuda(p), K, layout, heads, flip)
+        assert np.array_equal(to_np(y), ref.astype(np.float32)), layout
+        assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
+        assert np.array_equal(to_np(st), st_ref.astype(np.float32))
+
+
+def test_fused_se_full_size_properties():
+    """Configuration-2-sized input (B=4, L=8192, D=4096, bf16) through the SE kernel: oracle on a slice of
+    channels, causality, and channel-shard invariance (a shard of channels computed alone is bit-identical)."""
+    from vortex_b200 import hyena_ops
+    B, L, D, G, K = 4, 8192, 4096, 256, 7
+    p = make_block(1, B, L, D, G, K, "bf16")
+    pc = cuda(p)
+    y, _, _ = hyena_ops.hyena_se_fwd(pc["u"], pc["w3"], None, pc["h"])
+    # (1) oracle on channels [1024, 1088) of batch 1 and 3
+    d0, d1 = 1024, 1088
+    sub = {"u": p["u"][1::2, :, 3 * d0:3 * d1], "w3": p["w3"][3 * d0:3 * d1], "h": p["h"][d0 // 16:d1 // 16], "Dp": None}
+    ref, _, _ = _oracle(sub, d1 - d0, K, "bf16", "interleaved")
+    assert rel_l2(y[1::2, :, d0:d1], ref) <= TOL["bf16"]
+    # (2) shard invariance: the same 512 channels computed as their own problem give identical bits
+    c0, c1 = 2048, 2560
+    ys, _, _ = hyena_ops.hyena_se_fwd(pc["u"][:, :, 3 * c0:3 * c1].contiguous(), pc["w3"][3 * c0:3 * c1], None,
+                                      pc["h"][c0 // 16:c1 // 16])
+    assert torch.equal(ys, y[:, :, c0:c1])
+    # (3) causality: changing the input from t0 on leaves every earlier output untouched
+    t0 = 5000
+    u2 = pc["u"].clone()
+    u2[:, t0:] = -u2[:, t0:]
+    y2, _, _ = hyena_ops.hyena_se_fwd(u2, pc["w3"], None, pc["h"])
+    assert torch.equal(y2[:, :t0], y[:, :t0]) and not torch.equal(y2[:, t0:], y[:, t0:])
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("kind", ["se", "mr", "li"])
+def test_decode_layer_matches_step_sequence(io, kind):
+    """One-launch decode layer == the reference's sequence step_fir -> interleave/split -> step_fir|step_iir -> gate
+    (model.py:318-375), run here through the drop-in engine; caches bit-identical, outputs to rounding."""
+    from vortex_b200 import HyenaInferenceEngine, ops
+    eng = HyenaInferenceEngine()
+    B, D, G = 3, 96, 6
+    K = {"se": 7, "mr": 128, "li": 0}[kind]
+    g = torch.Generator().manual_seed(17)
+    dt = DT[io]
+    w3 = (torch.randn(3 * D, 1, 3, generator=g) / 3 ** 0.5).to(dt).cuda()
+    fs = torch.randn(B, 3 * D, 2, generator=g).to(dt).cuda()
+    Dp = torch.randn(D, generator=g).to(dt).cuda()
+    if kind == "li":
+        lp = torch.log(0.9 + 0.099 * torch.rand(D, 16, 1, generator=g)).cuda()
+        R = torch.randn(D, 16, generator=g).cuda()
+        st = torch.randn(B, D, 16, generator=g).cuda()
+    else:
+        h = (torch.randn(G, 1, K, generator=g) / K ** 0.5).to(dt).cuda()
+        st = torch.randn(B, D, K - 1, generator=g).to(dt).cuda()
+    fs_a, st_a, fs_b, st_b = fs, st, fs, st
+    for step in range(3):
+        u = torch.randn(B, 3 * D, generator=g).to(dt).cuda()
+        # reference sequence on the drop-in engine
+        z, fs_a = eng.step_fir(u, fs_a, w3)
+        q, k, v = z[:, 0::3], z[:, 1::3], z[:, 2::3]
+        if kind == "li":
+            ya, st_a = eng.step_iir(q, k, v, Dp, R, lp, st_a)
+            ya = ya.to(dt)
+            yb, fs_b, st_b = ops.decode_layer(u, w3, None, fs_b, D, log_poles=lp, residues=R, bias=Dp, iir_state=st_b)
+        else:
+            ya, st_a = eng.step_fir(k * v, st_a, h.repeat_interleave(D // G, 0), bias=Dp if K >= 128 else None,
+                                    flip_filter=K >= 128, gated_bias=K >= 128)
+            ya = ya * q
+            yb, fs_b, st_b = ops.decode_layer(u, w3, None, fs_b, D, h=h, inner_state=st_b,
+                                              bias=Dp if K >= 128 else None, flip_filter=K >= 128, gated_bias=K >= 128)
+        assert yb.dtype == dt and fs_b.dtype == torch.float32 and st_b.dtype == torch.float32
+        assert torch.equal(fs_a, fs_b)
+        assert rel_l2(yb, ya) <= (1e-6 if io == "f32" else 4e-3)
+        assert rel_l2(st_b, st_a) <= 1e-6
+
+
+def test_fused_li_vs_oracle():
+    from vortex_b200 import hyena_ops
+    B, L, D, S = 2, 900, 64, 16
+    for io in ("f32", "bf16"):
+        p = make_block(41, B, L, D, D, 0, io, modal=True, S=S)
+        pc = cuda(p)
+        y, fs, st = hyena_ops.hyena_li_fwd(pc["u"], pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"],
+                                           want_state=True)
+        zf, fs_ref = O.featurizer(to_np(p["u"]), to_np(p["w3"]), io=io, mirror=True)
+        h = O.modal_filter(to_np(p["log_poles"]), to_np(p["residues"]), L)
+        ref, kv = O.long_conv_gate(zf, h, to_np(p["Dp"]), D, io=io, layout="interleaved", mirror=False)
+        assert y.shape == (B, L, D)
+        assert rel_l2(y, ref) <= (1e-4 if io == "f32" else 3.5e-3)   # two-kernel path materialises z in the I/O dtype
+        assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
+        assert rel_l2(st, O.modal_state(O.round_io(kv, io), to_np(p["log_poles"]))) <= (1e-5 if io == "f32" else 2e-3)

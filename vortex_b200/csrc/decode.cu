@@ -1,0 +1,226 @@
+// Decode-time (one token) kernels: FIR shift-register step, modal IIR step,
+// and the whole per-layer sequence in one launch.  All of them are pure HBM
+// streaming over the caches; a row (one batch element, one channel) is served
+// by LPR cooperating lanes so that long rows (Hyena-MR: 127 cached samples)
+// are read and rewritten coalesced, with a shuffle reduction over the taps.
+#include "common.cuh"
+
+namespace vtx {
+
+// Sum over the LPR lanes of a row.  The mask names only the lanes of this row's group, so the
+// groups of a warp may diverge from one another (e.g. when the last rows of a launch are absent).
+template <int LPR>
+__device__ __forceinline__ float group_sum(float x) {
+    if (LPR > 1) {
+        const unsigned group = (threadIdx.x % 32) / LPR;
+        const unsigned mask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (group * LPR));
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) x += __shfl_xor_sync(mask, x, o);
+    }
+    return x;
+}
+
+// One FIR step on a row.  Returns the filter output (before bias) on every lane of the group.
+//   state_in [c] (any dtype), taps w [K] of the row's group, new sample u.
+//   state_out fp32 [min(c+1, K-1)].
+template <int LPR>
+__device__ __forceinline__ float fir_row_step(const void* state_in, int64_t sdt, int64_t row_off, int c, int K,
+                                              const void* w, int64_t wdt, int64_t w_off, bool flip, float u,
+                                              float* state_out, int lane) {
+    const bool grow = c < K - 1;
+    const int c_out = grow ? c + 1 : c;
+    float acc = 0.f;
+    for (int i = lane; i < c; i += LPR) {
+        float s = ld_param(state_in, sdt, row_off + i);
+        float tap = ld_param(w, wdt, w_off + (flip ? c - i : i));
+        acc = fmaf(s, tap, acc);
+        int o = grow ? i : i - 1;
+        if (o >= 0) state_out[o] = s;
+    }
+    acc = group_sum<LPR>(acc);
+    float tap_u = ld_param(w, wdt, w_off + (flip ? 0 : c));
+    if (lane == 0 && c_out > 0) state_out[c_out - 1] = u;
+    return fmaf(tap_u, u, acc);
+}
+
+template <typename T, int LPR>
+__global__ void __launch_bounds__(256) step_fir_kernel(vtx_step_fir_params p) {
+    const int lane = threadIdx.x % LPR;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+    if (row >= p.B * p.C) return;   // whole groups leave together (blockDim % LPR == 0)
+    const int64_t ch = row % p.C;
+    const int c = (int)p.c, K = (int)p.K;
+    const int c_out = c < K - 1 ? c + 1 : c;
+    const float u = to_f32<T>(static_cast<const T*>(p.u)[row]);
+    float y = fir_row_step<LPR>(p.state_in, p.state_dtype, row * c, c, K, p.w, p.w_dtype,
+                                (ch / (p.C / p.Gw)) * K, p.flip_filter != 0, u, p.state_out + row * c_out, lane);
+    if (lane == 0) {
+        if (p.bias_mode != VTX_BIAS_NONE) {
+            float b = ld_param(p.bias, p.bias_dtype, ch);
+            y = p.bias_mode == VTX_BIAS_GATED ? fmaf(b, u, y) : y + b;
+        }
+        static_cast<T*>(p.y)[row] = from_f32<T>(y);
+    }
+}
+
+// sigma <- p sigma + kv for the 16 lanes of a row; returns sum_s Re(R sigma) on every lane.
+__device__ __forceinline__ float iir_row_step(const vtx_modal_params& m, int64_t g, const float* st_in,
+                                              float* st_out, float kv, int lane) {
+    float part = 0.f;
+    if (lane < m.S) {
+        const int64_t gi = g * m.S + lane;
+        float mag = expf(static_cast<const float*>(m.log_poles)[gi]);
+        float rr = static_cast<const float*>(m.res_re)[gi];
+        if (m.theta) {
+            float sn, cs;
+            sincosf(static_cast<const float*>(m.theta)[gi], &sn, &cs);
+            float pr = mag * cs, pi = mag * sn;
+            float ri = m.res_im ? static_cast<const float*>(m.res_im)[gi] : 0.f;
+            float2 s = reinterpret_cast<const float2*>(st_in)[lane];
+            float nr = fmaf(pr, s.x, fmaf(-pi, s.y, kv));
+            float ni = fmaf(pr, s.y, pi * s.x);
+            reinterpret_cast<float2*>(st_out)[lane] = make_float2(nr, ni);
+            part = rr * nr - ri * ni;
+        } else {
+            float s = fmaf(mag, st_in[lane], kv);
+            st_out[lane] = s;
+            part = rr * s;
+        }
+    }
+    return group_sum<16>(part);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) step_iir_kernel(vtx_step_iir_params p) {
+    const int lane = threadIdx.x % 16;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 16;
+    if (row >= p.B * p.D) return;
+    const int64_t d = row % p.D;
+    const int64_t ss = p.modal.S * (p.modal.theta ? 2 : 1);
+    float q = to_f32<T>(static_cast<const T*>(p.q)[row]);
+    float kv = round_io<T>(to_f32<T>(static_cast<const T*>(p.k)[row]) * to_f32<T>(static_cast<const T*>(p.v)[row]));
+    float res = iir_row_step(p.modal, d / (p.D / p.modal.G), p.state_in + row * ss, p.state_out + row * ss, kv, lane);
+    if (lane == 0) {
+        float b = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+        p.y[row] = q * fmaf(b, kv, res);
+    }
+}
+
+// Whole layer.  LPR lanes per (batch, hidden channel); MODE 0 = FIR inner filter, 1 = modal IIR.
+template <typename T, int LPR, int MODE>
+__global__ void __launch_bounds__(256) decode_layer_kernel(vtx_decode_layer_params p) {
+    const int lane = threadIdx.x % LPR;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+    if (row >= p.B * p.D) return;
+    const int64_t b = row / p.D, d = row % p.D;
+    QkvMap map{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? p.D / p.num_heads : p.D};
+    int64_t ch[3];
+    map.get(d, ch[0], ch[1], ch[2]);
+    const int K3 = (int)p.K3, c3 = K3 - 1;
+    const T* u = static_cast<const T*>(p.u) + b * 3 * p.D;
+    float z[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        // featurizer step (engine.step_fir, not flipped, full cache): taps w3[c, :], newest last
+        const int64_t c = ch[i], so = (b * 3 * p.D + c) * c3;
+        float x = to_f32<T>(u[c]);
+        float acc = ld_param(p.w3, p.w3_dtype, c * K3 + c3) * x;
+        for (int j = 0; j < c3; ++j) {
+            float s = ld_param(p.fir_state_in, p.fir_state_dtype, so + j);
+            acc = fmaf(s, ld_param(p.w3, p.w3_dtype, c * K3 + j), acc);
+            if (lane == 0 && j > 0) p.fir_state_out[so + j - 1] = s;
+        }
+        if (lane == 0 && c3 > 0) p.fir_state_out[so + c3 - 1] = x;
+        if (p.b3) acc += ld_param(p.b3, p.b3_dtype, c);
+        z[i] = round_io<T>(acc);
+    }
+    const float q = z[0];
+    const float kv = round_io<T>(z[1] * z[2]);
+    const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+    float y;
+    if (MODE == 0) {
+        const int K = (int)p.K, c = K - 1;
+        float f = fir_row_step<LPR>(p.inner_state_in, p.inner_state_dtype, row * c, c, K, p.h, p.h_dtype,
+                                    (d / (p.D / p.G)) * K, p.flip_filter != 0, kv, p.inner_state_out + row * c, lane);
+        if (p.bias_mode == VTX_BIAS_GATED) f = fmaf(bias, kv, f);
+        else if (p.bias_mode == VTX_BIAS_ADD) f += bias;
+        y = round_io<T>(f) * q;
+    } else {
+        const int64_t ss = p.modal.S * (p.modal.theta ? 2 : 1);
+        float res = iir_row_step(p.modal, d / (p.D / p.modal.G), p.iir_state_in + row * ss,
+                                 p.iir_state_out + row * ss, kv, lane);
+        y = q * fmaf(bias, kv, res);
+    }
+    if (lane == 0) static_cast<T*>(p.y)[row] = from_f32<T>(y);
+}
+
+}  // namespace vtx
+
+extern "C" int vtx_step_fir(const vtx_step_fir_params* p, void* stream) {
+    using namespace vtx;
+    VTX_REQUIRE(p && p->u && p->w && p->y, VTX_ERR_BAD_ARG, "step_fir: null pointer");
+    VTX_REQUIRE(p->B > 0 && p->C > 0 && p->K > 0 && p->Gw > 0, VTX_ERR_BAD_ARG, "step_fir: sizes must be positive");
+    VTX_REQUIRE(p->C % p->Gw == 0, VTX_ERR_BAD_ARG, "step_fir: C not a multiple of the filter count");
+    VTX_REQUIRE(p->c >= 0 && p->c <= p->K - 1, VTX_ERR_BAD_ARG, "step_fir: cache length %lld outside [0, K-1]",
+                (long long)p->c);
+    VTX_REQUIRE(p->c == 0 || p->state_in, VTX_ERR_BAD_ARG, "step_fir: null state_in");
+    VTX_REQUIRE(p->K == 1 || p->state_out, VTX_ERR_BAD_ARG, "step_fir: null state_out");
+    VTX_REQUIRE((const void*)p->state_out != p->state_in || !p->state_in, VTX_ERR_BAD_ARG,
+                "step_fir: state_out aliases state_in");
+    VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || p->bias, VTX_ERR_BAD_ARG, "step_fir: bias mode set without a bias");
+    const int64_t rows = p->B * p->C;
+    cudaStream_t s = (cudaStream_t)stream;
+    VTX_DISPATCH_IO(p->io_dtype, T, {
+        if (p->c > 16) step_fir_kernel<T, 32><<<(unsigned)ceil_div<int64_t>(rows * 32, 256), 256, 0, s>>>(*p);
+        else step_fir_kernel<T, 1><<<(unsigned)ceil_div<int64_t>(rows, 256), 256, 0, s>>>(*p);
+    });
+    return check_launch("step_fir");
+}
+
+extern "C" int vtx_step_iir(const vtx_step_iir_params* p, void* stream) {
+    using namespace vtx;
+    VTX_REQUIRE(p && p->q && p->k && p->v && p->y && p->state_in && p->state_out, VTX_ERR_BAD_ARG,
+                "step_iir: null pointer");
+    VTX_REQUIRE(p->B > 0 && p->D > 0, VTX_ERR_BAD_ARG, "step_iir: sizes must be positive");
+    VTX_REQUIRE(p->modal.log_poles && p->modal.res_re && p->modal.G > 0 && p->modal.S > 0, VTX_ERR_BAD_ARG,
+                "step_iir: bad modal parameters");
+    VTX_REQUIRE(p->D % p->modal.G == 0, VTX_ERR_BAD_ARG, "step_iir: D not a multiple of the number of modal systems");
+    VTX_REQUIRE(p->modal.S <= 16, VTX_ERR_UNSUPPORTED, "step_iir: state size %lld > 16", (long long)p->modal.S);
+    const int64_t rows = p->B * p->D;
+    VTX_DISPATCH_IO(p->io_dtype, T,
+                    step_iir_kernel<T><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, (cudaStream_t)stream>>>(*p));
+    return check_launch("step_iir");
+}
+
+extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) {
+    using namespace vtx;
+    VTX_REQUIRE(p && p->u && p->w3 && p->y, VTX_ERR_BAD_ARG, "decode_layer: null pointer");
+    VTX_REQUIRE(p->B > 0 && p->D > 0 && p->K3 >= 1 && p->K3 <= 8 && p->K >= 0, VTX_ERR_BAD_ARG,
+                "decode_layer: bad sizes");
+    VTX_REQUIRE(p->K3 == 1 || (p->fir_state_in && p->fir_state_out), VTX_ERR_BAD_ARG, "decode_layer: null fir state");
+    VTX_REQUIRE((const void*)p->fir_state_out != p->fir_state_in, VTX_ERR_BAD_ARG,
+                "decode_layer: fir_state_out aliases fir_state_in");
+    VTX_REQUIRE(p->layout != VTX_QKV_COLUMN_SPLIT || (p->num_heads > 0 && p->D % p->num_heads == 0), VTX_ERR_BAD_ARG,
+                "decode_layer: column split needs num_heads dividing D");
+    const int64_t rows = p->B * p->D;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p->K > 0) {
+        VTX_REQUIRE(p->h && p->G > 0 && p->D % p->G == 0, VTX_ERR_BAD_ARG, "decode_layer: bad filter arguments");
+        VTX_REQUIRE(p->K == 1 || (p->inner_state_in && p->inner_state_out), VTX_ERR_BAD_ARG,
+                    "decode_layer: null inner state");
+        VTX_REQUIRE((const void*)p->inner_state_out != p->inner_state_in, VTX_ERR_BAD_ARG,
+                    "decode_layer: inner_state_out aliases inner_state_in");
+        VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || p->bias, VTX_ERR_BAD_ARG, "decode_layer: bias mode without a bias");
+        VTX_DISPATCH_IO(p->io_dtype, T, {
+            if (p->K > 17) decode_layer_kernel<T, 32, 0><<<(unsigned)ceil_div<int64_t>(rows * 32, 256), 256, 0, s>>>(*p);
+            else decode_layer_kernel<T, 1, 0><<<(unsigned)ceil_div<int64_t>(rows, 256), 256, 0, s>>>(*p);
+        });
+    } else {
+        VTX_REQUIRE(p->modal.log_poles && p->modal.res_re && p->modal.G > 0 && p->modal.S > 0 && p->modal.S <= 16 &&
+                        p->D % p->modal.G == 0 && p->iir_state_in && p->iir_state_out,
+                    VTX_ERR_BAD_ARG, "decode_layer: bad modal arguments");
+        VTX_DISPATCH_IO(p->io_dtype, T,
+                        decode_layer_kernel<T, 16, 1><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, s>>>(*p));
+    }
+    return check_launch("decode_layer");
+}

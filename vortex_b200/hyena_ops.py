@@ -1,0 +1,87 @@
+"""The ``hyena_ops`` surface: fused forward entry points and the (x, B, C, h) convention.
+
+``hyena_se_fwd`` / ``hyena_mr_fwd`` / ``hyena_li_fwd`` are the names the reference's model code
+tries to import (``vortex/model/layers.py:18-21``) without ever defining them; here they take the
+projection output ``u [B, L, 3D]`` (channel-last, before the featurizer) and run the whole Hyena
+block.  ``gcg_fwd`` follows the reference's gate-conv-gate convention
+(``vortex/ops/hyena_se/fwd.py:56-64``, math in ``vortex/ops/hyena_se/ref_fwd.py:80-127``):
+``y = C * xcorr(h_g, B * x)`` on ``(bs, l, g, dg)`` tensors with blocked filter sharing.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from ._lib import BIAS_ADD, BIAS_GATED, BIAS_NONE, TAPS_CONV, TAPS_XCORR
+
+
+def _general_fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state):
+    """Any filter length / dtype: featurizer kernel (channel-last -> channel-first) followed by the
+    general gate-FIR-gate kernel writing channel-last.  Two launches, z materialised once."""
+    D = u.shape[-1] // 3
+    z, fs = ops.featurizer_fwd(u, w3, b3, None, want_state=want_state)
+    y, st = ops.gcg_fwd(z, h, D_skip, D, taps=taps, bias_mode=bias_mode, layout=layout, num_heads=num_heads,
+                        flip=flip, want_state=want_state, round_kv=True, channel_last_out=True)
+    return y, fs, st
+
+
+def _fused_ok(u, h, layout, num_heads):
+    """Shapes the single-pass CUDA-core kernel takes (see vtx_fused_fir_fwd in include/vortex_b200.h)."""
+    D = u.shape[-1] // 3
+    es = u.element_size()
+    if h.shape[-1] > 16 or D % 2 or (u.stride(1) * es) % 16 or u.stride(2) != 1 or u.data_ptr() % 16:
+        return False
+    if layout != "interleaved" and (D * es) % 16:
+        return False
+    if layout == "column_split" and (D // num_heads) % 64:
+        return False
+    return True
+
+
+def hyena_se_fwd(u, short_filter_weight, short_filter_bias, h, *, layout="interleaved", num_heads=1, flip=False,
+                 want_state=False):
+    """Hyena-SE block (inner filter shorter than 128 taps, cross-correlation taps, no skip term).
+    u [B, L, 3D] -> y [B, L, D] (+ featurizer cache [B, 3D, 2], inner cache [B, D, K-1])."""
+    D = u.shape[-1] // 3
+    if not _fused_ok(u, h, layout, num_heads):
+        return _general_fir_block(u, short_filter_weight, short_filter_bias, h, None, TAPS_XCORR, BIAS_NONE, layout,
+                                  num_heads, flip, want_state)
+    return ops.fused_fir_fwd(u, short_filter_weight, short_filter_bias, h, None, D, taps=TAPS_XCORR,
+                             bias_mode=BIAS_NONE, layout=layout, num_heads=num_heads, flip=flip, want_state=want_state)
+
+
+def hyena_mr_fwd(u, short_filter_weight, short_filter_bias, h, D_skip, *, layout="interleaved", num_heads=1,
+                 flip=False, want_state=False):
+    """Hyena-MR block (128-tap grouped filter, convolution taps, per-channel skip term D_skip)."""
+    return _general_fir_block(u, short_filter_weight, short_filter_bias, h, D_skip, TAPS_CONV, BIAS_GATED, layout,
+                              num_heads, flip, want_state)
+
+
+def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues, D_skip, *, theta=None, res_im=None,
+                 layout="interleaved", num_heads=1, flip=False, want_state=False):
+    """Hyena-LI block (modal long filter).  u [B, L, 3D] -> y [B, L, D], featurizer cache, modal state
+    fp32 [B, D, S] (complex poles: [B, D, S, 2])."""
+    D = u.shape[-1] // 3
+    z, fs = ops.featurizer_fwd(u, short_filter_weight, short_filter_bias, None, want_state=want_state)
+    y, st = ops.iir_fwd(z, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads, flip=flip, theta=theta,
+                        res_im=res_im, want_state=want_state, round_kv=True)
+    return y.permute(0, 2, 1), fs, st
+
+
+def gcg_fwd(x, B, C, h, bias=None, gated_bias=False):
+    """y = C * xcorr(h_g, B * x) for (bs, l, g, dg) tensors, h (g, 1, hl); returns (bs, l, g, dg)."""
+    bs, l, g, dg = x.shape
+    to_bdl = lambda t: t.reshape(bs, l, g * dg).permute(0, 2, 1).contiguous()  # noqa: E731
+    y, _ = ops.gcg_fwd_bdl(to_bdl(C), to_bdl(B), to_bdl(x), h, bias, taps=TAPS_XCORR,
+                           bias_mode=BIAS_NONE if bias is None else (BIAS_GATED if gated_bias else BIAS_ADD),
+                           round_kv=True)
+    return y.permute(0, 2, 1).reshape(bs, l, g, dg)
+
+
+def hyena_se_bdl(x, k, q, h, bias=None, gated_bias=False):
+    """The 'bdl' form of the reference's ``inner_hyena_se_ref`` (``vortex/ops/hyena_se/interface.py:342-397``):
+    y = q * causal_conv(h, k * x) with (b, d, l) operands and h (g, 1, hl)."""
+    y, _ = ops.gcg_fwd_bdl(q, k, x, h, bias, taps=TAPS_XCORR,
+                           bias_mode=BIAS_NONE if bias is None else (BIAS_GATED if gated_bias else BIAS_ADD),
+                           round_kv=True)
+    return y

@@ -1,0 +1,358 @@
+"""Tensor-level wrappers over the C ABI.
+
+torch is used for device memory and streams only: every function here allocates its outputs
+with torch, hands raw pointers to ``libvortex_b200.so`` on the current stream of the input's
+device, and returns.  CPU tensors are rejected -- there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (BF16, BIAS_ADD, BIAS_GATED, BIAS_NONE, F16, F32, QKV_COLUMN_SPLIT, QKV_INTERLEAVED,
+                   QKV_SPLIT, TAPS_CONV, TAPS_XCORR)
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+LAYOUTS = {"split": QKV_SPLIT, "interleaved": QKV_INTERLEAVED, "column_split": QKV_COLUMN_SPLIT}
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"vortex_b200: unsupported dtype {t.dtype}") from None
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("vortex_b200 kernels need CUDA tensors (there is no CPU path)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _param(t: Optional[torch.Tensor], like: torch.Tensor) -> Optional[torch.Tensor]:
+    """Parameters are read with their own dtype; make them dense and co-located."""
+    if t is None:
+        return None
+    t = t.detach()
+    if t.device != like.device:
+        raise RuntimeError("vortex_b200: parameter on a different device than the activations")
+    if t.dtype not in _DT:
+        t = t.float()
+    return t.contiguous()
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+class _on:
+    """Make the tensor's device current for the duration of a call."""
+
+    def __init__(self, t):
+        self.g = torch.cuda.device(t.device)
+
+    def __enter__(self):
+        self.g.__enter__()
+
+    def __exit__(self, *a):
+        self.g.__exit__(*a)
+
+
+def device_status() -> None:
+    """Raise if a kernel recorded that one of its bounded waits ran out (synchronises)."""
+    torch.cuda.synchronize()
+    _lib.check(_lib.lib().vtx_device_status())
+
+
+# ----------------------------------------------------------------------------------------------
+def featurizer_fwd(u_blc: torch.Tensor, w: torch.Tensor, bias=None, mask=None, want_state=True):
+    """u_blc: logical [B, L, C] (any strides).  Returns z [B, C, L] and state [B, C, min(L,K-1)] or None."""
+    _need_cuda(u_blc, w, bias, mask)
+    B, L, Cc = u_blc.shape
+    w = _param(w, u_blc).reshape(Cc, -1)
+    K = w.shape[1]
+    bias, mask = _param(bias, u_blc), _param(mask, u_blc)
+    z = torch.empty(B, Cc, L, device=u_blc.device, dtype=u_blc.dtype)
+    ns = min(L, K - 1)
+    state = torch.empty(B, Cc, ns, device=u_blc.device, dtype=u_blc.dtype) if want_state else None
+    p = _lib.FeaturizerParams(
+        u=_ptr(u_blc), u_stride_b=u_blc.stride(0), u_stride_l=u_blc.stride(1), u_stride_c=u_blc.stride(2),
+        w=_ptr(w), w_dtype=_code(w), bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        mask=_ptr(mask), mask_dtype=_code(mask) if mask is not None else 0, z=_ptr(z),
+        state=_ptr(state) if (state is not None and ns > 0) else None, B=B, L=L, C=Cc, K=K, io_dtype=_code(u_blc))
+    with _on(u_blc):
+        _lib.check(_lib.lib().vtx_featurizer_fwd(C.byref(p), _stream(u_blc)))
+    return z, state
+
+
+def _qkv_views(z: torch.Tensor, D: int, layout: str, num_heads: int, flip: bool):
+    """z [B, 3D, L] (time stride 1) -> ((q,k,v) tensors sharing storage, head_dim, per-stream (stride_h, stride_d))."""
+    sc = z.stride(1)
+    if layout == "split":
+        views = (z[:, :D], z[:, D:2 * D], z[:, 2 * D:])
+        hd, strides = D, (0, sc)
+    elif layout == "interleaved":
+        views = (z[:, 0::3], z[:, 1::3], z[:, 2::3])
+        hd, strides = D, (0, 3 * sc)
+    elif layout == "column_split":
+        hd = D // num_heads
+        views = (z[:, 0:], z[:, hd:], z[:, 2 * hd:])   # base pointers; channel d -> head d//hd, lane d%hd
+        strides = (3 * hd * sc, sc)
+    else:
+        raise ValueError(f"unknown q/k/v layout {layout!r}")
+    q, k, v = views
+    if flip:
+        q, k = k, q
+    return (q, k, v), hd, strides
+
+
+def gcg_fwd(z_pre: torch.Tensor, h: torch.Tensor, bias, D: int, *, taps: int, bias_mode: int, layout="split",
+            num_heads=1, flip=False, mask=None, want_state=True, round_kv=True, channel_last_out=False):
+    """Gate -> grouped FIR -> gate on the packed channel-first tensor z_pre [B, 3D, L].
+
+    Returns y [B, D, L] (or [B, L, D] when channel_last_out) and state [B, D, min(L, K-1)] or None."""
+    _need_cuda(z_pre, h, bias, mask)
+    if z_pre.stride(2) != 1:
+        z_pre = z_pre.contiguous()
+    B, C3, L = z_pre.shape
+    if C3 != 3 * D:
+        raise ValueError(f"expected {3 * D} packed channels, got {C3}")
+    (q, k, v), hd, (sh, sd) = _qkv_views(z_pre, D, layout, num_heads, flip)
+    return _gcg_raw(q, k, v, z_pre.stride(0), sh, sd, hd, h, bias, B, L, D, taps=taps, bias_mode=bias_mode, mask=mask,
+                    want_state=want_state, round_kv=round_kv, channel_last_out=channel_last_out)
+
+
+def _gcg_raw(q, k, v, sb, sh, sd, hd, h, bias, B, L, D, *, taps, bias_mode, mask, want_state, round_kv,
+             channel_last_out):
+    dev, dt = q.device, q.dtype
+    h = _param(h, q)
+    G = h.shape[0]
+    h = h.reshape(G, -1)
+    K = h.shape[1]
+    bias, mask = _param(bias, q), _param(mask, q)
+    if channel_last_out:
+        y = torch.empty(B, L, D, device=dev, dtype=dt)
+        ysb, ysd, ysl = L * D, 1, D
+    else:
+        y = torch.empty(B, D, L, device=dev, dtype=dt)
+        ysb, ysd, ysl = D * L, L, 1
+    ns = min(L, K - 1)
+    state = torch.empty(B, D, ns, device=dev, dtype=dt) if want_state else None
+    sbs = sb if isinstance(sb, tuple) else (sb, sb, sb)
+    shs = sh if isinstance(sh, tuple) else (sh, sh, sh)
+    sds = sd if isinstance(sd, tuple) else (sd, sd, sd)
+    p = _lib.GcgParams(
+        q=_ptr(q), q_stride_b=sbs[0], q_stride_h=shs[0], q_stride_d=sds[0],
+        k=_ptr(k), k_stride_b=sbs[1], k_stride_h=shs[1], k_stride_d=sds[1],
+        v=_ptr(v), v_stride_b=sbs[2], v_stride_h=shs[2], v_stride_d=sds[2], head_dim=hd,
+        h=_ptr(h), h_dtype=_code(h), bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        mask=_ptr(mask), mask_dtype=_code(mask) if mask is not None else 0,
+        y=_ptr(y), y_stride_b=ysb, y_stride_d=ysd, y_stride_l=ysl,
+        state=_ptr(state) if (state is not None and ns > 0) else None,
+        B=B, L=L, D=D, G=G, K=K, taps=taps, bias_mode=bias_mode if bias is not None else BIAS_NONE,
+        round_kv=int(round_kv), io_dtype=_DT[dt])
+    with _on(q):
+        _lib.check(_lib.lib().vtx_gcg_fwd(C.byref(p), _stream(q)))
+    return y, state
+
+
+def gcg_fwd_bdl(q, k, v, h, bias=None, *, taps=TAPS_XCORR, bias_mode=BIAS_NONE, round_kv=True, want_state=False):
+    """Three separate contiguous [B, D, L] operands (hyena_ops 'bdl' layout)."""
+    _need_cuda(q, k, v, h, bias)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, D, L = q.shape
+    return _gcg_raw(q, k, v, D * L, 0, L, D, h, bias, B, L, D, taps=taps, bias_mode=bias_mode, mask=None,
+                    want_state=want_state, round_kv=round_kv, channel_last_out=False)
+
+
+def fused_fir_fwd(u: torch.Tensor, w3, b3, h, bias, D: int, *, taps: int, bias_mode: int, layout="interleaved",
+                  num_heads=1, flip=False, want_state=True):
+    """Channel-last fused block: u [B, L, 3D] -> y [B, L, D], fir_state [B, 3D, min(L,2)], inner [B, D, min(L,K-1)]."""
+    _need_cuda(u, w3, b3, h, bias)
+    if u.stride(2) != 1:
+        u = u.contiguous()
+    B, L, C3 = u.shape
+    if C3 != 3 * D:
+        raise ValueError(f"expected {3 * D} packed channels, got {C3}")
+    w3 = _param(w3, u).reshape(C3, -1)
+    h = _param(h, u)
+    G = h.shape[0]
+    h = h.reshape(G, -1)
+    K, K3 = h.shape[1], w3.shape[1]
+    b3, bias = _param(b3, u), _param(bias, u)
+    y = torch.empty(B, L, D, device=u.device, dtype=u.dtype)
+    fs = torch.empty(B, C3, min(L, K3 - 1), device=u.device, dtype=u.dtype) if want_state else None
+    ist = torch.empty(B, D, min(L, K - 1), device=u.device, dtype=u.dtype) if want_state else None
+    p = _lib.FusedFirParams(
+        u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3),
+        b3=_ptr(b3), b3_dtype=_code(b3) if b3 is not None else 0, h=_ptr(h), h_dtype=_code(h),
+        bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        y=_ptr(y), y_stride_b=L * D, y_stride_l=D,
+        fir_state=_ptr(fs) if (fs is not None and fs.numel()) else None,
+        inner_state=_ptr(ist) if (ist is not None and ist.numel()) else None,
+        B=B, L=L, D=D, G=G, K3=K3, K=K, layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip),
+        taps=taps, bias_mode=bias_mode if bias is not None else BIAS_NONE, io_dtype=_code(u))
+    with _on(u):
+        _lib.check(_lib.lib().vtx_fused_fir_fwd(C.byref(p), _stream(u)))
+    return y, fs, ist
+
+
+# ----------------------------------------------------------------------------------------------
+def _modal(log_poles, residues, like, theta=None, res_im=None):
+    """fp32 [G, S] parameter block; returns (struct, keep-alive tensors)."""
+    R = residues.detach().to(device=like.device, dtype=torch.float32).contiguous()
+    G, S = R.shape
+    lp = log_poles.detach().to(device=like.device, dtype=torch.float32).reshape(G, S).contiguous()
+    th = None if theta is None else theta.detach().to(device=like.device, dtype=torch.float32).reshape(G, S).contiguous()
+    ri = None if res_im is None else res_im.detach().to(device=like.device, dtype=torch.float32).reshape(G, S).contiguous()
+    m = _lib.ModalParams(log_poles=_ptr(lp), theta=_ptr(th), res_re=_ptr(R), res_im=_ptr(ri), G=G, S=S)
+    return m, (lp, R, th, ri)
+
+
+def modal_filter(log_poles, residues, L: int, theta=None, res_im=None) -> torch.Tensor:
+    """h [G, L] fp32 = sum_s R exp(lambda t)   (or sum_s Re(R p^t) with theta / res_im)."""
+    _need_cuda(residues)
+    m, keep = _modal(log_poles, residues, residues, theta, res_im)
+    h = torch.empty(m.G, L, device=residues.device, dtype=torch.float32)
+    with _on(residues):
+        _lib.check(_lib.lib().vtx_modal_filter(C.byref(m), _ptr(h), L, _stream(residues)))
+    return h
+
+
+def iir_fwd(z_pre: torch.Tensor, log_poles, residues, bias, D: int, *, layout="split", num_heads=1, flip=False,
+            theta=None, res_im=None, want_state=True, round_kv=True):
+    """Gate -> modal long convolution -> gate.  z_pre [B, 3D, L] -> y [B, D, L] (contiguous), state fp32
+    [B, D, S] (or [B, D, S, 2] for complex poles) or None."""
+    _need_cuda(z_pre, residues, bias)
+    if z_pre.stride(2) != 1:
+        z_pre = z_pre.contiguous()
+    B, C3, L = z_pre.shape
+    if C3 != 3 * D:
+        raise ValueError(f"expected {3 * D} packed channels, got {C3}")
+    (q, k, v), hd, (sh, sd) = _qkv_views(z_pre, D, layout, num_heads, flip)
+    m, keep = _modal(log_poles, residues, z_pre, theta, res_im)
+    cplx = theta is not None
+    bias = _param(bias, z_pre)
+    y = torch.empty(B, D, L, device=z_pre.device, dtype=z_pre.dtype)
+    state = None
+    if want_state:
+        state = torch.empty((B, D, m.S, 2) if cplx else (B, D, m.S), device=z_pre.device, dtype=torch.float32)
+    nbytes = _lib.lib().vtx_iir_scratch_bytes(B, L, D, m.S, int(cplx))
+    scratch = torch.empty(nbytes, device=z_pre.device, dtype=torch.uint8) if nbytes else None
+    p = _lib.IirParams(
+        q=_ptr(q), q_stride_b=z_pre.stride(0), q_stride_h=sh, q_stride_d=sd,
+        k=_ptr(k), k_stride_b=z_pre.stride(0), k_stride_h=sh, k_stride_d=sd,
+        v=_ptr(v), v_stride_b=z_pre.stride(0), v_stride_h=sh, v_stride_d=sd, head_dim=hd, modal=m,
+        bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        y=_ptr(y), y_stride_b=D * L, y_stride_d=L, y_stride_l=1, state=_ptr(state), scratch=_ptr(scratch),
+        B=B, L=L, D=D, round_kv=int(round_kv), io_dtype=_code(z_pre))
+    with _on(z_pre):
+        _lib.check(_lib.lib().vtx_iir_fwd(C.byref(p), _stream(z_pre)))
+    return y, state
+
+
+# ----------------------------------------------------------------------------------------------
+def step_fir(u: torch.Tensor, fir_state: torch.Tensor, weight, bias=None, gated_bias=False, flip_filter=False):
+    """One decode step of a depthwise FIR.  u [B, C]; fir_state [B, C, c]; weight [Gw, 1, K] / [Gw, K].
+    Returns y [B, C] (dtype of u) and the new fp32 state [B, C, min(c+1, K-1)]."""
+    _need_cuda(u, fir_state, weight, bias)
+    u = u.contiguous()
+    B, Cc = u.shape
+    w = _param(weight, u)
+    w = w.reshape(w.shape[0], -1)
+    Gw, K = w.shape
+    st = fir_state.contiguous()
+    if st.dtype not in _DT:
+        st = st.float()
+    c = st.shape[-1]
+    bias = _param(bias, u)
+    y = torch.empty_like(u)
+    c_out = c + 1 if c < K - 1 else c
+    out = torch.empty(B, Cc, c_out, device=u.device, dtype=torch.float32)
+    p = _lib.StepFirParams(
+        u=_ptr(u), state_in=_ptr(st) if c > 0 else None, state_dtype=_code(st), w=_ptr(w), w_dtype=_code(w),
+        bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0, y=_ptr(y),
+        state_out=_ptr(out) if c_out > 0 else None, B=B, C=Cc, Gw=Gw, K=K, c=c, flip_filter=int(flip_filter),
+        bias_mode=(BIAS_GATED if gated_bias else BIAS_ADD) if bias is not None else BIAS_NONE, io_dtype=_code(u))
+    with _on(u):
+        _lib.check(_lib.lib().vtx_step_fir(C.byref(p), _stream(u)))
+    return y, out
+
+
+def step_iir(q, k, v, bias, residues, log_poles, state, *, theta=None, res_im=None, inplace=False):
+    """One decode step of the modal recurrence.  q, k, v [B, D]; state fp32 [B, D, S(,2)].
+    Returns y fp32 [B, D] and the new state."""
+    _need_cuda(q, k, v, residues, state)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, D = q.shape
+    m, keep = _modal(log_poles, residues, q, theta, res_im)
+    bias = _param(bias, q)
+    st = state.contiguous()
+    if st.dtype != torch.float32:
+        st = st.float()
+    out = st if inplace else torch.empty_like(st)
+    y = torch.empty(B, D, device=q.device, dtype=torch.float32)
+    p = _lib.StepIirParams(q=_ptr(q), k=_ptr(k), v=_ptr(v), modal=m, bias=_ptr(bias),
+                           bias_dtype=_code(bias) if bias is not None else 0, state_in=_ptr(st), state_out=_ptr(out),
+                           y=_ptr(y), B=B, D=D, io_dtype=_code(q))
+    with _on(q):
+        _lib.check(_lib.lib().vtx_step_iir(C.byref(p), _stream(q)))
+    return y, out
+
+
+def decode_layer(u, w3, b3, fir_state, D, *, h=None, inner_state=None, bias=None, flip_filter=False, gated_bias=False,
+                 log_poles=None, residues=None, iir_state=None, theta=None, res_im=None, layout="interleaved",
+                 num_heads=1, flip=False):
+    """Whole Hyena layer for one token: u [B, 3D] -> y [B, D] plus the new caches.
+
+    FIR layers pass h / inner_state; the long (modal) layer passes log_poles / residues / iir_state.
+    Returns (y, new_fir_state fp32, new_inner_or_iir_state)."""
+    _need_cuda(u, w3, fir_state)
+    u = u.contiguous()
+    B, C3 = u.shape
+    if C3 != 3 * D:
+        raise ValueError(f"expected {3 * D} packed channels, got {C3}")
+    w3 = _param(w3, u).reshape(C3, -1)
+    K3 = w3.shape[1]
+    b3, bias = _param(b3, u), _param(bias, u)
+    fs = fir_state.contiguous()
+    if fs.shape[-1] != K3 - 1:
+        raise NotImplementedError("decode_layer needs a full featurizer cache (prompt of at least K3-1 tokens)")
+    fs_out = torch.empty(B, C3, K3 - 1, device=u.device, dtype=torch.float32)
+    y = torch.empty(B, D, device=u.device, dtype=u.dtype)
+    p = _lib.DecodeLayerParams(
+        u=_ptr(u), w3=_ptr(w3), w3_dtype=_code(w3), b3=_ptr(b3), b3_dtype=_code(b3) if b3 is not None else 0,
+        fir_state_in=_ptr(fs), fir_state_dtype=_code(fs), fir_state_out=_ptr(fs_out), bias=_ptr(bias),
+        bias_dtype=_code(bias) if bias is not None else 0, y=_ptr(y), B=B, D=D, K3=K3, layout=LAYOUTS[layout],
+        num_heads=num_heads, flip_x1x2=int(flip), flip_filter=int(flip_filter), io_dtype=_code(u))
+    keep = None
+    if h is not None:
+        h = _param(h, u)
+        G = h.shape[0]
+        h = h.reshape(G, -1)
+        K = h.shape[1]
+        ins = inner_state.contiguous()
+        if ins.shape[-1] != K - 1:
+            raise NotImplementedError("decode_layer needs a full inner cache (prompt of at least K-1 tokens)")
+        new_state = torch.empty(B, D, K - 1, device=u.device, dtype=torch.float32)
+        p.h, p.h_dtype, p.G, p.K = _ptr(h), _code(h), G, K
+        p.inner_state_in, p.inner_state_dtype, p.inner_state_out = _ptr(ins), _code(ins), _ptr(new_state)
+        p.bias_mode = (BIAS_GATED if gated_bias else BIAS_ADD) if bias is not None else BIAS_NONE
+    else:
+        m, keep = _modal(log_poles, residues, u, theta, res_im)
+        st = iir_state.contiguous()
+        if st.dtype != torch.float32:
+            st = st.float()
+        new_state = torch.empty_like(st)
+        p.modal, p.K, p.G = m, 0, m.G
+        p.iir_state_in, p.iir_state_out = _ptr(st), _ptr(new_state)
+    with _on(u):
+        _lib.check(_lib.lib().vtx_decode_layer(C.byref(p), _stream(u)))
+    return y, fs_out, new_state
