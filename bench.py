@@ -174,11 +174,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mr", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size (small cases for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
-    w = WORKLOADS[a.workload]
+    w = dict(WORKLOADS[a.workload])
+    if a.batch > 0:
+        w["B"] = a.batch
+        w["name"] += f" [batch overridden to {a.batch}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

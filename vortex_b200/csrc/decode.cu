@@ -101,8 +101,10 @@ __global__ void __launch_bounds__(256) step_iir_kernel(vtx_step_iir_params p) {
     float kv = round_io<T>(to_f32<T>(static_cast<const T*>(p.k)[row]) * to_f32<T>(static_cast<const T*>(p.v)[row]));
     float res = iir_row_step(p.modal, d / (p.D / p.modal.G), p.state_in + row * ss, p.state_out + row * ss, kv, lane);
     if (lane == 0) {
-        float b = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
-        p.y[row] = q * fmaf(b, kv, res);
+        // D * x1v is a product of two I/O-dtype tensors in the reference (rounded there) unless D is fp32
+        float skip = p.bias ? ld_param(p.bias, p.bias_dtype, d) * kv : 0.f;
+        if (p.bias && p.bias_dtype != VTX_F32) skip = round_io<T>(skip);
+        p.y[row] = q * (res + skip);
     }
 }
 
@@ -149,7 +151,9 @@ __global__ void __launch_bounds__(256) decode_layer_kernel(vtx_decode_layer_para
         const int64_t ss = p.modal.S * (p.modal.theta ? 2 : 1);
         float res = iir_row_step(p.modal, d / (p.D / p.modal.G), p.iir_state_in + row * ss,
                                  p.iir_state_out + row * ss, kv, lane);
-        y = q * fmaf(bias, kv, res);
+        float skip = bias * kv;
+        if (p.bias && p.bias_dtype != VTX_F32) skip = round_io<T>(skip);
+        y = q * (res + skip);
     }
     if (lane == 0) static_cast<T*>(p.y)[row] = from_f32<T>(y);
 }
