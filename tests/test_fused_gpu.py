@@ -50,6 +50,77 @@ def test_fused_se_vs_oracle(io, B, L, D, G, K, layout, heads, flip):
     assert rel_l2(st, st_ref) <= (1e-6 if io == "f32" else 2.5e-3)   # k*v rounded once to the I/O dtype
 
 
+MR_CASES = [
+    ("bf16", 1, 2048, 256, 16, 128, "interleaved", 1, False),   # configuration 2 shape, reduced B and D
+    ("bf16", 3, 1000, 64, 4, 128, "interleaved", 1, False),     # ragged L, stream quad partly idle
+    ("bf16", 2, 700, 128, 8, 64, "interleaved", 1, True),       # shorter filter on the tensor-core path, flip
+    ("bf16", 4, 300, 64, 4, 128, "split", 1, False),
+    ("bf16", 2, 520, 128, 8, 128, "column_split", 2, True),
+    ("bf16", 1, 100, 32, 2, 128, "interleaved", 1, False),      # L < K
+    ("bf16", 2, 1, 32, 2, 128, "interleaved", 1, False),        # single token
+    ("bf16", 1, 8192, 64, 4, 128, "interleaved", 1, False),     # several time segments per sequence
+]
+
+
+@pytest.mark.parametrize("io,B,L,D,G,K,layout,heads,flip", MR_CASES)
+def test_fused_mr_vs_oracle(io, B, L, D, G, K, layout, heads, flip):
+    """tcgen05 blocked-Toeplitz path: bf16 I/O, fp32 accumulation, k*v carried as bf16 head + remainder."""
+    from vortex_b200 import ops
+    p = make_block(33, B, L, D, G, K, io)
+    ref, fs_ref, st_ref = _oracle(p, D, K, io, layout, heads, flip)
+    y, fs, st = _fused(cuda(p), K, layout, heads, flip)
+    ops.device_status()
+    assert y.shape == (B, L, D) and y.dtype == DT[io]
+    assert rel_l2(y, ref) <= TOL[io]
+    assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
+    assert st.shape == st_ref.shape
+    assert rel_l2(st, st_ref) <= 2.5e-3
+
+
+def test_fused_mr_exact_on_integers():
+    """Integer data small enough for bf16 products and fp32 sums to be exact: output equals the oracle bit for bit
+    (pins the Toeplitz expansion, chunk/segment seams, stream skew and channel maps of the tensor-core path)."""
+    g = torch.Generator().manual_seed(6)
+    B, L, D, G, K = 3, 1300, 64, 4, 128
+    u = torch.randint(-1, 2, (B, L, 3 * D), generator=g).float()
+    w3 = torch.randint(-1, 2, (3 * D, 1, 3), generator=g).float()
+    h = torch.zeros(G, 1, K)
+    for pos in (0, 1, 64, K - 1):                      # first, second, a middle and the last tap
+        h[:, 0, pos] = torch.randint(0, 2, (G,), generator=g).float() * 2 - 1
+    Dp = torch.randint(-1, 2, (D,), generator=g).float()
+    p = {"u": u.bfloat16(), "w3": w3.bfloat16(), "h": h.bfloat16(), "Dp": Dp.bfloat16()}
+    for layout, heads, flip in (("interleaved", 1, False), ("split", 1, True), ("column_split", 2, False)):
+        ref, _, st_ref = _oracle(p, D, K, "f32", layout, heads, flip, mirror=True)
+        assert np.abs(ref).max() < 256          # exactly representable in bf16
+        y, _, st = _fused(cuda(p), K, layout, heads, flip)
+        assert np.array_equal(to_np(y), ref.astype(np.float32)), layout
+        assert np.array_equal(to_np(st), st_ref.astype(np.float32))
+
+
+def test_fused_mr_full_size_properties():
+    """Configuration 2 at full size (B=4, L=8192, D=4096, bf16): oracle on a slice of channels, channel-shard
+    invariance and causality."""
+    from vortex_b200 import hyena_ops
+    B, L, D, G, K = 4, 8192, 4096, 256, 128
+    p = make_block(1, B, L, D, G, K, "bf16")
+    pc = cuda(p)
+    y, _, _ = hyena_ops.hyena_mr_fwd(pc["u"], pc["w3"], None, pc["h"], pc["Dp"])
+    d0, d1 = 2000, 2032
+    sub = {"u": p["u"][::3, :, 3 * d0:3 * d1], "w3": p["w3"][3 * d0:3 * d1], "h": p["h"][d0 // 16:d1 // 16],
+           "Dp": p["Dp"][d0:d1]}
+    ref, _, _ = _oracle(sub, d1 - d0, K, "bf16", "interleaved")
+    assert rel_l2(y[::3, :, d0:d1], ref) <= TOL["bf16"]
+    c0, c1 = 1024, 1536
+    ys, _, _ = hyena_ops.hyena_mr_fwd(pc["u"][:, :, 3 * c0:3 * c1].contiguous(), pc["w3"][3 * c0:3 * c1], None,
+                                      pc["h"][c0 // 16:c1 // 16], pc["Dp"][c0:c1])
+    assert torch.equal(ys, y[:, :, c0:c1])
+    t0 = 4321
+    u2 = pc["u"].clone()
+    u2[:, t0:] = -u2[:, t0:]
+    y2, _, _ = hyena_ops.hyena_mr_fwd(u2, pc["w3"], None, pc["h"], pc["Dp"])
+    assert torch.equal(y2[:, :t0], y[:, :t0]) and not torch.equal(y2[:, t0:], y[:, t0:])
+
+
 def test_fused_se_exact_on_integers():
     """Small-integer data makes every intermediate exact: fused output and caches equal the oracle bit
     for bit, for every q/k/v layout -- pins the channel maps, tap order, halo handling and cache indexing."""

@@ -1,8 +1,515 @@
-// Hyena-MR fused block (placeholder translation unit until the tcgen05 kernel lands).
-#include "common.cuh"
+// Hyena-MR fused block on tcgen05 / TMEM (bf16 I/O, filters of 17..128 taps, one per channel group of 16):
+//   featurizer FIR (3 taps) -> q/k/v selection -> k*v -> grouped causal FIR -> (+ D*kv) -> q gate
+// in one pass over HBM, channel-last in and out.
+//
+// The FIR is a blocked-Toeplitz contraction.  For a chunk of 128 output samples of one channel group
+//   Y[128 x N] = [T^ | T][128 x 256] * KV[256 x N],   [T^|T][i][j] = h[128 + i - j]  (0 outside 0..K-1)
+// where KV holds the previous and the current chunk of k*v.  The Toeplitz matrix depends on the group
+// only, so it is expanded ONCE per CTA from the taps straight into tensor memory (A operand in TMEM,
+// 128 lanes x 128 columns of packed bf16) and every tcgen05.mma reads only the data tile from shared
+// memory.  A CTA owns one group and FOUR independent streams (a stream = one batch element and one
+// segment of the time axis), so N = 4 x 16 channels; k*v is split into a bf16 head and a bf16 remainder
+// (two MMAs accumulate into the same fp32 TMEM columns), which keeps the product exact to ~16 bits.
+// The skip term D[c]*kv is one more K=16 MMA per stream against diag(D) with the same shared-memory
+// tile read as a K-major A operand.
+//
+// Warp roles (10 warps): 0-3 front end (TMA-staged rows -> featurizer -> k*v head/remainder and q into
+// the MMA tile), 4-7 epilogue (tcgen05.ld -> q gate -> bf16 -> global), 8 MMA issue, 9 TMA issue.
+// A front-end lane owns one channel pair of one stream and walks 32 rows per chunk with the featurizer
+// history in registers; the four streams of a warp are staged one row apart in shared memory, which makes
+// every shared-memory access of the front end bank-conflict free.  All waits are bounded.
+#include "tma.cuh"
 
 namespace vtx {
-int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t) {
-    return fail(VTX_ERR_UNSUPPORTED, "fused_fir: filter length %lld has no fused kernel", (long long)p->K);
+
+VTX_DEFINE_STATUS_READER()
+
+int launch_fused_state_bf16(const vtx_fused_fir_params* p, cudaStream_t s);   // fused_fir.cu
+
+namespace mr {
+
+constexpr int NS = 4;                      // streams per CTA
+constexpr int CH = 16;                     // channels per group
+constexpr int CHUNK = 128;                 // output samples per MMA chunk
+constexpr int WROWS = 32;                  // rows of a chunk owned by one front-end warp
+constexpr int RB = 16;                     // rows per staged box: two boxes per front-end warp and chunk
+constexpr int BOX_ROWS = RB + 2 + (NS - 1);            // featurizer halo + stream skew
+constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;       // 2016
+constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;   // q | k | v planes of the non-interleaved layouts (TMA wants 128-byte aligned tiles)
+constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 2304 >= BOX_BYTES
+constexpr int IN_STAGES = 2;                           // = boxes per warp and chunk: box h of every chunk lands in stage h
+constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage of one front-end warp
+constexpr int PLS = CHUNK * 16 + 16;       // plane stride: [128 rows][16 B] + 16 B so that planes fall on different banks
+constexpr int NPLANE = NS * CH / 8;        // 8 planes of 8 bf16 channels
+constexpr int MAT_BYTES = NPLANE * PLS;    // one [128 x 64] bf16 matrix in plane form
+constexpr int SLOT_BYTES = 4 * MAT_BYTES;  // kv head, kv remainder, q (fp32: 16 planes of 4 channels)
+constexpr int HI_OFF = 0, LO_OFF = MAT_BYTES, Q_OFF = 2 * MAT_BYTES;
+constexpr int DIAG_BYTES = 2 * 256;        // diag(D): 2 planes of [16 rows][16 B]
+constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
+constexpr int SMEM_IN = 4 * IN_STAGES * STAGE_BYTES;
+constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
+constexpr int OFF_SLOTS = SMEM_IN;
+constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
+constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
+constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
+constexpr int NBARS = 4 * IN_STAGES * 2 + 2 * 4;       // in_full/in_empty per warp and stage; kv_full, kv_free, d_full, d_empty x2
+constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 128;
+constexpr int TMEM_COLS = 256;             // A: [0,128)  D0: [128,192)  D1: [192,256)
+constexpr int THREADS = 320;
+
+// L2 prefetch of a box that will be staged later (keeps HBM requests in flight without shared memory).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(x), "r"(y), "r"(z)
+                 : "memory");
 }
+
+struct Args {
+    const void* w3; int64_t w3_dtype;
+    const void* h;  int64_t h_dtype;
+    const void* bias; int64_t bias_dtype;
+    __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
+    int64_t B, L, D, G, K;
+    int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
+    int layout, flip, taps, has_bias;
+    int64_t hd;
+};
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (uint64_t)((lbo >> 4) & 0x3FFF) << 16 |
+           (uint64_t)((sbo >> 4) & 0x3FFF) << 32 | (uint64_t)1 << 46;
+}
+__device__ __forceinline__ uint32_t instr_desc(int M, int N, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
+           ((uint32_t)(M >> 4) << 24);      // f32 accumulate, bf16 x bf16, A K-major
+}
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {   // lo -> bits [15:0]
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+struct Stream {
+    int64_t b, ts, te;   // batch, first row, one past the last row this stream stores
+    bool active;
+};
+__device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) {
+    Stream st;
+    int64_t id = quad * NS + s;
+    st.active = id < a.nstream;
+    if (!st.active) id = a.nstream - 1;            // duplicate a real stream; its stores are suppressed
+    st.b = id / a.nseg;
+    st.ts = (id % a.nseg) * a.seg_len;
+    st.te = st.ts + a.seg_len < a.L ? st.ts + a.seg_len : a.L;
+    return st;
+}
+
+template <bool INTERLEAVED>
+__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap,
+                                                              const __grid_constant__ CUtensorMap tmap_pf, Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const uint32_t sm_u = smem_u32(sm);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BARS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BARS + NBARS * 8);
+    // barrier indices
+    auto in_full = [&](int w, int st) { return smem_u32(&bars[(w * IN_STAGES + st) * 2]); };
+    auto in_empty = [&](int w, int st) { return smem_u32(&bars[(w * IN_STAGES + st) * 2 + 1]); };
+    const int BB = 4 * IN_STAGES * 2;
+    auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };
+    auto kv_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
+    auto d_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };
+    auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int64_t g = blockIdx.x % a.G, quad = blockIdx.x / a.G;
+    const int K = (int)a.K;
+    const int nchunk = (int)(a.seg_len / CHUNK) + 1;     // chunk 0 is the halo chunk (front end only)
+
+    // ---------------- setup -------------------------------------------------------------------
+    if (tid == 0) {
+        for (int w = 0; w < 4; ++w)
+            for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(w, st), 1); mbar_init(in_empty(w, st), 1); }
+        for (int sl = 0; sl < 2; ++sl) {
+            mbar_init(kv_full(sl), 4); mbar_init(kv_free(sl), 1); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    {   // taps, zero padded: tp[m] = tap at lag (m - 128), lags outside [0, K) are zero
+        __nv_bfloat16* tp = reinterpret_cast<__nv_bfloat16*>(sm + OFF_TAPS);
+        for (int m = tid; m < 384; m += THREADS) {
+            int l = m - 128;
+            float v = 0.f;
+            if (l >= 0 && l < K) v = ld_param(a.h, a.h_dtype, g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
+            tp[m] = __float2bfloat16_rn(v);
+        }
+        __nv_bfloat16* dg = reinterpret_cast<__nv_bfloat16*>(sm + OFF_DIAG);   // diag(D) [k][n]: plane n/8, row k
+        for (int e = tid; e < 256; e += THREADS) {
+            int k = e / 16, n = e % 16;
+            float v = (a.has_bias && k == n) ? ld_param(a.bias, a.bias_dtype, g * CH + n) : 0.f;
+            dg[(n / 8) * 128 + k * 8 + (n % 8)] = __float2bfloat16_rn(v);
+        }
+        // the halo rows of the q matrices are never written by the front end: nothing to clear
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp >= 4 && warp < 8) {   // expand the Toeplitz matrix into TMEM: lane i holds row i
+        const int i = (warp - 4) * 32 + lane;
+        const uint16_t* tp = reinterpret_cast<const uint16_t*>(sm + OFF_TAPS);
+        for (int c0 = 0; c0 < 128; c0 += 16) {
+            uint32_t v[16];
+#pragma unroll
+            for (int m = 0; m < 16; ++m) {
+                int j = 2 * (c0 + m);                                  // columns j, j+1 of [T^|T]: lag = 128 + i - j
+                uint32_t e0 = tp[128 + 128 + i - j], e1 = tp[128 + 127 + i - j];
+                v[m] = e1 << 16 | e0;
+            }
+            tmem_st16(tmem + ((uint32_t)((warp - 4) * 32) << 16) + c0, v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+
+    // ---------------- roles ---------------------------------------------------------------------
+    if (warp < 4) {
+        // ======== front end: warp w owns rows [32w, 32w+32) of every chunk =========================
+        const int w = warp, p = lane % 8, s = lane / 8;
+        const Stream st = stream_of(a, quad, s);
+        float w3[2][3][3];
+        {
+            QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                int64_t pc[3];
+                map.get(g * CH + 2 * p + c, pc[0], pc[1], pc[2]);
+#pragma unroll
+                for (int x = 0; x < 3; ++x)
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) w3[c][x][j] = ld_param(a.w3, a.w3_dtype, pc[x] * 3 + j);
+            }
+        }
+        const bool swap_qk = INTERLEAVED && a.flip;
+        const uint32_t plane_off = (uint32_t)((s * 2 + p / 4) * PLS + (p % 4) * 4);       // bf16 pair in the kv matrices
+        const uint32_t qplane_off = (uint32_t)((s * 4 + p / 2) * PLS + (p % 2) * 8);       // fp32 pair in the q matrix
+        for (int k = 0; k < nchunk; ++k) {
+            const int slot = k % 2;
+            if (k >= 2) {   // slot reuse: MMAs that read chunk k-2 and the epilogue that read its q are done
+                if (!mbar_wait(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
+                if (k >= 3 && !mbar_wait(d_empty(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
+            }
+            bool ok = true;
+#pragma unroll 1
+            for (int hb = 0; hb < 2; ++hb) {
+                if (!mbar_wait(in_full(w, hb), (uint32_t)(k & 1), 4)) { ok = false; break; }
+                const uint8_t* box = sm + (w * IN_STAGES + hb) * STAGE_BYTES + s * BOX_STRIDE;
+                const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
+                const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES + row0 * 16;
+                // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early)
+                float x1[2][3], x2[2][3];
+                auto load_row = [&](int lr, float (&x)[2][3]) {
+                    if (INTERLEAVED) {
+                        const uint32_t* r = reinterpret_cast<const uint32_t*>(box + lr * 96) + 3 * p;
+                        uint32_t e0 = r[0], e1 = r[1], e2 = r[2];
+                        x[0][0] = bf_lo(e0); x[0][1] = bf_hi(e0); x[0][2] = bf_lo(e1);
+                        x[1][0] = bf_hi(e1); x[1][1] = bf_lo(e2); x[1][2] = bf_hi(e2);
+                    } else {
+#pragma unroll
+                        for (int pl = 0; pl < 3; ++pl) {
+                            uint32_t e = reinterpret_cast<const uint32_t*>(box + pl * IN_PLANE + lr * 32)[p];
+                            x[0][pl] = bf_lo(e); x[1][pl] = bf_hi(e);
+                        }
+                    }
+                };
+                load_row(s, x2);
+                load_row(s + 1, x1);
+#pragma unroll
+                for (int i = 0; i < RB; ++i) {
+                    float x0[2][3];
+                    load_row(i + 2 + s, x0);
+                    float z[2][3];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int x = 0; x < 3; ++x) {
+                            z[c][x] = fmaf(w3[c][x][0], x2[c][x], fmaf(w3[c][x][1], x1[c][x], w3[c][x][2] * x0[c][x]));
+                            x2[c][x] = x1[c][x];
+                            x1[c][x] = x0[c][x];
+                        }
+                    const float q0 = swap_qk ? z[0][1] : z[0][0], k0 = swap_qk ? z[0][0] : z[0][1];
+                    const float q1 = swap_qk ? z[1][1] : z[1][0], k1 = swap_qk ? z[1][0] : z[1][1];
+                    const float kv0 = k0 * z[0][2], kv1 = k1 * z[1][2];   // rows before the sequence start are zeros
+                    const uint32_t hi = pack_bf16(kv0, kv1);
+                    const uint32_t lo = pack_bf16(kv0 - bf_lo(hi), kv1 - bf_hi(hi));
+                    const uint32_t addr = slot_u + (uint32_t)i * 16;
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(hi) : "memory");
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + LO_OFF), "r"(lo) : "memory");
+                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr + qplane_off + Q_OFF), "f"(q0), "f"(q1) : "memory");
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(in_empty(w, hb));
+            }
+            if (!ok) break;
+            fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(kv_full(slot));
+        }
+    } else if (warp < 8) {
+        // ======== epilogue: thread = output row (TMEM lane) ========================================
+        const int e = warp - 4, r = e * 32 + lane;
+        Stream sts[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
+        for (int k = 1; k < nchunk; ++k) {
+            const int slot = k % 2;
+            if (!mbar_wait(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
+            tc_fence_after();
+            __syncwarp();
+            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 64;
+            uint32_t acc[NS][16];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) tmem_ld16(taddr + s * 16, acc[s]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const uint8_t* qm = sm + OFF_SLOTS + slot * SLOT_BYTES + Q_OFF + r * 16;
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                uint32_t o[8];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const float4 q = *reinterpret_cast<const float4*>(qm + (s * 4 + c4) * PLS);
+                    o[2 * c4] = pack_bf16(__uint_as_float(acc[s][4 * c4]) * q.x, __uint_as_float(acc[s][4 * c4 + 1]) * q.y);
+                    o[2 * c4 + 1] = pack_bf16(__uint_as_float(acc[s][4 * c4 + 2]) * q.z, __uint_as_float(acc[s][4 * c4 + 3]) * q.w);
+                }
+                const int64_t t = sts[s].ts + (int64_t)(k - 1) * CHUNK + r;
+                if (sts[s].active && t < sts[s].te) {
+                    uint4* dst = reinterpret_cast<uint4*>(a.y + sts[s].b * a.y_stride_b + t * a.y_stride_l + g * CH);
+                    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty(slot));
+        }
+    } else if (warp == 8) {
+        // ======== MMA issue =========================================================================
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(128, NS * CH, 1);
+            const uint32_t idesc_skip = instr_desc(128, CH, 1);
+            const uint64_t diag_desc = smem_desc(sm_u + OFF_DIAG, 128, 256);
+            // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
+            // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
+            // is released (kv_free) one whole chunk before the front end needs its slot again.
+            auto issue_half = [&](int k, bool cur) {
+                const int slot = cur ? k % 2 : (k - 1) % 2;
+                const uint32_t d = tmem + 128 + (k % 2) * 64;
+#pragma unroll 1
+                for (int jj = 0; jj < 8; ++jj) {
+                    const int j = cur ? 8 + jj : jj;
+                    const uint32_t base = sm_u + OFF_SLOTS + slot * SLOT_BYTES + (uint32_t)jj * 256;
+                    mma_ts(d, tmem + 8 * j, smem_desc(base + HI_OFF, 128, PLS), idesc, j > 0);
+                    mma_ts(d, tmem + 8 * j, smem_desc(base + LO_OFF, 128, PLS), idesc, 1);
+                }
+                if (cur && a.has_bias) {
+#pragma unroll 1
+                    for (int s = 0; s < NS; ++s) {
+                        const uint32_t base = sm_u + OFF_SLOTS + slot * SLOT_BYTES + (uint32_t)(s * 2) * PLS;
+                        mma_ss(d + s * CH, smem_desc(base + HI_OFF, PLS, 128), diag_desc, idesc_skip, 1);
+                        mma_ss(d + s * CH, smem_desc(base + LO_OFF, PLS, 128), diag_desc, idesc_skip, 1);
+                    }
+                }
+            };
+            bool ok = mbar_wait(kv_full(0), 0, 7);          // the halo chunk
+            if (ok && nchunk > 1) {
+                tc_fence_after();
+                issue_half(1, false);
+                mma_commit(kv_free(0));
+            }
+            for (int k = 1; k < nchunk && ok; ++k) {
+                if (!mbar_wait(kv_full(k % 2), (uint32_t)((k / 2) & 1), 6)) break;
+                tc_fence_after();
+                issue_half(k, true);
+                mma_commit(d_full(k % 2));
+                if (k + 1 < nchunk) {
+                    // D[(k+1)%2] was last read by the epilogue of chunk k-1
+                    if (k + 1 >= 3 && !mbar_wait(d_empty((k + 1) % 2), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
+                    tc_fence_after();
+                    issue_half(k + 1, false);
+                }
+                mma_commit(kv_free(k % 2));
+            }
+        }
+    } else {
+        // ======== TMA issue ==========================================================================
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap);
+            Stream sts[NS];
+            int64_t col[3] = {0, 0, 0};
+#pragma unroll
+            for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
+            if (INTERLEAVED) {
+                col[0] = 3 * g * CH;
+            } else {
+                const int64_t d0 = g * CH;
+                if (a.layout == VTX_QKV_COLUMN_SPLIT) {
+                    int64_t n = d0 / a.hd, j = d0 - n * a.hd;
+                    col[0] = n * 3 * a.hd + j; col[1] = col[0] + a.hd; col[2] = col[0] + 2 * a.hd;
+                } else {
+                    col[0] = d0; col[1] = a.D + d0; col[2] = 2 * a.D + d0;
+                }
+                if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
+            }
+            auto prefetch_chunk = [&](int k) {     // whole chunk k of every stream into L2
+                if (k >= nchunk) return;
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK);
+                    if (INTERLEAVED) {
+                        tma_prefetch_l2_3d(&tmap_pf, (int)col[0], row, (int)sts[s].b);
+                    } else {
+#pragma unroll
+                        for (int pl = 0; pl < 3; ++pl) tma_prefetch_l2_3d(&tmap_pf, (int)col[pl], row, (int)sts[s].b);
+                    }
+                }
+            };
+            prefetch_chunk(1);
+            prefetch_chunk(2);
+            bool ok = true;
+            for (int k = 0; k < nchunk && ok; ++k) {
+                prefetch_chunk(k + 3);
+                for (int hb = 0; hb < 2 && ok; ++hb) {
+                    for (int w = 0; w < 4 && ok; ++w) {
+                        if (k >= 1 && !mbar_wait(in_empty(w, hb), (uint32_t)((k - 1) & 1), 9)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t bar = in_full(w, hb);
+                        mbar_expect_tx(bar, NS * BOX_BYTES);
+#pragma unroll
+                        for (int s = 0; s < NS; ++s) {
+                            const uint32_t dst = sm_u + (uint32_t)((w * IN_STAGES + hb) * STAGE_BYTES + s * BOX_STRIDE);
+                            const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK + w * WROWS + hb * RB - 2 - s);
+                            if (INTERLEAVED) {
+                                tma_load_3d(dst, &tmap, bar, (int)col[0], row, (int)sts[s].b);
+                            } else {
+#pragma unroll
+                                for (int pl = 0; pl < 3; ++pl)
+                                    tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, (int)col[pl], row, (int)sts[s].b);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown -------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+}  // namespace mr
+
+int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
+    using namespace mr;
+    VTX_REQUIRE(p->io_dtype == VTX_BF16, VTX_ERR_UNSUPPORTED, "fused_fir: the tensor-core path takes bf16 I/O");
+    VTX_REQUIRE(p->K <= CHUNK, VTX_ERR_UNSUPPORTED, "fused_fir: filter length %lld > %d", (long long)p->K, CHUNK);
+    VTX_REQUIRE(p->D == p->G * CH, VTX_ERR_UNSUPPORTED, "fused_fir: the tensor-core path needs groups of %d channels", CH);
+    VTX_REQUIRE(p->K3 == 3 && !p->b3, VTX_ERR_UNSUPPORTED, "fused_fir: tensor-core path needs a 3-tap featurizer without bias");
+    VTX_REQUIRE(p->bias_mode != VTX_BIAS_ADD, VTX_ERR_UNSUPPORTED, "fused_fir: additive bias is not fused on this path");
+    VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 16) == 0 && (p->y_stride_l % 8) == 0 && (p->y_stride_b % 8) == 0,
+                VTX_ERR_ALIGNMENT, "fused_fir: y rows must be 16-byte aligned");
+    Args a{};
+    a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.h = p->h; a.h_dtype = p->h_dtype;
+    a.bias = p->bias; a.bias_dtype = p->bias_dtype; a.has_bias = p->bias_mode == VTX_BIAS_GATED;
+    a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
+    a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
+    a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
+    a.hd = p->D;
+    if (p->layout == VTX_QKV_COLUMN_SPLIT) {
+        VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_fir: bad num_heads");
+        a.hd = p->D / p->num_heads;
+        VTX_REQUIRE(a.hd % CH == 0, VTX_ERR_UNSUPPORTED, "fused_fir: column split needs head size %% %d == 0", CH);
+    }
+    VTX_REQUIRE(p->layout == VTX_QKV_INTERLEAVED || (p->D * 2) % 16 == 0, VTX_ERR_ALIGNMENT,
+                "fused_fir: D*itemsize must be a multiple of 16 bytes for this q/k/v layout");
+    // segments: enough CTAs (group x stream quads) for ~7 rounds over the SMs, whole chunks each
+    const int64_t nchunks_total = ceil_div<int64_t>(p->L, CHUNK);
+    int64_t nseg = 1;
+    while (p->G * ceil_div<int64_t>(p->B * nseg, NS) < (int64_t)kNumSMs * 6 && nseg * 2 <= nchunks_total &&
+           ceil_div<int64_t>(nchunks_total, nseg * 2) >= 8)
+        nseg *= 2;
+    a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
+    a.nseg = ceil_div<int64_t>(p->L, a.seg_len);
+    a.nstream = p->B * a.nseg;
+    const int64_t nquad = ceil_div<int64_t>(a.nstream, NS);
+    VTX_REQUIRE(p->G * nquad < (int64_t)1 << 31, VTX_ERR_UNSUPPORTED, "fused_fir: too many work items");
+
+    const bool inter = p->layout == VTX_QKV_INTERLEAVED;
+    CUtensorMap tmap;
+    if (int rc = make_tmap_3d(&tmap, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
+                              inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_fir(mr)"))
+        return rc;
+    CUtensorMap tmap_pf;      // same tensor, one box = a whole chunk of rows, used for L2 prefetch only
+    if (int rc = make_tmap_3d(&tmap_pf, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
+                              inter ? 3 * CH : CH, CHUNK, 0, "fused_fir(mr)"))
+        return rc;
+    auto kern = inter ? fused_mr_kernel<true> : fused_mr_kernel<false>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[inter]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
+        attr_set[inter] = true;
+    }
+    kern<<<(unsigned)(p->G * nquad), THREADS, SMEM_BYTES, stream>>>(tmap, tmap_pf, a);
+    if (int rc = check_launch("fused_fir(mr)")) return rc;
+    if (p->fir_state || p->inner_state) return launch_fused_state_bf16(p, stream);
+    return VTX_OK;
+}
+
 }  // namespace vtx

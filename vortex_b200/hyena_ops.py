@@ -38,23 +38,41 @@ def _fused_ok(u, h, layout, num_heads):
     return True
 
 
+def _tensor_core_ok(u, b3, h, layout, num_heads):
+    """Shapes the tcgen05 blocked-Toeplitz kernel takes: bf16 I/O, 17..128 taps, groups of 16 channels."""
+    D = u.shape[-1] // 3
+    if u.dtype != torch.bfloat16 or b3 is not None or not (16 < h.shape[-1] <= 128) or h.shape[0] * 16 != D:
+        return False
+    if (u.stride(1) * 2) % 16 or u.stride(2) != 1 or u.data_ptr() % 16 or (u.stride(0) * 2) % 16:
+        return False
+    if layout == "column_split" and (D // num_heads) % 16:
+        return False
+    return True
+
+
+def _fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state):
+    """Kernel choice per workload: single-pass CUDA-core kernel for filters up to 16 taps, tcgen05
+    blocked-Toeplitz kernel for 17..128 taps with bf16 I/O, two-launch general path otherwise."""
+    D = u.shape[-1] // 3
+    if _fused_ok(u, h, layout, num_heads) or _tensor_core_ok(u, b3, h, layout, num_heads):
+        return ops.fused_fir_fwd(u, w3, b3, h, D_skip, D, taps=taps, bias_mode=bias_mode, layout=layout,
+                                 num_heads=num_heads, flip=flip, want_state=want_state)
+    return _general_fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state)
+
+
 def hyena_se_fwd(u, short_filter_weight, short_filter_bias, h, *, layout="interleaved", num_heads=1, flip=False,
                  want_state=False):
     """Hyena-SE block (inner filter shorter than 128 taps, cross-correlation taps, no skip term).
     u [B, L, 3D] -> y [B, L, D] (+ featurizer cache [B, 3D, 2], inner cache [B, D, K-1])."""
-    D = u.shape[-1] // 3
-    if not _fused_ok(u, h, layout, num_heads):
-        return _general_fir_block(u, short_filter_weight, short_filter_bias, h, None, TAPS_XCORR, BIAS_NONE, layout,
-                                  num_heads, flip, want_state)
-    return ops.fused_fir_fwd(u, short_filter_weight, short_filter_bias, h, None, D, taps=TAPS_XCORR,
-                             bias_mode=BIAS_NONE, layout=layout, num_heads=num_heads, flip=flip, want_state=want_state)
+    return _fir_block(u, short_filter_weight, short_filter_bias, h, None, TAPS_XCORR, BIAS_NONE, layout, num_heads,
+                      flip, want_state)
 
 
 def hyena_mr_fwd(u, short_filter_weight, short_filter_bias, h, D_skip, *, layout="interleaved", num_heads=1,
                  flip=False, want_state=False):
     """Hyena-MR block (128-tap grouped filter, convolution taps, per-channel skip term D_skip)."""
-    return _general_fir_block(u, short_filter_weight, short_filter_bias, h, D_skip, TAPS_CONV, BIAS_GATED, layout,
-                              num_heads, flip, want_state)
+    return _fir_block(u, short_filter_weight, short_filter_bias, h, D_skip, TAPS_CONV, BIAS_GATED, layout, num_heads,
+                      flip, want_state)
 
 
 def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues, D_skip, *, theta=None, res_im=None,
