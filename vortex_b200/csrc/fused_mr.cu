@@ -18,6 +18,8 @@
 // A front-end lane owns one channel pair of one stream and walks 32 rows per chunk with the featurizer
 // history in registers; the four streams of a warp are staged one row apart in shared memory, which makes
 // every shared-memory access of the front end bank-conflict free.  All waits are bounded.
+#include <cstdlib>
+
 #include "tma.cuh"
 
 namespace vtx {
@@ -72,6 +74,7 @@ struct Args {
     int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
     int layout, flip, taps, has_bias;
     int64_t hd;
+    int pf;          // chunks of L2 prefetch distance (0 = off)
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -120,6 +123,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {   // lo -> b
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+
+#ifdef VTX_MR_PROFILE
+__device__ unsigned long long g_mr_prof[32];     // [code] waited cycles, [16 + code] number of waits
+__device__ __forceinline__ bool mbar_wait_p(uint32_t bar, uint32_t parity, int code) {
+    long long t0 = clock64();
+    bool ok = mbar_wait(bar, parity, code);
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(&g_mr_prof[code], (unsigned long long)(clock64() - t0));
+        atomicAdd(&g_mr_prof[16 + code], 1ull);
+    }
+    return ok;
+}
+#define MBAR_WAIT mbar_wait_p
+#else
+#define MBAR_WAIT mbar_wait
+#endif
 
 struct Stream {
     int64_t b, ts, te;   // batch, first row, one past the last row this stream stores
@@ -212,6 +231,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
 
+#ifdef VTX_MR_PROFILE
+    const long long prof_t0 = clock64();
+#endif
     // ---------------- roles ---------------------------------------------------------------------
     if (warp < 4) {
         // ======== front end: warp w owns rows [32w, 32w+32) of every chunk =========================
@@ -236,38 +258,47 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         for (int k = 0; k < nchunk; ++k) {
             const int slot = k % 2;
             if (k >= 2) {   // slot reuse: MMAs that read chunk k-2 and the epilogue that read its q are done
-                if (!mbar_wait(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
-                if (k >= 3 && !mbar_wait(d_empty(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
+                if (!MBAR_WAIT(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
+                if (k >= 3 && !MBAR_WAIT(d_empty(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
             }
             bool ok = true;
 #pragma unroll 1
             for (int hb = 0; hb < 2; ++hb) {
-                if (!mbar_wait(in_full(w, hb), (uint32_t)(k & 1), 4)) { ok = false; break; }
+                if (!MBAR_WAIT(in_full(w, hb), (uint32_t)(k & 1), 4)) { ok = false; break; }
                 const uint8_t* box = sm + (w * IN_STAGES + hb) * STAGE_BYTES + s * BOX_STRIDE;
                 const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
                 const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES + row0 * 16;
-                // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early)
-                float x1[2][3], x2[2][3];
-                auto load_row = [&](int lr, float (&x)[2][3]) {
+                // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early).
+                // All rows of the box are fetched into registers first so that the shared-memory latency is
+                // paid once per box, not once per row (the stores below order memory operations).
+                uint32_t raw[RB + 2][3];
+#pragma unroll
+                for (int r = 0; r < RB + 2; ++r) {
                     if (INTERLEAVED) {
-                        const uint32_t* r = reinterpret_cast<const uint32_t*>(box + lr * 96) + 3 * p;
-                        uint32_t e0 = r[0], e1 = r[1], e2 = r[2];
-                        x[0][0] = bf_lo(e0); x[0][1] = bf_hi(e0); x[0][2] = bf_lo(e1);
-                        x[1][0] = bf_hi(e1); x[1][1] = bf_lo(e2); x[1][2] = bf_hi(e2);
+                        const uint32_t* rp = reinterpret_cast<const uint32_t*>(box + (r + s) * 96) + 3 * p;
+                        raw[r][0] = rp[0]; raw[r][1] = rp[1]; raw[r][2] = rp[2];
                     } else {
 #pragma unroll
-                        for (int pl = 0; pl < 3; ++pl) {
-                            uint32_t e = reinterpret_cast<const uint32_t*>(box + pl * IN_PLANE + lr * 32)[p];
-                            x[0][pl] = bf_lo(e); x[1][pl] = bf_hi(e);
-                        }
+                        for (int pl = 0; pl < 3; ++pl)
+                            raw[r][pl] = reinterpret_cast<const uint32_t*>(box + pl * IN_PLANE + (r + s) * 32)[p];
+                    }
+                }
+                auto unpack = [&](const uint32_t (&e)[3], float (&x)[2][3]) {
+                    if (INTERLEAVED) {
+                        x[0][0] = bf_lo(e[0]); x[0][1] = bf_hi(e[0]); x[0][2] = bf_lo(e[1]);
+                        x[1][0] = bf_hi(e[1]); x[1][1] = bf_lo(e[2]); x[1][2] = bf_hi(e[2]);
+                    } else {
+#pragma unroll
+                        for (int pl = 0; pl < 3; ++pl) { x[0][pl] = bf_lo(e[pl]); x[1][pl] = bf_hi(e[pl]); }
                     }
                 };
-                load_row(s, x2);
-                load_row(s + 1, x1);
+                float x1[2][3], x2[2][3];
+                unpack(raw[0], x2);
+                unpack(raw[1], x1);
 #pragma unroll
                 for (int i = 0; i < RB; ++i) {
                     float x0[2][3];
-                    load_row(i + 2 + s, x0);
+                    unpack(raw[i + 2], x0);
                     float z[2][3];
 #pragma unroll
                     for (int c = 0; c < 2; ++c)
@@ -283,10 +314,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     const uint32_t hi = pack_bf16(kv0, kv1);
                     const uint32_t lo = pack_bf16(kv0 - bf_lo(hi), kv1 - bf_hi(hi));
                     const uint32_t addr = slot_u + (uint32_t)i * 16;
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(hi) : "memory");
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + LO_OFF), "r"(lo) : "memory");
-                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr + qplane_off + Q_OFF), "f"(q0), "f"(q1) : "memory");
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(hi));
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + LO_OFF), "r"(lo));
+                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr + qplane_off + Q_OFF), "f"(q0), "f"(q1));
                 }
+                asm volatile("" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(in_empty(w, hb));
             }
@@ -303,7 +335,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
         for (int k = 1; k < nchunk; ++k) {
             const int slot = k % 2;
-            if (!mbar_wait(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
+            if (!MBAR_WAIT(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
             tc_fence_after();
             __syncwarp();
             const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 64;
@@ -360,20 +392,20 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     }
                 }
             };
-            bool ok = mbar_wait(kv_full(0), 0, 7);          // the halo chunk
+            bool ok = MBAR_WAIT(kv_full(0), 0, 7);          // the halo chunk
             if (ok && nchunk > 1) {
                 tc_fence_after();
                 issue_half(1, false);
                 mma_commit(kv_free(0));
             }
             for (int k = 1; k < nchunk && ok; ++k) {
-                if (!mbar_wait(kv_full(k % 2), (uint32_t)((k / 2) & 1), 6)) break;
+                if (!MBAR_WAIT(kv_full(k % 2), (uint32_t)((k / 2) & 1), 6)) break;
                 tc_fence_after();
                 issue_half(k, true);
                 mma_commit(d_full(k % 2));
                 if (k + 1 < nchunk) {
                     // D[(k+1)%2] was last read by the epilogue of chunk k-1
-                    if (k + 1 >= 3 && !mbar_wait(d_empty((k + 1) % 2), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
+                    if (k + 1 >= 3 && !MBAR_WAIT(d_empty((k + 1) % 2), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
                     tc_fence_after();
                     issue_half(k + 1, false);
                 }
@@ -401,7 +433,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
             }
             auto prefetch_chunk = [&](int k) {     // whole chunk k of every stream into L2
-                if (k >= nchunk) return;
+                if (k >= nchunk || a.pf == 0) return;
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
                     const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK);
@@ -413,14 +445,13 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     }
                 }
             };
-            prefetch_chunk(1);
-            prefetch_chunk(2);
+            for (int k = 1; k <= a.pf; ++k) prefetch_chunk(k);
             bool ok = true;
             for (int k = 0; k < nchunk && ok; ++k) {
-                prefetch_chunk(k + 3);
+                prefetch_chunk(k + 1 + a.pf);
                 for (int hb = 0; hb < 2 && ok; ++hb) {
                     for (int w = 0; w < 4 && ok; ++w) {
-                        if (k >= 1 && !mbar_wait(in_empty(w, hb), (uint32_t)((k - 1) & 1), 9)) {
+                        if (k >= 1 && !MBAR_WAIT(in_empty(w, hb), (uint32_t)((k - 1) & 1), 9)) {
                             ok = false;
                             break;
                         }
@@ -444,6 +475,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         }
     }
 
+#ifdef VTX_MR_PROFILE
+    if (lane == 0) atomicAdd(&g_mr_prof[10 + (warp < 4 ? 0 : warp < 8 ? 1 : warp - 6)], (unsigned long long)(clock64() - prof_t0));
+#endif
     // ---------------- teardown -------------------------------------------------------------------
     tc_fence_before();
     __syncthreads();
@@ -454,6 +488,18 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 }
 
 }  // namespace mr
+
+#ifdef VTX_MR_PROFILE
+extern "C" int vtx_mr_profile_read(unsigned long long* out, int reset) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out, mr::g_mr_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
+    if (reset) {
+        unsigned long long z[32] = {0};
+        cudaMemcpyToSymbol(mr::g_mr_prof, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 
 int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     using namespace mr;
@@ -471,6 +517,7 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
     a.hd = p->D;
+    a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 2;
     if (p->layout == VTX_QKV_COLUMN_SPLIT) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_fir: bad num_heads");
         a.hd = p->D / p->num_heads;
