@@ -13,9 +13,9 @@
 // The skip term D[c]*kv is one more K=16 MMA per stream against diag(D) with the same shared-memory
 // tile read as a K-major A operand.
 //
-// Warp roles (10 warps): 0-3 front end (TMA-staged rows -> featurizer -> k*v head/remainder and q into
-// the MMA tile), 4-7 epilogue (tcgen05.ld -> q gate -> bf16 -> global), 8 MMA issue, 9 TMA issue.
-// A front-end lane owns one channel pair of one stream and walks 32 rows per chunk with the featurizer
+// Warp roles (14 warps): 0-7 front end (TMA-staged rows -> featurizer -> k*v head/remainder and q into
+// the MMA tile), 8-11 epilogue (tcgen05.ld -> q gate -> bf16 -> global), 12 MMA issue, 13 TMA issue.
+// A front-end lane owns one channel pair of one stream and walks 16 rows per chunk with the featurizer
 // history in registers; the four streams of a warp are staged one row apart in shared memory, which makes
 // every shared-memory access of the front end bank-conflict free.  All waits are bounded.
 #include <cstdlib>
@@ -33,14 +33,18 @@ namespace mr {
 constexpr int NS = 4;                      // streams per CTA
 constexpr int CH = 16;                     // channels per group
 constexpr int CHUNK = 128;                 // output samples per MMA chunk
-constexpr int WROWS = 32;                  // rows of a chunk owned by one front-end warp
-constexpr int RB = 16;                     // rows per staged box: two boxes per front-end warp and chunk
-constexpr int BOX_ROWS = RB + 2 + (NS - 1);            // featurizer halo + stream skew
-constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;       // 2016
+constexpr int NFE = 8;                     // front-end warps (two per scheduler: the featurizer chain is latency-bound)
+constexpr int WROWS = CHUNK / NFE;         // rows of a chunk owned by one front-end warp
+constexpr int RB = 16;                     // rows a front-end lane fetches into registers at a time
+constexpr int HROWS = 64;                  // rows per staged box: half a chunk, shared by two front-end warps
+                                           // (the TMA unit retires ~12 boxes per microsecond and SM whatever their
+                                           // size, so boxes are made as tall as the shared-memory budget allows)
+constexpr int BOX_ROWS = HROWS + 2 + (NS - 1);         // featurizer halo + stream skew
+constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;       // 6624
 constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;   // q | k | v planes of the non-interleaved layouts (TMA wants 128-byte aligned tiles)
-constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 2304 >= BOX_BYTES
-constexpr int IN_STAGES = 2;                           // = boxes per warp and chunk: box h of every chunk lands in stage h
-constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage of one front-end warp
+constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 6912 >= BOX_BYTES
+constexpr int IN_STAGES = 3;                           // ring of half-chunk stages
+constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage: the four streams' boxes of one half chunk
 constexpr int PLS = CHUNK * 16 + 16;       // plane stride: [128 rows][16 B] + 16 B so that planes fall on different banks
 constexpr int NPLANE = NS * CH / 8;        // 8 planes of 8 bf16 channels
 constexpr int MAT_BYTES = NPLANE * PLS;    // one [128 x 64] bf16 matrix in plane form
@@ -48,33 +52,34 @@ constexpr int SLOT_BYTES = 4 * MAT_BYTES;  // kv head, kv remainder, q (fp32: 16
 constexpr int HI_OFF = 0, LO_OFF = MAT_BYTES, Q_OFF = 2 * MAT_BYTES;
 constexpr int DIAG_BYTES = 2 * 256;        // diag(D): 2 planes of [16 rows][16 B]
 constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
-constexpr int SMEM_IN = 4 * IN_STAGES * STAGE_BYTES;
+constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
 constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
 constexpr int OFF_SLOTS = SMEM_IN;
 constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
 constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
 constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
-constexpr int NBARS = 4 * IN_STAGES * 2 + 2 * 4;       // in_full/in_empty per warp and stage; kv_full, kv_free, d_full, d_empty x2
+constexpr int NBARS = IN_STAGES * 2 + 2 * 5;           // in_full/in_empty per stage; kv_full, kv_free, d_full, d_empty, q_free x2
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 128;
 constexpr int TMEM_COLS = 256;             // A: [0,128)  D0: [128,192)  D1: [192,256)
-constexpr int THREADS = 320;
+constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA and TMA issue warps
+constexpr int THREADS = 32 * (NFE + 6);
 
-// L2 prefetch of a box that will be staged later (keeps HBM requests in flight without shared memory).
-__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int x, int y, int z) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(x), "r"(y), "r"(z)
-                 : "memory");
-}
+// L2 prefetch of rows that will be staged later: keeps HBM requests in flight without shared memory
+// (full HBM bandwidth needs ~100 KB in flight per SM; the staging ring holds a third of that).
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 struct Args {
     const void* w3; int64_t w3_dtype;
     const void* h;  int64_t h_dtype;
     const void* bias; int64_t bias_dtype;
+    const __nv_bfloat16* u; int64_t u_stride_b, u_stride_l;
     __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
     int64_t B, L, D, G, K;
     int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
     int layout, flip, taps, has_bias;
     int64_t hd;
     int pf;          // chunks of L2 prefetch distance (0 = off)
+    int dbg;         // diagnostic builds only: knock out parts of the kernel to time the rest
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -124,21 +129,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {   // lo -> b
     return r;
 }
 
-#ifdef VTX_MR_PROFILE
-__device__ unsigned long long g_mr_prof[32];     // [code] waited cycles, [16 + code] number of waits
-__device__ __forceinline__ bool mbar_wait_p(uint32_t bar, uint32_t parity, int code) {
-    long long t0 = clock64();
-    bool ok = mbar_wait(bar, parity, code);
-    if ((threadIdx.x & 31) == 0) {
-        atomicAdd(&g_mr_prof[code], (unsigned long long)(clock64() - t0));
-        atomicAdd(&g_mr_prof[16 + code], 1ull);
-    }
-    return ok;
-}
-#define MBAR_WAIT mbar_wait_p
+#ifdef VTX_MR_KNOCKOUT
+#define KO(bit) (a.dbg & (bit))
 #else
-#define MBAR_WAIT mbar_wait
+#define KO(bit) false
 #endif
+
+#define MBAR_WAIT mbar_wait
 
 struct Stream {
     int64_t b, ts, te;   // batch, first row, one past the last row this stream stores
@@ -156,21 +153,21 @@ __device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) 
 }
 
 template <bool INTERLEAVED>
-__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap,
-                                                              const __grid_constant__ CUtensorMap tmap_pf, Args a) {
+__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const uint32_t sm_u = smem_u32(sm);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BARS);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BARS + NBARS * 8);
     // barrier indices
-    auto in_full = [&](int w, int st) { return smem_u32(&bars[(w * IN_STAGES + st) * 2]); };
-    auto in_empty = [&](int w, int st) { return smem_u32(&bars[(w * IN_STAGES + st) * 2 + 1]); };
-    const int BB = 4 * IN_STAGES * 2;
+    auto in_full = [&](int st) { return smem_u32(&bars[st * 2]); };
+    auto in_empty = [&](int st) { return smem_u32(&bars[st * 2 + 1]); };
+    const int BB = IN_STAGES * 2;
     auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };
     auto kv_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
     auto d_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };
     auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };
+    auto q_free = [&](int sl) { return smem_u32(&bars[BB + 8 + sl]); };
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int64_t g = blockIdx.x % a.G, quad = blockIdx.x / a.G;
@@ -179,14 +176,13 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
-        for (int w = 0; w < 4; ++w)
-            for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(w, st), 1); mbar_init(in_empty(w, st), 1); }
+        for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), 1); mbar_init(in_empty(st), NFE / 2); }
         for (int sl = 0; sl < 2; ++sl) {
-            mbar_init(kv_full(sl), 4); mbar_init(kv_free(sl), 1); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
+            mbar_init(kv_full(sl), NFE); mbar_init(kv_free(sl), 1); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4); mbar_init(q_free(sl), 4);
         }
         fence_mbar_init();
     }
-    if (warp == 8) {
+    if (warp == W_MMA) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
@@ -212,8 +208,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp >= 4 && warp < 8) {   // expand the Toeplitz matrix into TMEM: lane i holds row i
-        const int i = (warp - 4) * 32 + lane;
+    if (warp >= W_EP && warp < W_EP + 4) {   // expand the Toeplitz matrix into TMEM: lane i holds row i
+        const int i = (warp - W_EP) * 32 + lane;
         const uint16_t* tp = reinterpret_cast<const uint16_t*>(sm + OFF_TAPS);
         for (int c0 = 0; c0 < 128; c0 += 16) {
             uint32_t v[16];
@@ -223,7 +219,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 uint32_t e0 = tp[128 + 128 + i - j], e1 = tp[128 + 127 + i - j];
                 v[m] = e1 << 16 | e0;
             }
-            tmem_st16(tmem + ((uint32_t)((warp - 4) * 32) << 16) + c0, v);
+            tmem_st16(tmem + ((uint32_t)((warp - W_EP) * 32) << 16) + c0, v);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
@@ -231,12 +227,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
 
-#ifdef VTX_MR_PROFILE
-    const long long prof_t0 = clock64();
-#endif
     // ---------------- roles ---------------------------------------------------------------------
-    if (warp < 4) {
-        // ======== front end: warp w owns rows [32w, 32w+32) of every chunk =========================
+    if (warp < NFE) {
+        // ======== front end: warp w owns rows [16w, 16w+16) of every chunk =========================
         const int w = warp, p = lane % 8, s = lane / 8;
         const Stream st = stream_of(a, quad, s);
         float w3[2][3][3];
@@ -259,13 +252,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             const int slot = k % 2;
             if (k >= 2) {   // slot reuse: MMAs that read chunk k-2 and the epilogue that read its q are done
                 if (!MBAR_WAIT(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
-                if (k >= 3 && !MBAR_WAIT(d_empty(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
+                if (k >= 3 && !MBAR_WAIT(q_free(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
             }
-            bool ok = true;
+            // half chunk n = 2k + (upper half ? 1 : 0) sits in stage n % IN_STAGES; this warp owns WROWS of its 64 rows
+            const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
+            if (!MBAR_WAIT(in_full(stg), (uint32_t)((nh / IN_STAGES) & 1), 4)) break;
 #pragma unroll 1
-            for (int hb = 0; hb < 2; ++hb) {
-                if (!MBAR_WAIT(in_full(w, hb), (uint32_t)(k & 1), 4)) { ok = false; break; }
-                const uint8_t* box = sm + (w * IN_STAGES + hb) * STAGE_BYTES + s * BOX_STRIDE;
+            for (int hb = 0; hb < WROWS / RB; ++hb) {
+                const uint8_t* box = sm + stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB) * (INTERLEAVED ? 96 : 32);
                 const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
                 const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES + row0 * 16;
                 // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early).
@@ -274,7 +268,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 uint32_t raw[RB + 2][3];
 #pragma unroll
                 for (int r = 0; r < RB + 2; ++r) {
-                    if (INTERLEAVED) {
+                    if (KO(2)) {
+                        raw[r][0] = raw[r][1] = raw[r][2] = 0x3f803f80u + r + lane;
+                    } else if (INTERLEAVED) {
                         const uint32_t* rp = reinterpret_cast<const uint32_t*>(box + (r + s) * 96) + 3 * p;
                         raw[r][0] = rp[0]; raw[r][1] = rp[1]; raw[r][2] = rp[2];
                     } else {
@@ -282,6 +278,16 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                         for (int pl = 0; pl < 3; ++pl)
                             raw[r][pl] = reinterpret_cast<const uint32_t*>(box + pl * IN_PLANE + (r + s) * 32)[p];
                     }
+                }
+                if (hb == WROWS / RB - 1) {
+                    // Every row this warp needs from the stage now sits in registers: hand the stage back to the
+                    // TMA warp before the arithmetic starts, so that nearly the whole ring can be in flight (HBM
+                    // latency under load is ~2 us; a stage that stayed busy during the arithmetic would leave a
+                    // single stage in flight).  The empty asm makes the loaded values a dependency of the arrive.
+#pragma unroll
+                    for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(raw[r][0]), "r"(raw[r][1]), "r"(raw[r][2]));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(in_empty(stg));
                 }
                 auto unpack = [&](const uint32_t (&e)[3], float (&x)[2][3]) {
                     if (INTERLEAVED) {
@@ -297,6 +303,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 unpack(raw[1], x1);
 #pragma unroll
                 for (int i = 0; i < RB; ++i) {
+                    if (KO(16)) {
+                        const uint32_t addr = slot_u + (uint32_t)i * 16;
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(raw[i + 2][0]));
+                        continue;
+                    }
                     float x0[2][3];
                     unpack(raw[i + 2], x0);
                     float z[2][3];
@@ -314,22 +325,20 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     const uint32_t hi = pack_bf16(kv0, kv1);
                     const uint32_t lo = pack_bf16(kv0 - bf_lo(hi), kv1 - bf_hi(hi));
                     const uint32_t addr = slot_u + (uint32_t)i * 16;
+                    if (KO(1) && hi != 0x12345678u) continue;
                     asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(hi));
                     asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + LO_OFF), "r"(lo));
                     asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr + qplane_off + Q_OFF), "f"(q0), "f"(q1));
                 }
                 asm volatile("" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(in_empty(w, hb));
             }
-            if (!ok) break;
             fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(kv_full(slot));
         }
-    } else if (warp < 8) {
+    } else if (warp < W_EP + 4) {
         // ======== epilogue: thread = output row (TMEM lane) ========================================
-        const int e = warp - 4, r = e * 32 + lane;
+        const int e = warp - W_EP, r = e * 32 + lane;
         Stream sts[NS];
 #pragma unroll
         for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
@@ -343,28 +352,45 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
             for (int s = 0; s < NS; ++s) tmem_ld16(taddr + s * 16, acc[s]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // The accumulator now lives in registers: give the TMEM buffer back before anything else, and the
+            // q tile as soon as it has been read, so that neither the next MMAs nor the front end two chunks
+            // ahead wait for this warp's arithmetic and global stores.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty(slot));
             const uint8_t* qm = sm + OFF_SLOTS + slot * SLOT_BYTES + Q_OFF + r * 16;
+            float y[NS][16];
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
-                uint32_t o[8];
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
-                    const float4 q = *reinterpret_cast<const float4*>(qm + (s * 4 + c4) * PLS);
-                    o[2 * c4] = pack_bf16(__uint_as_float(acc[s][4 * c4]) * q.x, __uint_as_float(acc[s][4 * c4 + 1]) * q.y);
-                    o[2 * c4 + 1] = pack_bf16(__uint_as_float(acc[s][4 * c4 + 2]) * q.z, __uint_as_float(acc[s][4 * c4 + 3]) * q.w);
+                    const float4 q = KO(32) ? make_float4(1.f, 1.f, 1.f, 1.f)
+                                            : *reinterpret_cast<const float4*>(qm + (s * 4 + c4) * PLS);
+                    y[s][4 * c4] = __uint_as_float(acc[s][4 * c4]) * q.x;
+                    y[s][4 * c4 + 1] = __uint_as_float(acc[s][4 * c4 + 1]) * q.y;
+                    y[s][4 * c4 + 2] = __uint_as_float(acc[s][4 * c4 + 2]) * q.z;
+                    y[s][4 * c4 + 3] = __uint_as_float(acc[s][4 * c4 + 3]) * q.w;
                 }
+            }
+#pragma unroll
+            for (int s = 0; s < NS; ++s) asm volatile("" ::"f"(y[s][0]), "f"(y[s][5]), "f"(y[s][10]), "f"(y[s][15]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_free(slot));
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                if (KO(32)) continue;
+                uint32_t o[8];
+#pragma unroll
+                for (int m = 0; m < 8; ++m) o[m] = pack_bf16(y[s][2 * m], y[s][2 * m + 1]);
                 const int64_t t = sts[s].ts + (int64_t)(k - 1) * CHUNK + r;
-                if (sts[s].active && t < sts[s].te) {
+                if (sts[s].active && t < sts[s].te && !(KO(4) && o[0] != 0x12345678u)) {
                     uint4* dst = reinterpret_cast<uint4*>(a.y + sts[s].b * a.y_stride_b + t * a.y_stride_l + g * CH);
                     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
                     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(d_empty(slot));
         }
-    } else if (warp == 8) {
+    } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
         if (lane == 0) {
             const uint32_t idesc = instr_desc(128, NS * CH, 1);
@@ -373,22 +399,37 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
             // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
             // is released (kv_free) one whole chunk before the front end needs its slot again.
+            // Descriptors are built once; a K step of 16 rows moves the start-address field by 256 B (16 units).
+            // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
+            uint64_t hi_desc[2], lo_desc[2], skip_hi[2], skip_lo[2];
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+                const uint32_t base = sm_u + OFF_SLOTS + sl * SLOT_BYTES;
+                hi_desc[sl] = smem_desc(base + HI_OFF, 128, PLS);
+                lo_desc[sl] = smem_desc(base + LO_OFF, 128, PLS);
+                skip_hi[sl] = smem_desc(base + HI_OFF, PLS, 128);
+                skip_lo[sl] = smem_desc(base + LO_OFF, PLS, 128);
+            }
             auto issue_half = [&](int k, bool cur) {
                 const int slot = cur ? k % 2 : (k - 1) % 2;
                 const uint32_t d = tmem + 128 + (k % 2) * 64;
-#pragma unroll 1
+                const uint32_t a0 = tmem + (cur ? 64 : 0);
+                const uint64_t dh = slot ? hi_desc[1] : hi_desc[0], dl = slot ? lo_desc[1] : lo_desc[0];
+                const uint64_t sh = slot ? skip_hi[1] : skip_hi[0], sl2 = slot ? skip_lo[1] : skip_lo[0];
+                const int nj = KO(64) ? 0 : KO(8) ? 1 : 8;
+#pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
-                    const int j = cur ? 8 + jj : jj;
-                    const uint32_t base = sm_u + OFF_SLOTS + slot * SLOT_BYTES + (uint32_t)jj * 256;
-                    mma_ts(d, tmem + 8 * j, smem_desc(base + HI_OFF, 128, PLS), idesc, j > 0);
-                    mma_ts(d, tmem + 8 * j, smem_desc(base + LO_OFF, 128, PLS), idesc, 1);
+                    if (jj < nj) {
+                        mma_ts(d, a0 + 8 * jj, dh + (uint64_t)(jj * 16), idesc, (cur || jj > 0) ? 1u : 0u);
+                        mma_ts(d, a0 + 8 * jj, dl + (uint64_t)(jj * 16), idesc, 1u);
+                    }
                 }
-                if (cur && a.has_bias) {
-#pragma unroll 1
+                if (cur && a.has_bias && !KO(64)) {
+#pragma unroll
                     for (int s = 0; s < NS; ++s) {
-                        const uint32_t base = sm_u + OFF_SLOTS + slot * SLOT_BYTES + (uint32_t)(s * 2) * PLS;
-                        mma_ss(d + s * CH, smem_desc(base + HI_OFF, PLS, 128), diag_desc, idesc_skip, 1);
-                        mma_ss(d + s * CH, smem_desc(base + LO_OFF, PLS, 128), diag_desc, idesc_skip, 1);
+                        const uint64_t off = (uint64_t)((s * 2 * PLS) >> 4);
+                        mma_ss(d + s * CH, sh + off, diag_desc, idesc_skip, 1u);
+                        mma_ss(d + s * CH, sl2 + off, diag_desc, idesc_skip, 1u);
                     }
                 }
             };
@@ -413,93 +454,57 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             }
         }
     } else {
-        // ======== TMA issue ==========================================================================
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap);
-            Stream sts[NS];
-            int64_t col[3] = {0, 0, 0};
+        // first packed column of this group's q | k | v data (one contiguous run when interleaved)
+        Stream sts[NS];
+        int64_t col[3] = {0, 0, 0};
 #pragma unroll
-            for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
-            if (INTERLEAVED) {
-                col[0] = 3 * g * CH;
+        for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
+        if (INTERLEAVED) {
+            col[0] = 3 * g * CH;
+        } else {
+            const int64_t d0 = g * CH;
+            if (a.layout == VTX_QKV_COLUMN_SPLIT) {
+                int64_t n = d0 / a.hd, j = d0 - n * a.hd;
+                col[0] = n * 3 * a.hd + j; col[1] = col[0] + a.hd; col[2] = col[0] + 2 * a.hd;
             } else {
-                const int64_t d0 = g * CH;
-                if (a.layout == VTX_QKV_COLUMN_SPLIT) {
-                    int64_t n = d0 / a.hd, j = d0 - n * a.hd;
-                    col[0] = n * 3 * a.hd + j; col[1] = col[0] + a.hd; col[2] = col[0] + 2 * a.hd;
-                } else {
-                    col[0] = d0; col[1] = a.D + d0; col[2] = 2 * a.D + d0;
-                }
-                if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
+                col[0] = d0; col[1] = a.D + d0; col[2] = 2 * a.D + d0;
             }
-            auto prefetch_chunk = [&](int k) {     // whole chunk k of every stream into L2
-                if (k >= nchunk || a.pf == 0) return;
+            if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
+        }
+        if (lane == 0) {
+            // ======== TMA issue ======================================================================
+            tma_prefetch_desc(&tmap);
+            for (int nh = 0; nh < 2 * nchunk; ++nh) {
+                const int stg = nh % IN_STAGES, k = nh / 2, h = nh % 2;
+                if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), (uint32_t)(((nh - IN_STAGES) / IN_STAGES) & 1), 9)) break;
+                const uint32_t bar = in_full(stg);
+                mbar_expect_tx(bar, NS * BOX_BYTES);
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
-                    const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK);
+                    const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
+                    const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK + h * HROWS - 2 - s);
                     if (INTERLEAVED) {
-                        tma_prefetch_l2_3d(&tmap_pf, (int)col[0], row, (int)sts[s].b);
+                        tma_load_3d(dst, &tmap, bar, (int)col[0], row, (int)sts[s].b);
                     } else {
 #pragma unroll
-                        for (int pl = 0; pl < 3; ++pl) tma_prefetch_l2_3d(&tmap_pf, (int)col[pl], row, (int)sts[s].b);
-                    }
-                }
-            };
-            for (int k = 1; k <= a.pf; ++k) prefetch_chunk(k);
-            bool ok = true;
-            for (int k = 0; k < nchunk && ok; ++k) {
-                prefetch_chunk(k + 1 + a.pf);
-                for (int hb = 0; hb < 2 && ok; ++hb) {
-                    for (int w = 0; w < 4 && ok; ++w) {
-                        if (k >= 1 && !MBAR_WAIT(in_empty(w, hb), (uint32_t)((k - 1) & 1), 9)) {
-                            ok = false;
-                            break;
-                        }
-                        const uint32_t bar = in_full(w, hb);
-                        mbar_expect_tx(bar, NS * BOX_BYTES);
-#pragma unroll
-                        for (int s = 0; s < NS; ++s) {
-                            const uint32_t dst = sm_u + (uint32_t)((w * IN_STAGES + hb) * STAGE_BYTES + s * BOX_STRIDE);
-                            const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK + w * WROWS + hb * RB - 2 - s);
-                            if (INTERLEAVED) {
-                                tma_load_3d(dst, &tmap, bar, (int)col[0], row, (int)sts[s].b);
-                            } else {
-#pragma unroll
-                                for (int pl = 0; pl < 3; ++pl)
-                                    tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, (int)col[pl], row, (int)sts[s].b);
-                            }
-                        }
+                        for (int pl = 0; pl < 3; ++pl)
+                            tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, (int)col[pl], row, (int)sts[s].b);
                     }
                 }
             }
         }
     }
 
-#ifdef VTX_MR_PROFILE
-    if (lane == 0) atomicAdd(&g_mr_prof[10 + (warp < 4 ? 0 : warp < 8 ? 1 : warp - 6)], (unsigned long long)(clock64() - prof_t0));
-#endif
     // ---------------- teardown -------------------------------------------------------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == W_MMA) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
     }
 }
 
 }  // namespace mr
-
-#ifdef VTX_MR_PROFILE
-extern "C" int vtx_mr_profile_read(unsigned long long* out, int reset) {
-    cudaDeviceSynchronize();
-    if (cudaMemcpyFromSymbol(out, mr::g_mr_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
-    if (reset) {
-        unsigned long long z[32] = {0};
-        cudaMemcpyToSymbol(mr::g_mr_prof, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
 
 int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     using namespace mr;
@@ -513,11 +518,13 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     Args a{};
     a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.h = p->h; a.h_dtype = p->h_dtype;
     a.bias = p->bias; a.bias_dtype = p->bias_dtype; a.has_bias = p->bias_mode == VTX_BIAS_GATED;
+    a.u = static_cast<const __nv_bfloat16*>(p->u); a.u_stride_b = p->u_stride_b; a.u_stride_l = p->u_stride_l;
     a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
     a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
     a.hd = p->D;
-    a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 2;
+    a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 0;
+    a.dbg = getenv("VTX_MR_DBG") ? atoi(getenv("VTX_MR_DBG")) : 0;
     if (p->layout == VTX_QKV_COLUMN_SPLIT) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_fir: bad num_heads");
         a.hd = p->D / p->num_heads;
@@ -542,10 +549,6 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     if (int rc = make_tmap_3d(&tmap, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
                               inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_fir(mr)"))
         return rc;
-    CUtensorMap tmap_pf;      // same tensor, one box = a whole chunk of rows, used for L2 prefetch only
-    if (int rc = make_tmap_3d(&tmap_pf, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
-                              inter ? 3 * CH : CH, CHUNK, 0, "fused_fir(mr)"))
-        return rc;
     auto kern = inter ? fused_mr_kernel<true> : fused_mr_kernel<false>;
     static bool attr_set[2] = {false, false};
     if (!attr_set[inter]) {
@@ -553,7 +556,7 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
         if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
         attr_set[inter] = true;
     }
-    kern<<<(unsigned)(p->G * nquad), THREADS, SMEM_BYTES, stream>>>(tmap, tmap_pf, a);
+    kern<<<(unsigned)(p->G * nquad), THREADS, SMEM_BYTES, stream>>>(tmap, a);
     if (int rc = check_launch("fused_fir(mr)")) return rc;
     if (p->fir_state || p->inner_state) return launch_fused_state_bf16(p, stream);
     return VTX_OK;
