@@ -45,11 +45,14 @@ constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;   // q | k | v plane
 constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 6912 >= BOX_BYTES
 constexpr int IN_STAGES = 3;                           // ring of half-chunk stages
 constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage: the four streams' boxes of one half chunk
-constexpr int PLS = CHUNK * 16 + 16;       // plane stride: [128 rows][16 B] + 16 B so that planes fall on different banks
-constexpr int NPLANE = NS * CH / 8;        // 8 planes of 8 bf16 channels
-constexpr int MAT_BYTES = NPLANE * PLS;    // one [128 x 64] bf16 matrix in plane form
-constexpr int SLOT_BYTES = 4 * MAT_BYTES;  // kv head, kv remainder, q (fp32: 16 planes of 4 channels)
-constexpr int HI_OFF = 0, LO_OFF = MAT_BYTES, Q_OFF = 2 * MAT_BYTES;
+// k*v tiles: [128 rows (time)][128 B = 64 channels] bf16 with the 128-byte swizzle (16-byte chunk c of row r is
+// stored at chunk c ^ (r & 7)); the tensor core fetches such rows whole, whereas the unswizzled form is fetched
+// 16 bytes at a time (measured: ~130 instead of ~32 cycles per MMA).  Tiles are 1024-byte aligned.
+constexpr int KV_TILE = CHUNK * 128;       // 16384
+constexpr int PLS = CHUNK * 16 + 16;       // q tile plane stride: [128 rows][16 B] + 16 B so that planes fall on different banks
+constexpr int Q_BYTES = (NS * CH / 4) * PLS;   // q in fp32: 16 planes of 4 channels
+constexpr int SLOT_BYTES = (2 * KV_TILE + Q_BYTES + 1023) / 1024 * 1024;   // kv head, kv remainder, q
+constexpr int HI_OFF = 0, LO_OFF = KV_TILE, Q_OFF = 2 * KV_TILE;
 constexpr int DIAG_BYTES = 2 * 256;        // diag(D): 2 planes of [16 rows][16 B]
 constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
 constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
@@ -59,7 +62,8 @@ constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
 constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
 constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
 constexpr int NBARS = IN_STAGES * 2 + 2 * 5;           // in_full/in_empty per stage; kv_full, kv_free, d_full, d_empty, q_free x2
-constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 128;
+constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
+static_assert(OFF_SLOTS % 1024 == 0, "k*v tiles must be 1024-byte aligned");
 constexpr int TMEM_COLS = 256;             // A: [0,128)  D0: [128,192)  D1: [192,256)
 constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA and TMA issue warps
 constexpr int THREADS = 32 * (NFE + 6);
@@ -80,11 +84,13 @@ struct Args {
     int64_t hd;
     int pf;          // chunks of L2 prefetch distance (0 = off)
     int dbg;         // diagnostic builds only: knock out parts of the kernel to time the rest
+    unsigned long long* trace;   // diagnostic builds only
 };
 
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor.  layout: 0 = no swizzle, 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout = 0) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | (uint64_t)((lbo >> 4) & 0x3FFF) << 16 |
-           (uint64_t)((sbo >> 4) & 0x3FFF) << 32 | (uint64_t)1 << 46;
+           (uint64_t)((sbo >> 4) & 0x3FFF) << 32 | (uint64_t)1 << 46 | (uint64_t)layout << 61;
 }
 __device__ __forceinline__ uint32_t instr_desc(int M, int N, int b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
@@ -137,6 +143,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {   // lo -> b
 
 #define MBAR_WAIT mbar_wait
 
+// Diagnostic builds only (-DVTX_MR_TRACE): CTA 0 logs (event, clock) pairs per warp into a.trace[warp][256].
+#ifdef VTX_MR_TRACE
+#define TRACE(code)                                                                              \
+    do {                                                                                         \
+        if (blockIdx.x == 0 && lane == 0 && a.trace && trace_n < 256)                            \
+            a.trace[warp * 256 + trace_n++] = ((unsigned long long)(code) << 48) | (unsigned long long)(clock64() & 0xffffffffffffull); \
+    } while (0)
+#else
+#define TRACE(code) do {} while (0)
+#endif
+
 struct Stream {
     int64_t b, ts, te;   // batch, first row, one past the last row this stream stores
     bool active;
@@ -155,7 +172,7 @@ __device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) 
 template <bool INTERLEAVED>
 __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, Args a) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sm_u = smem_u32(sm);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BARS);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BARS + NBARS * 8);
@@ -170,6 +187,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     auto q_free = [&](int sl) { return smem_u32(&bars[BB + 8 + sl]); };
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    int trace_n = 0;
+    (void)trace_n;
     const int64_t g = blockIdx.x % a.G, quad = blockIdx.x / a.G;
     const int K = (int)a.K;
     const int nchunk = (int)(a.seg_len / CHUNK) + 1;     // chunk 0 is the halo chunk (front end only)
@@ -246,22 +265,25 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             }
         }
         const bool swap_qk = INTERLEAVED && a.flip;
-        const uint32_t plane_off = (uint32_t)((s * 2 + p / 4) * PLS + (p % 4) * 4);       // bf16 pair in the kv matrices
+        const uint32_t kv_chunk = (uint32_t)(s * 2 + p / 4), kv_in = (uint32_t)((p % 4) * 4);   // 16-byte chunk and offset of this lane's bf16 pair in a k*v row
         const uint32_t qplane_off = (uint32_t)((s * 4 + p / 2) * PLS + (p % 2) * 8);       // fp32 pair in the q matrix
         for (int k = 0; k < nchunk; ++k) {
             const int slot = k % 2;
+            TRACE(0);
             if (k >= 2) {   // slot reuse: MMAs that read chunk k-2 and the epilogue that read its q are done
                 if (!MBAR_WAIT(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
                 if (k >= 3 && !MBAR_WAIT(q_free(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
             }
             // half chunk n = 2k + (upper half ? 1 : 0) sits in stage n % IN_STAGES; this warp owns WROWS of its 64 rows
             const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
+            TRACE(1);
             if (!MBAR_WAIT(in_full(stg), (uint32_t)((nh / IN_STAGES) & 1), 4)) break;
+            TRACE(2);
 #pragma unroll 1
             for (int hb = 0; hb < WROWS / RB; ++hb) {
                 const uint8_t* box = sm + stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB) * (INTERLEAVED ? 96 : 32);
                 const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
-                const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES + row0 * 16;
+                const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
                 // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early).
                 // All rows of the box are fetched into registers first so that the shared-memory latency is
                 // paid once per box, not once per row (the stores below order memory operations).
@@ -288,6 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(raw[r][0]), "r"(raw[r][1]), "r"(raw[r][2]));
                     __syncwarp();
                     if (lane == 0) mbar_arrive(in_empty(stg));
+                    TRACE(3);
                 }
                 auto unpack = [&](const uint32_t (&e)[3], float (&x)[2][3]) {
                     if (INTERLEAVED) {
@@ -304,8 +327,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
                 for (int i = 0; i < RB; ++i) {
                     if (KO(16)) {
-                        const uint32_t addr = slot_u + (uint32_t)i * 16;
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(raw[i + 2][0]));
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot_u + (row0 + i) * 128 + kv_in), "r"(raw[i + 2][0]));
                         continue;
                     }
                     float x0[2][3];
@@ -324,17 +346,20 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     const float kv0 = k0 * z[0][2], kv1 = k1 * z[1][2];   // rows before the sequence start are zeros
                     const uint32_t hi = pack_bf16(kv0, kv1);
                     const uint32_t lo = pack_bf16(kv0 - bf_lo(hi), kv1 - bf_hi(hi));
-                    const uint32_t addr = slot_u + (uint32_t)i * 16;
+                    // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
+                    const uint32_t kaddr = slot_u + (row0 + i) * 128 + ((kv_chunk ^ (uint32_t)(i & 7)) << 4) + kv_in;
                     if (KO(1) && hi != 0x12345678u) continue;
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + HI_OFF), "r"(hi));
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr + plane_off + LO_OFF), "r"(lo));
-                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr + qplane_off + Q_OFF), "f"(q0), "f"(q1));
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + HI_OFF), "r"(hi));
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + LO_OFF), "r"(lo));
+                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(slot_u + (row0 + i) * 16 + qplane_off + Q_OFF), "f"(q0), "f"(q1));
                 }
                 asm volatile("" ::: "memory");
             }
+            TRACE(4);
             fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(kv_full(slot));
+            TRACE(5);
         }
     } else if (warp < W_EP + 4) {
         // ======== epilogue: thread = output row (TMEM lane) ========================================
@@ -344,38 +369,46 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
         for (int k = 1; k < nchunk; ++k) {
             const int slot = k % 2;
+            TRACE(10);
             if (!MBAR_WAIT(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
+            TRACE(11);
             tc_fence_after();
             __syncwarp();
             const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 64;
-            uint32_t acc[NS][16];
+            float y[NS][16];
 #pragma unroll
-            for (int s = 0; s < NS; ++s) tmem_ld16(taddr + s * 16, acc[s]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            for (int s = 0; s < NS; ++s) {
+                uint32_t ah[16];
+                tmem_ld16(taddr + s * 16, ah);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) y[s][i] = __uint_as_float(ah[i]);
+            }
             // The accumulator now lives in registers: give the TMEM buffer back before anything else, and the
             // q tile as soon as it has been read, so that neither the next MMAs nor the front end two chunks
             // ahead wait for this warp's arithmetic and global stores.
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(d_empty(slot));
+            TRACE(12);
             const uint8_t* qm = sm + OFF_SLOTS + slot * SLOT_BYTES + Q_OFF + r * 16;
-            float y[NS][16];
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const float4 q = KO(32) ? make_float4(1.f, 1.f, 1.f, 1.f)
                                             : *reinterpret_cast<const float4*>(qm + (s * 4 + c4) * PLS);
-                    y[s][4 * c4] = __uint_as_float(acc[s][4 * c4]) * q.x;
-                    y[s][4 * c4 + 1] = __uint_as_float(acc[s][4 * c4 + 1]) * q.y;
-                    y[s][4 * c4 + 2] = __uint_as_float(acc[s][4 * c4 + 2]) * q.z;
-                    y[s][4 * c4 + 3] = __uint_as_float(acc[s][4 * c4 + 3]) * q.w;
+                    y[s][4 * c4] *= q.x;
+                    y[s][4 * c4 + 1] *= q.y;
+                    y[s][4 * c4 + 2] *= q.z;
+                    y[s][4 * c4 + 3] *= q.w;
                 }
             }
 #pragma unroll
             for (int s = 0; s < NS; ++s) asm volatile("" ::"f"(y[s][0]), "f"(y[s][5]), "f"(y[s][10]), "f"(y[s][15]));
             __syncwarp();
             if (lane == 0) mbar_arrive(q_free(slot));
+            TRACE(13);
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
                 if (KO(32)) continue;
@@ -399,37 +432,34 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
             // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
             // is released (kv_free) one whole chunk before the front end needs its slot again.
-            // Descriptors are built once; a K step of 16 rows moves the start-address field by 256 B (16 units).
+            // Descriptors are built once; a K step of 16 rows moves the start-address field by 2048 B (128 units).
             // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
-            uint64_t hi_desc[2], lo_desc[2], skip_hi[2], skip_lo[2];
+            uint64_t hi_desc[2], lo_desc[2];
 #pragma unroll
             for (int sl = 0; sl < 2; ++sl) {
                 const uint32_t base = sm_u + OFF_SLOTS + sl * SLOT_BYTES;
-                hi_desc[sl] = smem_desc(base + HI_OFF, 128, PLS);
-                lo_desc[sl] = smem_desc(base + LO_OFF, 128, PLS);
-                skip_hi[sl] = smem_desc(base + HI_OFF, PLS, 128);
-                skip_lo[sl] = smem_desc(base + LO_OFF, PLS, 128);
+                hi_desc[sl] = smem_desc(base + HI_OFF, 0, 1024, 2);    // B operand: N-major rows of 128 B, 8-row groups 1024 B apart
+                lo_desc[sl] = smem_desc(base + LO_OFF, 0, 1024, 2);
             }
             auto issue_half = [&](int k, bool cur) {
                 const int slot = cur ? k % 2 : (k - 1) % 2;
                 const uint32_t d = tmem + 128 + (k % 2) * 64;
                 const uint32_t a0 = tmem + (cur ? 64 : 0);
                 const uint64_t dh = slot ? hi_desc[1] : hi_desc[0], dl = slot ? lo_desc[1] : lo_desc[0];
-                const uint64_t sh = slot ? skip_hi[1] : skip_hi[0], sl2 = slot ? skip_lo[1] : skip_lo[0];
                 const int nj = KO(64) ? 0 : KO(8) ? 1 : 8;
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
-                    if (jj < nj) {
-                        mma_ts(d, a0 + 8 * jj, dh + (uint64_t)(jj * 16), idesc, (cur || jj > 0) ? 1u : 0u);
-                        mma_ts(d, a0 + 8 * jj, dl + (uint64_t)(jj * 16), idesc, 1u);
-                    }
+                    if (jj >= nj) continue;
+                    const uint64_t off = (uint64_t)(jj * (16 * 128 / 16));     // 16 rows of 128 B per K step, in 16-byte units
+                    mma_ts(d, a0 + 8 * jj, dh + off, idesc, (cur || jj > 0) ? 1u : 0u);
+                    mma_ts(d, a0 + 8 * jj, dl + off, idesc, 1u);
                 }
                 if (cur && a.has_bias && !KO(64)) {
+                    // skip term: the same tile read as a K-major A operand, 32-byte column slice of stream s
 #pragma unroll
                     for (int s = 0; s < NS; ++s) {
-                        const uint64_t off = (uint64_t)((s * 2 * PLS) >> 4);
-                        mma_ss(d + s * CH, sh + off, diag_desc, idesc_skip, 1u);
-                        mma_ss(d + s * CH, sl2 + off, diag_desc, idesc_skip, 1u);
+                        mma_ss(d + s * CH, dh + (uint64_t)(s * 2), diag_desc, idesc_skip, 1u);
+                        mma_ss(d + s * CH, dl + (uint64_t)(s * 2), diag_desc, idesc_skip, 1u);
                     }
                 }
             };
@@ -440,17 +470,22 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 mma_commit(kv_free(0));
             }
             for (int k = 1; k < nchunk && ok; ++k) {
+                TRACE(20);
                 if (!MBAR_WAIT(kv_full(k % 2), (uint32_t)((k / 2) & 1), 6)) break;
+                TRACE(21);
                 tc_fence_after();
                 issue_half(k, true);
                 mma_commit(d_full(k % 2));
+                TRACE(22);
                 if (k + 1 < nchunk) {
                     // D[(k+1)%2] was last read by the epilogue of chunk k-1
                     if (k + 1 >= 3 && !MBAR_WAIT(d_empty((k + 1) % 2), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
+                    TRACE(23);
                     tc_fence_after();
                     issue_half(k + 1, false);
                 }
                 mma_commit(kv_free(k % 2));
+                TRACE(24);
             }
         }
     } else {
@@ -477,6 +512,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             for (int nh = 0; nh < 2 * nchunk; ++nh) {
                 const int stg = nh % IN_STAGES, k = nh / 2, h = nh % 2;
                 if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), (uint32_t)(((nh - IN_STAGES) / IN_STAGES) & 1), 9)) break;
+                TRACE(30);
                 const uint32_t bar = in_full(stg);
                 mbar_expect_tx(bar, NS * BOX_BYTES);
 #pragma unroll
@@ -525,6 +561,7 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     a.hd = p->D;
     a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 0;
     a.dbg = getenv("VTX_MR_DBG") ? atoi(getenv("VTX_MR_DBG")) : 0;
+    a.trace = getenv("VTX_MR_TRACE_PTR") ? (unsigned long long*)strtoull(getenv("VTX_MR_TRACE_PTR"), nullptr, 0) : nullptr;
     if (p->layout == VTX_QKV_COLUMN_SPLIT) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_fir: bad num_heads");
         a.hd = p->D / p->num_heads;

@@ -61,6 +61,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded spin without suspending (for single issuing threads that sit on the critical path).
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, int code) {
+    for (int it = 0; it < (1 << 26); ++it)
+        if (mbar_test_wait(bar, parity)) return true;
+    atomicCAS(&g_device_status, 0, code);
+    return false;
+}
 // Bounded wait: gives up after ~2^22 polls (each poll may itself block for a
 // hardware-defined interval), records `code` in the status word and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
