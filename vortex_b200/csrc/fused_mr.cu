@@ -53,7 +53,7 @@ constexpr int PLS = CHUNK * 16 + 16;       // q tile plane stride: [128 rows][16
 constexpr int Q_BYTES = (NS * CH / 4) * PLS;   // q in fp32: 16 planes of 4 channels
 constexpr int SLOT_BYTES = (2 * KV_TILE + Q_BYTES + 1023) / 1024 * 1024;   // kv head, kv remainder, q
 constexpr int HI_OFF = 0, LO_OFF = KV_TILE, Q_OFF = 2 * KV_TILE;
-constexpr int DIAG_BYTES = 2 * 256;        // diag(D): 2 planes of [16 rows][16 B]
+constexpr int DIAG_BYTES = 128;            // skip parameters D[16] of the group, fp32
 constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
 constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
 constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
@@ -64,7 +64,7 @@ constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
 constexpr int NBARS = IN_STAGES * 2 + 2 * 5;           // in_full/in_empty per stage; kv_full, kv_free, d_full, d_empty, q_free x2
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
 static_assert(OFF_SLOTS % 1024 == 0, "k*v tiles must be 1024-byte aligned");
-constexpr int TMEM_COLS = 256;             // A: [0,128)  D0: [128,192)  D1: [192,256)
+constexpr int TMEM_COLS = 512;             // A: [0,128); accumulator buffer b at 128 + 128 b: [head part 64 | remainder part 64]
 constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA and TMA issue warps
 constexpr int THREADS = 32 * (NFE + 6);
 
@@ -213,13 +213,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             if (l >= 0 && l < K) v = ld_param(a.h, a.h_dtype, g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
             tp[m] = __float2bfloat16_rn(v);
         }
-        __nv_bfloat16* dg = reinterpret_cast<__nv_bfloat16*>(sm + OFF_DIAG);   // diag(D) [k][n]: plane n/8, row k
-        for (int e = tid; e < 256; e += THREADS) {
-            int k = e / 16, n = e % 16;
-            float v = (a.has_bias && k == n) ? ld_param(a.bias, a.bias_dtype, g * CH + n) : 0.f;
-            dg[(n / 8) * 128 + k * 8 + (n % 8)] = __float2bfloat16_rn(v);
-        }
-        // the halo rows of the q matrices are never written by the front end: nothing to clear
+        float* dsk = reinterpret_cast<float*>(sm + OFF_DIAG);                 // skip parameters of this group, fp32
+        for (int c = tid; c < CH; c += THREADS) dsk[c] = a.has_bias ? ld_param(a.bias, a.bias_dtype, g * CH + c) : 0.f;
     }
     fence_proxy_async_smem();
     tc_fence_before();
@@ -364,9 +359,18 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     } else if (warp < W_EP + 4) {
         // ======== epilogue: thread = output row (TMEM lane) ========================================
         const int e = warp - W_EP, r = e * 32 + lane;
-        Stream sts[NS];
+        // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
+        // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
+        __nv_bfloat16* yrow[NS];
+        int nleft[NS];
 #pragma unroll
-        for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
+        for (int s = 0; s < NS; ++s) {
+            const Stream st = stream_of(a, quad, s);
+            yrow[s] = a.y + st.b * a.y_stride_b + (st.ts + r) * a.y_stride_l + g * CH;
+            nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
+        }
+        const float4* dsk = reinterpret_cast<const float4*>(sm + OFF_DIAG);    // skip parameters D[g*16 .. +16), fp32
+        const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
         for (int k = 1; k < nchunk; ++k) {
             const int slot = k % 2;
             TRACE(10);
@@ -374,15 +378,16 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             TRACE(11);
             tc_fence_after();
             __syncwarp();
-            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 64;
+            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 128;
             float y[NS][16];
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
-                uint32_t ah[16];
+                uint32_t ah[16], al[16];
                 tmem_ld16(taddr + s * 16, ah);
+                tmem_ld16(taddr + 64 + s * 16, al);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 16; ++i) y[s][i] = __uint_as_float(ah[i]);
+                for (int i = 0; i < 16; ++i) y[s][i] = __uint_as_float(ah[i]) + __uint_as_float(al[i]);
             }
             // The accumulator now lives in registers: give the TMEM buffer back before anything else, and the
             // q tile as soon as it has been read, so that neither the next MMAs nor the front end two chunks
@@ -391,76 +396,79 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(d_empty(slot));
             TRACE(12);
-            const uint8_t* qm = sm + OFF_SLOTS + slot * SLOT_BYTES + Q_OFF + r * 16;
+            const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
+            uint32_t o[NS][8];
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
+                if (a.has_bias) {
+                    // skip term D[c] * kv[t, c] from this row of the k*v tile (head + remainder); the tile is still
+                    // resident because the front end reuses the slot only after q_free below
+#pragma unroll
+                    for (int hc = 0; hc < 2; ++hc) {
+                        const int c = 2 * s + hc;
+                        const uint32_t off = (uint32_t)(r * 128) + (uint32_t)((c ^ (r & 7)) << 4);
+                        const uint4 h4 = *reinterpret_cast<const uint4*>(slot_p + HI_OFF + off);
+                        const uint4 l4 = *reinterpret_cast<const uint4*>(slot_p + LO_OFF + off);
+                        const float4 d0 = dsk[2 * hc], d1 = dsk[2 * hc + 1];
+                        float* yy = &y[s][8 * hc];
+                        yy[0] = fmaf(d0.x, bf_lo(h4.x) + bf_lo(l4.x), yy[0]);
+                        yy[1] = fmaf(d0.y, bf_hi(h4.x) + bf_hi(l4.x), yy[1]);
+                        yy[2] = fmaf(d0.z, bf_lo(h4.y) + bf_lo(l4.y), yy[2]);
+                        yy[3] = fmaf(d0.w, bf_hi(h4.y) + bf_hi(l4.y), yy[3]);
+                        yy[4] = fmaf(d1.x, bf_lo(h4.z) + bf_lo(l4.z), yy[4]);
+                        yy[5] = fmaf(d1.y, bf_hi(h4.z) + bf_hi(l4.z), yy[5]);
+                        yy[6] = fmaf(d1.z, bf_lo(h4.w) + bf_lo(l4.w), yy[6]);
+                        yy[7] = fmaf(d1.w, bf_hi(h4.w) + bf_hi(l4.w), yy[7]);
+                    }
+                }
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const float4 q = KO(32) ? make_float4(1.f, 1.f, 1.f, 1.f)
-                                            : *reinterpret_cast<const float4*>(qm + (s * 4 + c4) * PLS);
-                    y[s][4 * c4] *= q.x;
-                    y[s][4 * c4 + 1] *= q.y;
-                    y[s][4 * c4 + 2] *= q.z;
-                    y[s][4 * c4 + 3] *= q.w;
+                                            : *reinterpret_cast<const float4*>(slot_p + Q_OFF + r * 16 + (s * 4 + c4) * PLS);
+                    o[s][2 * c4] = pack_bf16(y[s][4 * c4] * q.x, y[s][4 * c4 + 1] * q.y);
+                    o[s][2 * c4 + 1] = pack_bf16(y[s][4 * c4 + 2] * q.z, y[s][4 * c4 + 3] * q.w);
                 }
             }
 #pragma unroll
-            for (int s = 0; s < NS; ++s) asm volatile("" ::"f"(y[s][0]), "f"(y[s][5]), "f"(y[s][10]), "f"(y[s][15]));
+            for (int s = 0; s < NS; ++s) asm volatile("" ::"r"(o[s][0]), "r"(o[s][3]), "r"(o[s][5]), "r"(o[s][7]));
             __syncwarp();
             if (lane == 0) mbar_arrive(q_free(slot));
             TRACE(13);
+            const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
                 if (KO(32)) continue;
-                uint32_t o[8];
-#pragma unroll
-                for (int m = 0; m < 8; ++m) o[m] = pack_bf16(y[s][2 * m], y[s][2 * m + 1]);
-                const int64_t t = sts[s].ts + (int64_t)(k - 1) * CHUNK + r;
-                if (sts[s].active && t < sts[s].te && !(KO(4) && o[0] != 0x12345678u)) {
-                    uint4* dst = reinterpret_cast<uint4*>(a.y + sts[s].b * a.y_stride_b + t * a.y_stride_l + g * CH);
-                    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-                }
+                if ((k - 1) * CHUNK < nleft[s] && !(KO(4) && o[s][0] != 0x12345678u))
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[s][0]),
+                                 "r"(o[s][1]), "r"(o[s][2]), "r"(o[s][3]), "r"(o[s][4]), "r"(o[s][5]), "r"(o[s][6]), "r"(o[s][7])
+                                 : "memory");
             }
         }
     } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(128, NS * CH, 1);
-            const uint32_t idesc_skip = instr_desc(128, CH, 1);
-            const uint64_t diag_desc = smem_desc(sm_u + OFF_DIAG, 128, 256);
+            const uint32_t idesc = instr_desc(128, 2 * NS * CH, 1);
             // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
             // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
             // is released (kv_free) one whole chunk before the front end needs its slot again.
             // Descriptors are built once; a K step of 16 rows moves the start-address field by 2048 B (128 units).
             // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
-            uint64_t hi_desc[2], lo_desc[2];
+            // B operand of one K step: 16 rows x [head tile | remainder tile] = N-major, two 64-channel atoms
+            // KV_TILE bytes apart (LBO), 8-row groups 1024 B apart (SBO), 128-byte swizzle.  N = 128 per MMA:
+            // narrower MMAs run at a fixed ~70 cycles each at this tile height, so both parts go into one.
+            uint64_t kv_desc[2];
 #pragma unroll
-            for (int sl = 0; sl < 2; ++sl) {
-                const uint32_t base = sm_u + OFF_SLOTS + sl * SLOT_BYTES;
-                hi_desc[sl] = smem_desc(base + HI_OFF, 0, 1024, 2);    // B operand: N-major rows of 128 B, 8-row groups 1024 B apart
-                lo_desc[sl] = smem_desc(base + LO_OFF, 0, 1024, 2);
-            }
+            for (int sl = 0; sl < 2; ++sl) kv_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES + HI_OFF, KV_TILE, 1024, 2);
             auto issue_half = [&](int k, bool cur) {
                 const int slot = cur ? k % 2 : (k - 1) % 2;
-                const uint32_t d = tmem + 128 + (k % 2) * 64;
+                const uint32_t d = tmem + 128 + (k % 2) * 128;
                 const uint32_t a0 = tmem + (cur ? 64 : 0);
-                const uint64_t dh = slot ? hi_desc[1] : hi_desc[0], dl = slot ? lo_desc[1] : lo_desc[0];
+                const uint64_t dk = slot ? kv_desc[1] : kv_desc[0];
                 const int nj = KO(64) ? 0 : KO(8) ? 1 : 8;
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
                     if (jj >= nj) continue;
-                    const uint64_t off = (uint64_t)(jj * (16 * 128 / 16));     // 16 rows of 128 B per K step, in 16-byte units
-                    mma_ts(d, a0 + 8 * jj, dh + off, idesc, (cur || jj > 0) ? 1u : 0u);
-                    mma_ts(d, a0 + 8 * jj, dl + off, idesc, 1u);
-                }
-                if (cur && a.has_bias && !KO(64)) {
-                    // skip term: the same tile read as a K-major A operand, 32-byte column slice of stream s
-#pragma unroll
-                    for (int s = 0; s < NS; ++s) {
-                        mma_ss(d + s * CH, dh + (uint64_t)(s * 2), diag_desc, idesc_skip, 1u);
-                        mma_ss(d + s * CH, dl + (uint64_t)(s * 2), diag_desc, idesc_skip, 1u);
-                    }
+                    mma_ts(d, a0 + 8 * jj, dk + (uint64_t)(jj * (16 * 128 / 16)), idesc, (cur || jj > 0) ? 1u : 0u);
                 }
             };
             bool ok = MBAR_WAIT(kv_full(0), 0, 7);          // the halo chunk
@@ -549,8 +557,8 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     VTX_REQUIRE(p->D == p->G * CH, VTX_ERR_UNSUPPORTED, "fused_fir: the tensor-core path needs groups of %d channels", CH);
     VTX_REQUIRE(p->K3 == 3 && !p->b3, VTX_ERR_UNSUPPORTED, "fused_fir: tensor-core path needs a 3-tap featurizer without bias");
     VTX_REQUIRE(p->bias_mode != VTX_BIAS_ADD, VTX_ERR_UNSUPPORTED, "fused_fir: additive bias is not fused on this path");
-    VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 16) == 0 && (p->y_stride_l % 8) == 0 && (p->y_stride_b % 8) == 0,
-                VTX_ERR_ALIGNMENT, "fused_fir: y rows must be 16-byte aligned");
+    VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0,
+                VTX_ERR_ALIGNMENT, "fused_fir: y rows must be 32-byte aligned");
     Args a{};
     a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.h = p->h; a.h_dtype = p->h_dtype;
     a.bias = p->bias; a.bias_dtype = p->bias_dtype; a.has_bias = p->bias_mode == VTX_BIAS_GATED;
