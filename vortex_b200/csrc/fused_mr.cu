@@ -370,6 +370,12 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
         }
         const float4* dsk = reinterpret_cast<const float4*>(sm + OFF_DIAG);    // skip parameters D[g*16 .. +16), fp32
+        bool has_skip = false;       // the skip parameter is all zeros at initialisation: then its term is not evaluated
+#pragma unroll
+        for (int c = 0; c < CH / 4; ++c) {
+            const float4 d = dsk[c];
+            has_skip = has_skip || d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f;
+        }
         const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
         for (int k = 1; k < nchunk; ++k) {
             const int slot = k % 2;
@@ -400,7 +406,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             uint32_t o[NS][8];
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
-                if (a.has_bias) {
+                if (has_skip) {
                     // skip term D[c] * kv[t, c] from this row of the k*v tile (head + remainder); the tile is still
                     // resident because the front end reuses the slot only after q_free below
 #pragma unroll
