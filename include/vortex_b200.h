@@ -200,6 +200,17 @@ typedef struct vtx_iir_params {
 int64_t vtx_iir_scratch_bytes(int64_t B, int64_t L, int64_t D, int64_t S, int64_t complex_poles);
 int vtx_iir_fwd(const vtx_iir_params* p, void* stream);
 
+/* Same operator for callers that cannot allocate device memory where they need it (a server that gave all
+ * free HBM to its cache pool, a C host without a device allocator, a latency-critical loop).  It has no
+ * counterpart in the reference.  p->scratch is ignored: the segment carries live in an array of
+ * VTX_IIR_STATIC_SCRATCH_BYTES that is part of the library image (each GPU that loads the library holds it
+ * until exit).  Sizes needing more (see vtx_iir_scratch_bytes) return VTX_ERR_UNSUPPORTED.  The first call on
+ * a device resolves the array's device address; make it before any stream capture.  All calls share the
+ * array and it keeps the last call's contents (nothing needs clearing); calls that overlap on the GPU race.
+ * Calls no cudaMalloc, cudaFree or other allocating routine. */
+#define VTX_IIR_STATIC_SCRATCH_BYTES (16u << 20)
+int vtx_iir_fwd_noalloc(const vtx_iir_params* p, void* stream);
+
 /* ------------------------------------------------------------------------
  * Decode (one token).
  *

@@ -92,6 +92,7 @@ SYMBOLS = {
     "vtx_modal_filter": (C.c_int, [C.POINTER(ModalParams), _p, _i, _p]),
     "vtx_iir_scratch_bytes": (_i, [_i, _i, _i, _i, _i]),
     "vtx_iir_fwd": (C.c_int, [C.POINTER(IirParams), _p]),
+    "vtx_iir_fwd_noalloc": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),
     "vtx_decode_layer": (C.c_int, [C.POINTER(DecodeLayerParams), _p]),

@@ -329,3 +329,53 @@ extern "C" int vtx_iir_fwd(const vtx_iir_params* p, void* stream) {
     });
     return check_launch("iir");
 }
+
+// ---------------------------------------------------------------------------------------------------
+// vtx_iir_fwd_noalloc: the same modal long convolution for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc (or torch's allocator) at the point where they need the
+// operator: an inference server that handed all free HBM to its KV-cache pool at start-up, a plain C caller
+// that has no allocator of its own on the device, or code in the middle of a latency-critical loop where an
+// allocation could stall or fail.  vtx_iir_fwd asks such a caller for a scratch buffer (the carries between
+// time segments).  This variant brings its own: a fixed array in device global memory that is part of the
+// library image, so every GPU that loads the library sets VTX_IIR_STATIC_SCRATCH_BYTES aside until the
+// process exits.  Inputs and outputs are still the caller's.
+//
+// * Sizes whose carries do not fit (vtx_iir_scratch_bytes(...) > VTX_IIR_STATIC_SCRATCH_BYTES) are refused
+//   with VTX_ERR_UNSUPPORTED; nothing is launched.
+// * The first call on a device looks the array's device address up (cudaGetSymbolAddress with that device
+//   current -- the array's name is only a host-side handle, never a pointer a kernel could use) and keeps it
+//   per device.  Make that first call outside any stream capture.
+// * All calls share the one array and it keeps whatever the last call left in it.  Nothing in it has to be
+//   zero at the start: every word a call reads was written earlier by the same call, except the carry slot of
+//   the last segment, whose value is computed but never used.  Two calls that overlap on the GPU (different
+//   streams, or different host threads) race on the array: serialise them.
+// * No cudaMalloc / cudaFree / allocating library routine is called on this path.
+constexpr size_t kIirStaticScratchBytes = VTX_IIR_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_iir_static_scratch[kIirStaticScratchBytes];
+
+extern "C" int vtx_iir_fwd_noalloc(const vtx_iir_params* p, void* stream) {
+    using namespace vtx;
+    VTX_REQUIRE(p, VTX_ERR_BAD_ARG, "iir(noalloc): null parameter block");
+    VTX_REQUIRE(p->B > 0 && p->L > 0 && p->D > 0 && p->modal.S > 0, VTX_ERR_BAD_ARG, "iir(noalloc): sizes must be positive");
+    const int64_t need = vtx_iir_scratch_bytes(p->B, p->L, p->D, p->modal.S, p->modal.theta != nullptr);
+    VTX_REQUIRE(need <= (int64_t)kIirStaticScratchBytes, VTX_ERR_UNSUPPORTED,
+                "iir(noalloc): this size needs %lld bytes of carries, the built-in scratch holds %lld; "
+                "use vtx_iir_fwd with a caller-provided buffer",
+                (long long)need, (long long)kIirStaticScratchBytes);
+    constexpr int kMaxDevices = 64;
+    static void* dev_ptr[kMaxDevices] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return fail(VTX_ERR_LAUNCH, "iir(noalloc): cudaGetDevice: %s", e == cudaSuccess ? "device index out of range" : cudaGetErrorString(e));
+    if (!dev_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_iir_static_scratch);
+        if (e != cudaSuccess || !ptr) return fail(VTX_ERR_LAUNCH, "iir(noalloc): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        dev_ptr[dev] = ptr;
+    }
+    vtx_iir_params q = *p;
+    q.scratch = dev_ptr[dev];
+    return vtx_iir_fwd(&q, stream);
+}

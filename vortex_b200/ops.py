@@ -356,3 +356,34 @@ def decode_layer(u, w3, b3, fir_state, D, *, h=None, inner_state=None, bias=None
     with _on(u):
         _lib.check(_lib.lib().vtx_decode_layer(C.byref(p), _stream(u)))
     return y, fs_out, new_state
+
+
+def iir_fwd_noalloc(z_pre: torch.Tensor, log_poles, residues, bias, D: int, y: torch.Tensor, state: Optional[torch.Tensor],
+                    *, layout="split", num_heads=1, flip=False, theta=None, res_im=None, round_kv=True) -> None:
+    """``vtx_iir_fwd_noalloc``: the modal long convolution for callers that may not allocate on the device.
+
+    Nothing is allocated here or in the library: ``y`` [B, D, L] (dtype of ``z_pre``) and ``state`` (fp32
+    [B, D, S] or [B, D, S, 2], or None) are the caller's, the parameters must already be fp32, contiguous and
+    on the device, and the segment carries go into the scratch array built into the library.  Sizes beyond
+    that array raise NotImplementedError.  Calls share the array: do not overlap them on the GPU."""
+    _need_cuda(z_pre, residues, log_poles, bias, y, state)
+    B, C3, L = z_pre.shape
+    if C3 != 3 * D or z_pre.stride(2) != 1:
+        raise ValueError("z_pre must be [B, 3D, L] with unit time stride")
+    for t in (log_poles, residues, theta, res_im):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise ValueError("modal parameters must be contiguous fp32 tensors (no conversion is done on this path)")
+    if y.shape != (B, D, L) or not y.is_contiguous() or y.dtype != z_pre.dtype:
+        raise ValueError("y must be a contiguous [B, D, L] tensor of the input dtype")
+    G, S = residues.shape
+    (q, k, v), hd, (sh, sd) = _qkv_views(z_pre, D, layout, num_heads, flip)
+    m = _lib.ModalParams(log_poles=_ptr(log_poles), theta=_ptr(theta), res_re=_ptr(residues), res_im=_ptr(res_im), G=G, S=S)
+    p = _lib.IirParams(
+        q=_ptr(q), q_stride_b=z_pre.stride(0), q_stride_h=sh, q_stride_d=sd,
+        k=_ptr(k), k_stride_b=z_pre.stride(0), k_stride_h=sh, k_stride_d=sd,
+        v=_ptr(v), v_stride_b=z_pre.stride(0), v_stride_h=sh, v_stride_d=sd, head_dim=hd, modal=m,
+        bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        y=_ptr(y), y_stride_b=D * L, y_stride_d=L, y_stride_l=1, state=_ptr(state), scratch=None,
+        B=B, L=L, D=D, round_kv=int(round_kv), io_dtype=_code(z_pre))
+    with _on(z_pre):
+        _lib.check(_lib.lib().vtx_iir_fwd_noalloc(C.byref(p), _stream(z_pre)))
