@@ -1,0 +1,668 @@
+// Hyena-MR fused block on tcgen05 / TMEM (bf16 I/O, filters of 17..128 taps, one per channel group of 16):
+//   featurizer FIR (3 taps) -> q/k/v selection -> k*v -> grouped causal FIR -> (+ D*kv) -> q gate
+// in one pass over HBM, channel-last in and out.
+//
+// The FIR is a blocked-Toeplitz contraction.  For a chunk of 128 output samples of one channel group
+//   Y[128 x N] = [T^ | T][128 x 256] * KV[256 x N],   [T^|T][i][j] = h[128 + i - j]  (0 outside 0..K-1)
+// where KV holds the previous and the current chunk of k*v.  The Toeplitz matrix depends on the group
+// only, so it is expanded ONCE per CTA from the taps straight into tensor memory (A operand in TMEM,
+// 128 lanes x 128 columns of packed bf16) and every tcgen05.mma reads only the data tile from shared
+// memory.  A CTA owns one group and FOUR independent streams (a stream = one batch element and one
+// segment of the time axis), so N = 4 x 16 channels; k*v is split into a bf16 head and a bf16 remainder
+// (two MMAs accumulate into the same fp32 TMEM columns), which keeps the product exact to ~16 bits.
+// The skip term D[c]*kv is one more K=16 MMA per stream against diag(D) with the same shared-memory
+// tile read as a K-major A operand.
+//
+// Warp roles (14 warps): 0-7 front end (TMA-staged rows -> featurizer -> k*v head/remainder and q into
+// the MMA tile), 8-11 epilogue (tcgen05.ld -> q gate -> bf16 -> global), 12 MMA issue, 13 TMA issue.
+// A front-end lane owns one channel pair of one stream and walks 16 rows per chunk with the featurizer
+// history in registers; the four streams of a warp are staged one row apart in shared memory, which makes
+// every shared-memory access of the front end bank-conflict free.  All waits are bounded.
+#include <cstdlib>
+
+#include "tma.cuh"
+
+namespace vtx {
+
+VTX_DEFINE_STATUS_READER()
+
+int launch_fused_state_bf16(const vtx_fused_fir_params* p, cudaStream_t s);   // fused_fir.cu
+
+namespace mr {
+
+constexpr int NS = 4;                      // streams per CTA
+constexpr int CH = 16;                     // channels per group
+constexpr int CHUNK = 128;                 // output samples per MMA chunk
+constexpr int NFE = 8;                     // front-end warps (two per scheduler: the featurizer chain is latency-bound)
+constexpr int WROWS = CHUNK / NFE;         // rows of a chunk owned by one front-end warp
+constexpr int RB = 16;                     // rows a front-end lane fetches into registers at a time
+constexpr int HROWS = 64;                  // rows per staged box: half a chunk, shared by two front-end warps
+                                           // (the TMA unit retires ~12 boxes per microsecond and SM whatever their
+                                           // size, so boxes are made as tall as the shared-memory budget allows)
+constexpr int BOX_ROWS = HROWS + 2 + (NS - 1);         // featurizer halo + stream skew
+constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;       // 6624
+constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;   // q | k | v planes of the non-interleaved layouts (TMA wants 128-byte aligned tiles)
+constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 6912 >= BOX_BYTES
+constexpr int IN_STAGES = 2;                           // half-chunk stages: the lower half of every chunk lands in stage 0, the upper in 1
+                                                       // (a stage is handed back as soon as its rows sit in registers)
+constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage: the four streams' boxes of one half chunk
+// k*v tiles: [128 rows (time)][128 B = 64 channels] bf16 with the 128-byte swizzle (16-byte chunk c of row r is
+// stored at chunk c ^ (r & 7)); the tensor core fetches such rows whole, whereas the unswizzled form is fetched
+// 16 bytes at a time (measured: ~130 instead of ~32 cycles per MMA).  Tiles are 1024-byte aligned.
+constexpr int KV_TILE = CHUNK * 128;       // 16384
+constexpr int PLS = CHUNK * 16 + 16;       // q tile plane stride: [128 rows][16 B] + 16 B so that planes fall on different banks
+constexpr int Q_BYTES = (NS * CH / 4) * PLS;   // q in fp32: 16 planes of 4 channels
+constexpr int SLOT_BYTES = 2 * KV_TILE;    // k*v slot: head tile, remainder tile (two slots: chunks k and k+1)
+constexpr int HI_OFF = 0, LO_OFF = KV_TILE;
+constexpr int Q_SLOTS = 3;                 // q tiles live until the epilogue of their chunk: one more than the k*v slots, so
+                                           // that the front end never waits for the epilogue of the previous chunk
+constexpr int DIAG_BYTES = 128;            // skip parameters D[16] of the group, fp32
+constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
+constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
+constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
+constexpr int OFF_SLOTS = SMEM_IN;
+constexpr int OFF_Q = OFF_SLOTS + SMEM_SLOTS;
+constexpr int OFF_DIAG = OFF_Q + Q_SLOTS * Q_BYTES;
+constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
+constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
+constexpr int NBARS = IN_STAGES * 2 + 2 * 5 + Q_SLOTS;   // in_full/in_empty per stage; kv_full, kv_free, d_full, d_empty, kvr_free x2; q_free x3
+constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
+static_assert(OFF_SLOTS % 1024 == 0, "k*v tiles must be 1024-byte aligned");
+constexpr int TMEM_COLS = 512;             // A: [0,128); accumulator buffer b at 128 + 128 b: [head part 64 | remainder part 64]
+constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA and TMA issue warps
+constexpr int THREADS = 32 * (NFE + 6);
+
+// L2 prefetch of rows that will be staged later: keeps HBM requests in flight without shared memory
+// (full HBM bandwidth needs ~100 KB in flight per SM; the staging ring holds a third of that).
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+struct Args {
+    const void* w3; int64_t w3_dtype;
+    const void* h;  int64_t h_dtype;
+    const void* bias; int64_t bias_dtype;
+    const __nv_bfloat16* u; int64_t u_stride_b, u_stride_l;
+    __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
+    int64_t B, L, D, G, K;
+    int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
+    int layout, flip, taps, has_bias;
+    int64_t hd;
+    int pf;          // chunks of L2 prefetch distance (0 = off)
+    int dbg;         // diagnostic builds only: knock out parts of the kernel to time the rest
+    unsigned long long* trace;   // diagnostic builds only
+};
+
+// Shared-memory matrix descriptor.  layout: 0 = no swizzle, 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout = 0) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (uint64_t)((lbo >> 4) & 0x3FFF) << 16 |
+           (uint64_t)((sbo >> 4) & 0x3FFF) << 32 | (uint64_t)1 << 46 | (uint64_t)layout << 61;
+}
+__device__ __forceinline__ uint32_t instr_desc(int M, int N, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
+           ((uint32_t)(M >> 4) << 24);      // f32 accumulate, bf16 x bf16, A K-major
+}
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {   // lo -> bits [15:0]
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Packed fp32 pairs (one 64-bit register pair per value, low half = first element): the front end and the
+// epilogue are bound by CUDA-core issue slots, and Blackwell executes these as one instruction per pair.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void up2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+#ifdef VTX_MR_KNOCKOUT
+#define KO(bit) (a.dbg & (bit))
+#else
+#define KO(bit) false
+#endif
+
+#define MBAR_WAIT mbar_wait
+
+// Diagnostic builds only (-DVTX_MR_TRACE): CTA 0 logs (event, clock) pairs per warp into a.trace[warp][256].
+#ifdef VTX_MR_TRACE
+#define TRACE(code)                                                                              \
+    do {                                                                                         \
+        if (blockIdx.x == 0 && lane == 0 && a.trace && trace_n < 256)                            \
+            a.trace[warp * 256 + trace_n++] = ((unsigned long long)(code) << 48) | (unsigned long long)(clock64() & 0xffffffffffffull); \
+    } while (0)
+#else
+#define TRACE(code) do {} while (0)
+#endif
+
+struct Stream {
+    int64_t b, ts, te;   // batch, first row, one past the last row this stream stores
+    bool active;
+};
+__device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) {
+    Stream st;
+    int64_t id = quad * NS + s;
+    st.active = id < a.nstream;
+    if (!st.active) id = a.nstream - 1;            // duplicate a real stream; its stores are suppressed
+    st.b = id / a.nseg;
+    st.ts = (id % a.nseg) * a.seg_len;
+    st.te = st.ts + a.seg_len < a.L ? st.ts + a.seg_len : a.L;
+    return st;
+}
+
+// SWAP: interleaved layout with the q and k roles exchanged (the planar layouts exchange their TMA columns instead).
+template <bool INTERLEAVED, bool SWAP>
+__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sm_u = smem_u32(sm);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BARS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BARS + NBARS * 8);
+    // barrier indices
+    auto in_full = [&](int st) { return smem_u32(&bars[st * 2]); };
+    auto in_empty = [&](int st) { return smem_u32(&bars[st * 2 + 1]); };
+    const int BB = IN_STAGES * 2;
+    auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };
+    auto kv_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
+    auto d_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };
+    auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };
+    auto kvr_free = [&](int sl) { return smem_u32(&bars[BB + 8 + sl]); };    // epilogue has read its rows of the k*v slot (skip term)
+    auto q_free = [&](int sl) { return smem_u32(&bars[BB + 10 + sl]); };     // epilogue has read the q tile
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    int trace_n = 0;
+    (void)trace_n;
+    const int64_t g = blockIdx.x % a.G, quad = blockIdx.x / a.G;
+    const int K = (int)a.K;
+    const int nchunk = (int)(a.seg_len / CHUNK) + 1;     // chunk 0 is the halo chunk (front end only)
+
+    // ---------------- setup -------------------------------------------------------------------
+    if (tid == 0) {
+        for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), 1); mbar_init(in_empty(st), NFE / 2); }
+        for (int sl = 0; sl < 2; ++sl) {
+            mbar_init(kv_full(sl), NFE); mbar_init(kv_free(sl), 1); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4); mbar_init(kvr_free(sl), 4);
+        }
+        for (int sl = 0; sl < Q_SLOTS; ++sl) mbar_init(q_free(sl), 4);
+        fence_mbar_init();
+    }
+    if (warp == W_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    {   // taps, zero padded: tp[m] = tap at lag (m - 128), lags outside [0, K) are zero
+        __nv_bfloat16* tp = reinterpret_cast<__nv_bfloat16*>(sm + OFF_TAPS);
+        for (int m = tid; m < 384; m += THREADS) {
+            int l = m - 128;
+            float v = 0.f;
+            if (l >= 0 && l < K) v = ld_param(a.h, a.h_dtype, g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
+            tp[m] = __float2bfloat16_rn(v);
+        }
+        float* dsk = reinterpret_cast<float*>(sm + OFF_DIAG);                 // skip parameters of this group, fp32
+        for (int c = tid; c < CH; c += THREADS) dsk[c] = a.has_bias ? ld_param(a.bias, a.bias_dtype, g * CH + c) : 0.f;
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp >= W_EP && warp < W_EP + 4) {   // expand the Toeplitz matrix into TMEM: lane i holds row i
+        const int i = (warp - W_EP) * 32 + lane;
+        const uint16_t* tp = reinterpret_cast<const uint16_t*>(sm + OFF_TAPS);
+        for (int c0 = 0; c0 < 128; c0 += 16) {
+            uint32_t v[16];
+#pragma unroll
+            for (int m = 0; m < 16; ++m) {
+                int j = 2 * (c0 + m);                                  // columns j, j+1 of [T^|T]: lag = 128 + i - j
+                uint32_t e0 = tp[128 + 128 + i - j], e1 = tp[128 + 127 + i - j];
+                v[m] = e1 << 16 | e0;
+            }
+            tmem_st16(tmem + ((uint32_t)((warp - W_EP) * 32) << 16) + c0, v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+
+    // ---------------- roles ---------------------------------------------------------------------
+    if (warp < NFE) {
+        // ======== front end: warp w owns rows [16w, 16w+16) of every chunk =========================
+        const int w = warp, p = lane % 8, s = lane / 8;
+        const Stream st = stream_of(a, quad, s);
+        f32x2 w3[3][3];     // [q|k|v][tap], each the pair of this lane's two channels
+        {
+            QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
+            int64_t pc[2][3];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) map.get(g * CH + 2 * p + c, pc[c][0], pc[c][1], pc[c][2]);
+#pragma unroll
+            for (int x = 0; x < 3; ++x)
+#pragma unroll
+                for (int j = 0; j < 3; ++j)
+                    w3[x][j] = pk2(ld_param(a.w3, a.w3_dtype, pc[0][x] * 3 + j), ld_param(a.w3, a.w3_dtype, pc[1][x] * 3 + j));
+        }
+        const uint32_t kv_chunk = (uint32_t)(s * 2 + p / 4), kv_in = (uint32_t)((p % 4) * 4);   // 16-byte chunk and offset of this lane's bf16 pair in a k*v row
+        const uint32_t qplane_off = (uint32_t)((s * 4 + p / 2) * PLS + (p % 2) * 8);       // fp32 pair in the q matrix
+        for (int k = 0; k < nchunk; ++k) {
+            const int slot = k % 2;
+            TRACE(0);
+            if (k >= 2) {   // slot reuse: MMAs that read chunk k-2 and the epilogue that read its q are done
+                if (!MBAR_WAIT(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
+                if (k >= 3 && !MBAR_WAIT(kvr_free(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
+                // q tile k % 3 was last read by the epilogue of chunk k-3 (chunk 0 has no epilogue)
+                if (k >= 4) {
+                    const int j = k - 3, first = (j % Q_SLOTS) ? (j % Q_SLOTS) : Q_SLOTS;
+                    if (!MBAR_WAIT(q_free(k % Q_SLOTS), (uint32_t)(((j - first) / Q_SLOTS) & 1), 11)) break;
+                }
+            }
+            // half chunk n = 2k + (upper half ? 1 : 0) sits in stage n % IN_STAGES; this warp owns WROWS of its 64 rows
+            const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
+            TRACE(1);
+            if (!MBAR_WAIT(in_full(stg), (uint32_t)((nh / IN_STAGES) & 1), 4)) break;
+            TRACE(2);
+#pragma unroll 1
+            for (int hb = 0; hb < WROWS / RB; ++hb) {
+                const uint8_t* box = sm + stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB) * (INTERLEAVED ? 96 : 32);
+                const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
+                const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
+                const uint32_t q_u = sm_u + OFF_Q + (k % Q_SLOTS) * Q_BYTES;
+                // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early).
+                // All rows of the box are fetched into registers first so that the shared-memory latency is
+                // paid once per box, not once per row (the stores below order memory operations).
+                uint32_t raw[RB + 2][3];
+#pragma unroll
+                for (int r = 0; r < RB + 2; ++r) {
+                    if (KO(2)) {
+                        raw[r][0] = raw[r][1] = raw[r][2] = 0x3f803f80u + r + lane;
+                    } else if (INTERLEAVED) {
+                        const uint32_t* rp = reinterpret_cast<const uint32_t*>(box + (r + s) * 96) + 3 * p;
+                        raw[r][0] = rp[0]; raw[r][1] = rp[1]; raw[r][2] = rp[2];
+                    } else {
+#pragma unroll
+                        for (int pl = 0; pl < 3; ++pl)
+                            raw[r][pl] = reinterpret_cast<const uint32_t*>(box + pl * IN_PLANE + (r + s) * 32)[p];
+                    }
+                }
+                if (hb == WROWS / RB - 1) {
+                    // Every row this warp needs from the stage now sits in registers: hand the stage back to the
+                    // TMA warp before the arithmetic starts, so that nearly the whole ring can be in flight (HBM
+                    // latency under load is ~2 us; a stage that stayed busy during the arithmetic would leave a
+                    // single stage in flight).  The empty asm makes the loaded values a dependency of the arrive.
+#pragma unroll
+                    for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(raw[r][0]), "r"(raw[r][1]), "r"(raw[r][2]));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(in_empty(stg));
+                    TRACE(3);
+                }
+                // x[0..2] = q | k | v samples of the lane's channel pair (packed positions before any q/k swap)
+                auto unpack = [&](const uint32_t (&e)[3], f32x2 (&x)[3]) {
+                    if (INTERLEAVED) {
+                        x[0] = pk2(bf_lo(e[0]), bf_hi(e[1]));
+                        x[1] = pk2(bf_hi(e[0]), bf_lo(e[2]));
+                        x[2] = pk2(bf_lo(e[1]), bf_hi(e[2]));
+                    } else {
+#pragma unroll
+                        for (int pl = 0; pl < 3; ++pl) x[pl] = pk2(bf_lo(e[pl]), bf_hi(e[pl]));
+                    }
+                };
+                f32x2 x1[3], x2[3];
+                unpack(raw[0], x2);
+                unpack(raw[1], x1);
+#pragma unroll
+                for (int i = 0; i < RB; ++i) {
+                    if (KO(16)) {
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot_u + (row0 + i) * 128 + kv_in), "r"(raw[i + 2][0]));
+                        continue;
+                    }
+                    f32x2 x0[3], z[3];
+                    unpack(raw[i + 2], x0);
+#pragma unroll
+                    for (int x = 0; x < 3; ++x) {
+                        z[x] = fma2(w3[x][0], x2[x], fma2(w3[x][1], x1[x], mul2(w3[x][2], x0[x])));
+                        x2[x] = x1[x];
+                        x1[x] = x0[x];
+                    }
+                    const f32x2 q = SWAP ? z[1] : z[0];
+                    const f32x2 kv = mul2(SWAP ? z[0] : z[1], z[2]);          // rows before the sequence start are zeros
+                    float kv0, kv1;
+                    up2(kv, kv0, kv1);
+                    const uint32_t hi = pack_bf16(kv0, kv1);
+                    float r0, r1;
+                    up2(sub2(kv, pk2(bf_lo(hi), bf_hi(hi))), r0, r1);
+                    const uint32_t lo = pack_bf16(r0, r1);
+                    // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
+                    const uint32_t kaddr = slot_u + (row0 + i) * 128 + ((kv_chunk ^ (uint32_t)(i & 7)) << 4) + kv_in;
+                    if (KO(1) && hi != 0x12345678u) continue;
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + HI_OFF), "r"(hi));
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + LO_OFF), "r"(lo));
+                    asm volatile("st.shared.b64 [%0], %1;" ::"r"(q_u + (row0 + i) * 16 + qplane_off), "l"(q));
+                }
+                asm volatile("" ::: "memory");
+            }
+            TRACE(4);
+            fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(kv_full(slot));
+            TRACE(5);
+        }
+    } else if (warp < W_EP + 4) {
+        // ======== epilogue: thread = output row (TMEM lane) ========================================
+        const int e = warp - W_EP, r = e * 32 + lane;
+        // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
+        // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
+        __nv_bfloat16* yrow[NS];
+        int nleft[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const Stream st = stream_of(a, quad, s);
+            yrow[s] = a.y + st.b * a.y_stride_b + (st.ts + r) * a.y_stride_l + g * CH;
+            nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
+        }
+        const float4* dsk = reinterpret_cast<const float4*>(sm + OFF_DIAG);    // skip parameters D[g*16 .. +16), fp32
+        bool has_skip = false;       // the skip parameter is all zeros at initialisation: then its term is not evaluated
+#pragma unroll
+        for (int c = 0; c < CH / 4; ++c) {
+            const float4 d = dsk[c];
+            has_skip = has_skip || d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f;
+        }
+        const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
+        for (int k = 1; k < nchunk; ++k) {
+            const int slot = k % 2;
+            TRACE(10);
+            if (!MBAR_WAIT(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
+            TRACE(11);
+            tc_fence_after();
+            __syncwarp();
+            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 128;
+            // head parts of all streams first (straight into y), then one remainder part at a time: keeps the peak
+            // register count at 64 + 16 values
+            uint32_t ah[NS][16];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) tmem_ld16(taddr + s * 16, ah[s]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            f32x2 y[NS][8];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                uint32_t al[16];
+                tmem_ld16(taddr + 64 + s * 16, al);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    y[s][i] = add2(pk2(__uint_as_float(ah[s][2 * i]), __uint_as_float(ah[s][2 * i + 1])),
+                                   pk2(__uint_as_float(al[2 * i]), __uint_as_float(al[2 * i + 1])));
+            }
+            // The accumulator now lives in registers: give the TMEM buffer back before anything else, so that the
+            // next MMAs do not wait for this warp's arithmetic and global stores.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty(slot));
+            TRACE(12);
+            const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
+            const uint8_t* q_p = sm + OFF_Q + (k % Q_SLOTS) * Q_BYTES + r * 16;
+            const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                if (has_skip) {
+                    // skip term D[c] * kv[t, c] from this row of the k*v tile (head + remainder)
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const int c = 2 * s + hf;
+                        const uint32_t off = (uint32_t)(r * 128) + (uint32_t)((c ^ (r & 7)) << 4);
+                        const uint4 h4 = *reinterpret_cast<const uint4*>(slot_p + HI_OFF + off);
+                        const uint4 l4 = *reinterpret_cast<const uint4*>(slot_p + LO_OFF + off);
+                        const float4 d0 = dsk[2 * hf], d1 = dsk[2 * hf + 1];
+                        f32x2* yy = &y[s][4 * hf];
+                        yy[0] = fma2(pk2(d0.x, d0.y), add2(pk2(bf_lo(h4.x), bf_hi(h4.x)), pk2(bf_lo(l4.x), bf_hi(l4.x))), yy[0]);
+                        yy[1] = fma2(pk2(d0.z, d0.w), add2(pk2(bf_lo(h4.y), bf_hi(h4.y)), pk2(bf_lo(l4.y), bf_hi(l4.y))), yy[1]);
+                        yy[2] = fma2(pk2(d1.x, d1.y), add2(pk2(bf_lo(h4.z), bf_hi(h4.z)), pk2(bf_lo(l4.z), bf_hi(l4.z))), yy[2]);
+                        yy[3] = fma2(pk2(d1.z, d1.w), add2(pk2(bf_lo(h4.w), bf_hi(h4.w)), pk2(bf_lo(l4.w), bf_hi(l4.w))), yy[3]);
+                    }
+                }
+                uint32_t o[8];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    float2 qa = make_float2(1.f, 1.f), qb = qa;
+                    if (!KO(32)) {
+                        const float4 q = *reinterpret_cast<const float4*>(q_p + (s * 4 + c4) * PLS);
+                        qa = make_float2(q.x, q.y);
+                        qb = make_float2(q.z, q.w);
+                    }
+                    float o0, o1, o2, o3;
+                    up2(mul2(y[s][2 * c4], pk2(qa.x, qa.y)), o0, o1);
+                    up2(mul2(y[s][2 * c4 + 1], pk2(qb.x, qb.y)), o2, o3);
+                    o[2 * c4] = pack_bf16(o0, o1);
+                    o[2 * c4 + 1] = pack_bf16(o2, o3);
+                }
+                if (KO(32)) continue;
+                if ((k - 1) * CHUNK < nleft[s] && !(KO(4) && o[0] != 0x12345678u))
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[0]),
+                                 "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                                 : "memory");
+            }
+            // every shared-memory read of this chunk is done: its k*v slot and q tile may be rewritten
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(kvr_free(slot)); mbar_arrive(q_free(k % Q_SLOTS)); }
+            TRACE(13);
+        }
+    } else if (warp == W_MMA) {
+        // ======== MMA issue =========================================================================
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(128, 2 * NS * CH, 1);
+            // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
+            // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
+            // is released (kv_free) one whole chunk before the front end needs its slot again.
+            // Descriptors are built once; a K step of 16 rows moves the start-address field by 2048 B (128 units).
+            // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
+            // B operand of one K step: 16 rows x [head tile | remainder tile] = N-major, two 64-channel atoms
+            // KV_TILE bytes apart (LBO), 8-row groups 1024 B apart (SBO), 128-byte swizzle.  N = 128 per MMA:
+            // narrower MMAs run at a fixed ~70 cycles each at this tile height, so both parts go into one.
+            uint64_t kv_desc[2];
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) kv_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES + HI_OFF, KV_TILE, 1024, 2);
+            auto issue_half = [&](int k, bool cur) {
+                const int slot = cur ? k % 2 : (k - 1) % 2;
+                const uint32_t d = tmem + 128 + (k % 2) * 128;
+                const uint32_t a0 = tmem + (cur ? 64 : 0);
+                const uint64_t dk = slot ? kv_desc[1] : kv_desc[0];
+                const int nj = KO(64) ? 0 : KO(8) ? 1 : 8;
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                    if (jj >= nj) continue;
+                    mma_ts(d, a0 + 8 * jj, dk + (uint64_t)(jj * (16 * 128 / 16)), idesc, (cur || jj > 0) ? 1u : 0u);
+                }
+            };
+            bool ok = MBAR_WAIT(kv_full(0), 0, 7);          // the halo chunk
+            if (ok && nchunk > 1) {
+                tc_fence_after();
+                issue_half(1, false);
+                mma_commit(kv_free(0));
+            }
+            for (int k = 1; k < nchunk && ok; ++k) {
+                TRACE(20);
+                if (!MBAR_WAIT(kv_full(k % 2), (uint32_t)((k / 2) & 1), 6)) break;
+                TRACE(21);
+                tc_fence_after();
+                issue_half(k, true);
+                mma_commit(d_full(k % 2));
+                TRACE(22);
+                if (k + 1 < nchunk) {
+                    // D[(k+1)%2] was last read by the epilogue of chunk k-1
+                    if (k + 1 >= 3 && !MBAR_WAIT(d_empty((k + 1) % 2), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
+                    TRACE(23);
+                    tc_fence_after();
+                    issue_half(k + 1, false);
+                }
+                mma_commit(kv_free(k % 2));
+                TRACE(24);
+            }
+        }
+    } else {
+        // first packed column of this group's q | k | v data (one contiguous run when interleaved)
+        Stream sts[NS];
+        int64_t col[3] = {0, 0, 0};
+#pragma unroll
+        for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
+        if (INTERLEAVED) {
+            col[0] = 3 * g * CH;
+        } else {
+            const int64_t d0 = g * CH;
+            if (a.layout == VTX_QKV_COLUMN_SPLIT) {
+                int64_t n = d0 / a.hd, j = d0 - n * a.hd;
+                col[0] = n * 3 * a.hd + j; col[1] = col[0] + a.hd; col[2] = col[0] + 2 * a.hd;
+            } else {
+                col[0] = d0; col[1] = a.D + d0; col[2] = 2 * a.D + d0;
+            }
+            if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
+        }
+        if (lane == 0) {
+            // ======== TMA issue ======================================================================
+            tma_prefetch_desc(&tmap);
+            for (int nh = 0; nh < 2 * nchunk; ++nh) {
+                const int stg = nh % IN_STAGES, k = nh / 2, h = nh % 2;
+                if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), (uint32_t)(((nh - IN_STAGES) / IN_STAGES) & 1), 9)) break;
+                TRACE(30);
+                const uint32_t bar = in_full(stg);
+                mbar_expect_tx(bar, NS * BOX_BYTES);
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
+                    const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK + h * HROWS - 2 - s);
+                    if (INTERLEAVED) {
+                        tma_load_3d(dst, &tmap, bar, (int)col[0], row, (int)sts[s].b);
+                    } else {
+#pragma unroll
+                        for (int pl = 0; pl < 3; ++pl)
+                            tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, (int)col[pl], row, (int)sts[s].b);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown -------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == W_MMA) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+}  // namespace mr
+
+int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
+    using namespace mr;
+    VTX_REQUIRE(p->io_dtype == VTX_BF16, VTX_ERR_UNSUPPORTED, "fused_fir: the tensor-core path takes bf16 I/O");
+    VTX_REQUIRE(p->K <= CHUNK, VTX_ERR_UNSUPPORTED, "fused_fir: filter length %lld > %d", (long long)p->K, CHUNK);
+    VTX_REQUIRE(p->D == p->G * CH, VTX_ERR_UNSUPPORTED, "fused_fir: the tensor-core path needs groups of %d channels", CH);
+    VTX_REQUIRE(p->K3 == 3 && !p->b3, VTX_ERR_UNSUPPORTED, "fused_fir: tensor-core path needs a 3-tap featurizer without bias");
+    VTX_REQUIRE(p->bias_mode != VTX_BIAS_ADD, VTX_ERR_UNSUPPORTED, "fused_fir: additive bias is not fused on this path");
+    VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0,
+                VTX_ERR_ALIGNMENT, "fused_fir: y rows must be 32-byte aligned");
+    Args a{};
+    a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.h = p->h; a.h_dtype = p->h_dtype;
+    a.bias = p->bias; a.bias_dtype = p->bias_dtype; a.has_bias = p->bias_mode == VTX_BIAS_GATED;
+    a.u = static_cast<const __nv_bfloat16*>(p->u); a.u_stride_b = p->u_stride_b; a.u_stride_l = p->u_stride_l;
+    a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
+    a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
+    a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
+    a.hd = p->D;
+    a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 0;
+    a.dbg = getenv("VTX_MR_DBG") ? atoi(getenv("VTX_MR_DBG")) : 0;
+    a.trace = getenv("VTX_MR_TRACE_PTR") ? (unsigned long long*)strtoull(getenv("VTX_MR_TRACE_PTR"), nullptr, 0) : nullptr;
+    if (p->layout == VTX_QKV_COLUMN_SPLIT) {
+        VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_fir: bad num_heads");
+        a.hd = p->D / p->num_heads;
+        VTX_REQUIRE(a.hd % CH == 0, VTX_ERR_UNSUPPORTED, "fused_fir: column split needs head size %% %d == 0", CH);
+    }
+    VTX_REQUIRE(p->layout == VTX_QKV_INTERLEAVED || (p->D * 2) % 16 == 0, VTX_ERR_ALIGNMENT,
+                "fused_fir: D*itemsize must be a multiple of 16 bytes for this q/k/v layout");
+    // segments: enough CTAs (group x stream quads) for ~7 rounds over the SMs, whole chunks each
+    const int64_t nchunks_total = ceil_div<int64_t>(p->L, CHUNK);
+    int64_t nseg = 1;
+    while (p->G * ceil_div<int64_t>(p->B * nseg, NS) < (int64_t)kNumSMs * 6 && nseg * 2 <= nchunks_total &&
+           ceil_div<int64_t>(nchunks_total, nseg * 2) >= 8)
+        nseg *= 2;
+    a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
+    a.nseg = ceil_div<int64_t>(p->L, a.seg_len);
+    a.nstream = p->B * a.nseg;
+    const int64_t nquad = ceil_div<int64_t>(a.nstream, NS);
+    VTX_REQUIRE(p->G * nquad < (int64_t)1 << 31, VTX_ERR_UNSUPPORTED, "fused_fir: too many work items");
+
+    const bool inter = p->layout == VTX_QKV_INTERLEAVED;
+    CUtensorMap tmap;
+    if (int rc = make_tmap_3d(&tmap, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
+                              inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_fir(mr)"))
+        return rc;
+    const int variant = !inter ? 0 : (a.flip ? 2 : 1);
+    auto kern = variant == 0 ? fused_mr_kernel<false, false> : variant == 1 ? fused_mr_kernel<true, false> : fused_mr_kernel<true, true>;
+    // the opt-in is a per-device property of the function: remember it per device
+    static bool attr_set[64][3] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev][variant]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
+        if (dev >= 0 && dev < 64) attr_set[dev][variant] = true;
+    }
+    kern<<<(unsigned)(p->G * nquad), THREADS, SMEM_BYTES, stream>>>(tmap, a);
+    if (int rc = check_launch("fused_fir(mr)")) return rc;
+    if (p->fir_state || p->inner_state) return launch_fused_state_bf16(p, stream);
+    return VTX_OK;
+}
+
+}  // namespace vtx

@@ -33,9 +33,15 @@ namespace mr {
 constexpr int NS = 4;                      // streams per CTA
 constexpr int CH = 16;                     // channels per group
 constexpr int CHUNK = 128;                 // output samples per MMA chunk
-constexpr int NFE = 8;                     // front-end warps (two per scheduler: the featurizer chain is latency-bound)
+#ifndef VTX_MR_NFE
+#define VTX_MR_NFE 8
+#endif
+constexpr int NFE = VTX_MR_NFE;                     // front-end warps (two per scheduler: the featurizer chain is latency-bound)
 constexpr int WROWS = CHUNK / NFE;         // rows of a chunk owned by one front-end warp
-constexpr int RB = 16;                     // rows a front-end lane fetches into registers at a time
+#ifndef VTX_MR_RB
+#define VTX_MR_RB 8
+#endif
+constexpr int RB = VTX_MR_RB;                     // rows a front-end lane fetches into registers at a time
 constexpr int HROWS = 64;                  // rows per staged box: half a chunk, shared by two front-end warps
                                            // (the TMA unit retires ~12 boxes per microsecond and SM whatever their
                                            // size, so boxes are made as tall as the shared-memory budget allows)
@@ -43,16 +49,25 @@ constexpr int BOX_ROWS = HROWS + 2 + (NS - 1);         // featurizer halo + stre
 constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;       // 6624
 constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;   // q | k | v planes of the non-interleaved layouts (TMA wants 128-byte aligned tiles)
 constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 6912 >= BOX_BYTES
-constexpr int IN_STAGES = 3;                           // ring of half-chunk stages
+#ifndef VTX_MR_IN_STAGES
+#define VTX_MR_IN_STAGES 4
+#endif
+constexpr int IN_STAGES = VTX_MR_IN_STAGES;            // ring of half-chunk stages (a stage is handed back as soon as its rows sit
+                                                       // in registers); HBM latency under load is ~2 us, so full bandwidth needs
+                                                       // ~100 KB in flight per SM: the ring gets all the shared memory that is left
 constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage: the four streams' boxes of one half chunk
 // k*v tiles: [128 rows (time)][128 B = 64 channels] bf16 with the 128-byte swizzle (16-byte chunk c of row r is
 // stored at chunk c ^ (r & 7)); the tensor core fetches such rows whole, whereas the unswizzled form is fetched
 // 16 bytes at a time (measured: ~130 instead of ~32 cycles per MMA).  Tiles are 1024-byte aligned.
 constexpr int KV_TILE = CHUNK * 128;       // 16384
-constexpr int PLS = CHUNK * 16 + 16;       // q tile plane stride: [128 rows][16 B] + 16 B so that planes fall on different banks
-constexpr int Q_BYTES = (NS * CH / 4) * PLS;   // q in fp32: 16 planes of 4 channels
-constexpr int SLOT_BYTES = (2 * KV_TILE + Q_BYTES + 1023) / 1024 * 1024;   // kv head, kv remainder, q
-constexpr int HI_OFF = 0, LO_OFF = KV_TILE, Q_OFF = 2 * KV_TILE;
+// q tile: the gate is kept to 24 bits (sign, exponent, 15 mantissa bits: a bf16-rounded gate would by itself cost as
+// much accuracy as the rounding of the output).  Upper 16 bits in a tile shaped like a k*v tile (same swizzle, so the
+// front end reuses its store address), third byte in a [128 rows][64 B] tile whose 16-byte chunk c of row r sits at
+// chunk c ^ ((r >> 1) & 3) (conflict-free for the row-per-lane 16-byte reads of the epilogue).
+constexpr int QH_TILE = KV_TILE, QM_TILE = CHUNK * 64;
+constexpr int Q_BYTES = QH_TILE + QM_TILE;     // 24576
+constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE, QM_OFF = 2 * KV_TILE + QH_TILE;
+constexpr int SLOT_BYTES = 2 * KV_TILE + Q_BYTES;      // one chunk: k*v head, k*v remainder, q upper halves, q third bytes
 constexpr int DIAG_BYTES = 128;            // skip parameters D[16] of the group, fp32
 constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
 constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
@@ -61,12 +76,18 @@ constexpr int OFF_SLOTS = SMEM_IN;
 constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
 constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
 constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
-constexpr int NBARS = IN_STAGES * 2 + 2 * 5;           // in_full/in_empty per stage; kv_full, kv_free, d_full, d_empty, q_free x2
+constexpr int NBARS = IN_STAGES * 2 + 2 * 4;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty x2
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
-static_assert(OFF_SLOTS % 1024 == 0, "k*v tiles must be 1024-byte aligned");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0, "k*v tiles must be 1024-byte aligned");
 constexpr int TMEM_COLS = 512;             // A: [0,128); accumulator buffer b at 128 + 128 b: [head part 64 | remainder part 64]
-constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA and TMA issue warps
-constexpr int THREADS = 32 * (NFE + 6);
+#ifndef VTX_MR_NTMA
+#define VTX_MR_NTMA 2
+#endif
+constexpr int NTMA = VTX_MR_NTMA;          // TMA issue warps: one thread issues a box of 96-byte rows every ~300 cycles only
+constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA warp, first TMA warp
+constexpr int THREADS = 32 * (NFE + 5 + NTMA);
+static_assert(NS % NTMA == 0 && THREADS <= 1024 && NFE % 8 == 0 && (CHUNK / NFE) % RB == 0, "warp roles");
 
 // L2 prefetch of rows that will be staged later: keeps HBM requests in flight without shared memory
 // (full HBM bandwidth needs ~100 KB in flight per SM; the staging ring holds a third of that).
@@ -117,7 +138,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr) : "memory");
+        : "r"(taddr));
+}
+// Wait for the thread's tcgen05.ld operations.  The loaded registers are passed through an (empty) volatile asm right
+// behind the wait, so that no use of them can be scheduled above it.
+__device__ __forceinline__ void tmem_ld_touch(uint32_t (&v)[16]) {
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                      "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]));
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[16], uint32_t (&b)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    tmem_ld_touch(a);
+    tmem_ld_touch(b);
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
     asm volatile(
@@ -135,13 +167,60 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {   // lo -> b
     return r;
 }
 
+// Packed fp32 pairs (one 64-bit register pair per value, low half = first element): the front end and the
+// epilogue are bound by CUDA-core issue slots, and Blackwell executes these as one instruction per pair.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void up2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 #ifdef VTX_MR_KNOCKOUT
 #define KO(bit) (a.dbg & (bit))
 #else
 #define KO(bit) false
 #endif
 
+#ifdef VTX_MR_LANE0_WAIT
+// One lane polls, the warp learns the outcome through a shuffle (the warp-level barrier inside it orders memory).
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int code) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, code);
+    return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+}
+#define WARP_WAIT warp_wait
+#else
+#define WARP_WAIT mbar_wait
+#endif
+#ifdef VTX_MR_SPIN
+#undef WARP_WAIT
+#define WARP_WAIT mbar_spin
+#define MBAR_WAIT mbar_spin
+#else
 #define MBAR_WAIT mbar_wait
+#endif
 
 // Diagnostic builds only (-DVTX_MR_TRACE): CTA 0 logs (event, clock) pairs per warp into a.trace[warp][256].
 #ifdef VTX_MR_TRACE
@@ -169,7 +248,8 @@ __device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) 
     return st;
 }
 
-template <bool INTERLEAVED>
+// SWAP: interleaved layout with the q and k roles exchanged (the planar layouts exchange their TMA columns instead).
+template <bool INTERLEAVED, bool SWAP>
 __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -181,23 +261,24 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     auto in_empty = [&](int st) { return smem_u32(&bars[st * 2 + 1]); };
     const int BB = IN_STAGES * 2;
     auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };
-    auto kv_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
+    // slot_free: the chunk in this slot is no longer needed.  Five arrivals: the four epilogue warps (k*v rows of the skip
+    // term and the q tile read) and the MMA warp's commit behind the MMAs of the next chunk that read the k*v tile.
+    auto slot_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
     auto d_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };
     auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };
-    auto q_free = [&](int sl) { return smem_u32(&bars[BB + 8 + sl]); };
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     int trace_n = 0;
     (void)trace_n;
     const int64_t g = blockIdx.x % a.G, quad = blockIdx.x / a.G;
     const int K = (int)a.K;
-    const int nchunk = (int)(a.seg_len / CHUNK) + 1;     // chunk 0 is the halo chunk (front end only)
+    const int nchunk = KO(512) ? 0 : (int)(a.seg_len / CHUNK) + 1;     // chunk 0 is the halo chunk (front end only)
 
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
-        for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), 1); mbar_init(in_empty(st), NFE / 2); }
+        for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), NTMA); mbar_init(in_empty(st), NFE / 2); }
         for (int sl = 0; sl < 2; ++sl) {
-            mbar_init(kv_full(sl), NFE); mbar_init(kv_free(sl), 1); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4); mbar_init(q_free(sl), 4);
+            mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 5); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
         }
         fence_mbar_init();
     }
@@ -246,39 +327,44 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         // ======== front end: warp w owns rows [16w, 16w+16) of every chunk =========================
         const int w = warp, p = lane % 8, s = lane / 8;
         const Stream st = stream_of(a, quad, s);
-        float w3[2][3][3];
+        f32x2 w3[3][3];     // [q|k|v][tap], each the pair of this lane's two channels
         {
             QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
+            int64_t pc[2][3];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                int64_t pc[3];
-                map.get(g * CH + 2 * p + c, pc[0], pc[1], pc[2]);
+            for (int c = 0; c < 2; ++c) map.get(g * CH + 2 * p + c, pc[c][0], pc[c][1], pc[c][2]);
 #pragma unroll
-                for (int x = 0; x < 3; ++x)
+            for (int x = 0; x < 3; ++x)
 #pragma unroll
-                    for (int j = 0; j < 3; ++j) w3[c][x][j] = ld_param(a.w3, a.w3_dtype, pc[x] * 3 + j);
-            }
+                for (int j = 0; j < 3; ++j)
+                    w3[x][j] = pk2(ld_param(a.w3, a.w3_dtype, pc[0][x] * 3 + j), ld_param(a.w3, a.w3_dtype, pc[1][x] * 3 + j));
         }
-        const bool swap_qk = INTERLEAVED && a.flip;
         const uint32_t kv_chunk = (uint32_t)(s * 2 + p / 4), kv_in = (uint32_t)((p % 4) * 4);   // 16-byte chunk and offset of this lane's bf16 pair in a k*v row
-        const uint32_t qplane_off = (uint32_t)((s * 4 + p / 2) * PLS + (p % 2) * 8);       // fp32 pair in the q matrix
+        const uint32_t qm_in = (uint32_t)(2 * p);                                          // this lane's two third-bytes in the 16-byte chunk s of a q row
+#ifdef VTX_MR_STAGGER_NS
+        // The two front-end warps of a scheduler (w and w + 4) alternate between a phase that waits and fetches and a
+        // phase that is bound by the arithmetic pipes; started half a period apart they keep each other's pipes busy.
+        if (w >= NFE / 2) __nanosleep(VTX_MR_STAGGER_NS);
+#endif
         for (int k = 0; k < nchunk; ++k) {
             const int slot = k % 2;
             TRACE(0);
-            if (k >= 2) {   // slot reuse: MMAs that read chunk k-2 and the epilogue that read its q are done
-                if (!MBAR_WAIT(kv_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
-                if (k >= 3 && !MBAR_WAIT(q_free(slot), (uint32_t)(((k - 3) / 2) & 1), 3)) break;
-            }
             // half chunk n = 2k + (upper half ? 1 : 0) sits in stage n % IN_STAGES; this warp owns WROWS of its 64 rows
             const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
-            TRACE(1);
-            if (!MBAR_WAIT(in_full(stg), (uint32_t)((nh / IN_STAGES) & 1), 4)) break;
+            if (!KO(128) && !WARP_WAIT(in_full(stg), (uint32_t)((nh / IN_STAGES) & 1), 4)) break;
             TRACE(2);
+            bool slot_ok = true;
 #pragma unroll 1
             for (int hb = 0; hb < WROWS / RB; ++hb) {
                 const uint8_t* box = sm + stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB) * (INTERLEAVED ? 96 : 32);
                 const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
                 const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
+                const uint32_t q_u = slot_u + QH_OFF;
+                // Tiles are 1024-byte aligned, so the swizzle (16-byte chunk index XOR row phase) is one XOR on the address
+                // of the lane's element in row 0; row offsets are compile-time immediates of the stores.
+                const uint32_t kv_a0 = slot_u + (kv_chunk << 4) + kv_in + row0 * 128;
+                const uint32_t qh_a0 = q_u + (kv_chunk << 4) + kv_in + row0 * 128;
+                const uint32_t qm_a0 = q_u + QH_TILE + ((uint32_t)s << 4) + qm_in + row0 * 64;
                 // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early).
                 // All rows of the box are fetched into registers first so that the shared-memory latency is
                 // paid once per box, not once per row (the stores below order memory operations).
@@ -304,52 +390,67 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
                     for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(raw[r][0]), "r"(raw[r][1]), "r"(raw[r][2]));
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(in_empty(stg));
+                    if (lane == 0 && !KO(128)) mbar_arrive(in_empty(stg));
                     TRACE(3);
                 }
-                auto unpack = [&](const uint32_t (&e)[3], float (&x)[2][3]) {
+                if (hb == 0 && k >= 2) {
+                    // slot reuse (the loads above are in flight meanwhile): the MMAs that read chunk k-2 and the epilogue
+                    // that read its k*v rows and q tile are done
+                    slot_ok = WARP_WAIT(slot_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2);
+                    TRACE(1);
+                    if (!slot_ok) break;
+                }
+                // x[0..2] = q | k | v samples of the lane's channel pair (packed positions before any q/k swap)
+                auto unpack = [&](const uint32_t (&e)[3], f32x2 (&x)[3]) {
                     if (INTERLEAVED) {
-                        x[0][0] = bf_lo(e[0]); x[0][1] = bf_hi(e[0]); x[0][2] = bf_lo(e[1]);
-                        x[1][0] = bf_hi(e[1]); x[1][1] = bf_lo(e[2]); x[1][2] = bf_hi(e[2]);
+                        x[0] = pk2(bf_lo(e[0]), bf_hi(e[1]));
+                        x[1] = pk2(bf_hi(e[0]), bf_lo(e[2]));
+                        x[2] = pk2(bf_lo(e[1]), bf_hi(e[2]));
                     } else {
 #pragma unroll
-                        for (int pl = 0; pl < 3; ++pl) { x[0][pl] = bf_lo(e[pl]); x[1][pl] = bf_hi(e[pl]); }
+                        for (int pl = 0; pl < 3; ++pl) x[pl] = pk2(bf_lo(e[pl]), bf_hi(e[pl]));
                     }
                 };
-                float x1[2][3], x2[2][3];
+                f32x2 x1[3], x2[3];
                 unpack(raw[0], x2);
                 unpack(raw[1], x1);
 #pragma unroll
                 for (int i = 0; i < RB; ++i) {
                     if (KO(16)) {
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot_u + (row0 + i) * 128 + kv_in), "r"(raw[i + 2][0]));
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(kv_a0 + i * 128), "r"(raw[i + 2][0]));
                         continue;
                     }
-                    float x0[2][3];
+                    f32x2 x0[3], z[3];
                     unpack(raw[i + 2], x0);
-                    float z[2][3];
 #pragma unroll
-                    for (int c = 0; c < 2; ++c)
-#pragma unroll
-                        for (int x = 0; x < 3; ++x) {
-                            z[c][x] = fmaf(w3[c][x][0], x2[c][x], fmaf(w3[c][x][1], x1[c][x], w3[c][x][2] * x0[c][x]));
-                            x2[c][x] = x1[c][x];
-                            x1[c][x] = x0[c][x];
-                        }
-                    const float q0 = swap_qk ? z[0][1] : z[0][0], k0 = swap_qk ? z[0][0] : z[0][1];
-                    const float q1 = swap_qk ? z[1][1] : z[1][0], k1 = swap_qk ? z[1][0] : z[1][1];
-                    const float kv0 = k0 * z[0][2], kv1 = k1 * z[1][2];   // rows before the sequence start are zeros
+                    for (int x = 0; x < 3; ++x) {
+                        z[x] = fma2(w3[x][0], x2[x], fma2(w3[x][1], x1[x], mul2(w3[x][2], x0[x])));
+                        x2[x] = x1[x];
+                        x1[x] = x0[x];
+                    }
+                    const f32x2 q = SWAP ? z[1] : z[0];
+                    const f32x2 kv = mul2(SWAP ? z[0] : z[1], z[2]);          // rows before the sequence start are zeros
+                    float kv0, kv1;
+                    up2(kv, kv0, kv1);
                     const uint32_t hi = pack_bf16(kv0, kv1);
-                    const uint32_t lo = pack_bf16(kv0 - bf_lo(hi), kv1 - bf_hi(hi));
+                    float r0, r1;
+                    up2(sub2(kv, pk2(bf_lo(hi), bf_hi(hi))), r0, r1);
+                    const uint32_t lo = pack_bf16(r0, r1);
                     // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
-                    const uint32_t kaddr = slot_u + (row0 + i) * 128 + ((kv_chunk ^ (uint32_t)(i & 7)) << 4) + kv_in;
+                    const uint32_t kaddr = kv_a0 ^ (uint32_t)((i & 7) << 4);
                     if (KO(1) && hi != 0x12345678u) continue;
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + HI_OFF), "r"(hi));
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + LO_OFF), "r"(lo));
-                    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(slot_u + (row0 + i) * 16 + qplane_off + Q_OFF), "f"(q0), "f"(q1));
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (HI_OFF + i * 128)), "r"(hi));
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (LO_OFF + i * 128)), "r"(lo));
+                    float q0, q1;
+                    up2(q, q0, q1);
+                    const uint32_t qh = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x7632);   // upper halves
+                    const uint32_t qm = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5151);   // third bytes
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"((qh_a0 ^ (uint32_t)((i & 7) << 4)) + i * 128), "r"(qh));
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)(((i >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
                 }
                 asm volatile("" ::: "memory");
             }
+            if (!slot_ok) break;
             TRACE(4);
             fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
@@ -377,78 +478,88 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             has_skip = has_skip || d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f;
         }
         const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
+        if (lane == 0) mbar_arrive(slot_free(0));      // chunk 0 (the halo chunk) has no epilogue
         for (int k = 1; k < nchunk; ++k) {
             const int slot = k % 2;
             TRACE(10);
-            if (!MBAR_WAIT(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
+            if (!WARP_WAIT(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
             TRACE(11);
             tc_fence_after();
             __syncwarp();
             const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 128;
-            float y[NS][16];
-#pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                uint32_t ah[16], al[16];
-                tmem_ld16(taddr + s * 16, ah);
-                tmem_ld16(taddr + 64 + s * 16, al);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 16; ++i) y[s][i] = __uint_as_float(ah[i]) + __uint_as_float(al[i]);
-            }
-            // The accumulator now lives in registers: give the TMEM buffer back before anything else, and the
-            // q tile as soon as it has been read, so that neither the next MMAs nor the front end two chunks
-            // ahead wait for this warp's arithmetic and global stores.
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(d_empty(slot));
-            TRACE(12);
             const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
-            uint32_t o[NS][8];
+            const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
+            const uint8_t* qm_p = qh_p + QH_TILE - r * 64;
+            const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
+            // One stream at a time (16 channels: head and remainder accumulators -> gate -> 32 bytes of output), with the
+            // accumulators of the next stream already on their way from TMEM: at most two streams' values are live, so
+            // nothing spills (a spilled value is reloaded from L2 here: L1 is almost entirely carved out as shared memory).
+            uint32_t acc[2][2][16];
+            tmem_ld16(taddr, acc[0][0]);
+            tmem_ld16(taddr + 64, acc[0][1]);
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
-                if (has_skip) {
-                    // skip term D[c] * kv[t, c] from this row of the k*v tile (head + remainder); the tile is still
-                    // resident because the front end reuses the slot only after q_free below
+                uint32_t (&ah)[16] = acc[s & 1][0];
+                uint32_t (&al)[16] = acc[s & 1][1];
+                tmem_ld_wait(ah, al);
+                if (s + 1 < NS) {
+                    tmem_ld16(taddr + (s + 1) * 16, acc[(s + 1) & 1][0]);
+                    tmem_ld16(taddr + 64 + (s + 1) * 16, acc[(s + 1) & 1][1]);
+                } else {
+                    // every accumulator of this chunk has left TMEM: hand the buffer back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(d_empty(slot));
+                    TRACE(12);
+                }
+                f32x2 y[8];
 #pragma unroll
-                    for (int hc = 0; hc < 2; ++hc) {
-                        const int c = 2 * s + hc;
-                        const uint32_t off = (uint32_t)(r * 128) + (uint32_t)((c ^ (r & 7)) << 4);
+                for (int i = 0; i < 8; ++i)
+                    y[i] = add2(pk2(__uint_as_float(ah[2 * i]), __uint_as_float(ah[2 * i + 1])),
+                                pk2(__uint_as_float(al[2 * i]), __uint_as_float(al[2 * i + 1])));
+                if (has_skip) {
+                    // skip term D[c] * kv[t, c] from this row of the k*v tile (head + remainder)
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const uint32_t off = (uint32_t)(r * 128) + (uint32_t)(((2 * s + hf) ^ (r & 7)) << 4);
                         const uint4 h4 = *reinterpret_cast<const uint4*>(slot_p + HI_OFF + off);
                         const uint4 l4 = *reinterpret_cast<const uint4*>(slot_p + LO_OFF + off);
-                        const float4 d0 = dsk[2 * hc], d1 = dsk[2 * hc + 1];
-                        float* yy = &y[s][8 * hc];
-                        yy[0] = fmaf(d0.x, bf_lo(h4.x) + bf_lo(l4.x), yy[0]);
-                        yy[1] = fmaf(d0.y, bf_hi(h4.x) + bf_hi(l4.x), yy[1]);
-                        yy[2] = fmaf(d0.z, bf_lo(h4.y) + bf_lo(l4.y), yy[2]);
-                        yy[3] = fmaf(d0.w, bf_hi(h4.y) + bf_hi(l4.y), yy[3]);
-                        yy[4] = fmaf(d1.x, bf_lo(h4.z) + bf_lo(l4.z), yy[4]);
-                        yy[5] = fmaf(d1.y, bf_hi(h4.z) + bf_hi(l4.z), yy[5]);
-                        yy[6] = fmaf(d1.z, bf_lo(h4.w) + bf_lo(l4.w), yy[6]);
-                        yy[7] = fmaf(d1.w, bf_hi(h4.w) + bf_hi(l4.w), yy[7]);
+                        const float4 d0 = dsk[2 * hf], d1 = dsk[2 * hf + 1];
+                        f32x2* yy = &y[4 * hf];
+                        yy[0] = fma2(pk2(d0.x, d0.y), add2(pk2(bf_lo(h4.x), bf_hi(h4.x)), pk2(bf_lo(l4.x), bf_hi(l4.x))), yy[0]);
+                        yy[1] = fma2(pk2(d0.z, d0.w), add2(pk2(bf_lo(h4.y), bf_hi(h4.y)), pk2(bf_lo(l4.y), bf_hi(l4.y))), yy[1]);
+                        yy[2] = fma2(pk2(d1.x, d1.y), add2(pk2(bf_lo(h4.z), bf_hi(h4.z)), pk2(bf_lo(l4.z), bf_hi(l4.z))), yy[2]);
+                        yy[3] = fma2(pk2(d1.z, d1.w), add2(pk2(bf_lo(h4.w), bf_hi(h4.w)), pk2(bf_lo(l4.w), bf_hi(l4.w))), yy[3]);
                     }
                 }
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    const float4 q = KO(32) ? make_float4(1.f, 1.f, 1.f, 1.f)
-                                            : *reinterpret_cast<const float4*>(slot_p + Q_OFF + r * 16 + (s * 4 + c4) * PLS);
-                    o[s][2 * c4] = pack_bf16(y[s][4 * c4] * q.x, y[s][4 * c4 + 1] * q.y);
-                    o[s][2 * c4 + 1] = pack_bf16(y[s][4 * c4 + 2] * q.z, y[s][4 * c4 + 3] * q.w);
-                }
-            }
-#pragma unroll
-            for (int s = 0; s < NS; ++s) asm volatile("" ::"r"(o[s][0]), "r"(o[s][3]), "r"(o[s][5]), "r"(o[s][7]));
-            __syncwarp();
-            if (lane == 0) mbar_arrive(q_free(slot));
-            TRACE(13);
-            const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
-#pragma unroll
-            for (int s = 0; s < NS; ++s) {
                 if (KO(32)) continue;
-                if ((k - 1) * CHUNK < nleft[s] && !(KO(4) && o[s][0] != 0x12345678u))
-                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[s][0]),
-                                 "r"(o[s][1]), "r"(o[s][2]), "r"(o[s][3]), "r"(o[s][4]), "r"(o[s][5]), "r"(o[s][6]), "r"(o[s][7])
-                                 : "memory");
+                uint32_t o[8];
+                const uint4 qm4 = *reinterpret_cast<const uint4*>(qm_p + ((s ^ ((r >> 1) & 3)) << 4));
+                const uint32_t qm[4] = {qm4.x, qm4.y, qm4.z, qm4.w};
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const uint4 qh4 = *reinterpret_cast<const uint4*>(qh_p + (((2 * s + hf) ^ (r & 7)) << 4));
+                    const uint32_t qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {          // channels 8 hf + 2 j, + 1: third bytes 2 (j % 2), + 1 of word 2 hf + j / 2
+                        const uint32_t mw = qm[2 * hf + j / 2];
+                        const uint32_t qa = __byte_perm(qh[j], mw, (j % 2) ? 0x1066 : 0x1044);
+                        const uint32_t qb = __byte_perm(qh[j], mw, (j % 2) ? 0x3277 : 0x3255);
+                        float o0, o1;
+                        up2(mul2(y[4 * hf + j], pk2(__uint_as_float(qa), __uint_as_float(qb))), o0, o1);
+                        o[4 * hf + j] = pack_bf16(o0, o1);
+                    }
+                }
+                // (no "memory" clobber: nothing in this kernel reads y, and the shared-memory reads of the next stream
+                // may then be scheduled above this store)
+                if ((k - 1) * CHUNK < nleft[s] && !(KO(4) && o[0] != 0x12345678u))
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[0]),
+                                 "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
             }
+            // every shared-memory read of this chunk is done: its k*v slot and q tile may be rewritten
+            __syncwarp();
+            if (lane == 0) mbar_arrive(slot_free(slot));
+            TRACE(13);
         }
     } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
@@ -456,7 +567,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             const uint32_t idesc = instr_desc(128, 2 * NS * CH, 1);
             // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
             // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
-            // is released (kv_free) one whole chunk before the front end needs its slot again.
+            // is released (slot_free) one whole chunk before the front end needs its slot again.
             // Descriptors are built once; a K step of 16 rows moves the start-address field by 2048 B (128 units).
             // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
             // B operand of one K step: 16 rows x [head tile | remainder tile] = N-major, two 64-channel atoms
@@ -481,7 +592,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             if (ok && nchunk > 1) {
                 tc_fence_after();
                 issue_half(1, false);
-                mma_commit(kv_free(0));
+                mma_commit(slot_free(0));
             }
             for (int k = 1; k < nchunk && ok; ++k) {
                 TRACE(20);
@@ -498,7 +609,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     tc_fence_after();
                     issue_half(k + 1, false);
                 }
-                mma_commit(kv_free(k % 2));
+                mma_commit(slot_free(k % 2));
                 TRACE(24);
             }
         }
@@ -520,17 +631,20 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             }
             if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
         }
+        const int tw = warp - W_TMA;                 // this warp issues the boxes of streams tw, tw + NTMA, ...
         if (lane == 0) {
             // ======== TMA issue ======================================================================
             tma_prefetch_desc(&tmap);
             for (int nh = 0; nh < 2 * nchunk; ++nh) {
+                if (KO(128)) break;
                 const int stg = nh % IN_STAGES, k = nh / 2, h = nh % 2;
                 if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), (uint32_t)(((nh - IN_STAGES) / IN_STAGES) & 1), 9)) break;
                 TRACE(30);
                 const uint32_t bar = in_full(stg);
-                mbar_expect_tx(bar, NS * BOX_BYTES);
+                mbar_expect_tx(bar, NS / NTMA * BOX_BYTES);
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
+                    if (s % NTMA != tw) continue;
                     const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
                     const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK + h * HROWS - 2 - s);
                     if (INTERLEAVED) {
@@ -589,6 +703,9 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     while (p->G * ceil_div<int64_t>(p->B * nseg, NS) < (int64_t)kNumSMs * 6 && nseg * 2 <= nchunks_total &&
            ceil_div<int64_t>(nchunks_total, nseg * 2) >= 8)
         nseg *= 2;
+#ifdef VTX_MR_KNOCKOUT
+    if (getenv("VTX_MR_NSEG")) nseg = atoi(getenv("VTX_MR_NSEG"));
+#endif
     a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
     a.nseg = ceil_div<int64_t>(p->L, a.seg_len);
     a.nstream = p->B * a.nseg;
@@ -600,12 +717,16 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     if (int rc = make_tmap_3d(&tmap, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
                               inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_fir(mr)"))
         return rc;
-    auto kern = inter ? fused_mr_kernel<true> : fused_mr_kernel<false>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[inter]) {
+    const int variant = !inter ? 0 : (a.flip ? 2 : 1);
+    auto kern = variant == 0 ? fused_mr_kernel<false, false> : variant == 1 ? fused_mr_kernel<true, false> : fused_mr_kernel<true, true>;
+    // the opt-in is a per-device property of the function: remember it per device
+    static bool attr_set[64][3] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev][variant]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
-        attr_set[inter] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev][variant] = true;
     }
     kern<<<(unsigned)(p->G * nquad), THREADS, SMEM_BYTES, stream>>>(tmap, a);
     if (int rc = check_launch("fused_fir(mr)")) return rc;
