@@ -66,7 +66,7 @@ constexpr int KV_TILE = CHUNK * 128;       // 16384
 // chunk c ^ ((r >> 1) & 3) (conflict-free for the row-per-lane 16-byte reads of the epilogue).
 constexpr int QH_TILE = KV_TILE, QM_TILE = CHUNK * 64;
 constexpr int Q_BYTES = QH_TILE + QM_TILE;     // 24576
-constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE, QM_OFF = 2 * KV_TILE + QH_TILE;
+constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE;   // (third bytes of q follow at QH_OFF + QH_TILE)
 constexpr int SLOT_BYTES = 2 * KV_TILE + Q_BYTES;      // one chunk: k*v head, k*v remainder, q upper halves, q third bytes
 constexpr int DIAG_BYTES = 128;            // skip parameters D[16] of the group, fp32
 constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
@@ -86,7 +86,8 @@ constexpr int TMEM_COLS = 512;             // A: [0,128); accumulator buffer b a
 #endif
 constexpr int NTMA = VTX_MR_NTMA;          // TMA issue warps: one thread issues a box of 96-byte rows every ~300 cycles only
 constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA warp, first TMA warp
-constexpr int THREADS = 32 * (NFE + 5 + NTMA);
+constexpr int NWARPS = (NFE + 5 + NTMA + 3) / 4 * 4;    // whole warpgroups (register reallocation is per warpgroup)
+constexpr int THREADS = 32 * NWARPS;
 static_assert(NS % NTMA == 0 && THREADS <= 1024 && NFE % 8 == 0 && (CHUNK / NFE) % RB == 0, "warp roles");
 
 // L2 prefetch of rows that will be staged later: keeps HBM requests in flight without shared memory
@@ -341,116 +342,117 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         }
         const uint32_t kv_chunk = (uint32_t)(s * 2 + p / 4), kv_in = (uint32_t)((p % 4) * 4);   // 16-byte chunk and offset of this lane's bf16 pair in a k*v row
         const uint32_t qm_in = (uint32_t)(2 * p);                                          // this lane's two third-bytes in the 16-byte chunk s of a q row
-#ifdef VTX_MR_STAGGER_NS
-        // The two front-end warps of a scheduler (w and w + 4) alternate between a phase that waits and fetches and a
-        // phase that is bound by the arithmetic pipes; started half a period apart they keep each other's pipes busy.
-        if (w >= NFE / 2) __nanosleep(VTX_MR_STAGGER_NS);
-#endif
-        for (int k = 0; k < nchunk; ++k) {
+        static_assert(WROWS == 2 * RB, "the front end walks a chunk as two register batches");
+        constexpr int ROWB = INTERLEAVED ? 96 : 32;             // bytes per staged row (per plane in the planar layouts)
+        // shared-memory address of this lane's first word of batch hb of chunk k (the box row of the batch's first
+        // sample minus the two featurizer history rows; stream s was staged s rows early)
+        auto box_addr = [&](int k, int hb) {
+            const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
+            return sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB + s) * ROWB +
+                                     (INTERLEAVED ? 12 : 4) * p);
+        };
+        // Volatile loads: they are issued where they stand, one batch ahead of the arithmetic that consumes them, so
+        // that their latency (and the wait for the stage before them) overlaps the previous batch's arithmetic.
+        auto fetch = [&](uint32_t addr, uint32_t (&raw)[RB + 2][3]) {
+#pragma unroll
+            for (int r = 0; r < RB + 2; ++r) {
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    if (KO(2))
+                        raw[r][j] = 0x3f803f80u + r + lane;
+                    else
+                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw[r][j]) : "r"(addr + (uint32_t)(r * ROWB + (INTERLEAVED ? 4 * j : j * IN_PLANE))));
+                }
+            }
+        };
+        // x[0..2] = q | k | v samples of the lane's channel pair (packed positions before any q/k swap)
+        auto unpack = [&](const uint32_t (&e)[3], f32x2 (&x)[3]) {
+            if (INTERLEAVED) {
+                x[0] = pk2(bf_lo(e[0]), bf_hi(e[1]));
+                x[1] = pk2(bf_hi(e[0]), bf_lo(e[2]));
+                x[2] = pk2(bf_lo(e[1]), bf_hi(e[2]));
+            } else {
+#pragma unroll
+                for (int pl = 0; pl < 3; ++pl) x[pl] = pk2(bf_lo(e[pl]), bf_hi(e[pl]));
+            }
+        };
+        // featurizer -> k*v head/remainder and q of RB rows, written into the chunk's slot
+        auto compute = [&](int slot, int hb, const uint32_t (&raw)[RB + 2][3]) {
+            const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
+            const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
+            // Tiles are 1024-byte aligned, so the swizzle (16-byte chunk index XOR row phase) is one XOR on the address
+            // of the lane's element in row 0; row offsets are compile-time immediates of the stores.
+            const uint32_t kv_a0 = slot_u + (kv_chunk << 4) + kv_in + row0 * 128;
+            const uint32_t qh_a0 = kv_a0 + QH_OFF;
+            const uint32_t qm_a0 = slot_u + QH_OFF + QH_TILE + ((uint32_t)s << 4) + qm_in + row0 * 64;
+            f32x2 x1[3], x2[3];
+            unpack(raw[0], x2);
+            unpack(raw[1], x1);
+#pragma unroll
+            for (int i = 0; i < RB; ++i) {
+                if (KO(16)) {
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kv_a0 + i * 128), "r"(raw[i + 2][0]));
+                    continue;
+                }
+                f32x2 x0[3], z[3];
+                unpack(raw[i + 2], x0);
+#pragma unroll
+                for (int x = 0; x < 3; ++x) {
+                    z[x] = fma2(w3[x][0], x2[x], fma2(w3[x][1], x1[x], mul2(w3[x][2], x0[x])));
+                    x2[x] = x1[x];
+                    x1[x] = x0[x];
+                }
+                const f32x2 q = SWAP ? z[1] : z[0];
+                const f32x2 kv = mul2(SWAP ? z[0] : z[1], z[2]);          // rows before the sequence start are zeros
+                float kv0, kv1;
+                up2(kv, kv0, kv1);
+                const uint32_t hi = pack_bf16(kv0, kv1);
+                float r0, r1;
+                up2(sub2(kv, pk2(bf_lo(hi), bf_hi(hi))), r0, r1);
+                const uint32_t lo = pack_bf16(r0, r1);
+                // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
+                const uint32_t kaddr = kv_a0 ^ (uint32_t)((i & 7) << 4);
+                if (KO(1) && hi != 0x12345678u) continue;
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (HI_OFF + i * 128)), "r"(hi));
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (LO_OFF + i * 128)), "r"(lo));
+                float q0, q1;
+                up2(q, q0, q1);
+                const uint32_t qh = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x7632);   // upper halves
+                const uint32_t qm = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5151);   // third bytes
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"((qh_a0 ^ (uint32_t)((i & 7) << 4)) + i * 128), "r"(qh));
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)(((i >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
+            }
+        };
+        auto stage_of = [&](int k) { return (2 * k + w / (NFE / 2)) % IN_STAGES; };
+        auto stage_parity = [&](int k) { return (uint32_t)(((2 * k + w / (NFE / 2)) / IN_STAGES) & 1); };
+
+        // Software pipeline over register batches A (rows 0..RB-1 of the warp's rows) and B (the rest):
+        //   fetch B(k) | wait slot | compute A(k) | release stage | wait stage(k+1), fetch A(k+1) | compute B(k) | publish
+        uint32_t rawA[RB + 2][3], rawB[RB + 2][3];
+        bool ok = KO(128) || WARP_WAIT(in_full(stage_of(0)), stage_parity(0), 4);
+        if (ok) fetch(box_addr(0, 0), rawA);
+        for (int k = 0; k < nchunk && ok; ++k) {
             const int slot = k % 2;
             TRACE(0);
-            // half chunk n = 2k + (upper half ? 1 : 0) sits in stage n % IN_STAGES; this warp owns WROWS of its 64 rows
-            const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
-            if (!KO(128) && !WARP_WAIT(in_full(stg), (uint32_t)((nh / IN_STAGES) & 1), 4)) break;
-            TRACE(2);
-            bool slot_ok = true;
-#pragma unroll 1
-            for (int hb = 0; hb < WROWS / RB; ++hb) {
-                const uint8_t* box = sm + stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB) * (INTERLEAVED ? 96 : 32);
-                const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
-                const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
-                const uint32_t q_u = slot_u + QH_OFF;
-                // Tiles are 1024-byte aligned, so the swizzle (16-byte chunk index XOR row phase) is one XOR on the address
-                // of the lane's element in row 0; row offsets are compile-time immediates of the stores.
-                const uint32_t kv_a0 = slot_u + (kv_chunk << 4) + kv_in + row0 * 128;
-                const uint32_t qh_a0 = q_u + (kv_chunk << 4) + kv_in + row0 * 128;
-                const uint32_t qm_a0 = q_u + QH_TILE + ((uint32_t)s << 4) + qm_in + row0 * 64;
-                // local row of the box's i-th sample is i + 2 + s (stream s was staged s rows early).
-                // All rows of the box are fetched into registers first so that the shared-memory latency is
-                // paid once per box, not once per row (the stores below order memory operations).
-                uint32_t raw[RB + 2][3];
+            fetch(box_addr(k, 1), rawB);
+            // slot reuse: the MMAs that read chunk k-2 and the epilogue that read its k*v rows and q tile are done
+            if (k >= 2 && !WARP_WAIT(slot_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
+            TRACE(1);
+            compute(slot, 0, rawA);
+            // Every row this warp needs from the stage now sits in registers: hand the stage back to the TMA warp (HBM
+            // latency under load is ~2 us, so as much of the ring as possible should be in flight).  The empty asm
+            // makes the loaded values a dependency of the arrive.
 #pragma unroll
-                for (int r = 0; r < RB + 2; ++r) {
-                    if (KO(2)) {
-                        raw[r][0] = raw[r][1] = raw[r][2] = 0x3f803f80u + r + lane;
-                    } else if (INTERLEAVED) {
-                        const uint32_t* rp = reinterpret_cast<const uint32_t*>(box + (r + s) * 96) + 3 * p;
-                        raw[r][0] = rp[0]; raw[r][1] = rp[1]; raw[r][2] = rp[2];
-                    } else {
-#pragma unroll
-                        for (int pl = 0; pl < 3; ++pl)
-                            raw[r][pl] = reinterpret_cast<const uint32_t*>(box + pl * IN_PLANE + (r + s) * 32)[p];
-                    }
-                }
-                if (hb == WROWS / RB - 1) {
-                    // Every row this warp needs from the stage now sits in registers: hand the stage back to the
-                    // TMA warp before the arithmetic starts, so that nearly the whole ring can be in flight (HBM
-                    // latency under load is ~2 us; a stage that stayed busy during the arithmetic would leave a
-                    // single stage in flight).  The empty asm makes the loaded values a dependency of the arrive.
-#pragma unroll
-                    for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(raw[r][0]), "r"(raw[r][1]), "r"(raw[r][2]));
-                    __syncwarp();
-                    if (lane == 0 && !KO(128)) mbar_arrive(in_empty(stg));
-                    TRACE(3);
-                }
-                if (hb == 0 && k >= 2) {
-                    // slot reuse (the loads above are in flight meanwhile): the MMAs that read chunk k-2 and the epilogue
-                    // that read its k*v rows and q tile are done
-                    slot_ok = WARP_WAIT(slot_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2);
-                    TRACE(1);
-                    if (!slot_ok) break;
-                }
-                // x[0..2] = q | k | v samples of the lane's channel pair (packed positions before any q/k swap)
-                auto unpack = [&](const uint32_t (&e)[3], f32x2 (&x)[3]) {
-                    if (INTERLEAVED) {
-                        x[0] = pk2(bf_lo(e[0]), bf_hi(e[1]));
-                        x[1] = pk2(bf_hi(e[0]), bf_lo(e[2]));
-                        x[2] = pk2(bf_lo(e[1]), bf_hi(e[2]));
-                    } else {
-#pragma unroll
-                        for (int pl = 0; pl < 3; ++pl) x[pl] = pk2(bf_lo(e[pl]), bf_hi(e[pl]));
-                    }
-                };
-                f32x2 x1[3], x2[3];
-                unpack(raw[0], x2);
-                unpack(raw[1], x1);
-#pragma unroll
-                for (int i = 0; i < RB; ++i) {
-                    if (KO(16)) {
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(kv_a0 + i * 128), "r"(raw[i + 2][0]));
-                        continue;
-                    }
-                    f32x2 x0[3], z[3];
-                    unpack(raw[i + 2], x0);
-#pragma unroll
-                    for (int x = 0; x < 3; ++x) {
-                        z[x] = fma2(w3[x][0], x2[x], fma2(w3[x][1], x1[x], mul2(w3[x][2], x0[x])));
-                        x2[x] = x1[x];
-                        x1[x] = x0[x];
-                    }
-                    const f32x2 q = SWAP ? z[1] : z[0];
-                    const f32x2 kv = mul2(SWAP ? z[0] : z[1], z[2]);          // rows before the sequence start are zeros
-                    float kv0, kv1;
-                    up2(kv, kv0, kv1);
-                    const uint32_t hi = pack_bf16(kv0, kv1);
-                    float r0, r1;
-                    up2(sub2(kv, pk2(bf_lo(hi), bf_hi(hi))), r0, r1);
-                    const uint32_t lo = pack_bf16(r0, r1);
-                    // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
-                    const uint32_t kaddr = kv_a0 ^ (uint32_t)((i & 7) << 4);
-                    if (KO(1) && hi != 0x12345678u) continue;
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (HI_OFF + i * 128)), "r"(hi));
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (LO_OFF + i * 128)), "r"(lo));
-                    float q0, q1;
-                    up2(q, q0, q1);
-                    const uint32_t qh = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x7632);   // upper halves
-                    const uint32_t qm = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5151);   // third bytes
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"((qh_a0 ^ (uint32_t)((i & 7) << 4)) + i * 128), "r"(qh));
-                    asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)(((i >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
-                }
-                asm volatile("" ::: "memory");
+            for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(rawB[r][0]), "r"(rawB[r][1]), "r"(rawB[r][2]));
+            __syncwarp();
+            if (lane == 0 && !KO(128)) mbar_arrive(in_empty(stage_of(k)));
+            TRACE(3);
+            if (k + 1 < nchunk) {
+                if (!KO(128) && !WARP_WAIT(in_full(stage_of(k + 1)), stage_parity(k + 1), 4)) break;
+                fetch(box_addr(k + 1, 0), rawA);
             }
-            if (!slot_ok) break;
+            TRACE(2);
+            compute(slot, 1, rawB);
             TRACE(4);
             fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
@@ -613,23 +615,27 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 TRACE(24);
             }
         }
-    } else {
+    } else if (warp < W_TMA + NTMA) {
         // first packed column of this group's q | k | v data (one contiguous run when interleaved)
-        Stream sts[NS];
-        int64_t col[3] = {0, 0, 0};
+        int row_base[NS], bidx[NS];      // first staged row of chunk 0 (the halo chunk) and batch index, per stream
+        int col[3] = {0, 0, 0};
 #pragma unroll
-        for (int s = 0; s < NS; ++s) sts[s] = stream_of(a, quad, s);
+        for (int s = 0; s < NS; ++s) {
+            const Stream st = stream_of(a, quad, s);
+            row_base[s] = (int)st.ts - CHUNK - 2 - s;
+            bidx[s] = (int)st.b;
+        }
         if (INTERLEAVED) {
-            col[0] = 3 * g * CH;
+            col[0] = (int)(3 * g * CH);
         } else {
             const int64_t d0 = g * CH;
             if (a.layout == VTX_QKV_COLUMN_SPLIT) {
                 int64_t n = d0 / a.hd, j = d0 - n * a.hd;
-                col[0] = n * 3 * a.hd + j; col[1] = col[0] + a.hd; col[2] = col[0] + 2 * a.hd;
+                col[0] = (int)(n * 3 * a.hd + j); col[1] = col[0] + (int)a.hd; col[2] = col[0] + 2 * (int)a.hd;
             } else {
-                col[0] = d0; col[1] = a.D + d0; col[2] = 2 * a.D + d0;
+                col[0] = (int)d0; col[1] = (int)(a.D + d0); col[2] = (int)(2 * a.D + d0);
             }
-            if (a.flip) { int64_t t = col[0]; col[0] = col[1]; col[1] = t; }
+            if (a.flip) { int t = col[0]; col[0] = col[1]; col[1] = t; }
         }
         const int tw = warp - W_TMA;                 // this warp issues the boxes of streams tw, tw + NTMA, ...
         if (lane == 0) {
@@ -646,13 +652,13 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 for (int s = 0; s < NS; ++s) {
                     if (s % NTMA != tw) continue;
                     const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
-                    const int row = (int)(sts[s].ts + (int64_t)(k - 1) * CHUNK + h * HROWS - 2 - s);
+                    const int row = row_base[s] + k * CHUNK + h * HROWS;
                     if (INTERLEAVED) {
-                        tma_load_3d(dst, &tmap, bar, (int)col[0], row, (int)sts[s].b);
+                        tma_load_3d(dst, &tmap, bar, col[0], row, bidx[s]);
                     } else {
 #pragma unroll
                         for (int pl = 0; pl < 3; ++pl)
-                            tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, (int)col[pl], row, (int)sts[s].b);
+                            tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, col[pl], row, bidx[s]);
                     }
                 }
             }
