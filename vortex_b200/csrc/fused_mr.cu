@@ -76,7 +76,7 @@ constexpr int OFF_SLOTS = SMEM_IN;
 constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
 constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
 constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
-constexpr int NBARS = IN_STAGES * 2 + 2 * 4;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty x2
+constexpr int NBARS = IN_STAGES * 2 + 2 * 4 + 1;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty x2; a_ready
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0, "k*v tiles must be 1024-byte aligned");
@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     auto slot_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
     auto d_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };
     auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };
+    const uint32_t a_ready = smem_u32(&bars[BB + 8]);       // the Toeplitz operand is in TMEM (one arrival per expanding warp)
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     int trace_n = 0;
@@ -281,6 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         for (int sl = 0; sl < 2; ++sl) {
             mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 5); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
         }
+        mbar_init(a_ready, NFE + 4);
         fence_mbar_init();
     }
     if (warp == W_MMA) {
@@ -304,10 +306,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp >= W_EP && warp < W_EP + 4) {   // expand the Toeplitz matrix into TMEM: lane i holds row i
-        const int i = (warp - W_EP) * 32 + lane;
+    if (warp < NFE + 4) {
+        // Expand the Toeplitz matrix into TMEM: lane i holds row i.  A warp reaches the TMEM lanes of its quarter
+        // (warp % 4); the front-end and epilogue warps of a quarter share its 8 column blocks.  Only the MMA warp
+        // waits for the result (a_ready): the TMA warps start fetching at once and the other roles follow as soon as
+        // their share is written.
+        const int i = (warp % 4) * 32 + lane, part = warp / 4, nparts = (NFE + 4) / 4;
         const uint16_t* tp = reinterpret_cast<const uint16_t*>(sm + OFF_TAPS);
-        for (int c0 = 0; c0 < 128; c0 += 16) {
+        for (int c0 = 16 * part; c0 < 128; c0 += 16 * nparts) {
             uint32_t v[16];
 #pragma unroll
             for (int m = 0; m < 16; ++m) {
@@ -315,13 +321,13 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 uint32_t e0 = tp[128 + 128 + i - j], e1 = tp[128 + 127 + i - j];
                 v[m] = e1 << 16 | e0;
             }
-            tmem_st16(tmem + ((uint32_t)((warp - W_EP) * 32) << 16) + c0, v);
+            tmem_st16(tmem + ((uint32_t)((warp % 4) * 32) << 16) + c0, v);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
     }
-    __syncthreads();
-    tc_fence_after();
 
     // ---------------- roles ---------------------------------------------------------------------
     if (warp < NFE) {
@@ -590,7 +596,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     mma_ts(d, a0 + 8 * jj, dk + (uint64_t)(jj * (16 * 128 / 16)), idesc, (cur || jj > 0) ? 1u : 0u);
                 }
             };
-            bool ok = MBAR_WAIT(kv_full(0), 0, 7);          // the halo chunk
+            bool ok = MBAR_WAIT(a_ready, 0, 10) && MBAR_WAIT(kv_full(0), 0, 7);          // the Toeplitz operand; the halo chunk
             if (ok && nchunk > 1) {
                 tc_fence_after();
                 issue_half(1, false);
