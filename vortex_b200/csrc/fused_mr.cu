@@ -560,6 +560,15 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 }
                 // (no "memory" clobber: nothing in this kernel reads y, and the shared-memory reads of the next stream
                 // may then be scheduled above this store)
+#ifdef VTX_MR_CHECK
+                {   // diagnostic builds: a store outside y is recorded and skipped
+                    const int64_t off = (yrow[s] + yoff) - a.y;
+                    if ((k - 1) * CHUNK < nleft[s] && (off < 0 || off + 16 > a.B * a.y_stride_b)) {
+                        atomicCAS(&g_device_status, 0, 21);
+                        continue;
+                    }
+                }
+#endif
                 if ((k - 1) * CHUNK < nleft[s] && !(KO(4) && o[0] != 0x12345678u))
                     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[0]),
                                  "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
@@ -593,6 +602,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
                     if (jj >= nj) continue;
+                    // the first MMA of a chunk (K step 0 of the previous-chunk part) overwrites the accumulator
                     mma_ts(d, a0 + 8 * jj, dk + (uint64_t)(jj * (16 * 128 / 16)), idesc, (cur || jj > 0) ? 1u : 0u);
                 }
             };
