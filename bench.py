@@ -295,7 +295,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload (no cache outputs requested)
-LAUNCHES = {"mr": 1, "se": 1, "li": 4}
+LAUNCHES = {"mr": 1, "se": 1, "li": 1}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.018e9, "se": 0.986e9, "li": None}   # small-case (B=1) captures scaled by the units of a bench launch

@@ -211,6 +211,29 @@ int vtx_iir_fwd(const vtx_iir_params* p, void* stream);
 #define VTX_IIR_STATIC_SCRATCH_BYTES (16u << 20)
 int vtx_iir_fwd_noalloc(const vtx_iir_params* p, void* stream);
 
+/* Fused Hyena-LI block on the projection output, channel-last in and out (bf16 I/O, groups of 16 channels
+ * sharing one modal system of up to 16 poles): featurizer (3 taps) -> q/k/v selection -> k*v -> modal long
+ * convolution -> (+ bias*kv) -> q gate in ONE pass over HBM, as a chunked state-space scan whose Toeplitz,
+ * state-input and state-update contractions run on tcgen05 tensor cores.  Fuses model.py:233-316
+ * (HyenaCascade.parallel_forward for a long-filter layer: featurizer parallel_fir + parallel_iir with its FFT
+ * branch, engine.py:262-353) -- the hyena_li_fwd entry point the reference imports but never defines
+ * (vortex/model/layers.py:18-21).
+ *   u [B,L,3D] -> y [B,L,D].  state must be NULL (the state after the last token comes from vtx_iir_fwd).
+ * ------------------------------------------------------------------------ */
+typedef struct vtx_fused_iir_params {
+    const void* u;       int64_t u_stride_b, u_stride_l;   /* channel stride 1 */
+    const void* w3;      int64_t w3_dtype;     /* [3D,3] featurizer taps                  */
+    const void* b3;      int64_t b3_dtype;     /* must be NULL                            */
+    vtx_modal_params modal;                     /* G * 16 == D                             */
+    const void* bias;    int64_t bias_dtype;   /* [D] skip term or NULL                   */
+    void* y;             int64_t y_stride_b, y_stride_l;   /* channel stride 1 */
+    float* state;                               /* must be NULL                            */
+    int64_t B, L, D, K3;
+    int64_t layout, num_heads, flip_x1x2;
+    int64_t io_dtype;
+} vtx_fused_iir_params;
+int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream);
+
 /* ------------------------------------------------------------------------
  * Decode (one token).
  *

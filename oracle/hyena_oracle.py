@@ -229,12 +229,13 @@ def _fft_causal_conv(x, h):
 
 
 def long_conv_gate(z_pre, h, bias, D, io="f32", layout="split", num_heads=1,
-                   flip_x1x2=False, mirror=True):
+                   flip_x1x2=False, mirror=True, round_input=True):
     """engine.parallel_iir, default FFT branch (engine.py:282-353,404).
 
     z_pre [B, 3D, L], h [D, L] per channel -> y [B, L, D] and kv [B, D, L]
-    (the pre-gated signal the state is computed from)."""
-    z = round_io(z_pre, io)
+    (the pre-gated signal the state is computed from).  round_input=False keeps
+    the featurizer output unrounded (a fused kernel never materialises it)."""
+    z = round_io(z_pre, io) if round_input else np.asarray(z_pre, dtype=np.float64)
     q, k, v = select_qkv(z, D, layout, num_heads, flip_x1x2)
     kv = _maybe(k * v, io, mirror)
     h = np.asarray(h, dtype=np.float64)

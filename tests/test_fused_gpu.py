@@ -223,3 +223,40 @@ def test_fused_li_vs_oracle():
         assert rel_l2(y, ref) <= (1e-4 if io == "f32" else 5e-3)   # two-kernel path materialises z in the I/O dtype
         assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
         assert rel_l2(st, O.modal_state(O.round_io(kv, io), to_np(p["log_poles"]))) <= (3e-5 if io == "f32" else 2e-3)
+
+
+# B, L, D, S, complex poles, layout, heads, flip
+LI_TC_CASES = [
+    (2, 900, 64, 16, False, "interleaved", 1, False),     # real poles, ragged last step
+    (1, 2500, 128, 16, True, "interleaved", 1, False),    # complex poles, several steps of 4 x 96 samples
+    (1, 384, 32, 8, True, "split", 1, False),             # exactly one step, fewer poles than the tile holds
+    (2, 200, 64, 16, True, "column_split", 2, True),
+    (3, 1, 32, 16, True, "interleaved", 1, True),         # single token
+    (1, 10000, 32, 16, True, "interleaved", 1, False),    # long walk: the state carries ~100 chunks
+]
+
+
+def _li_oracle(p, L, D, cplx, layout, heads, flip):
+    zf, _ = O.featurizer(to_np(p["u"]), to_np(p["w3"]), io="bf16", mirror=False)
+    if cplx:
+        poles = np.exp(to_np(p["log_poles"])[..., 0]) * np.exp(1j * to_np(p["theta"]))
+        h = O.modal_filter_complex(poles, to_np(p["residues"]) + 1j * to_np(p["res_im"]), L)
+    else:
+        h = O.modal_filter(to_np(p["log_poles"]), to_np(p["residues"]), L)
+    return O.long_conv_gate(zf, O.expand_groups(h, D), to_np(p["Dp"]), D, io="bf16", layout=layout, num_heads=heads,
+                            flip_x1x2=flip, mirror=False, round_input=False)[0]
+
+
+@pytest.mark.parametrize("B,L,D,S,cplx,layout,heads,flip", LI_TC_CASES)
+def test_fused_li_tensor_core_vs_oracle(B, L, D, S, cplx, layout, heads, flip):
+    """tcgen05 chunked state-space scan: bf16 I/O, fp32 states, every fp32 operand carried as bf16 head + remainder."""
+    from vortex_b200 import hyena_ops, ops
+    p = make_block(43, B, L, D, D // 16, 0, "bf16", modal=True, S=S, complex_poles=cplx)
+    pc = cuda(p)
+    y, fs, st = hyena_ops.hyena_li_fwd(pc["u"], pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"],
+                                       theta=pc.get("theta"), res_im=pc.get("res_im"), layout=layout, num_heads=heads,
+                                       flip=flip, want_state=False)
+    ops.device_status()
+    assert y.shape == (B, L, D) and y.dtype == torch.bfloat16 and fs is None and st is None
+    ref = _li_oracle(p, L, D, cplx, layout, heads, flip)
+    assert rel_l2(y, ref) <= TOL["bf16"]

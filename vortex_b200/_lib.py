@@ -46,6 +46,14 @@ FusedFirParams = _struct("FusedFirParams", """
 ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G i:S")
 
 
+class FusedIirParams(C.Structure):
+    _fields_ = [("u", _p), ("u_stride_b", _i), ("u_stride_l", _i), ("w3", _p), ("w3_dtype", _i),
+                ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
+                ("y", _p), ("y_stride_b", _i), ("y_stride_l", _i), ("state", _p),
+                ("B", _i), ("L", _i), ("D", _i), ("K3", _i), ("layout", _i), ("num_heads", _i), ("flip_x1x2", _i),
+                ("io_dtype", _i)]
+
+
 class IirParams(C.Structure):
     _fields_ = [("q", _p), ("q_stride_b", _i), ("q_stride_h", _i), ("q_stride_d", _i),
                 ("k", _p), ("k_stride_b", _i), ("k_stride_h", _i), ("k_stride_d", _i),
@@ -78,7 +86,7 @@ class DecodeLayerParams(C.Structure):
 
 
 STRUCTS = [FeaturizerParams, GcgParams, FusedFirParams, ModalParams, IirParams, StepFirParams, StepIirParams,
-           DecodeLayerParams]
+           DecodeLayerParams, FusedIirParams]
 
 # name -> (restype, argtypes); every symbol include/vortex_b200.h declares
 SYMBOLS = {
@@ -93,6 +101,7 @@ SYMBOLS = {
     "vtx_iir_scratch_bytes": (_i, [_i, _i, _i, _i, _i]),
     "vtx_iir_fwd": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_iir_fwd_noalloc": (C.c_int, [C.POINTER(IirParams), _p]),
+    "vtx_fused_iir_fwd": (C.c_int, [C.POINTER(FusedIirParams), _p]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),
     "vtx_decode_layer": (C.c_int, [C.POINTER(DecodeLayerParams), _p]),

@@ -80,10 +80,29 @@ def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues,
     """Hyena-LI block (modal long filter).  u [B, L, 3D] -> y [B, L, D], featurizer cache, modal state
     fp32 [B, D, S] (complex poles: [B, D, S, 2])."""
     D = u.shape[-1] // 3
+    if not want_state and _li_tensor_core_ok(u, short_filter_weight, short_filter_bias, residues, layout, num_heads):
+        y = ops.fused_iir_fwd(u, short_filter_weight, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads,
+                              flip=flip, theta=theta, res_im=res_im)
+        return y, None, None
     z, fs = ops.featurizer_fwd(u, short_filter_weight, short_filter_bias, None, want_state=want_state)
     y, st = ops.iir_fwd(z, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads, flip=flip, theta=theta,
                         res_im=res_im, want_state=want_state, round_kv=True)
     return y.permute(0, 2, 1), fs, st
+
+
+def _li_tensor_core_ok(u, w3, b3, residues, layout, num_heads):
+    """Shapes the tcgen05 chunked-scan kernel takes: bf16 I/O, 3-tap featurizer without bias, one modal system of up
+    to 16 poles per group of 16 channels."""
+    D = u.shape[-1] // 3
+    if u.dtype != torch.bfloat16 or b3 is not None or w3.shape[-1] != 3:
+        return False
+    if residues.shape[0] * 16 != D or residues.shape[-1] > 16:
+        return False
+    if (u.stride(1) * 2) % 16 or u.stride(2) != 1 or u.data_ptr() % 16 or (u.stride(0) * 2) % 16:
+        return False
+    if layout == "column_split" and (D // num_heads) % 16:
+        return False
+    return True
 
 
 def gcg_fwd(x, B, C, h, bias=None, gated_bias=False):
