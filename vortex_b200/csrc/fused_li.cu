@@ -45,7 +45,7 @@ constexpr int BOX_ROWS = HROWS + 2 + (NS - 1);         // featurizer halo + stre
 constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;
 constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;
 constexpr int BOX_STRIDE = 3 * IN_PLANE;
-constexpr int IN_STAGES = 4;
+constexpr int IN_STAGES = 3;
 constexpr int STAGE_BYTES = NS * BOX_STRIDE;
 constexpr int KV_TILE = CHUNK * 128;       // [96 rows][64 channels] bf16, 128-byte swizzle
 constexpr int QH_TILE = KV_TILE, QM_TILE = CHUNK * 64;
@@ -54,13 +54,17 @@ constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE, QM_OFF = QH_OF
               SL_OFF = SH_OFF + S_TILE;
 constexpr int SLOT_BYTES = SL_OFF + S_TILE;
 constexpr int NPW = CHUNK + 4;             // pole powers p^0 .. p^96 (padded)
+constexpr int NSLOT = 3;                   // a slot lives from the front end's stores to the end of its epilogue, i.e.
+                                           // across MMA -> state recurrence -> MMA -> epilogue: two front-end periods
 constexpr int OFF_SLOTS = IN_STAGES * STAGE_BYTES;
-constexpr int OFF_PW = OFF_SLOTS + 2 * SLOT_BYTES;           // float2 [16][NPW]
+// set-up tables live in the last slot, which the front end does not touch before the operands are expanded
+constexpr int OFF_PW = OFF_SLOTS + (NSLOT - 1) * SLOT_BYTES; // float2 [16][NPW]
 constexpr int OFF_H = OFF_PW + NPOLE * NPW * 8;              // float [96]: first taps of the filter
 constexpr int OFF_RES = OFF_H + CHUNK * 4;                   // float2 [16]: residues
-constexpr int OFF_DIAG = OFF_RES + NPOLE * 8;                // float [16]: skip parameters
+static_assert(OFF_RES + NPOLE * 8 <= OFF_SLOTS + NSLOT * SLOT_BYTES, "set-up tables must fit into a slot");
+constexpr int OFF_DIAG = OFF_SLOTS + NSLOT * SLOT_BYTES;     // float [16]: skip parameters
 constexpr int OFF_BARS = OFF_DIAG + 64;
-constexpr int NBARS = IN_STAGES * 2 + 2 * 6 + 1;
+constexpr int NBARS = IN_STAGES * 2 + NSLOT * 3 + 2 * 3 + 1;
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
 static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0 && QH_OFF % 1024 == 0 && QM_OFF % 1024 == 0 &&
               SH_OFF % 1024 == 0 && SL_OFF % 1024 == 0, "tiles must be 1024-byte aligned");
@@ -68,7 +72,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 // TMEM columns: stacked [T; Bm] head and remainder (96 K elements = 48 columns each), [C; 0] head and remainder
 // (32 K elements = 16 columns each), two accumulators of 128 columns
 constexpr int A_HI = 0, A_LO = 48, C_HI = 96, C_LO = 112, D_COL = 128, TMEM_COLS = 512;
-constexpr int W_EP = NFE, W_ST = NFE + 3, W_MMA = NFE + 4, W_TMA = NFE + 5, NTMA = 2;
+constexpr int W_EP = NFE, W_ST = NFE + 3, W_MMA = NFE + 4, W_TMA = NFE + 5, NTMA = 2, W_ST2 = NFE + 7;   // state warps: warp % 4 == 3
 constexpr int THREADS = 32 * 16;
 
 struct Args {
@@ -91,13 +95,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
     auto in_full = [&](int st) { return smem_u32(&bars[st * 2]); };
     auto in_empty = [&](int st) { return smem_u32(&bars[st * 2 + 1]); };
     const int BB = IN_STAGES * 2;
-    auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };          // front end -> MMA: k*v and q tiles written
-    auto slot_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };    // 3 epilogue warps + MMA commit: slot reusable
-    auto inc_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };     // MMA commit: T/Bm part accumulated
-    auto s_full = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };       // state warp: chunk-start states in shared memory
-    auto d_full = [&](int sl) { return smem_u32(&bars[BB + 8 + sl]); };       // MMA commit: C S part accumulated too
-    auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 10 + sl]); };     // 3 epilogue warps + state warp: accumulator read
-    const uint32_t a_ready = smem_u32(&bars[BB + 12]);
+    auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };                      // front end -> MMA: k*v and q tiles written
+    auto slot_free = [&](int sl) { return smem_u32(&bars[BB + NSLOT + sl]); };            // 3 epilogue warps + MMA commit: slot reusable
+    auto s_full = [&](int sl) { return smem_u32(&bars[BB + 2 * NSLOT + sl]); };           // state warps: chunk-start states in shared memory
+    const int BD = BB + 3 * NSLOT;
+    auto inc_full = [&](int d) { return smem_u32(&bars[BD + d]); };                       // MMA commit: T/Bm part accumulated
+    auto d_full = [&](int d) { return smem_u32(&bars[BD + 2 + d]); };                     // MMA commit: C S part accumulated too
+    auto d_empty = [&](int d) { return smem_u32(&bars[BD + 4 + d]); };                    // 3 epilogue warps + 2 state warps: accumulator read
+    const uint32_t a_ready = smem_u32(&bars[BD + 6]);                                     // operands expanded, set-up tables no longer needed
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int64_t g = blockIdx.x % a.G, b = blockIdx.x / a.G;
@@ -106,11 +111,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
         for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), NTMA); mbar_init(in_empty(st), NFE / 2); }
-        for (int sl = 0; sl < 2; ++sl) {
-            mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 4); mbar_init(inc_full(sl), 1);
-            mbar_init(s_full(sl), 1); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
-        }
-        mbar_init(a_ready, NFE + 4);
+        for (int sl = 0; sl < NSLOT; ++sl) { mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 4); mbar_init(s_full(sl), 2); }
+        for (int d = 0; d < 2; ++d) { mbar_init(inc_full(d), 1); mbar_init(d_full(d), 1); mbar_init(d_empty(d), 5); }
+        mbar_init(a_ready, NFE + 5);
         fence_mbar_init();
     }
     if (warp == W_MMA) {
@@ -159,6 +162,10 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
         htab[lag] = acc;
     }
     __syncthreads();
+
+    // p^96 of this lane's pole (used by the state warps), read before the tables' slot is released through a_ready
+    const float2 Pst = pw[(lane >> 1) * NPW + CHUNK];
+    asm volatile("" ::"f"(Pst.x), "f"(Pst.y));
 
     if (warp < NFE + 4) {
         // Expand the operands into TMEM: lane i holds row i.  A warp reaches the lanes of its quarter (warp % 4); the
@@ -298,9 +305,10 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
         bool ok = mbar_wait(in_full(stage_of(0)), stage_parity(0), 4);
         if (ok) fetch(box_addr(0, 0), rawA);
         for (int k = 0; k < nsc && ok; ++k) {
-            const int slot = k % 2;
+            const int slot = k % NSLOT;
             fetch(box_addr(k, 1), rawB);
-            if (k >= 2 && !mbar_wait(slot_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
+            if (k >= NSLOT && !mbar_wait(slot_free(slot), (uint32_t)(((k - NSLOT) / NSLOT) & 1), 2)) break;
+            if (k == NSLOT - 1 && !mbar_wait(a_ready, 0, 14)) break;      // the set-up tables live in the last slot
             compute(slot, 0, rawA);
 #pragma unroll
             for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(rawB[r][0]), "r"(rawB[r][1]), "r"(rawB[r][2]));
@@ -334,11 +342,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
         }
         const int64_t step_pitch = (int64_t)SUPER * a.y_stride_l;
         for (int k = 0; k < nsc; ++k) {
-            const int slot = k % 2;
-            if (!mbar_wait(d_full(slot), (uint32_t)((k / 2) & 1), 5)) break;
+            const int slot = k % NSLOT, dbuf = k % 2;
+            if (!mbar_wait(d_full(dbuf), (uint32_t)((k / 2) & 1), 5)) break;
             tc_fence_after();
             __syncwarp();
-            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + D_COL + slot * 128;
+            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + D_COL + dbuf * 128;
             const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
             const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
             const uint8_t* qm_p = slot_p + QM_OFF + r * 64;
@@ -357,7 +365,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 } else {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(d_empty(slot));
+                    if (lane == 0) mbar_arrive(d_empty(dbuf));
                 }
                 f32x2 y[8];
 #pragma unroll
@@ -403,49 +411,51 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_free(slot));
         }
-    } else if (warp == W_ST) {
-        // ======== state recurrence: lane = row of the state tile (pole lane/2, real or imaginary part) ==========
-        const int jj = lane, sp = jj >> 1;
-        const float2 P = pw[sp * NPW + CHUNK];                 // p^96: one chunk ahead
+    } else if (warp == W_ST || warp == W_ST2) {
+        // ======== state recurrence: lane = row of the state tile (pole lane/2, real or imaginary part); each of the
+        // two warps owns eight of the sixteen channels ========================================================
+        const int jj = lane, half = warp == W_ST2;
+        const float2 P = Pst;                                  // p^96: one chunk ahead
         const float Pa = P.x, Pb = (jj & 1) ? P.y : -P.y;      // new = Pa * own + Pb * partner + increment
-        float S[CH];                                           // this component of the state at a chunk start, 16 channels
+        if (warp == W_ST2) {                                   // (the other state warp arrives with the expanding warps)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_ready);
+        }
+        float S[8];                                            // this component of the state at a chunk start
 #pragma unroll
-        for (int c = 0; c < CH; ++c) S[c] = 0.f;
+        for (int c = 0; c < 8; ++c) S[c] = 0.f;
         for (int k = 0; k < nsc; ++k) {
-            const int slot = k % 2;
-            if (!mbar_wait(inc_full(slot), (uint32_t)((k / 2) & 1), 12)) break;
+            const int slot = k % NSLOT, dbuf = k % 2;
+            if (!mbar_wait(inc_full(dbuf), (uint32_t)((k / 2) & 1), 12)) break;
             tc_fence_after();
             __syncwarp();
-            const uint32_t taddr = tmem + ((uint32_t)CHUNK << 16) + D_COL + slot * 128;
+            const uint32_t taddr = tmem + ((uint32_t)CHUNK << 16) + D_COL + dbuf * 128 + 8 * half;
             uint8_t* sh_row = sm + OFF_SLOTS + slot * SLOT_BYTES + SH_OFF + jj * 128;
-            uint32_t inc[2][2][16];
-            tmem_ld16(taddr, inc[0][0]);
-            tmem_ld16(taddr + 64, inc[0][1]);
+            uint32_t inc[2][2][8];
+            tmem_ld8(taddr, inc[0][0]);
+            tmem_ld8(taddr + 64, inc[0][1]);
 #pragma unroll
             for (int i = 0; i < NS; ++i) {
-                // state at the start of chunk i -> shared memory (head + remainder), columns 16 i .. 16 i + 15 of the tile
-                uint32_t hi[8], lo[8];
+                // state at the start of chunk i -> shared memory (head + remainder): 16-byte chunk 2 i + half of the row
+                uint32_t hi[4], lo[4];
 #pragma unroll
-                for (int m = 0; m < 8; ++m) {
+                for (int m = 0; m < 4; ++m) {
                     hi[m] = pack_bf16(S[2 * m], S[2 * m + 1]);
                     lo[m] = pack_bf16(S[2 * m] - bf_lo(hi[m]), S[2 * m + 1] - bf_hi(hi[m]));
                 }
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const uint32_t off = (uint32_t)(((2 * i + hf) ^ (jj & 7)) << 4);
-                    *reinterpret_cast<uint4*>(sh_row + off) = make_uint4(hi[4 * hf], hi[4 * hf + 1], hi[4 * hf + 2], hi[4 * hf + 3]);
-                    *reinterpret_cast<uint4*>(sh_row + S_TILE + off) = make_uint4(lo[4 * hf], lo[4 * hf + 1], lo[4 * hf + 2], lo[4 * hf + 3]);
-                }
-                uint32_t (&ia)[16] = inc[i & 1][0];
-                uint32_t (&ib)[16] = inc[i & 1][1];
-                tmem_ld_wait(ia, ib);
+                const uint32_t off = (uint32_t)(((2 * i + half) ^ (jj & 7)) << 4);
+                *reinterpret_cast<uint4*>(sh_row + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(sh_row + S_TILE + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                uint32_t (&ia)[8] = inc[i & 1][0];
+                uint32_t (&ib)[8] = inc[i & 1][1];
+                tmem_ld8_wait(ia, ib);
                 if (i + 1 < NS) {
-                    tmem_ld16(taddr + (i + 1) * 16, inc[(i + 1) & 1][0]);
-                    tmem_ld16(taddr + 64 + (i + 1) * 16, inc[(i + 1) & 1][1]);
+                    tmem_ld8(taddr + (i + 1) * 16, inc[(i + 1) & 1][0]);
+                    tmem_ld8(taddr + 64 + (i + 1) * 16, inc[(i + 1) & 1][1]);
                 }
                 // state at the start of the next chunk
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {
+                for (int c = 0; c < 8; ++c) {
                     const float partner = __shfl_xor_sync(0xffffffffu, S[c], 1);
                     const float add = __uint_as_float(ia[c]) + __uint_as_float(ib[c]);
                     S[c] = fmaf(Pa, S[c], fmaf(Pb, partner, add));
@@ -454,42 +464,39 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             tc_fence_before();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(s_full(slot)); mbar_arrive(d_empty(slot)); }
+            if (lane == 0) { mbar_arrive(s_full(slot)); mbar_arrive(d_empty(dbuf)); }
         }
     } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
         if (lane == 0) {
             const uint32_t idesc = instr_desc(128, 2 * NS * CH, 1);
-            uint64_t kv_desc[2], s_desc[2];
-#pragma unroll
-            for (int sl = 0; sl < 2; ++sl) {
-                kv_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES + HI_OFF, KV_TILE, 1024, 2);
-                s_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES + SH_OFF, S_TILE, 1024, 2);
-            }
+            const uint64_t kv_desc0 = smem_desc(sm_u + OFF_SLOTS + HI_OFF, KV_TILE, 1024, 2);
+            const uint64_t s_desc0 = smem_desc(sm_u + OFF_SLOTS + SH_OFF, S_TILE, 1024, 2);
             bool ok = mbar_wait(a_ready, 0, 10);
             for (int k = 0; k < nsc && ok; ++k) {
-                const int slot = k % 2;
-                if (!mbar_wait(kv_full(slot), (uint32_t)((k / 2) & 1), 6)) break;
-                if (k >= 2 && !mbar_wait(d_empty(slot), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
+                const int slot = k % NSLOT, dbuf = k % 2;
+                if (!mbar_wait(kv_full(slot), (uint32_t)((k / NSLOT) & 1), 6)) break;
+                if (k >= 2 && !mbar_wait(d_empty(dbuf), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
                 tc_fence_after();
-                const uint32_t d = tmem + D_COL + slot * 128;
-                const uint64_t dk = slot ? kv_desc[1] : kv_desc[0], ds = slot ? s_desc[1] : s_desc[0];
+                const uint32_t d = tmem + D_COL + dbuf * 128;
+                // descriptors of the slot's tiles: the start-address field counts 16-byte units
+                const uint64_t dk = kv_desc0 + (uint64_t)(slot * (SLOT_BYTES / 16)), ds = s_desc0 + (uint64_t)(slot * (SLOT_BYTES / 16));
                 // outputs of the four chunks (lanes 0..95) and their state increments (lanes 96..127)
 #pragma unroll
                 for (int part = 0; part < 2; ++part)
 #pragma unroll
                     for (int jj = 0; jj < CHUNK / 16; ++jj)
                         mma_ts(d, tmem + (part ? A_LO : A_HI) + 8 * jj, dk + (uint64_t)(jj * 128), idesc, (part || jj) ? 1u : 0u);
-                mma_commit(inc_full(slot));
+                mma_commit(inc_full(dbuf));
                 // + C S: contribution of everything before each chunk
-                if (!mbar_wait(s_full(slot), (uint32_t)((k / 2) & 1), 13)) break;
+                if (!mbar_wait(s_full(slot), (uint32_t)((k / NSLOT) & 1), 13)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int part = 0; part < 2; ++part)
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj)
                         mma_ts(d, tmem + (part ? C_LO : C_HI) + 8 * jj, ds + (uint64_t)(jj * 128), idesc, 1u);
-                mma_commit(d_full(slot));
+                mma_commit(d_full(dbuf));
                 mma_commit(slot_free(slot));
             }
         }
