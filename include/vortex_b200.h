@@ -218,7 +218,7 @@ int vtx_iir_fwd_noalloc(const vtx_iir_params* p, void* stream);
  * (HyenaCascade.parallel_forward for a long-filter layer: featurizer parallel_fir + parallel_iir with its FFT
  * branch, engine.py:262-353) -- the hyena_li_fwd entry point the reference imports but never defines
  * (vortex/model/layers.py:18-21).
- *   u [B,L,3D] -> y [B,L,D].  state must be NULL (the state after the last token comes from vtx_iir_fwd).
+ *   u [B,L,3D] -> y [B,L,D]; state fp32 [B,D,S] (real poles) or [B,D,S,2] (complex) after the last token, or NULL.
  * ------------------------------------------------------------------------ */
 typedef struct vtx_fused_iir_params {
     const void* u;       int64_t u_stride_b, u_stride_l;   /* channel stride 1 */
@@ -227,7 +227,7 @@ typedef struct vtx_fused_iir_params {
     vtx_modal_params modal;                     /* G * 16 == D                             */
     const void* bias;    int64_t bias_dtype;   /* [D] skip term or NULL                   */
     void* y;             int64_t y_stride_b, y_stride_l;   /* channel stride 1 */
-    float* state;                               /* must be NULL                            */
+    float* state;                               /* or NULL                                 */
     int64_t B, L, D, K3;
     int64_t layout, num_heads, flip_x1x2;
     int64_t io_dtype;

@@ -244,7 +244,7 @@ def _li_oracle(p, L, D, cplx, layout, heads, flip):
     else:
         h = O.modal_filter(to_np(p["log_poles"]), to_np(p["residues"]), L)
     return O.long_conv_gate(zf, O.expand_groups(h, D), to_np(p["Dp"]), D, io="bf16", layout=layout, num_heads=heads,
-                            flip_x1x2=flip, mirror=False, round_input=False)[0]
+                            flip_x1x2=flip, mirror=False, round_input=False)
 
 
 @pytest.mark.parametrize("B,L,D,S,cplx,layout,heads,flip", LI_TC_CASES)
@@ -255,8 +255,26 @@ def test_fused_li_tensor_core_vs_oracle(B, L, D, S, cplx, layout, heads, flip):
     pc = cuda(p)
     y, fs, st = hyena_ops.hyena_li_fwd(pc["u"], pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"],
                                        theta=pc.get("theta"), res_im=pc.get("res_im"), layout=layout, num_heads=heads,
-                                       flip=flip, want_state=False)
+                                       flip=flip, want_state=True)
     ops.device_status()
-    assert y.shape == (B, L, D) and y.dtype == torch.bfloat16 and fs is None and st is None
-    ref = _li_oracle(p, L, D, cplx, layout, heads, flip)
+    assert y.shape == (B, L, D) and y.dtype == torch.bfloat16
+    ref, kv = _li_oracle(p, L, D, cplx, layout, heads, flip)
     assert rel_l2(y, ref) <= TOL["bf16"]
+    # caches: copy of the last inputs (bit-exact) and the modal state after the last token (fp32)
+    assert np.array_equal(to_np(fs), to_np(p["u"])[:, max(L - 2, 0):, :].transpose(0, 2, 1))
+    lp = np.repeat(to_np(p["log_poles"])[..., 0], 16, axis=0)
+    if cplx:
+        poles = np.exp(lp) * np.exp(1j * np.repeat(to_np(p["theta"]), 16, axis=0))
+        st_ref = O.modal_state_complex(kv, poles)
+        assert st.shape == (B, D, S, 2)
+        st_c = to_np(st)[..., 0] + 1j * to_np(st)[..., 1]
+        assert np.linalg.norm(st_c - st_ref) / np.linalg.norm(st_ref) <= 2e-5
+    else:
+        st_ref = O.modal_state(kv, lp)
+        assert st.shape == (B, D, S)
+        assert rel_l2(st, st_ref) <= 2e-5
+    # without caches the same output
+    y2, fs2, st2 = hyena_ops.hyena_li_fwd(pc["u"], pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"],
+                                          theta=pc.get("theta"), res_im=pc.get("res_im"), layout=layout, num_heads=heads,
+                                          flip=flip, want_state=False)
+    assert fs2 is None and st2 is None and torch.equal(y2, y)

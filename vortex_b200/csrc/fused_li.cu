@@ -16,6 +16,9 @@
 // memory as bf16 head + remainder, and a second, short MMA sequence adds C S.  All operands that come from fp32 math
 // (taps, pole powers, states, k*v) are carried as bf16 head + remainder, which keeps ~16 bits.
 //
+// The walk is aligned to the END of the sequence: the first step is padded in front with rows before the sequence start
+// (zeros, like the featurizer's own history), so the state after the last step is the state after the last token.
+//
 // Warp roles (16 warps): 0-7 front end (as in the medium-filter kernel: TMA-staged rows -> featurizer -> k*v and q
 // tiles), 8-10 epilogue (TMEM lanes 0..95), 11 state recurrence (lanes 96..127), 12 MMA issue, 13-14 TMA issue.
 // All waits are bounded.
@@ -80,6 +83,7 @@ struct Args {
     const void* bias; int64_t bias_dtype;
     const float* log_poles; const float* theta; const float* res_re; const float* res_im;
     __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
+    float* state;
     int64_t L, D, G, S;
     int layout, flip;
     int64_t hd;
@@ -107,6 +111,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int64_t g = blockIdx.x % a.G, b = blockIdx.x / a.G;
     const int nsc = (int)((a.L + SUPER - 1) / SUPER);        // steps of the walk
+    const int pad = (int)((int64_t)nsc * SUPER - a.L);       // rows in front of the sequence in the first step
 
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
@@ -327,11 +332,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
         // ======== epilogue: thread = output row of a chunk (TMEM lanes 0..95) ==============================
         const int e = warp - W_EP, r = e * 32 + lane;
         __nv_bfloat16* yrow[NS];
-        int nleft[NS];        // rows of the sequence from this thread's first row on (<= 0: nothing to store)
+        int first[NS];        // this thread's row of step 0, relative to the sequence start (negative: padding, not stored)
 #pragma unroll
         for (int s = 0; s < NS; ++s) {
-            yrow[s] = a.y + b * a.y_stride_b + (int64_t)(s * CHUNK + r) * a.y_stride_l + g * CH;
-            nleft[s] = (int)a.L - (s * CHUNK + r);
+            first[s] = s * CHUNK + r - pad;
+            yrow[s] = a.y + b * a.y_stride_b + (int64_t)first[s] * a.y_stride_l + g * CH;
         }
         const float4* dsk = reinterpret_cast<const float4*>(sm + OFF_DIAG);    // skip parameters D[g*16 .. +16), fp32
         bool has_skip = false;
@@ -404,7 +409,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                         o[4 * hf + j] = pack_bf16(o0, o1);
                     }
                 }
-                if (k * SUPER < nleft[s])
+                if (k * SUPER + first[s] >= 0)
                     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[0]),
                                  "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
             }
@@ -465,6 +470,18 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) { mbar_arrive(s_full(slot)); mbar_arrive(d_empty(dbuf)); }
+        }
+        if (a.state && (jj >> 1) < (int)a.S) {
+            // state after the last token: [B, D, S] (real poles) or [B, D, S, 2]
+            const bool cplx = a.theta != nullptr;
+            if (cplx || !(jj & 1)) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int64_t d = g * CH + 8 * half + c;
+                    const int64_t idx = (b * a.D + d) * a.S + (jj >> 1);
+                    a.state[cplx ? 2 * idx + (jj & 1) : idx] = S[c];
+                }
+            }
         }
     } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
@@ -527,7 +544,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 for (int s = 0; s < NS; ++s) {
                     if (s % NTMA != tw) continue;
                     const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
-                    const int row = (NS * k + s) * CHUNK + h * HROWS - 2 - s;      // stream s is staged s rows early
+                    const int row = (NS * k + s) * CHUNK + h * HROWS - 2 - s - pad;      // stream s is staged s rows early
                     if (INTERLEAVED) {
                         tma_load_3d(dst, &tmap, bar, col[0], row, (int)b);
                     } else {
@@ -562,7 +579,6 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     VTX_REQUIRE(p->D == p->modal.G * CH, VTX_ERR_UNSUPPORTED, "fused_iir: needs modal systems shared by groups of %d channels", CH);
     VTX_REQUIRE(p->modal.S <= NPOLE, VTX_ERR_UNSUPPORTED, "fused_iir: state size %lld > %d", (long long)p->modal.S, NPOLE);
     VTX_REQUIRE(p->K3 == 3 && !p->b3, VTX_ERR_UNSUPPORTED, "fused_iir: needs a 3-tap featurizer without bias");
-    VTX_REQUIRE(!p->state, VTX_ERR_UNSUPPORTED, "fused_iir: the state after the last token is not produced on this path");
     VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0,
                 VTX_ERR_ALIGNMENT, "fused_iir: y rows must be 32-byte aligned");
     VTX_REQUIRE(p->L < ((int64_t)1 << 30) && p->B <= 65535 && p->modal.G * p->B < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED,
@@ -572,6 +588,7 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     a.log_poles = static_cast<const float*>(p->modal.log_poles); a.theta = static_cast<const float*>(p->modal.theta);
     a.res_re = static_cast<const float*>(p->modal.res_re); a.res_im = static_cast<const float*>(p->modal.res_im);
     a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
+    a.state = p->state;
     a.L = p->L; a.D = p->D; a.G = p->modal.G; a.S = p->modal.S;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0;
     a.hd = p->D;

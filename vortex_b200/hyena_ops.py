@@ -80,10 +80,15 @@ def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues,
     """Hyena-LI block (modal long filter).  u [B, L, 3D] -> y [B, L, D], featurizer cache, modal state
     fp32 [B, D, S] (complex poles: [B, D, S, 2])."""
     D = u.shape[-1] // 3
-    if not want_state and _li_tensor_core_ok(u, short_filter_weight, short_filter_bias, residues, layout, num_heads):
-        y = ops.fused_iir_fwd(u, short_filter_weight, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads,
-                              flip=flip, theta=theta, res_im=res_im)
-        return y, None, None
+    if _li_tensor_core_ok(u, short_filter_weight, short_filter_bias, residues, layout, num_heads):
+        out = ops.fused_iir_fwd(u, short_filter_weight, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads,
+                                flip=flip, theta=theta, res_im=res_im, want_state=want_state)
+        if not want_state:
+            return out, None, None
+        # featurizer cache: the last two input rows, channel-first (a strided copy, no arithmetic)
+        L = u.shape[1]
+        fs = u[:, max(L - 2, 0):, :].transpose(1, 2).contiguous()
+        return out[0], fs, out[1]
     z, fs = ops.featurizer_fwd(u, short_filter_weight, short_filter_bias, None, want_state=want_state)
     y, st = ops.iir_fwd(z, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads, flip=flip, theta=theta,
                         res_im=res_im, want_state=want_state, round_kv=True)

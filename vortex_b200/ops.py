@@ -227,8 +227,9 @@ def modal_filter(log_poles, residues, L: int, theta=None, res_im=None) -> torch.
 
 
 def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, layout="interleaved", num_heads=1,
-                  flip=False, theta=None, res_im=None):
-    """Channel-last fused long-filter block (tensor cores): u [B, L, 3D] bf16 -> y [B, L, D]."""
+                  flip=False, theta=None, res_im=None, want_state=False):
+    """Channel-last fused long-filter block (tensor cores): u [B, L, 3D] bf16 -> y [B, L, D] and, on request, the
+    modal state after the last token (fp32 [B, D, S], complex poles [B, D, S, 2])."""
     _need_cuda(u, w3, residues, bias)
     if u.stride(2) != 1:
         u = u.contiguous()
@@ -239,15 +240,18 @@ def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, lay
     bias = _param(bias, u)
     m, keep = _modal(log_poles, residues, u, theta, res_im)
     y = torch.empty(B, L, D, device=u.device, dtype=u.dtype)
+    st = None
+    if want_state:
+        st = torch.empty((B, D, m.S, 2) if theta is not None else (B, D, m.S), device=u.device, dtype=torch.float32)
     p = _lib.FusedIirParams(
         u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3), b3=None, b3_dtype=0,
         modal=m, bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
-        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=None, B=B, L=L, D=D, K3=w3.shape[1],
+        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), B=B, L=L, D=D, K3=w3.shape[1],
         layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip), io_dtype=_code(u))
     with _on(u):
         _lib.check(_lib.lib().vtx_fused_iir_fwd(C.byref(p), _stream(u)))
     del keep
-    return y
+    return (y, st) if want_state else y
 
 
 def iir_fwd(z_pre: torch.Tensor, log_poles, residues, bias, D: int, *, layout="split", num_heads=1, flip=False,
