@@ -59,6 +59,8 @@ MR_CASES = [
     ("bf16", 1, 100, 32, 2, 128, "interleaved", 1, False),      # L < K
     ("bf16", 2, 1, 32, 2, 128, "interleaved", 1, False),        # single token
     ("bf16", 1, 8192, 64, 4, 128, "interleaved", 1, False),     # several time segments per sequence
+    ("bf16", 2, 1000, 256, 16, 128, "interleaved", 1, False),   # two idle streams in the quad, 16 groups
+    ("bf16", 2, 1000, 256, 16, 17, "interleaved", 1, False),    # shortest filter on the tensor-core path
 ]
 
 

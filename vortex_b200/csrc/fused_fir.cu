@@ -300,7 +300,12 @@ extern "C" int vtx_fused_fir_fwd(const vtx_fused_fir_params* p, void* stream) {
     VTX_REQUIRE(valid_dtype(p->io_dtype), VTX_ERR_BAD_ARG, "fused_fir: bad io dtype");
     VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || p->bias, VTX_ERR_BAD_ARG, "fused_fir: bias mode set without a bias");
     VTX_REQUIRE(p->B <= 65535, VTX_ERR_UNSUPPORTED, "fused_fir: batch too large");
-    if (p->K > 16) return fused_mr_tc_fwd(p, (cudaStream_t)stream);
+    // Kernel choice: the tensor-core kernel (bf16, groups of 16 channels, up to 128 taps) is the faster one for every
+    // filter length it takes; the CUDA-core kernel below covers the other dtypes and group sizes up to 16 taps.
+    const bool tc_shape = p->io_dtype == VTX_BF16 && p->D == p->G * 16 && p->K <= 128 && !p->b3 && p->bias_mode != VTX_BIAS_ADD &&
+                          (reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0 &&
+                          (p->layout != VTX_QKV_COLUMN_SPLIT || (p->num_heads > 0 && p->D % p->num_heads == 0 && (p->D / p->num_heads) % 16 == 0));
+    if (tc_shape || p->K > 16) return fused_mr_tc_fwd(p, (cudaStream_t)stream);
 
     const int64_t es = dtype_size(p->io_dtype);
     FusedArgs a{};

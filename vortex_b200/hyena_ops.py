@@ -39,9 +39,9 @@ def _fused_ok(u, h, layout, num_heads):
 
 
 def _tensor_core_ok(u, b3, h, layout, num_heads):
-    """Shapes the tcgen05 blocked-Toeplitz kernel takes: bf16 I/O, 17..128 taps, groups of 16 channels."""
+    """Shapes the tcgen05 blocked-Toeplitz kernel takes: bf16 I/O, up to 128 taps, groups of 16 channels."""
     D = u.shape[-1] // 3
-    if u.dtype != torch.bfloat16 or b3 is not None or not (16 < h.shape[-1] <= 128) or h.shape[0] * 16 != D:
+    if u.dtype != torch.bfloat16 or b3 is not None or h.shape[-1] > 128 or h.shape[0] * 16 != D:
         return False
     if (u.stride(1) * 2) % 16 or u.stride(2) != 1 or u.data_ptr() % 16 or (u.stride(0) * 2) % 16:
         return False
@@ -51,8 +51,9 @@ def _tensor_core_ok(u, b3, h, layout, num_heads):
 
 
 def _fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state):
-    """Kernel choice per workload: single-pass CUDA-core kernel for filters up to 16 taps, tcgen05
-    blocked-Toeplitz kernel for 17..128 taps with bf16 I/O, two-launch general path otherwise."""
+    """Kernel choice per workload: tcgen05 blocked-Toeplitz kernel for bf16 I/O with groups of 16 channels and up
+    to 128 taps, single-pass CUDA-core kernel for other dtypes / group sizes up to 16 taps, two-launch general path
+    otherwise (the choice between the first two is made inside vtx_fused_fir_fwd)."""
     D = u.shape[-1] // 3
     if _fused_ok(u, h, layout, num_heads) or _tensor_core_ok(u, b3, h, layout, num_heads):
         return ops.fused_fir_fwd(u, w3, b3, h, D_skip, D, taps=taps, bias_mode=bias_mode, layout=layout,
