@@ -175,6 +175,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mr", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small cases for profiling)")
+    ap.add_argument("--seq", type=int, default=0, help="override the sequence length (small cases for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args()
@@ -183,6 +184,9 @@ def main():
     if a.batch > 0:
         w["B"] = a.batch
         w["name"] += f" [batch overridden to {a.batch}]"
+    if a.seq > 0:
+        w["L"] = a.seq
+        w["name"] += f" [sequence length overridden to {a.seq}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -298,7 +302,7 @@ def main():
 LAUNCHES = {"mr": 1, "se": 1, "li": 1}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
-NCU_TRAFFIC = {"mr": 1.018e9, "se": 0.986e9, "li": None}   # small-case (B=1) captures scaled by the units of a bench launch
+NCU_TRAFFIC = {"mr": 1.013e9, "se": 1.017e9, "li": 4.14e9}   # small-case captures scaled by the units of a bench launch
 
 if __name__ == "__main__":
     main()
