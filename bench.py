@@ -214,6 +214,8 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"      # keep the version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
