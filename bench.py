@@ -37,6 +37,13 @@ WORKLOADS = {
                name="hyena_se_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + 7-tap grouped FIR + gate)"),
     "li": dict(B=1, L=131072, D=4096, G=256, K=0, io="bf16", seed=2,
                name="hyena_li_prefill B=1 L=131072 D=4096 bf16 (featurizer3 + gate + 16-pole modal filter + gate)"),
+    # one-token decode of one Hyena layer (one launch): a step = B tokens; fp32 caches as after the first decode step
+    "decode_mr": dict(B=64, L=1, D=4096, G=256, K=128, io="bf16", seed=3, decode=True,
+                      name="hyena_mr_decode B=64 D=4096 bf16 (one layer, one token: featurizer + 128-tap FIR caches)"),
+    "decode_se": dict(B=64, L=1, D=4096, G=256, K=7, io="bf16", seed=3, decode=True,
+                      name="hyena_se_decode B=64 D=4096 bf16 (one layer, one token: featurizer + 7-tap FIR caches)"),
+    "decode_li": dict(B=64, L=1, D=4096, G=256, K=0, io="bf16", seed=3, decode=True,
+                      name="hyena_li_decode B=64 D=4096 bf16 (one layer, one token: featurizer cache + 16 complex modal states)"),
 }
 
 
@@ -71,13 +78,45 @@ def make_inputs(w, device, dtype=torch.bfloat16):
         p["residues"] = torch.randn(G, 16, generator=g)
         p["res_im"] = torch.randn(G, 16, generator=g)
         p["Dp"] = torch.randn(D, generator=g).to(dtype)
+    if w.get("decode"):
+        # caches as a decode step leaves them (fp32); several sets, used in turn, so that the timed steps stream
+        # their caches from HBM instead of finding them in the 126 MB L2
+        p["D"] = D
+        per_set = B * 3 * D * 2 * 4 + (B * D * (K - 1) * 4 if K > 0 else B * D * 16 * 2 * 4)
+        nsets = max(2, min(32, -(-300_000_000 // per_set)))
+        p["sets"] = []
+        for _ in range(nsets):
+            c = {"fir_state": torch.randn(B, 3 * D, 2, generator=g)}
+            if K > 0:
+                c["inner_state"] = torch.randn(B, D, K - 1, generator=g)
+            else:
+                c["iir_state"] = torch.randn(B, D, 16, 2, generator=g)
+            p["sets"].append(c)
+        p["turn"] = [0]
     return p
+
+
+def decode_bytes(w):
+    """Algorithmic HBM bytes of one decode launch: every cache element read and written once, plus the token."""
+    B, D, K = w["B"], w["D"], w["K"]
+    cache = B * 3 * D * 2 * 4 + (B * D * (K - 1) * 4 if K > 0 else B * D * 16 * 2 * 4)
+    return 2 * cache + B * 3 * D * 2 + B * D * 2
 
 
 def run_block(name, pc, u=None):
     """One step through the public API; returns y [B, L, D]."""
-    from vortex_b200 import hyena_ops
+    from vortex_b200 import hyena_ops, ops
     u = pc["u"] if u is None else u
+    if name.startswith("decode"):
+        un = u[:, 0]
+        c = pc["sets"][pc["turn"][0] % len(pc["sets"])]
+        pc["turn"][0] += 1
+        if name == "decode_li":
+            return ops.decode_layer(un, pc["w3"], None, c["fir_state"], pc["D"], log_poles=pc["log_poles"],
+                                    residues=pc["residues"], iir_state=c["iir_state"], theta=pc["theta"],
+                                    res_im=pc["res_im"], bias=pc["Dp"])[0]
+        return ops.decode_layer(un, pc["w3"], None, c["fir_state"], pc["D"], h=pc["h"], inner_state=c["inner_state"],
+                                bias=pc["Dp"], flip_filter=name == "decode_mr", gated_bias=name == "decode_mr")[0]
     if name == "mr":
         return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"])[0]
     if name == "se":
@@ -225,6 +264,8 @@ def main():
 
     p = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), dev)
     pc = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
+    if "sets" in pc:
+        pc["sets"] = [{k: v.to(dev) for k, v in c.items()} for c in pc["sets"]]
     from vortex_b200 import ops
 
     for _ in range(a.warmup):
@@ -232,11 +273,28 @@ def main():
     ops.device_status()
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph = None
+    if w.get("decode"):
+        # a decode step is one short launch: replay the timed steps from a CUDA graph (as a serving loop would), so
+        # that the device, not the Python caller, sets the pace
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(a.steps):
+                    y = run_block(a.workload, pc)
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
     with ClockSampler(local) as cs:
         barrier()
         ev0.record()
-        for _ in range(a.steps):
-            y = run_block(a.workload, pc)
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(a.steps):
+                y = run_block(a.workload, pc)
         ev1.record()
         barrier()
     ms = ev0.elapsed_time(ev1)
@@ -249,7 +307,7 @@ def main():
 
     # ---- end to end: pinned host input -> device -> kernel -> pinned host output, every step
     e2e = None
-    if not a.no_e2e:
+    if not a.no_e2e and not w.get("decode"):
         hu = p["u"].pin_memory()
         hy = [torch.empty(y.shape, dtype=y.dtype).pin_memory() for _ in range(2)]
         du = [torch.empty_like(pc["u"]) for _ in range(2)]
@@ -302,11 +360,12 @@ def main():
             dist.destroy_process_group()
         return
     peak, peak_kind = _peaks()
-    algo_bytes = 8 * w["B"] * w["D"] * w["L"]          # 3 reads + 1 write of 2-byte elements per channel and token
+    # prefill: 3 reads + 1 write of 2-byte elements per channel and token; decode: the caches, read and written once
+    algo_bytes = decode_bytes(w) if w.get("decode") else 8 * w["B"] * w["D"] * w["L"]
     launches_per_step = LAUNCHES.get(a.workload, 1)
     achieved = algo_bytes / (ms_step * 1e-3) / 1e9
     line = {
-        "metric": "hyena_prefill_throughput", "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
+        "metric": "hyena_decode_throughput" if w.get("decode") else "hyena_prefill_throughput", "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
         "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
         "gpu_launches": launches_per_step * a.steps,
@@ -317,7 +376,7 @@ def main():
                              f"{launches_per_step} kernel launch(es)"},
         "e2e": e2e,
     }
-    if not a.no_cpu_baseline and world == 1:
+    if not a.no_cpu_baseline and world == 1 and not w.get("decode"):
         line["cpu_baseline"] = cpu_baseline(a.workload, w, steps=3)[0]
     print(json.dumps(line))
     if dist is not None:
@@ -325,7 +384,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload (no cache outputs requested)
-LAUNCHES = {"mr": 1, "se": 1, "li": 1}
+LAUNCHES = {"mr": 1, "se": 1, "li": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.013e9, "se": 1.017e9, "li": 4.14e9}   # small-case captures scaled by the units of a bench launch

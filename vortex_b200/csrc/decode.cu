@@ -158,6 +158,168 @@ __global__ void __launch_bounds__(256) decode_layer_kernel(vtx_decode_layer_para
     if (lane == 0) static_cast<T*>(p.y)[row] = from_f32<T>(y);
 }
 
+// ---- tiled layer kernels (fp32 caches, i.e. every decode step but the first after a prefill) -------------------
+// A tile of RW consecutive hidden channels of one batch element is owned by one warp (long FIR rows) or half-warp
+// (modal rows).  Lane r < RW takes the featurizer step of row r once (instead of every lane of a row repeating it);
+// then the lanes stream the RW cache rows together, with all their loads issued before the first use: a decode step
+// is pure cache traffic, so what counts is bytes in flight per SM.
+
+// featurizer step of hidden channel d of batch element b: new q and k*v, featurizer cache shifted (K3 == 3)
+template <typename T>
+__device__ __forceinline__ void featurizer_step3(const vtx_decode_layer_params& p, int64_t b, int64_t d, float& q, float& kv) {
+    QkvMap map{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? p.D / p.num_heads : p.D};
+    int64_t ch[3];
+    map.get(d, ch[0], ch[1], ch[2]);
+    const T* u = static_cast<const T*>(p.u) + b * 3 * p.D;
+    const float* fin = static_cast<const float*>(p.fir_state_in);
+    float z[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const int64_t c = ch[i], so = (b * 3 * p.D + c) * 2;
+        const float2 st = *reinterpret_cast<const float2*>(fin + so);
+        const float x = to_f32<T>(u[c]);
+        float acc = ld_param(p.w3, p.w3_dtype, c * 3 + 2) * x;
+        acc = fmaf(st.x, ld_param(p.w3, p.w3_dtype, c * 3), acc);
+        acc = fmaf(st.y, ld_param(p.w3, p.w3_dtype, c * 3 + 1), acc);
+        *reinterpret_cast<float2*>(p.fir_state_out + so) = make_float2(st.y, x);
+        if (p.b3) acc += ld_param(p.b3, p.b3_dtype, c);
+        z[i] = round_io<T>(acc);
+    }
+    q = z[0];
+    kv = round_io<T>(z[1] * z[2]);
+}
+
+// FIR layer, full fp32 inner cache of c = K-1 <= 128 samples per row, RW rows per warp.
+template <typename T, int RW>
+__global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_params p) {
+    const int lane = threadIdx.x % 32;
+    const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int64_t row0 = tile * RW;
+    if (row0 >= p.B * p.D) return;
+    const int64_t b = row0 / p.D, d0 = row0 % p.D;
+    float q_own = 0.f, kv_own = 0.f;
+    if (lane < RW) featurizer_step3<T>(p, b, d0 + lane, q_own, kv_own);
+    const int K = (int)p.K, c = K - 1;
+    const bool flip = p.flip_filter != 0;
+    const int64_t cpg = p.D / p.G;
+    const float* sin_ = static_cast<const float*>(p.inner_state_in) + row0 * c;
+    float* sout = p.inner_state_out + row0 * c;
+    // all cache loads of the tile first
+    float s[RW][4];
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = lane + 32 * j;
+            s[r][j] = i < c ? sin_[r * c + i] : 0.f;
+        }
+    float tap[4], tap_u = 0.f;
+    int64_t g_have = -1;
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        const int64_t d = d0 + r, g = d / cpg;
+        if (g != g_have) {          // taps of the row's group (usually the same for the whole tile)
+            g_have = g;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = lane + 32 * j;
+                tap[j] = i < c ? ld_param(p.h, p.h_dtype, g * K + (flip ? c - i : i)) : 0.f;
+            }
+            tap_u = ld_param(p.h, p.h_dtype, g * K + (flip ? 0 : c));
+        }
+        const float kv = __shfl_sync(0xffffffffu, kv_own, r), q = __shfl_sync(0xffffffffu, q_own, r);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = lane + 32 * j;
+            acc = fmaf(s[r][j], tap[j], acc);
+            if (i >= 1 && i < c) sout[r * c + i - 1] = s[r][j];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            sout[r * c + c - 1] = kv;
+            float f = fmaf(tap_u, kv, acc);
+            if (p.bias_mode != VTX_BIAS_NONE) {
+                const float bias = ld_param(p.bias, p.bias_dtype, d);
+                f = p.bias_mode == VTX_BIAS_GATED ? fmaf(bias, kv, f) : f + bias;
+            }
+            static_cast<T*>(p.y)[row0 + r] = from_f32<T>(round_io<T>(f) * q);
+        }
+    }
+}
+
+// Modal layer, RW rows per half-warp (lane = pole).
+template <typename T, int RW, bool CPLX>
+__global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_params p) {
+    const int lane = threadIdx.x % 16;
+    const unsigned mask = 0xffffu << (threadIdx.x % 32 - lane);
+    const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 16;
+    const int64_t row0 = tile * RW;
+    if (row0 >= p.B * p.D) return;        // whole half-warps leave together
+    const int64_t b = row0 / p.D, d0 = row0 % p.D;
+    float q_own = 0.f, kv_own = 0.f;
+    if (lane < RW) featurizer_step3<T>(p, b, d0 + lane, q_own, kv_own);
+    const int S = (int)p.modal.S;
+    const int64_t cpg = p.D / p.modal.G, ss = S * (CPLX ? 2 : 1);
+    const float* st_in = p.iir_state_in + row0 * ss;
+    float* st_out = p.iir_state_out + row0 * ss;
+    float2 s[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        s[r] = make_float2(0.f, 0.f);
+        if (lane < S) {
+            if (CPLX) s[r] = reinterpret_cast<const float2*>(st_in + r * ss)[lane];
+            else s[r].x = st_in[r * ss + lane];
+        }
+    }
+    float pr = 0.f, pi = 0.f, rr = 0.f, ri = 0.f;
+    int64_t g_have = -1;
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        const int64_t d = d0 + r, g = d / cpg;
+        if (g != g_have) {
+            g_have = g;
+            pr = pi = rr = ri = 0.f;
+            if (lane < S) {
+                const int64_t gi = g * S + lane;
+                const float mag = expf(static_cast<const float*>(p.modal.log_poles)[gi]);
+                rr = static_cast<const float*>(p.modal.res_re)[gi];
+                if (CPLX) {
+                    float sn, cs;
+                    sincosf(static_cast<const float*>(p.modal.theta)[gi], &sn, &cs);
+                    pr = mag * cs; pi = mag * sn;
+                    ri = p.modal.res_im ? static_cast<const float*>(p.modal.res_im)[gi] : 0.f;
+                } else {
+                    pr = mag;
+                }
+            }
+        }
+        const float kv = __shfl_sync(mask, kv_own, r, 16), q = __shfl_sync(mask, q_own, r, 16);
+        float part = 0.f;
+        if (lane < S) {
+            if (CPLX) {
+                const float nr = fmaf(pr, s[r].x, fmaf(-pi, s[r].y, kv));
+                const float ni = fmaf(pr, s[r].y, pi * s[r].x);
+                reinterpret_cast<float2*>(st_out + r * ss)[lane] = make_float2(nr, ni);
+                part = rr * nr - ri * ni;
+            } else {
+                const float n = fmaf(pr, s[r].x, kv);
+                st_out[r * ss + lane] = n;
+                part = rr * n;
+            }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(mask, part, o, 16);
+        if (lane == 0) {
+            const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+            float skip = bias * kv;
+            if (p.bias && p.bias_dtype != VTX_F32) skip = round_io<T>(skip);
+            static_cast<T*>(p.y)[row0 + r] = from_f32<T>(q * (part + skip));
+        }
+    }
+}
+
 }  // namespace vtx
 
 extern "C" int vtx_step_fir(const vtx_step_fir_params* p, void* stream) {
@@ -215,16 +377,25 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
         VTX_REQUIRE((const void*)p->inner_state_out != p->inner_state_in, VTX_ERR_BAD_ARG,
                     "decode_layer: inner_state_out aliases inner_state_in");
         VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || p->bias, VTX_ERR_BAD_ARG, "decode_layer: bias mode without a bias");
+        // tiled kernel: full fp32 caches (every step but the first after a prefill), 3-tap featurizer, 18..129 taps
+        const bool tiled = p->K > 17 && p->K <= 129 && p->K3 == 3 && p->D % 8 == 0 && p->fir_state_dtype == VTX_F32 &&
+                           p->inner_state_dtype == VTX_F32;
         VTX_DISPATCH_IO(p->io_dtype, T, {
-            if (p->K > 17) decode_layer_kernel<T, 32, 0><<<(unsigned)ceil_div<int64_t>(rows * 32, 256), 256, 0, s>>>(*p);
+            if (tiled) decode_fir_tile_kernel<T, 8><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);
+            else if (p->K > 17) decode_layer_kernel<T, 32, 0><<<(unsigned)ceil_div<int64_t>(rows * 32, 256), 256, 0, s>>>(*p);
             else decode_layer_kernel<T, 1, 0><<<(unsigned)ceil_div<int64_t>(rows, 256), 256, 0, s>>>(*p);
         });
     } else {
         VTX_REQUIRE(p->modal.log_poles && p->modal.res_re && p->modal.G > 0 && p->modal.S > 0 && p->modal.S <= 16 &&
                         p->D % p->modal.G == 0 && p->iir_state_in && p->iir_state_out,
                     VTX_ERR_BAD_ARG, "decode_layer: bad modal arguments");
-        VTX_DISPATCH_IO(p->io_dtype, T,
-                        decode_layer_kernel<T, 16, 1><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, s>>>(*p));
+        const bool tiled = p->K3 == 3 && p->D % 8 == 0 && p->fir_state_dtype == VTX_F32;
+        const bool cplx = p->modal.theta != nullptr;
+        VTX_DISPATCH_IO(p->io_dtype, T, {
+            if (tiled && cplx) decode_iir_tile_kernel<T, 8, true><<<(unsigned)ceil_div<int64_t>(rows / 8 * 16, 256), 256, 0, s>>>(*p);
+            else if (tiled) decode_iir_tile_kernel<T, 8, false><<<(unsigned)ceil_div<int64_t>(rows / 8 * 16, 256), 256, 0, s>>>(*p);
+            else decode_layer_kernel<T, 16, 1><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, s>>>(*p);
+        });
     }
     return check_launch("decode_layer");
 }
