@@ -249,6 +249,48 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
     }
 }
 
+// Short FIR layer (K == 7: six cached samples per row), four consecutive rows per thread: the thread's 24 cache
+// values are contiguous and 16-byte aligned, so they move as six 16-byte loads and six 16-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(256) decode_fir7_kernel(vtx_decode_layer_params p) {
+    constexpr int K = 7, c = 6, RT = 4;
+    const int64_t row0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * RT;
+    if (row0 >= p.B * p.D) return;
+    const int64_t b = row0 / p.D, d0 = row0 % p.D;
+    const float4* sin4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.inner_state_in) + row0 * c);
+    float4 v[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) v[j] = sin4[j];
+    float s[RT * c];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) { s[4 * j] = v[j].x; s[4 * j + 1] = v[j].y; s[4 * j + 2] = v[j].z; s[4 * j + 3] = v[j].w; }
+    const bool flip = p.flip_filter != 0;
+    const int64_t cpg = p.D / p.G;
+    float o[RT * c];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+        const int64_t d = d0 + r, g = d / cpg;
+        float q, kv;
+        featurizer_step3<T>(p, b, d, q, kv);
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < c; ++i) {
+            acc = fmaf(s[r * c + i], ld_param(p.h, p.h_dtype, g * K + (flip ? c - i : i)), acc);
+            if (i >= 1) o[r * c + i - 1] = s[r * c + i];
+        }
+        o[r * c + c - 1] = kv;
+        float f = fmaf(ld_param(p.h, p.h_dtype, g * K + (flip ? 0 : c)), kv, acc);
+        if (p.bias_mode != VTX_BIAS_NONE) {
+            const float bias = ld_param(p.bias, p.bias_dtype, d);
+            f = p.bias_mode == VTX_BIAS_GATED ? fmaf(bias, kv, f) : f + bias;
+        }
+        static_cast<T*>(p.y)[row0 + r] = from_f32<T>(round_io<T>(f) * q);
+    }
+    float4* sout4 = reinterpret_cast<float4*>(p.inner_state_out + row0 * c);
+#pragma unroll
+    for (int j = 0; j < 6; ++j) sout4[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+}
+
 // Modal layer, RW rows per half-warp (lane = pole).
 template <typename T, int RW, bool CPLX>
 __global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_params p) {
@@ -380,8 +422,12 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
         // tiled kernel: full fp32 caches (every step but the first after a prefill), 3-tap featurizer, 18..129 taps
         const bool tiled = p->K > 17 && p->K <= 129 && p->K3 == 3 && p->D % 8 == 0 && p->fir_state_dtype == VTX_F32 &&
                            p->inner_state_dtype == VTX_F32;
+        const bool short7 = p->K == 7 && p->K3 == 3 && p->D % 4 == 0 && p->fir_state_dtype == VTX_F32 &&
+                            p->inner_state_dtype == VTX_F32 && reinterpret_cast<uintptr_t>(p->inner_state_in) % 16 == 0 &&
+                            reinterpret_cast<uintptr_t>(p->inner_state_out) % 16 == 0;
         VTX_DISPATCH_IO(p->io_dtype, T, {
-            if (tiled) decode_fir_tile_kernel<T, 8><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);
+            if (short7) decode_fir7_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 4, 256), 256, 0, s>>>(*p);
+            else if (tiled) decode_fir_tile_kernel<T, 8><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);
             else if (p->K > 17) decode_layer_kernel<T, 32, 0><<<(unsigned)ceil_div<int64_t>(rows * 32, 256), 256, 0, s>>>(*p);
             else decode_layer_kernel<T, 1, 0><<<(unsigned)ceil_div<int64_t>(rows, 256), 256, 0, s>>>(*p);
         });
