@@ -331,13 +331,10 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
     } else if (warp < W_EP + 3) {
         // ======== epilogue: thread = output row of a chunk (TMEM lanes 0..95) ==============================
         const int e = warp - W_EP, r = e * 32 + lane;
-        __nv_bfloat16* yrow[NS];
-        int first[NS];        // this thread's row of step 0, relative to the sequence start (negative: padding, not stored)
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            first[s] = s * CHUNK + r - pad;
-            yrow[s] = a.y + b * a.y_stride_b + (int64_t)first[s] * a.y_stride_l + g * CH;
-        }
+        // this thread's row of chunk 0 of step 0, relative to the sequence start (negative: padding, not stored)
+        const int first0 = r - pad;
+        __nv_bfloat16* const yrow0 = a.y + b * a.y_stride_b + (int64_t)first0 * a.y_stride_l + g * CH;
+        const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
         const float4* dsk = reinterpret_cast<const float4*>(sm + OFF_DIAG);    // skip parameters D[g*16 .. +16), fp32
         bool has_skip = false;
 #pragma unroll
@@ -356,18 +353,15 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
             const uint8_t* qm_p = slot_p + QM_OFF + r * 64;
             const int64_t yoff = (int64_t)k * step_pitch;
-            uint32_t acc[2][2][16];
-            tmem_ld16(taddr, acc[0][0]);
-            tmem_ld16(taddr + 64, acc[0][1]);
-#pragma unroll
+            // (rolled over the four chunks: the unrolled form of this loop, with the skip term, does not fit the
+            // instruction cache next to the other roles' loops)
+#pragma unroll 1
             for (int s = 0; s < NS; ++s) {
-                uint32_t (&ah)[16] = acc[s & 1][0];
-                uint32_t (&al)[16] = acc[s & 1][1];
+                uint32_t ah[16], al[16];
+                tmem_ld16(taddr + s * 16, ah);
+                tmem_ld16(taddr + 64 + s * 16, al);
                 tmem_ld_wait(ah, al);
-                if (s + 1 < NS) {
-                    tmem_ld16(taddr + (s + 1) * 16, acc[(s + 1) & 1][0]);
-                    tmem_ld16(taddr + 64 + (s + 1) * 16, acc[(s + 1) & 1][1]);
-                } else {
+                if (s + 1 == NS) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(d_empty(dbuf));
@@ -409,8 +403,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                         o[4 * hf + j] = pack_bf16(o0, o1);
                     }
                 }
-                if (k * SUPER + first[s] >= 0)
-                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[0]),
+                if (k * SUPER + s * CHUNK + first0 >= 0)
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow0 + yoff + s * chunk_pitch), "r"(o[0]),
                                  "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
             }
             __syncwarp();
