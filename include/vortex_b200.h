@@ -228,10 +228,13 @@ typedef struct vtx_fused_iir_params {
     const void* bias;    int64_t bias_dtype;   /* [D] skip term or NULL                   */
     void* y;             int64_t y_stride_b, y_stride_l;   /* channel stride 1 */
     float* state;                               /* or NULL                                 */
+    void* scratch;                              /* vtx_fused_iir_scratch_bytes(B,L,D) bytes, 16-byte aligned, or NULL:
+                                                   lets a sequence be cut into time slices that run on different SMs */
     int64_t B, L, D, K3;
     int64_t layout, num_heads, flip_x1x2;
     int64_t io_dtype;
 } vtx_fused_iir_params;
+int64_t vtx_fused_iir_scratch_bytes(int64_t B, int64_t L, int64_t D);
 int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream);
 
 /* ------------------------------------------------------------------------

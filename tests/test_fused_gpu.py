@@ -235,6 +235,8 @@ LI_TC_CASES = [
     (2, 200, 64, 16, True, "column_split", 2, True),
     (3, 1, 32, 16, True, "interleaved", 1, True),         # single token
     (1, 10000, 32, 16, True, "interleaved", 1, False),    # long walk: the state carries ~100 chunks
+    (1, 15360, 32, 16, True, "interleaved", 1, False),    # walk cut into two time slices handed over through global memory
+    (2, 30001, 32, 16, False, "interleaved", 1, False),   # four slices, ragged front padding
 ]
 
 

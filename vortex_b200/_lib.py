@@ -49,7 +49,7 @@ ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G 
 class FusedIirParams(C.Structure):
     _fields_ = [("u", _p), ("u_stride_b", _i), ("u_stride_l", _i), ("w3", _p), ("w3_dtype", _i),
                 ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
-                ("y", _p), ("y_stride_b", _i), ("y_stride_l", _i), ("state", _p),
+                ("y", _p), ("y_stride_b", _i), ("y_stride_l", _i), ("state", _p), ("scratch", _p),
                 ("B", _i), ("L", _i), ("D", _i), ("K3", _i), ("layout", _i), ("num_heads", _i), ("flip_x1x2", _i),
                 ("io_dtype", _i)]
 
@@ -102,6 +102,7 @@ SYMBOLS = {
     "vtx_iir_fwd": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_iir_fwd_noalloc": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_fused_iir_fwd": (C.c_int, [C.POINTER(FusedIirParams), _p]),
+    "vtx_fused_iir_scratch_bytes": (_i, [_i, _i, _i]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),
     "vtx_decode_layer": (C.c_int, [C.POINTER(DecodeLayerParams), _p]),

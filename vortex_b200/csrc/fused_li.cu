@@ -84,7 +84,9 @@ struct Args {
     const float* log_poles; const float* theta; const float* res_re; const float* res_im;
     __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
     float* state;
-    int64_t L, D, G, S;
+    float* carry; int* flags;      // [walk][slice][32][16] states handed from slice to slice, arrival counters
+    int64_t L, D, G, S, B;
+    int spp, nslice;               // steps per slice, slices per walk
     int layout, flip;
     int64_t hd;
 };
@@ -109,9 +111,15 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
     const uint32_t a_ready = smem_u32(&bars[BD + 6]);                                     // operands expanded, set-up tables no longer needed
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const int64_t g = blockIdx.x % a.G, b = blockIdx.x / a.G;
-    const int nsc = (int)((a.L + SUPER - 1) / SUPER);        // steps of the walk
-    const int pad = (int)((int64_t)nsc * SUPER - a.L);       // rows in front of the sequence in the first step
+    // blockIdx = (time slice, batch element, group), slices of a walk in increasing block order: a slice starts from the
+    // state its predecessor leaves in global memory (a.carry), which an earlier block of the same launch produces
+    const int64_t nwalk = a.G * a.B, walk = blockIdx.x % nwalk;
+    const int slice = (int)(blockIdx.x / nwalk);
+    const int64_t g = walk % a.G, b = walk / a.G;
+    const int ntotal = (int)((a.L + SUPER - 1) / SUPER);     // steps of the whole walk
+    const int pad = (int)((int64_t)ntotal * SUPER - a.L);    // rows in front of the sequence in the first step
+    const int kbase = slice * a.spp;                         // first step of this slice
+    const int nsc = ntotal - kbase < a.spp ? ntotal - kbase : a.spp;   // steps of this slice
 
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
@@ -352,7 +360,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
             const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
             const uint8_t* qm_p = slot_p + QM_OFF + r * 64;
-            const int64_t yoff = (int64_t)k * step_pitch;
+            const int64_t yoff = (int64_t)(kbase + k) * step_pitch;
             // (rolled over the four chunks: the unrolled form of this loop, with the skip term, does not fit the
             // instruction cache next to the other roles' loops)
 #pragma unroll 1
@@ -403,7 +411,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                         o[4 * hf + j] = pack_bf16(o0, o1);
                     }
                 }
-                if (k * SUPER + s * CHUNK + first0 >= 0)
+                if ((kbase + k) * SUPER + s * CHUNK + first0 >= 0)
                     asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow0 + yoff + s * chunk_pitch), "r"(o[0]),
                                  "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
             }
@@ -423,6 +431,24 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
         float S[8];                                            // this component of the state at a chunk start
 #pragma unroll
         for (int c = 0; c < 8; ++c) S[c] = 0.f;
+        if (slice > 0) {
+            // wait (bounded) for both state warps of the previous slice, then take its final state over
+            const int64_t prev = walk * (a.nslice - 1) + (slice - 1);
+            bool have = false;
+            for (int it = 0; it < (1 << 21) && !have; ++it) {
+                int v;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.flags + prev) : "memory");
+                have = v >= 2;
+                if (!have) __nanosleep(200);
+            }
+            if (!have) atomicCAS(&g_device_status, 0, 15);
+            have = __all_sync(0xffffffffu, have);
+            if (have) {
+                const float4* src = reinterpret_cast<const float4*>(a.carry + (prev * 32 + jj) * 16 + 8 * half);
+                const float4 v0 = src[0], v1 = src[1];
+                S[0] = v0.x; S[1] = v0.y; S[2] = v0.z; S[3] = v0.w; S[4] = v1.x; S[5] = v1.y; S[6] = v1.z; S[7] = v1.w;
+            }
+        }
         for (int k = 0; k < nsc; ++k) {
             const int slot = k % NSLOT, dbuf = k % 2;
             if (!mbar_wait(inc_full(dbuf), (uint32_t)((k / 2) & 1), 12)) break;
@@ -465,7 +491,16 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) { mbar_arrive(s_full(slot)); mbar_arrive(d_empty(dbuf)); }
         }
-        if (a.state && (jj >> 1) < (int)a.S) {
+        if (slice + 1 < a.nslice) {
+            // hand the state to the next slice
+            const int64_t mine = walk * (a.nslice - 1) + slice;
+            float4* dst = reinterpret_cast<float4*>(a.carry + (mine * 32 + jj) * 16 + 8 * half);
+            dst[0] = make_float4(S[0], S[1], S[2], S[3]);
+            dst[1] = make_float4(S[4], S[5], S[6], S[7]);
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(a.flags + mine, 1);
+        } else if (a.state && (jj >> 1) < (int)a.S) {
             // state after the last token: [B, D, S] (real poles) or [B, D, S, 2]
             const bool cplx = a.theta != nullptr;
             if (cplx || !(jj & 1)) {
@@ -538,7 +573,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 for (int s = 0; s < NS; ++s) {
                     if (s % NTMA != tw) continue;
                     const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
-                    const int row = (NS * k + s) * CHUNK + h * HROWS - 2 - s - pad;      // stream s is staged s rows early
+                    const int row = (NS * (kbase + k) + s) * CHUNK + h * HROWS - 2 - s - pad;      // stream s is staged s rows early
                     if (INTERLEAVED) {
                         tma_load_3d(dst, &tmap, bar, col[0], row, (int)b);
                     } else {
@@ -559,8 +594,30 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
     }
 }
 
+// Time slices per walk: with one CTA per SM, B*G walks fill the SMs in whole rounds; cutting every walk into slices
+// (handed from block to block through global memory) evens the last round out.
+static void plan_slices(int64_t walks, int64_t ntotal, int& nslice, int& spp) {
+    int best = 1;
+    double best_cost = 1e30;
+    for (int nt = 1; nt <= 8; ++nt) {
+        if (nt > 1 && ntotal / nt < 16) break;
+        const double cost = (double)ceil_div<int64_t>(walks * nt, kNumSMs) / nt + 0.002 * nt;   // + per-CTA set-up
+        if (cost < best_cost * 0.98) { best_cost = cost; best = nt; }
+    }
+    spp = (int)ceil_div<int64_t>(ntotal, best);
+    nslice = (int)ceil_div<int64_t>(ntotal, spp);
+}
+
 }  // namespace li
 }  // namespace vtx
+
+extern "C" int64_t vtx_fused_iir_scratch_bytes(int64_t B, int64_t L, int64_t D) {
+    using namespace vtx::li;
+    if (B <= 0 || L <= 0 || D <= 0) return 0;
+    int nslice, spp;
+    plan_slices(B * (D / CH), (L + SUPER - 1) / SUPER, nslice, spp);
+    return (int64_t)B * (D / CH) * (nslice - 1) * (32 * 16 * 4 + 4);
+}
 
 extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     using namespace vtx;
@@ -575,7 +632,7 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     VTX_REQUIRE(p->K3 == 3 && !p->b3, VTX_ERR_UNSUPPORTED, "fused_iir: needs a 3-tap featurizer without bias");
     VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0,
                 VTX_ERR_ALIGNMENT, "fused_iir: y rows must be 32-byte aligned");
-    VTX_REQUIRE(p->L < ((int64_t)1 << 30) && p->B <= 65535 && p->modal.G * p->B < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED,
+    VTX_REQUIRE(p->L < ((int64_t)1 << 30) && p->B <= 65535 && p->modal.G * p->B < ((int64_t)1 << 27), VTX_ERR_UNSUPPORTED,
                 "fused_iir: problem too large");
     Args a{};
     a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.bias = p->bias; a.bias_dtype = p->bias_dtype;
@@ -583,7 +640,19 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     a.res_re = static_cast<const float*>(p->modal.res_re); a.res_im = static_cast<const float*>(p->modal.res_im);
     a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
     a.state = p->state;
-    a.L = p->L; a.D = p->D; a.G = p->modal.G; a.S = p->modal.S;
+    a.L = p->L; a.D = p->D; a.G = p->modal.G; a.S = p->modal.S; a.B = p->B;
+    const int64_t walks = p->B * p->modal.G, ntotal = (p->L + SUPER - 1) / SUPER;
+    a.nslice = 1; a.spp = (int)ntotal;
+    if (p->scratch) {       // without scratch every walk is one block
+        plan_slices(walks, ntotal, a.nslice, a.spp);
+        if (a.nslice > 1) {
+            VTX_REQUIRE(reinterpret_cast<uintptr_t>(p->scratch) % 16 == 0, VTX_ERR_ALIGNMENT, "fused_iir: scratch must be 16-byte aligned");
+            a.carry = static_cast<float*>(p->scratch);
+            a.flags = reinterpret_cast<int*>(a.carry + walks * (a.nslice - 1) * 32 * 16);
+            cudaError_t e = cudaMemsetAsync(a.flags, 0, (size_t)(walks * (a.nslice - 1)) * sizeof(int), stream);
+            if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_iir: clearing the slice counters: %s", cudaGetErrorString(e));
+        }
+    }
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0;
     a.hd = p->D;
     if (p->layout == VTX_QKV_COLUMN_SPLIT) {
@@ -608,6 +677,6 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
         if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_iir: shared memory opt-in: %s", cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev][variant] = true;
     }
-    kern<<<(unsigned)(p->modal.G * p->B), THREADS, SMEM_BYTES, stream>>>(tmap, a);
+    kern<<<(unsigned)(walks * a.nslice), THREADS, SMEM_BYTES, stream>>>(tmap, a);
     return check_launch("fused_iir");
 }

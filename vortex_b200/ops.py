@@ -243,10 +243,12 @@ def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, lay
     st = None
     if want_state:
         st = torch.empty((B, D, m.S, 2) if theta is not None else (B, D, m.S), device=u.device, dtype=torch.float32)
+    nscratch = _lib.lib().vtx_fused_iir_scratch_bytes(B, L, D)
+    scratch = torch.empty(nscratch, device=u.device, dtype=torch.uint8) if nscratch > 0 else None
     p = _lib.FusedIirParams(
         u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3), b3=None, b3_dtype=0,
         modal=m, bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
-        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), B=B, L=L, D=D, K3=w3.shape[1],
+        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), scratch=_ptr(scratch), B=B, L=L, D=D, K3=w3.shape[1],
         layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip), io_dtype=_code(u))
     with _on(u):
         _lib.check(_lib.lib().vtx_fused_iir_fwd(C.byref(p), _stream(u)))
