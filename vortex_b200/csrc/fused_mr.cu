@@ -416,6 +416,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             // One stream at a time (16 channels: head and remainder accumulators -> gate -> 32 bytes of output), with the
             // accumulators of the next stream already on their way from TMEM: at most two streams' values are live, so
             // nothing spills (a spilled value is reloaded from L2 here: L1 is almost entirely carved out as shared memory).
+#ifdef VTX_MR_EP_UNROLLED
             uint32_t acc[2][2][16];
             tmem_ld16(taddr, acc[0][0]);
             tmem_ld16(taddr + 64, acc[0][1]);
@@ -428,12 +429,28 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     tmem_ld16(taddr + (s + 1) * 16, acc[(s + 1) & 1][0]);
                     tmem_ld16(taddr + 64 + (s + 1) * 16, acc[(s + 1) & 1][1]);
                 } else {
+#else
+            // (rolled over the streams: keeps the instruction-cache footprint of this role small)
+#pragma unroll 1
+            for (int s = 0; s < NS; ++s) {
+                uint32_t ah[16], al[16];
+                tmem_ld16(taddr + s * 16, ah);
+                tmem_ld16(taddr + 64 + s * 16, al);
+                tmem_ld_wait(ah, al);
+                if (s + 1 == NS) {
+#endif
                     // every accumulator of this chunk has left TMEM: hand the buffer back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(d_empty(slot));
                     TRACE(12);
                 }
+                // this stream's output pointer and row count (selects, not indexed arrays: the loop may be rolled)
+                __nv_bfloat16* ys = yrow[0];
+                int nl = nleft[0];
+#pragma unroll
+                for (int t = 1; t < NS; ++t)
+                    if (s == t) { ys = yrow[t]; nl = nleft[t]; }
                 f32x2 y[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
@@ -476,15 +493,15 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 // may then be scheduled above this store)
 #ifdef VTX_MR_CHECK
                 {   // diagnostic builds: a store outside y is recorded and skipped
-                    const int64_t off = (yrow[s] + yoff) - a.y;
-                    if ((k - 1) * CHUNK < nleft[s] && (off < 0 || off + 16 > a.B * a.y_stride_b)) {
+                    const int64_t off = (ys + yoff) - a.y;
+                    if ((k - 1) * CHUNK < nl && (off < 0 || off + 16 > a.B * a.y_stride_b)) {
                         atomicCAS(&g_device_status, 0, 21);
                         continue;
                     }
                 }
 #endif
-                if ((k - 1) * CHUNK < nleft[s] && !(KO(4) && o[0] != 0x12345678u))
-                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow[s] + yoff), "r"(o[0]),
+                if ((k - 1) * CHUNK < nl && !(KO(4) && o[0] != 0x12345678u))
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ys + yoff), "r"(o[0]),
                                  "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
             }
             // every shared-memory read of this chunk is done: its k*v slot and q tile may be rewritten
