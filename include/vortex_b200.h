@@ -237,6 +237,18 @@ typedef struct vtx_fused_iir_params {
 int64_t vtx_fused_iir_scratch_bytes(int64_t B, int64_t L, int64_t D);
 int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream);
 
+/* Hyena-X forward (vortex/ops/hyena_x/triton_indirect_fwd.py:262 hyena_x_bdl_fwd, reference :413-424):
+ * o = fir(h[0:D], q) * fir(h[D:2D], k) * fir(h[2D:3D], v), depthwise causal filters of Lh <= 16 taps
+ * (cross-correlation order), q, k, v, o [B,D,L] contiguous, h [3D,Lh]. */
+typedef struct vtx_hyena_x_params {
+    const void* q; const void* k; const void* v;
+    const void* h;       int64_t h_dtype;
+    void* y;
+    int64_t B, D, L, Lh;
+    int64_t io_dtype;
+} vtx_hyena_x_params;
+int vtx_hyena_x_fwd(const vtx_hyena_x_params* p, void* stream);
+
 /* ------------------------------------------------------------------------
  * Decode (one token).
  *

@@ -198,6 +198,21 @@ def gate_conv_gate(z_pre, h, bias, D, fir_length, io="f32", layout="split",
     return y, np.ascontiguousarray(state)
 
 
+def hyena_x(qkv, h, io="f32", mirror=True):
+    """Hyena-X forward (vortex/ops/hyena_x/triton_indirect_fwd.py:413-424): depthwise causal FIR
+    (cross-correlation taps, F.conv1d with padding L_h - 1 cut to L) on each of the 3D packed channels,
+    then o = z_q * z_k * z_v.  qkv [B, 3D, L], h [3D, 1, L_h] or [3D, L_h] -> [B, D, L].
+    mirror=True rounds where the reference's bf16 tensors round (conv output, first product, result)."""
+    x = round_io(qkv, io)
+    w = round_io(np.asarray(h, dtype=np.float64), io)
+    if w.ndim == 3:
+        w = w[:, 0, :]
+    z = _maybe(causal_fir(x, w, "xcorr"), io, mirror)
+    D = z.shape[1] // 3
+    q, k, v = z[:, :D], z[:, D:2 * D], z[:, 2 * D:]
+    return _maybe(_maybe(q * k, io, mirror) * v, io, mirror)
+
+
 def modal_filter(log_poles, residues, L):
     """HyenaCascade.compute_filter (model.py:390-398): real modal form,
     h[g, t] = sum_s R[g, s] * exp(lambda[g, s] * t), float32 arithmetic.

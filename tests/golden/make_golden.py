@@ -183,6 +183,17 @@ def main(ref_root):
         hf = h.flip(-1)[:, 0]
         out[k + "_T"], out[k + "_That"] = np32(toeplitz(hf, 128)), np32(correction_toeplitz(hf, 128))
 
+    # ---- Hyena-X reference (depthwise FIR on q, k, v, three-way gate) -----------------
+    from vortex.ops.hyena_x.triton_indirect_fwd import hyena_x_fwd_ref
+    for io, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        for Lh in (4, 16):
+            g = torch.Generator().manual_seed(7000 + Lh)
+            B, D, L = 2, 24, 75
+            qkv = (torch.rand(B, 3 * D, L, generator=g) - 0.5).to(dt)
+            h = (torch.rand(3 * D, 1, Lh, generator=g) - 0.5).to(dt)
+            k = f"hx_{io}_Lh{Lh}"
+            out[k + "_qkv"], out[k + "_h"], out[k + "_y"] = np32(qkv), np32(h), np32(hyena_x_fwd_ref(qkv, h))
+
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

@@ -304,3 +304,22 @@ def test_padding_mask_and_errors(eng):
     with pytest.raises(NotImplementedError):
         eng.parallel_iir(z0, None, p["u"][0, 0, :D], L, poles=None, residues=None, t=None, dims=dims, layer_idx=0,
                          use_flashfft=True)
+
+
+@pytest.mark.parametrize("io,B,D,L,Lh", [("bf16", 2, 24, 75, 16), ("bf16", 3, 64, 256, 4), ("f32", 1, 8, 33, 7),
+                                         ("bf16", 1, 16, 8, 16), ("f16", 2, 8, 1, 3)])
+def test_hyena_x_vs_oracle(io, B, D, L, Lh):
+    """Hyena-X (depthwise FIR on q, k, v and three-way gate) against the oracle with the reference's roundings."""
+    import torch
+    from helpers import DT, rel_l2, to_np
+    from oracle import hyena_oracle as O
+    from vortex_b200 import hyena_ops
+    g = torch.Generator().manual_seed(77)
+    qkv = (torch.rand(B, 3 * D, L, generator=g) - 0.5).to(DT[io])
+    h = (torch.rand(3 * D, 1, Lh, generator=g) - 0.5).to(DT[io])
+    y = hyena_ops.hyena_x_fwd(qkv.cuda(), h.cuda())
+    ref = O.hyena_x(to_np(qkv), to_np(h), io=io)
+    assert y.shape == (B, D, L) and y.dtype == DT[io]
+    assert rel_l2(y, ref) <= {"f32": 2e-6, "bf16": 2.5e-3, "f16": 1e-3}[io]
+    q, k, v = qkv.cuda().split([D, D, D], dim=1)
+    assert torch.equal(hyena_ops.hyena_x_bdl_fwd(q, k, v, h.cuda()), y)

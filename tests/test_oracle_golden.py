@@ -136,3 +136,11 @@ def test_hyena_ops_layout(golden, hl):
         T, Th = O.toeplitz_pair(h[g, 0, ::-1], 128)
         assert np.array_equal(T.astype(np.float32), golden[k + "_T"][g])
         assert np.array_equal(Th.astype(np.float32), golden[k + "_That"][g])
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("Lh", [4, 16])
+def test_hyena_x(golden, io, Lh):
+    k = f"hx_{io}_Lh{Lh}"
+    y = O.hyena_x(golden[k + "_qkv"], golden[k + "_h"], io=io)
+    close(y, golden[k + "_y"], io, scale=2.0)

@@ -46,6 +46,9 @@ FusedFirParams = _struct("FusedFirParams", """
 ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G i:S")
 
 
+HyenaXParams = _struct("HyenaXParams", "p:q p:k p:v p:h i:h_dtype p:y i:B i:D i:L i:Lh i:io_dtype")
+
+
 class FusedIirParams(C.Structure):
     _fields_ = [("u", _p), ("u_stride_b", _i), ("u_stride_l", _i), ("w3", _p), ("w3_dtype", _i),
                 ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
@@ -86,7 +89,7 @@ class DecodeLayerParams(C.Structure):
 
 
 STRUCTS = [FeaturizerParams, GcgParams, FusedFirParams, ModalParams, IirParams, StepFirParams, StepIirParams,
-           DecodeLayerParams, FusedIirParams]
+           DecodeLayerParams, FusedIirParams, HyenaXParams]
 
 # name -> (restype, argtypes); every symbol include/vortex_b200.h declares
 SYMBOLS = {
@@ -103,6 +106,7 @@ SYMBOLS = {
     "vtx_iir_fwd_noalloc": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_fused_iir_fwd": (C.c_int, [C.POINTER(FusedIirParams), _p]),
     "vtx_fused_iir_scratch_bytes": (_i, [_i, _i, _i]),
+    "vtx_hyena_x_fwd": (C.c_int, [C.POINTER(HyenaXParams), _p]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),
     "vtx_decode_layer": (C.c_int, [C.POINTER(DecodeLayerParams), _p]),

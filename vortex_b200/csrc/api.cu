@@ -107,6 +107,7 @@ extern "C" int64_t vtx_struct_size(int64_t which) {
         case 6: return sizeof(vtx_step_iir_params);
         case 7: return sizeof(vtx_decode_layer_params);
         case 8: return sizeof(vtx_fused_iir_params);
+        case 9: return sizeof(vtx_hyena_x_params);
         default: return -1;
     }
 }

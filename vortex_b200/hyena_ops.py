@@ -128,3 +128,15 @@ def hyena_se_bdl(x, k, q, h, bias=None, gated_bias=False):
                            bias_mode=BIAS_NONE if bias is None else (BIAS_GATED if gated_bias else BIAS_ADD),
                            round_kv=True)
     return y
+
+
+def hyena_x_bdl_fwd(q, k, v, h):
+    """Hyena-X forward with the reference's name and (b, d, l) operands
+    (``vortex/ops/hyena_x/triton_indirect_fwd.py:262``; math ``hyena_x_fwd_ref``, ``:413-424``)."""
+    return ops.hyena_x_fwd(q, k, v, h)
+
+
+def hyena_x_fwd(qkv, h):
+    """The packed form of the reference's ``hyena_x_fwd_ref``: qkv [B, 3D, L] -> [B, D, L]."""
+    D = qkv.shape[1] // 3
+    return ops.hyena_x_fwd(qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:], h)

@@ -256,6 +256,22 @@ def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, lay
     return (y, st) if want_state else y
 
 
+def hyena_x_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, h) -> torch.Tensor:
+    """o = fir(h_q, q) * fir(h_k, k) * fir(h_v, v); q, k, v [B, D, L], h [3D, 1, Lh] or [3D, Lh] -> [B, D, L]."""
+    _need_cuda(q, k, v, h)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if not (q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k, v must share shape and dtype")
+    B, D, L = q.shape
+    h = _param(h, q).reshape(3 * D, -1)
+    y = torch.empty_like(q)
+    p = _lib.HyenaXParams(q=_ptr(q), k=_ptr(k), v=_ptr(v), h=_ptr(h), h_dtype=_code(h), y=_ptr(y), B=B, D=D, L=L,
+                          Lh=h.shape[1], io_dtype=_code(q))
+    with _on(q):
+        _lib.check(_lib.lib().vtx_hyena_x_fwd(C.byref(p), _stream(q)))
+    return y
+
+
 def iir_fwd(z_pre: torch.Tensor, log_poles, residues, bias, D: int, *, layout="split", num_heads=1, flip=False,
             theta=None, res_im=None, want_state=True, round_kv=True):
     """Gate -> modal long convolution -> gate.  z_pre [B, 3D, L] -> y [B, D, L] (contiguous), state fp32
