@@ -58,3 +58,15 @@ def test_cpu_tensors_are_rejected():
                          dims=(4, 1, 4, 16, 4))
     with pytest.raises(AssertionError):
         HyenaInferenceEngine(iir_prefill_style="nope")
+
+
+def test_fused_iir_scratch_plan():
+    """Host-side planning of the long-filter kernel's time slices (no GPU work): no scratch for short walks or many
+    walks, a few KB per walk once a launch has too few walks to fill the SMs evenly."""
+    from vortex_b200 import _lib
+    f = _lib.lib().vtx_fused_iir_scratch_bytes
+    assert f(1, 1000, 4096) == 0                       # 3 steps: nothing to slice
+    assert f(0, 1000, 4096) == 0 and f(1, 0, 4096) == 0
+    n = f(1, 131072, 4096)                             # 256 walks on 148 SMs: sliced
+    assert n > 0 and n % (32 * 16 * 4 + 4) == 0
+    assert f(8, 131072, 4096 * 4) == 0                 # 8192 walks: whole rounds anyway
