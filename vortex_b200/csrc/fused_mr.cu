@@ -5,19 +5,21 @@
 // The FIR is a blocked-Toeplitz contraction.  For a chunk of 128 output samples of one channel group
 //   Y[128 x N] = [T^ | T][128 x 256] * KV[256 x N],   [T^|T][i][j] = h[128 + i - j]  (0 outside 0..K-1)
 // where KV holds the previous and the current chunk of k*v.  The Toeplitz matrix depends on the group
-// only, so it is expanded ONCE per CTA from the taps straight into tensor memory (A operand in TMEM,
-// 128 lanes x 128 columns of packed bf16) and every tcgen05.mma reads only the data tile from shared
-// memory.  A CTA owns one group and FOUR independent streams (a stream = one batch element and one
-// segment of the time axis), so N = 4 x 16 channels; k*v is split into a bf16 head and a bf16 remainder
-// (two MMAs accumulate into the same fp32 TMEM columns), which keeps the product exact to ~16 bits.
-// The skip term D[c]*kv is one more K=16 MMA per stream against diag(D) with the same shared-memory
-// tile read as a K-major A operand.
+// only: it is expanded from the taps straight into tensor memory (A operand in TMEM, 128 lanes x 128 columns of
+// packed bf16) and every tcgen05.mma reads only the data tile from shared memory.  A work item is one group and
+// FOUR independent streams (a stream = one batch element and one segment of the time axis), so N = 4 x 16 channels;
+// k*v is split into a bf16 head and a bf16 remainder (the MMA's 128 columns are [head | remainder], summed in the
+// epilogue), which keeps the product exact to ~16 bits.  The skip term D[c]*kv is added in the epilogue from the
+// same tile.
 //
-// Warp roles (14 warps): 0-7 front end (TMA-staged rows -> featurizer -> k*v head/remainder and q into
-// the MMA tile), 8-11 epilogue (tcgen05.ld -> q gate -> bf16 -> global), 12 MMA issue, 13 TMA issue.
-// A front-end lane owns one channel pair of one stream and walks 16 rows per chunk with the featurizer
-// history in registers; the four streams of a warp are staged one row apart in shared memory, which makes
-// every shared-memory access of the front end bank-conflict free.  All waits are bounded.
+// One persistent CTA per SM walks through its work items (blockIdx, blockIdx + gridDim, ...: at any time the CTAs of
+// the launch read neighbouring groups of the same rows).  Warp roles (16 warps): 0-7 front end (TMA-staged rows ->
+// featurizer -> k*v head/remainder and 24-bit q into the chunk's slot), 8-11 epilogue (tcgen05.ld -> skip -> q gate
+// -> bf16 -> global; they also expand the NEXT item's Toeplitz operand into the other half of a TMEM double buffer
+// while the current item streams), 12 MMA issue, 13-14 TMA issue.  A front-end lane owns one channel pair of one
+// stream and walks 16 rows per chunk in two register batches, the next batch fetched before the current one is
+// computed; the four streams of a warp are staged one row apart in shared memory, which makes every shared-memory
+// access of the front end bank-conflict free.  All waits are bounded.
 #include <cstdlib>
 
 #include "tma.cuh"
@@ -71,19 +73,21 @@ constexpr int QH_TILE = KV_TILE, QM_TILE = CHUNK * 64;
 constexpr int Q_BYTES = QH_TILE + QM_TILE;     // 24576
 constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE;   // (third bytes of q follow at QH_OFF + QH_TILE)
 constexpr int SLOT_BYTES = 2 * KV_TILE + Q_BYTES;      // one chunk: k*v head, k*v remainder, q upper halves, q third bytes
-constexpr int DIAG_BYTES = 128;            // skip parameters D[16] of the group, fp32
-constexpr int TAPS_BYTES = 384 * 2;        // zero-padded taps, bf16
+constexpr int DIAG_BYTES = 2 * 64;         // skip parameters D[16] of the group, fp32; two buffers (this item, next item)
+constexpr int TAPS_BYTES = 2 * 384 * 2;    // zero-padded taps, bf16; two buffers
 constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
 constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
 constexpr int OFF_SLOTS = SMEM_IN;
 constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
 constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
 constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
-constexpr int NBARS = IN_STAGES * 2 + 2 * 4 + 1;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty x2; a_ready
-constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
+constexpr int NBARS = IN_STAGES * 2 + 2 * 6;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty, a_ready, taps_ready x2
+constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 48 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0, "k*v tiles must be 1024-byte aligned");
-constexpr int TMEM_COLS = 512;             // A: [0,128); accumulator buffer b at 128 + 128 b: [head part 64 | remainder part 64]
+constexpr int TMEM_COLS = 512;             // Toeplitz operand of item t at 128 (t & 1); accumulator buffer b at 256 + 128 b:
+                                           // [head part 64 | remainder part 64]
+constexpr int D_COL = 256;
 #ifndef VTX_MR_NTMA
 #define VTX_MR_NTMA 2
 #endif
@@ -105,6 +109,7 @@ struct Args {
     __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
     int64_t B, L, D, G, K;
     int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
+    int64_t nquad, nitems;                 // stream quads per group; work items (group x quad) of the launch
     int layout, flip, taps, has_bias;
     int64_t hd;
     int pf;          // chunks of L2 prefetch distance (0 = off)
@@ -167,109 +172,91 @@ __device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) 
 template <bool INTERLEAVED, bool SWAP>
 __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, Args a) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t sm_u = smem_u32(sm);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BARS);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BARS + NBARS * 8);
-    // barrier indices
-    auto in_full = [&](int st) { return smem_u32(&bars[st * 2]); };
-    auto in_empty = [&](int st) { return smem_u32(&bars[st * 2 + 1]); };
-    const int BB = IN_STAGES * 2;
-    auto kv_full = [&](int sl) { return smem_u32(&bars[BB + sl]); };
+    // Only the 32-bit shared-memory address of the (1024-byte aligned) buffer stays live; generic pointers are made
+    // from it where a role needs one (the front end runs at the register limit).
+    const uint32_t sm_u = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    auto smp = [&](uint32_t off) { return reinterpret_cast<uint8_t*>(__cvta_shared_to_generic(sm_u + off)); };
+    constexpr uint32_t OFF_TSLOT = OFF_BARS + NBARS * 8;
+    // barrier addresses (32-bit shared-memory addresses: no generic pointer has to stay live in the role loops)
+    const uint32_t bar_u = sm_u + OFF_BARS;
+    auto in_full = [&](int st) { return bar_u + 16u * (uint32_t)st; };
+    auto in_empty = [&](int st) { return bar_u + 16u * (uint32_t)st + 8u; };
+    constexpr uint32_t BB = IN_STAGES * 2;
+    auto kv_full = [&](int sl) { return bar_u + 8u * (BB + (uint32_t)sl); };
     // slot_free: the chunk in this slot is no longer needed.  Five arrivals: the four epilogue warps (k*v rows of the skip
     // term and the q tile read) and the MMA warp's commit behind the MMAs of the next chunk that read the k*v tile.
-    auto slot_free = [&](int sl) { return smem_u32(&bars[BB + 2 + sl]); };
-    auto d_full = [&](int sl) { return smem_u32(&bars[BB + 4 + sl]); };
-    auto d_empty = [&](int sl) { return smem_u32(&bars[BB + 6 + sl]); };
-    const uint32_t a_ready = smem_u32(&bars[BB + 8]);       // the Toeplitz operand is in TMEM (one arrival per expanding warp)
+    auto slot_free = [&](int sl) { return bar_u + 8u * (BB + 2 + (uint32_t)sl); };
+    auto d_full = [&](int sl) { return bar_u + 8u * (BB + 4 + (uint32_t)sl); };
+    auto d_empty = [&](int sl) { return bar_u + 8u * (BB + 6 + (uint32_t)sl); };
+    auto a_ready = [&](int ab) { return bar_u + 8u * (BB + 8 + (uint32_t)ab); };     // Toeplitz operand expanded (4 epilogue warps)
+    auto taps_ready = [&](int ab) { return bar_u + 8u * (BB + 10 + (uint32_t)ab); };  // taps of the next item in shared memory (4 epilogue warps)
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     int trace_n = 0;
     (void)trace_n;
-    const int64_t g = blockIdx.x % a.G, quad = blockIdx.x / a.G;
+    // Persistent CTA: work items (item = quad * G + group, as many as the launch has blocks apart: at any time the CTAs
+    // of the launch read neighbouring groups of the same rows, which keeps the concurrent reads inside few DRAM
+    // pages).  Every item has its own group, hence its own Toeplitz operand: the epilogue warps expand the operand
+    // of the NEXT item into the other half of a double buffer while the current item streams, so the roles run
+    // through the items without draining.  Per-role running counters give the barrier phases.
+    const int ncta = (int)gridDim.x;
+    const int nmine = (int)((a.nitems - (int64_t)blockIdx.x + ncta - 1) / ncta);      // items blockIdx, blockIdx + ncta, ...
     const int K = (int)a.K;
-    const int nchunk = KO(512) ? 0 : (int)(a.seg_len / CHUNK) + 1;     // chunk 0 is the halo chunk (front end only)
+    const int nchunk = (int)(a.seg_len / CHUNK) + 1;     // chunk 0 of an item is its halo chunk (front end only)
+    auto item_group = [&](int t) { return (int)(((int64_t)blockIdx.x + (int64_t)t * ncta) % a.G); };
+    auto item_quad = [&](int t) { return (int)(((int64_t)blockIdx.x + (int64_t)t * ncta) / a.G); };
 
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
         for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), NTMA); mbar_init(in_empty(st), NFE / 2); }
         for (int sl = 0; sl < 2; ++sl) {
             mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 5); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
+            mbar_init(a_ready(sl), 4); mbar_init(taps_ready(sl), 4);
         }
-        mbar_init(a_ready, NFE + 4);
         fence_mbar_init();
     }
     if (warp == W_MMA) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u + OFF_TSLOT), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
-    {   // taps, zero padded: tp[m] = tap at lag (m - 128), lags outside [0, K) are zero
-        __nv_bfloat16* tp = reinterpret_cast<__nv_bfloat16*>(sm + OFF_TAPS);
-        for (int m = tid; m < 384; m += THREADS) {
-            int l = m - 128;
-            float v = 0.f;
-            if (l >= 0 && l < K) v = ld_param(a.h, a.h_dtype, g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
-            tp[m] = __float2bfloat16_rn(v);
-        }
-        float* dsk = reinterpret_cast<float*>(sm + OFF_DIAG);                 // skip parameters of this group, fp32
-        for (int c = tid; c < CH; c += THREADS) dsk[c] = a.has_bias ? ld_param(a.bias, a.bias_dtype, g * CH + c) : 0.f;
-    }
-    fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-
-    if (warp < NFE + 4) {
-        // Expand the Toeplitz matrix into TMEM: lane i holds row i.  A warp reaches the TMEM lanes of its quarter
-        // (warp % 4); the front-end and epilogue warps of a quarter share its 8 column blocks.  Only the MMA warp
-        // waits for the result (a_ready): the TMA warps start fetching at once and the other roles follow as soon as
-        // their share is written.
-        const int i = (warp % 4) * 32 + lane, part = warp / 4, nparts = (NFE + 4) / 4;
-        const uint16_t* tp = reinterpret_cast<const uint16_t*>(sm + OFF_TAPS);
-        for (int c0 = 16 * part; c0 < 128; c0 += 16 * nparts) {
-            uint32_t v[16];
-#pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                int j = 2 * (c0 + m);                                  // columns j, j+1 of [T^|T]: lag = 128 + i - j
-                uint32_t e0 = tp[128 + 128 + i - j], e1 = tp[128 + 127 + i - j];
-                v[m] = e1 << 16 | e0;
-            }
-            tmem_st16(tmem + ((uint32_t)((warp % 4) * 32) << 16) + c0, v);
-        }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(a_ready);
-    }
+    uint32_t tmem;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(sm_u + OFF_TSLOT) : "memory");
+    uint32_t cc = 0;          // chunks this role has gone through (halo chunks included): slot = cc & 1
+    uint32_t oc = 0;          // output chunks: accumulator buffer = oc & 1
 
     // ---------------- roles ---------------------------------------------------------------------
     if (warp < NFE) {
         // ======== front end: warp w owns rows [16w, 16w+16) of every chunk =========================
+        // (item-agnostic: the rows arrive staged; only the featurizer taps depend on the group)
         const int w = warp, p = lane % 8, s = lane / 8;
-        const Stream st = stream_of(a, quad, s);
-        f32x2 w3[3][3];     // [q|k|v][tap], each the pair of this lane's two channels
-        {
+        f32x2 w3[3][3];     // [q|k|v][tap], each the pair of this lane's two channels (of the current item's group)
+        auto load_w3 = [&](int g) {
             QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
             int64_t pc[2][3];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) map.get(g * CH + 2 * p + c, pc[c][0], pc[c][1], pc[c][2]);
+            for (int c = 0; c < 2; ++c) map.get((int64_t)g * CH + 2 * p + c, pc[c][0], pc[c][1], pc[c][2]);
 #pragma unroll
             for (int x = 0; x < 3; ++x)
 #pragma unroll
                 for (int j = 0; j < 3; ++j)
                     w3[x][j] = pk2(ld_param(a.w3, a.w3_dtype, pc[0][x] * 3 + j), ld_param(a.w3, a.w3_dtype, pc[1][x] * 3 + j));
-        }
-        const uint32_t kv_chunk = (uint32_t)(s * 2 + p / 4), kv_in = (uint32_t)((p % 4) * 4);   // 16-byte chunk and offset of this lane's bf16 pair in a k*v row
-        const uint32_t qm_in = (uint32_t)(2 * p);                                          // this lane's two third-bytes in the 16-byte chunk s of a q row
+        };
+        // lane constants folded into three offsets: the lane's first staged word of a half chunk, its bf16 pair in row
+        // 16 w of a k*v tile (16-byte chunk 2 s + p / 4, bytes 4 (p % 4)), its two third-bytes in row 16 w of a q tile
+        const uint32_t lane_box = (uint32_t)(s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + s) * (INTERLEAVED ? 96 : 32) + (INTERLEAVED ? 12 : 4) * p);
+        const uint32_t lane_kv = (uint32_t)(((s * 2 + p / 4) << 4) + (p % 4) * 4 + w * WROWS * 128);
+        const uint32_t lane_qm = (uint32_t)((s << 4) + 2 * p + w * WROWS * 64);
+        const uint32_t half = (uint32_t)(w / (NFE / 2));
         static_assert(WROWS == 2 * RB, "the front end walks a chunk as two register batches");
         constexpr int ROWB = INTERLEAVED ? 96 : 32;             // bytes per staged row (per plane in the planar layouts)
         // shared-memory address of this lane's first word of batch hb of chunk k (the box row of the batch's first
         // sample minus the two featurizer history rows; stream s was staged s rows early)
-        auto box_addr = [&](int k, int hb) {
-            const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
-            return sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + hb * RB + s) * ROWB +
-                                     (INTERLEAVED ? 12 : 4) * p);
+        auto box_addr = [&](uint32_t k, int hb) {
+            const uint32_t stg = (2 * k + half) % IN_STAGES;
+            return sm_u + stg * STAGE_BYTES + lane_box + (uint32_t)(hb * RB * ROWB);
         };
         // Volatile loads: they are issued where they stand, one batch ahead of the arithmetic that consumes them, so
         // that their latency (and the wait for the stage before them) overlaps the previous batch's arithmetic.
@@ -298,13 +285,12 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         };
         // featurizer -> k*v head/remainder and q of RB rows, written into the chunk's slot
         auto compute = [&](int slot, int hb, const uint32_t (&raw)[RB + 2][3]) {
-            const uint32_t row0 = (uint32_t)(w * WROWS + hb * RB);
             const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
             // Tiles are 1024-byte aligned, so the swizzle (16-byte chunk index XOR row phase) is one XOR on the address
             // of the lane's element in row 0; row offsets are compile-time immediates of the stores.
-            const uint32_t kv_a0 = slot_u + (kv_chunk << 4) + kv_in + row0 * 128;
+            const uint32_t kv_a0 = slot_u + lane_kv + (uint32_t)(hb * RB * 128);
             const uint32_t qh_a0 = kv_a0 + QH_OFF;
-            const uint32_t qm_a0 = slot_u + QH_OFF + QH_TILE + ((uint32_t)s << 4) + qm_in + row0 * 64;
+            const uint32_t qm_a0 = slot_u + QH_OFF + QH_TILE + lane_qm + (uint32_t)(hb * RB * 64);
             f32x2 x1[3], x2[3];
             unpack(raw[0], x2);
             unpack(raw[1], x1);
@@ -343,20 +329,24 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)(((i >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
             }
         };
-        auto stage_of = [&](int k) { return (2 * k + w / (NFE / 2)) % IN_STAGES; };
-        auto stage_parity = [&](int k) { return (uint32_t)(((2 * k + w / (NFE / 2)) / IN_STAGES) & 1); };
+        auto stage_of = [&](uint32_t k) { return (int)((2 * k + half) % IN_STAGES); };
+        auto stage_parity = [&](uint32_t k) { return ((2 * k + half) / IN_STAGES) & 1u; };
 
         // Software pipeline over register batches A (rows 0..RB-1 of the warp's rows) and B (the rest):
         //   fetch B(k) | wait slot | compute A(k) | release stage | wait stage(k+1), fetch A(k+1) | compute B(k) | publish
         uint32_t rawA[RB + 2][3], rawB[RB + 2][3];
-        bool ok = KO(128) || WARP_WAIT(in_full(stage_of(0)), stage_parity(0), 4);
-        if (ok) fetch(box_addr(0, 0), rawA);
-        for (int k = 0; k < nchunk && ok; ++k) {
-            const int slot = k % 2;
+        uint32_t c_end = (uint32_t)nmine * (uint32_t)nchunk;
+        int kin = 0, t = 0;       // chunk within the item, item
+        if (!WARP_WAIT(in_full(stage_of(cc)), stage_parity(cc), 4)) c_end = cc;     // (gave up: nothing to do)
+        fetch(box_addr(cc, 0), rawA);
+        for (; cc < c_end; ++cc) {
+            const int slot = cc & 1;
+            if (kin == 0) load_w3(item_group(t));       // a new item: its group's featurizer taps
+            if (++kin == nchunk) { kin = 0; ++t; }
             TRACE(0);
-            fetch(box_addr(k, 1), rawB);
-            // slot reuse: the MMAs that read chunk k-2 and the epilogue that read its k*v rows and q tile are done
-            if (k >= 2 && !WARP_WAIT(slot_free(slot), (uint32_t)(((k - 2) / 2) & 1), 2)) break;
+            fetch(box_addr(cc, 1), rawB);
+            // slot reuse: the MMAs that read chunk cc-2 and the epilogue that read its k*v rows and q tile are done
+            if (cc >= 2 && !WARP_WAIT(slot_free(slot), ((cc - 2) >> 1) & 1u, 2)) break;
             TRACE(1);
             compute(slot, 0, rawA);
             // Every row this warp needs from the stage now sits in registers: hand the stage back to the TMA warp (HBM
@@ -365,11 +355,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
             for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(rawB[r][0]), "r"(rawB[r][1]), "r"(rawB[r][2]));
             __syncwarp();
-            if (lane == 0 && !KO(128)) mbar_arrive(in_empty(stage_of(k)));
+            if (lane == 0) mbar_arrive(in_empty(stage_of(cc)));
             TRACE(3);
-            if (k + 1 < nchunk) {
-                if (!KO(128) && !WARP_WAIT(in_full(stage_of(k + 1)), stage_parity(k + 1), 4)) break;
-                fetch(box_addr(k + 1, 0), rawA);
+            if (cc + 1 < c_end) {
+                if (!WARP_WAIT(in_full(stage_of(cc + 1)), stage_parity(cc + 1), 4)) break;
+                fetch(box_addr(cc + 1, 0), rawA);
             }
             TRACE(2);
             compute(slot, 1, rawB);
@@ -384,32 +374,71 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         const int e = warp - W_EP, r = e * 32 + lane;
         // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
         // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
-        __nv_bfloat16* yrow[NS];
-        int nleft[NS];
+        const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
+        // Toeplitz operand of item t -> TMEM buffer t & 1: the group's taps (zero padded: tp[m] = tap at lag m - 128) and
+        // skip parameters go through shared memory, then lane i writes row i of [T^|T].  Runs while the item before
+        // streams; the four epilogue warps meet on a barrier of their own (bounded wait) between the two steps.
+        auto expand = [&](int t) {
+            const int g = item_group(t), ab = t & 1;
+            __nv_bfloat16* tp = reinterpret_cast<__nv_bfloat16*>(smp(OFF_TAPS + ab * 768));
+            for (int m = r; m < 384; m += 128) {
+                const int l = m - 128;
+                float v = 0.f;
+                if (l >= 0 && l < K) v = ld_param(a.h, a.h_dtype, (int64_t)g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
+                tp[m] = __float2bfloat16_rn(v);
+            }
+            if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? ld_param(a.bias, a.bias_dtype, (int64_t)g * CH + r) : 0.f;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(taps_ready(ab));
+            if (!WARP_WAIT(taps_ready(ab), (uint32_t)((t >> 1) & 1), 16)) return false;
+            const uint16_t* tpr = reinterpret_cast<const uint16_t*>(tp);
+            for (int c0 = 0; c0 < 128; c0 += 16) {
+                uint32_t v[16];
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const Stream st = stream_of(a, quad, s);
-            yrow[s] = a.y + st.b * a.y_stride_b + (st.ts + r) * a.y_stride_l + g * CH;
-            nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
-        }
-        const float4* dsk = reinterpret_cast<const float4*>(sm + OFF_DIAG);    // skip parameters D[g*16 .. +16), fp32
+                for (int m = 0; m < 16; ++m) {
+                    const int j = 2 * (c0 + m);                            // columns j, j+1 of [T^|T]: lag = 128 + i - j
+                    const uint32_t e0 = tpr[128 + 128 + r - j], e1 = tpr[128 + 127 + r - j];
+                    v[m] = e1 << 16 | e0;
+                }
+                tmem_st16(tmem + ((uint32_t)(e * 32) << 16) + ab * 128 + c0, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_ready(ab));
+            return true;
+        };
+        bool ok = expand(0);
+        for (int t = 0; t < nmine && ok; ++t) {
+        const int g = item_group(t);
+        const float4* dsk = reinterpret_cast<const float4*>(smp(OFF_DIAG + (t & 1) * 64));    // skip parameters D[g*16 .. +16), fp32
         bool has_skip = false;       // the skip parameter is all zeros at initialisation: then its term is not evaluated
 #pragma unroll
         for (int c = 0; c < CH / 4; ++c) {
             const float4 d = dsk[c];
             has_skip = has_skip || d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f;
         }
-        const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
-        if (lane == 0) mbar_arrive(slot_free(0));      // chunk 0 (the halo chunk) has no epilogue
-        for (int k = 1; k < nchunk; ++k) {
-            const int slot = k % 2;
+        // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
+        // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
+        __nv_bfloat16* yrow[NS];
+        int nleft[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const Stream st = stream_of(a, item_quad(t), s);
+            yrow[s] = a.y + st.b * a.y_stride_b + (st.ts + r) * a.y_stride_l + (int64_t)g * CH;
+            nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
+        }
+        if (lane == 0) mbar_arrive(slot_free(cc & 1));      // the item's halo chunk has no epilogue
+        ++cc;
+        for (int k = 1; k < nchunk; ++k, ++cc, ++oc) {
+            const int slot = cc & 1, dbuf = oc & 1;
             TRACE(10);
-            if (!WARP_WAIT(d_full(slot), (uint32_t)(((k - 1) / 2) & 1), 5)) break;
+            if (!WARP_WAIT(d_full(dbuf), (oc >> 1) & 1u, 5)) { ok = false; break; }
             TRACE(11);
             tc_fence_after();
             __syncwarp();
-            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + 128 + slot * 128;
-            const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
+            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + D_COL + dbuf * 128;
+            const uint8_t* slot_p = smp(OFF_SLOTS + slot * SLOT_BYTES);
             const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
             const uint8_t* qm_p = qh_p + QH_TILE - r * 64;
             const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
@@ -442,7 +471,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     // every accumulator of this chunk has left TMEM: hand the buffer back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(d_empty(slot));
+                    if (lane == 0) mbar_arrive(d_empty(dbuf));
                     TRACE(12);
                 }
                 // this stream's output pointer and row count (selects, not indexed arrays: the loop may be rolled)
@@ -508,13 +537,15 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_free(slot));
             TRACE(13);
+            if (k == 1 && t + 1 < nmine && !expand(t + 1)) { ok = false; break; }
+        }
         }
     } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
         if (lane == 0) {
             const uint32_t idesc = instr_desc(128, 2 * NS * CH, 1);
-            // Chunk k accumulates into D[k%2]:  prev(k) = T^ * kv(k-1)  and  cur(k) = T * kv(k) (+ skip).
-            // prev(k+1) is issued right behind cur(k), long before chunk k+1 is staged, so the tile of chunk k
+            // An output chunk accumulates  prev = T^ * kv(chunk before)  and  cur = T * kv(chunk)  into one buffer.
+            // The prev half of the NEXT chunk is issued right behind cur, long before that chunk is staged, so a tile
             // is released (slot_free) one whole chunk before the front end needs its slot again.
             // Descriptors are built once; a K step of 16 rows moves the start-address field by 2048 B (128 units).
             // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
@@ -524,88 +555,102 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             uint64_t kv_desc[2];
 #pragma unroll
             for (int sl = 0; sl < 2; ++sl) kv_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES + HI_OFF, KV_TILE, 1024, 2);
-            auto issue_half = [&](int k, bool cur) {
-                const int slot = cur ? k % 2 : (k - 1) % 2;
-                const uint32_t d = tmem + 128 + (k % 2) * 128;
-                const uint32_t a0 = tmem + (cur ? 64 : 0);
+            // one half of a chunk's contraction: T^ (cur == false) or T (cur == true) times the k*v tile in `slot`,
+            // accumulated into buffer `dbuf`; the previous-chunk half comes first and overwrites the accumulator
+            auto issue_half = [&](int abuf, int slot, int dbuf, bool cur) {
+                const uint32_t d = tmem + D_COL + dbuf * 128;
+                const uint32_t a0 = tmem + abuf * 128 + (cur ? 64 : 0);
                 const uint64_t dk = slot ? kv_desc[1] : kv_desc[0];
                 const int nj = KO(64) ? 0 : KO(8) ? 1 : 8;
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
                     if (jj >= nj) continue;
-                    // the first MMA of a chunk (K step 0 of the previous-chunk part) overwrites the accumulator
                     mma_ts(d, a0 + 8 * jj, dk + (uint64_t)(jj * (16 * 128 / 16)), idesc, (cur || jj > 0) ? 1u : 0u);
                 }
             };
-            bool ok = MBAR_WAIT(a_ready, 0, 10) && MBAR_WAIT(kv_full(0), 0, 7);          // the Toeplitz operand; the halo chunk
-            if (ok && nchunk > 1) {
-                tc_fence_after();
-                issue_half(1, false);
-                mma_commit(slot_free(0));
-            }
-            for (int k = 1; k < nchunk && ok; ++k) {
-                TRACE(20);
-                if (!MBAR_WAIT(kv_full(k % 2), (uint32_t)((k / 2) & 1), 6)) break;
-                TRACE(21);
-                tc_fence_after();
-                issue_half(k, true);
-                mma_commit(d_full(k % 2));
-                TRACE(22);
-                if (k + 1 < nchunk) {
-                    // D[(k+1)%2] was last read by the epilogue of chunk k-1
-                    if (k + 1 >= 3 && !MBAR_WAIT(d_empty((k + 1) % 2), (uint32_t)(((k - 2) / 2) & 1), 8)) break;
-                    TRACE(23);
+            bool ok = true;
+            for (int t = 0; t < nmine && ok; ++t) {
+                const int ab = t & 1;
+                // the item's Toeplitz operand (expanded by the epilogue warps while the item before was streaming)
+                if (!MBAR_WAIT(a_ready(ab), (uint32_t)((t >> 1) & 1), 10)) { ok = false; break; }
+                // halo chunk of the item: its tile only feeds the previous-chunk half of the first output chunk
+                if (!MBAR_WAIT(kv_full(cc & 1), (cc >> 1) & 1u, 7)) { ok = false; break; }
+                if (nchunk > 1) {
+                    // the accumulator of output chunk oc was last read by the epilogue of output chunk oc - 2
+                    if (oc >= 2 && !MBAR_WAIT(d_empty(oc & 1), ((oc - 2) >> 1) & 1u, 8)) { ok = false; break; }
                     tc_fence_after();
-                    issue_half(k + 1, false);
+                    issue_half(ab, cc & 1, oc & 1, false);
                 }
-                mma_commit(slot_free(k % 2));
-                TRACE(24);
+                mma_commit(slot_free(cc & 1));
+                ++cc;
+                for (int k = 1; k < nchunk; ++k, ++cc, ++oc) {
+                    TRACE(20);
+                    if (!MBAR_WAIT(kv_full(cc & 1), (cc >> 1) & 1u, 6)) { ok = false; break; }
+                    TRACE(21);
+                    tc_fence_after();
+                    issue_half(ab, cc & 1, oc & 1, true);
+                    mma_commit(d_full(oc & 1));
+                    TRACE(22);
+                    if (k + 1 < nchunk) {
+                        // the next output chunk's accumulator was last read by the epilogue of output chunk oc - 1
+                        if (oc >= 1 && !MBAR_WAIT(d_empty((oc + 1) & 1), ((oc - 1) >> 1) & 1u, 8)) { ok = false; break; }
+                        TRACE(23);
+                        tc_fence_after();
+                        issue_half(ab, cc & 1, (oc + 1) & 1, false);
+                    }
+                    mma_commit(slot_free(cc & 1));
+                    TRACE(24);
+                }
             }
         }
     } else if (warp < W_TMA + NTMA) {
-        // first packed column of this group's q | k | v data (one contiguous run when interleaved)
-        int row_base[NS], bidx[NS];      // first staged row of chunk 0 (the halo chunk) and batch index, per stream
-        int col[3] = {0, 0, 0};
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const Stream st = stream_of(a, quad, s);
-            row_base[s] = (int)st.ts - CHUNK - 2 - s;
-            bidx[s] = (int)st.b;
-        }
-        if (INTERLEAVED) {
-            col[0] = (int)(3 * g * CH);
-        } else {
-            const int64_t d0 = g * CH;
-            if (a.layout == VTX_QKV_COLUMN_SPLIT) {
-                int64_t n = d0 / a.hd, j = d0 - n * a.hd;
-                col[0] = (int)(n * 3 * a.hd + j); col[1] = col[0] + (int)a.hd; col[2] = col[0] + 2 * (int)a.hd;
-            } else {
-                col[0] = (int)d0; col[1] = (int)(a.D + d0); col[2] = (int)(2 * a.D + d0);
-            }
-            if (a.flip) { int t = col[0]; col[0] = col[1]; col[1] = t; }
-        }
         const int tw = warp - W_TMA;                 // this warp issues the boxes of streams tw, tw + NTMA, ...
         if (lane == 0) {
             // ======== TMA issue ======================================================================
             tma_prefetch_desc(&tmap);
-            for (int nh = 0; nh < 2 * nchunk; ++nh) {
-                if (KO(128)) break;
-                const int stg = nh % IN_STAGES, k = nh / 2, h = nh % 2;
-                if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), (uint32_t)(((nh - IN_STAGES) / IN_STAGES) & 1), 9)) break;
-                TRACE(30);
-                const uint32_t bar = in_full(stg);
-                mbar_expect_tx(bar, NS / NTMA * BOX_BYTES);
+            uint32_t nh = 2 * cc;                    // staged half chunks so far
+            bool ok = true;
+            for (int t = 0; t < nmine && ok; ++t) {
+                // first packed column of the item's group in q | k | v (one contiguous run when interleaved)
+                const int g = item_group(t);
+                int col[3] = {0, 0, 0};
+                if (INTERLEAVED) {
+                    col[0] = 3 * g * CH;
+                } else {
+                    const int64_t d0 = (int64_t)g * CH;
+                    if (a.layout == VTX_QKV_COLUMN_SPLIT) {
+                        int64_t n = d0 / a.hd, j = d0 - n * a.hd;
+                        col[0] = (int)(n * 3 * a.hd + j); col[1] = col[0] + (int)a.hd; col[2] = col[0] + 2 * (int)a.hd;
+                    } else {
+                        col[0] = (int)d0; col[1] = (int)(a.D + d0); col[2] = (int)(2 * a.D + d0);
+                    }
+                    if (a.flip) { int tt = col[0]; col[0] = col[1]; col[1] = tt; }
+                }
+                int row_base[NS], bidx[NS];          // first staged row of the item's halo chunk and batch index, per stream
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
-                    if (s % NTMA != tw) continue;
-                    const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
-                    const int row = row_base[s] + k * CHUNK + h * HROWS;
-                    if (INTERLEAVED) {
-                        tma_load_3d(dst, &tmap, bar, col[0], row, bidx[s]);
-                    } else {
+                    const Stream st = stream_of(a, item_quad(t), s);
+                    row_base[s] = (int)st.ts - CHUNK - 2 - s;
+                    bidx[s] = (int)st.b;
+                }
+                for (int hh = 0; hh < 2 * nchunk; ++hh, ++nh) {
+                    const int stg = (int)(nh % IN_STAGES), k = hh / 2, h = hh % 2;
+                    if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), ((nh - IN_STAGES) / IN_STAGES) & 1u, 9)) { ok = false; break; }
+                    TRACE(30);
+                    const uint32_t bar = in_full(stg);
+                    mbar_expect_tx(bar, NS / NTMA * BOX_BYTES);
 #pragma unroll
-                        for (int pl = 0; pl < 3; ++pl)
-                            tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, col[pl], row, bidx[s]);
+                    for (int s = 0; s < NS; ++s) {
+                        if (s % NTMA != tw) continue;
+                        const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
+                        const int row = row_base[s] + k * CHUNK + h * HROWS;
+                        if (INTERLEAVED) {
+                            tma_load_3d(dst, &tmap, bar, col[0], row, bidx[s]);
+                        } else {
+#pragma unroll
+                            for (int pl = 0; pl < 3; ++pl)
+                                tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, col[pl], row, bidx[s]);
+                        }
                     }
                 }
             }
@@ -617,6 +662,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     __syncthreads();
     if (warp == W_MMA) {
         __syncwarp();
+        uint32_t tmem;
+        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(sm_u + OFF_TSLOT) : "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
     }
 }
@@ -664,6 +711,8 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     a.nstream = p->B * a.nseg;
     const int64_t nquad = ceil_div<int64_t>(a.nstream, NS);
     VTX_REQUIRE(p->G * nquad < (int64_t)1 << 31, VTX_ERR_UNSUPPORTED, "fused_fir: too many work items");
+    a.nquad = nquad;
+    a.nitems = p->G * nquad;
 
     const bool inter = p->layout == VTX_QKV_INTERLEAVED;
     CUtensorMap tmap;
@@ -681,7 +730,20 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
         if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev][variant] = true;
     }
-    kern<<<(unsigned)(p->G * nquad), THREADS, SMEM_BYTES, stream>>>(tmap, a);
+    // one persistent CTA per SM that can hold one (the shared-memory footprint allows no more), each with a contiguous
+    // range of items.  The CTA count must not exceed what is resident at once: a second round would double the time.
+    static int resident[64][3] = {};
+    int nres = (dev >= 0 && dev < 64) ? resident[dev][variant] : 0;
+    if (nres == 0) {
+        int sms = 0, per_sm = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, SMEM_BYTES);
+        nres = sms * per_sm;
+        if (nres <= 0) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): the kernel does not fit an SM (%d SMs, %d blocks each)", sms, per_sm);
+        if (dev >= 0 && dev < 64) resident[dev][variant] = nres;
+    }
+    const int64_t ncta = a.nitems < nres ? a.nitems : nres;
+    kern<<<(unsigned)ncta, THREADS, SMEM_BYTES, stream>>>(tmap, a);
     if (int rc = check_launch("fused_fir(mr)")) return rc;
     if (p->fir_state || p->inner_state) return launch_fused_state_bf16(p, stream);
     return VTX_OK;
