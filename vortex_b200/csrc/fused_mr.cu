@@ -80,7 +80,9 @@ constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
 constexpr int OFF_SLOTS = SMEM_IN;
 constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
 constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
-constexpr int OFF_BARS = OFF_TAPS + TAPS_BYTES;
+constexpr int W3S_BYTES = 3 * 3 * CH * 4;   // featurizer taps of a group as fp32 [q|k|v][tap][channel]; two buffers
+constexpr int OFF_W3S = OFF_TAPS + TAPS_BYTES;
+constexpr int OFF_BARS = OFF_W3S + 2 * W3S_BYTES;
 constexpr int NBARS = IN_STAGES * 2 + 2 * 6;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty, a_ready, taps_ready x2
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 48 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -233,16 +235,17 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         // (item-agnostic: the rows arrive staged; only the featurizer taps depend on the group)
         const int w = warp, p = lane % 8, s = lane / 8;
         f32x2 w3[3][3];     // [q|k|v][tap], each the pair of this lane's two channels (of the current item's group)
-        auto load_w3 = [&](int g) {
-            QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
-            int64_t pc[2][3];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) map.get((int64_t)g * CH + 2 * p + c, pc[c][0], pc[c][1], pc[c][2]);
+        // featurizer taps of item t: staged in shared memory by the epilogue warps together with the item's Toeplitz
+        // operand (a_ready); [feature][tap][channel] fp32, this lane's two channels as one 8-byte load
+        auto load_w3 = [&](int t) {
+            if (!WARP_WAIT(a_ready(t & 1), (uint32_t)((t >> 1) & 1), 17)) return false;
+            const uint32_t base = sm_u + OFF_W3S + (uint32_t)((t & 1) * W3S_BYTES) + 8u * (uint32_t)p;
 #pragma unroll
             for (int x = 0; x < 3; ++x)
 #pragma unroll
                 for (int j = 0; j < 3; ++j)
-                    w3[x][j] = pk2(ld_param(a.w3, a.w3_dtype, pc[0][x] * 3 + j), ld_param(a.w3, a.w3_dtype, pc[1][x] * 3 + j));
+                    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(w3[x][j]) : "r"(base + (uint32_t)((x * 3 + j) * CH * 4)));
+            return true;
         };
         // lane constants folded into three offsets: the lane's first staged word of a half chunk, its bf16 pair in row
         // 16 w of a k*v tile (16-byte chunk 2 s + p / 4, bytes 4 (p % 4)), its two third-bytes in row 16 w of a q tile
@@ -341,7 +344,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         fetch(box_addr(cc, 0), rawA);
         for (; cc < c_end; ++cc) {
             const int slot = cc & 1;
-            if (kin == 0) load_w3(item_group(t));       // a new item: its group's featurizer taps
+            if (kin == 0 && !load_w3(t)) break;         // a new item: its group's featurizer taps
             if (++kin == nchunk) { kin = 0; ++t; }
             TRACE(0);
             fetch(box_addr(cc, 1), rawB);
@@ -388,6 +391,16 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 tp[m] = __float2bfloat16_rn(v);
             }
             if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? ld_param(a.bias, a.bias_dtype, (int64_t)g * CH + r) : 0.f;
+            {   // featurizer taps of the group's 16 channels (the front end picks them up at the item's first chunk)
+                QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
+                float* w3s = reinterpret_cast<float*>(smp(OFF_W3S + ab * W3S_BYTES));
+                for (int m = r; m < 3 * 3 * CH; m += 128) {
+                    const int c = m % CH, j = (m / CH) % 3, x = m / (3 * CH);
+                    int64_t pc[3];
+                    map.get((int64_t)g * CH + c, pc[0], pc[1], pc[2]);
+                    w3s[m] = ld_param(a.w3, a.w3_dtype, pc[x] * 3 + j);
+                }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(taps_ready(ab));
             if (!WARP_WAIT(taps_ready(ab), (uint32_t)((t >> 1) & 1), 16)) return false;
