@@ -387,7 +387,7 @@ def main():
 LAUNCHES = {"mr": 1, "se": 1, "li": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
-NCU_TRAFFIC = {"mr": 1.013e9, "se": 1.017e9, "li": 4.14e9}   # small-case captures scaled by the units of a bench launch
+NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9}   # small-case captures scaled by the units of a bench launch
 
 if __name__ == "__main__":
     main()
