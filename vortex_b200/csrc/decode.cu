@@ -291,19 +291,46 @@ __global__ void __launch_bounds__(256) decode_fir7_kernel(vtx_decode_layer_param
     for (int j = 0; j < 6; ++j) sout4[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
 }
 
-// Modal layer, RW rows per half-warp (lane = pole).
+// Modal layer, RW rows per half-warp (lane = pole).  A block of 16 half-warps covers GPB channel groups of BPB batch
+// elements; the groups' pole and residue parameters (expf, sincosf) are evaluated once per block into shared memory
+// instead of once per tile.
 template <typename T, int RW, bool CPLX>
-__global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_params p) {
-    const int lane = threadIdx.x % 16;
+__global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_params p, int tiles_per_group, int gpb) {
+    __shared__ float4 prm[16][16];                // [group of the block][pole]: p_re, p_im, R_re, R_im
+    const int lane = threadIdx.x % 16, hw = threadIdx.x / 16;
     const unsigned mask = 0xffffu << (threadIdx.x % 32 - lane);
-    const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 16;
-    const int64_t row0 = tile * RW;
-    if (row0 >= p.B * p.D) return;        // whole half-warps leave together
-    const int64_t b = row0 / p.D, d0 = row0 % p.D;
+    const int S = (int)p.modal.S;
+    const int64_t cpg = p.D / p.modal.G;
+    // block -> (batch slab, first group): blockIdx.x = slab * (G / gpb) + group block
+    const int64_t gblocks = p.modal.G / gpb, g0 = (blockIdx.x % gblocks) * gpb, slab = blockIdx.x / gblocks;
+    for (int i = threadIdx.x; i < gpb * 16; i += blockDim.x) {
+        const int gl = i / 16, sp = i % 16;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sp < S) {
+            const int64_t gi = (g0 + gl) * S + sp;
+            const float mag = expf(static_cast<const float*>(p.modal.log_poles)[gi]);
+            v.z = static_cast<const float*>(p.modal.res_re)[gi];
+            if (CPLX) {
+                float sn, cs;
+                sincosf(static_cast<const float*>(p.modal.theta)[gi], &sn, &cs);
+                v.x = mag * cs; v.y = mag * sn;
+                v.w = p.modal.res_im ? static_cast<const float*>(p.modal.res_im)[gi] : 0.f;
+            } else {
+                v.x = mag;
+            }
+        }
+        prm[gl][sp] = v;
+    }
+    __syncthreads();
+    // half-warp hw -> tile: group gl = (hw / tiles_per_group) % gpb, tile within the group, batch element within the slab
+    const int tpb = gpb * tiles_per_group;            // tiles of one batch element in this block
+    const int gl = (hw % tpb) / tiles_per_group, tg = hw % tiles_per_group;
+    const int64_t b = slab * (16 / tpb) + hw / tpb;
+    if (b >= p.B) return;
+    const int64_t d0 = (g0 + gl) * cpg + (int64_t)tg * RW, row0 = b * p.D + d0;
     float q_own = 0.f, kv_own = 0.f;
     if (lane < RW) featurizer_step3<T>(p, b, d0 + lane, q_own, kv_own);
-    const int S = (int)p.modal.S;
-    const int64_t cpg = p.D / p.modal.G, ss = S * (CPLX ? 2 : 1);
+    const int64_t ss = S * (CPLX ? 2 : 1);
     const float* st_in = p.iir_state_in + row0 * ss;
     float* st_out = p.iir_state_out + row0 * ss;
     float2 s[RW];
@@ -315,28 +342,11 @@ __global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_p
             else s[r].x = st_in[r * ss + lane];
         }
     }
-    float pr = 0.f, pi = 0.f, rr = 0.f, ri = 0.f;
-    int64_t g_have = -1;
+    const float4 pm = prm[gl][lane];
+    const float pr = pm.x, pi = pm.y, rr = pm.z, ri = pm.w;
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
-        const int64_t d = d0 + r, g = d / cpg;
-        if (g != g_have) {
-            g_have = g;
-            pr = pi = rr = ri = 0.f;
-            if (lane < S) {
-                const int64_t gi = g * S + lane;
-                const float mag = expf(static_cast<const float*>(p.modal.log_poles)[gi]);
-                rr = static_cast<const float*>(p.modal.res_re)[gi];
-                if (CPLX) {
-                    float sn, cs;
-                    sincosf(static_cast<const float*>(p.modal.theta)[gi], &sn, &cs);
-                    pr = mag * cs; pi = mag * sn;
-                    ri = p.modal.res_im ? static_cast<const float*>(p.modal.res_im)[gi] : 0.f;
-                } else {
-                    pr = mag;
-                }
-            }
-        }
+        const int64_t d = d0 + r;
         const float kv = __shfl_sync(mask, kv_own, r, 16), q = __shfl_sync(mask, q_own, r, 16);
         float part = 0.f;
         if (lane < S) {
@@ -435,12 +445,22 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
         VTX_REQUIRE(p->modal.log_poles && p->modal.res_re && p->modal.G > 0 && p->modal.S > 0 && p->modal.S <= 16 &&
                         p->D % p->modal.G == 0 && p->iir_state_in && p->iir_state_out,
                     VTX_ERR_BAD_ARG, "decode_layer: bad modal arguments");
-        const bool tiled = p->K3 == 3 && p->D % 8 == 0 && p->fir_state_dtype == VTX_F32;
+        // tiled kernel: channel groups that are whole tiles of 8 (1, 2, 4, 8 or 16 tiles per block of 16 half-warps)
+        const int64_t cpg = p->D / p->modal.G;
+        const int64_t tpg = cpg / 8;                    // tiles per group
+        const bool tiled = p->K3 == 3 && p->fir_state_dtype == VTX_F32 && cpg % 8 == 0 && (tpg == 1 || tpg == 2 || tpg == 4 || tpg == 8 || tpg == 16);
         const bool cplx = p->modal.theta != nullptr;
         VTX_DISPATCH_IO(p->io_dtype, T, {
-            if (tiled && cplx) decode_iir_tile_kernel<T, 8, true><<<(unsigned)ceil_div<int64_t>(rows / 8 * 16, 256), 256, 0, s>>>(*p);
-            else if (tiled) decode_iir_tile_kernel<T, 8, false><<<(unsigned)ceil_div<int64_t>(rows / 8 * 16, 256), 256, 0, s>>>(*p);
-            else decode_layer_kernel<T, 16, 1><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, s>>>(*p);
+            if (tiled) {
+                // a block = 16 tiles of one group: 16 / tpg batch elements share one evaluation of the group's poles
+                const int gpb = 1;
+                const int64_t bpb = 16 / (gpb * tpg);
+                const int64_t nblk = (p->modal.G / gpb) * ceil_div<int64_t>(p->B, bpb);
+                if (cplx) decode_iir_tile_kernel<T, 8, true><<<(unsigned)nblk, 256, 0, s>>>(*p, (int)tpg, gpb);
+                else decode_iir_tile_kernel<T, 8, false><<<(unsigned)nblk, 256, 0, s>>>(*p, (int)tpg, gpb);
+            } else {
+                decode_layer_kernel<T, 16, 1><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, s>>>(*p);
+            }
         });
     }
     return check_launch("decode_layer");
