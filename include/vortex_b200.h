@@ -136,8 +136,9 @@ int vtx_gcg_fwd(const vtx_gcg_params* p, void* stream);
  * (vortex/model/layers.py:18-21).
  *   u [B,L,3D] -> y [B,L,D]; fir_state [B,3D,min(L,K3-1)];
  *   inner_state [B,D,min(L,K-1)]  (both channel-first, as the caches are)
- * K <= 16 runs on CUDA cores with TMA-staged rows (any io dtype);
- * K == 128 with bf16 io runs as a blocked-Toeplitz contraction on tcgen05.
+ * bf16 io with groups of 16 channels and K <= 128 runs as a blocked-Toeplitz contraction on tcgen05
+ * (persistent CTAs, Toeplitz operand in TMEM); other dtypes / group sizes with K <= 16 run on CUDA cores
+ * with TMA-staged rows.
  * The base address and the row pitch of u and y must be 16-byte aligned.
  * ------------------------------------------------------------------------ */
 typedef struct vtx_fused_fir_params {
