@@ -274,8 +274,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
             // Tiles are 1024-byte aligned: the swizzle (16-byte chunk index XOR row phase) is an XOR on the address of the
             // lane's element; the row phase is (row & 7) for the 128-byte rows and ((row >> 1) & 3) for the 64-byte rows.
-            const uint32_t kv_a0 = slot_u + (kv_chunk << 4) + kv_in + row0 * 128;
-            const uint32_t qm_a0 = slot_u + QM_OFF + ((uint32_t)s << 4) + qm_in + row0 * 64;
+            // row = 12 w + 6 hb + i, and adding 4 (mod 8) or 2 (mod 4) is an XOR: the warp's part of the phase,
+            // 4 (w & 1) resp. 2 (w & 1), is folded into the lane's chunk index once, the rest, (6 hb + i) & 7 resp.
+            // ((6 hb + i) >> 1) & 3, is a compile-time constant of each store.
+            const uint32_t kv_a0 = slot_u + ((kv_chunk ^ (uint32_t)((w & 1) * 4)) << 4) + kv_in + row0 * 128;
+            const uint32_t qm_a0 = slot_u + QM_OFF + (((uint32_t)s ^ (uint32_t)((w & 1) * 2)) << 4) + qm_in + row0 * 64;
             f32x2 x1[3], x2[3];
             unpack(raw[0], x2);
             unpack(raw[1], x1);
@@ -297,8 +300,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 float r0, r1;
                 up2(sub2(kv, pk2(bf_lo(hi), bf_hi(hi))), r0, r1);
                 const uint32_t lo = pack_bf16(r0, r1);
-                const uint32_t row = row0 + i;
-                const uint32_t kaddr = (kv_a0 ^ ((row & 7u) << 4)) + i * 128;
+                const uint32_t kaddr = (kv_a0 ^ (uint32_t)(((RB * hb + i) & 7) << 4)) + i * 128;
                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + HI_OFF), "r"(hi));
                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + LO_OFF), "r"(lo));
                 float q0, q1;
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 const uint32_t qh = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x7632);   // upper halves
                 const uint32_t qm = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5151);   // third bytes
                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + QH_OFF), "r"(qh));
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (((row >> 1) & 3u) << 4)) + i * 64), "h"((unsigned short)qm));
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)((((RB * hb + i) >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
             }
         };
         auto stage_of = [&](int k) { return (2 * k + w / (NFE / 2)) % IN_STAGES; };
