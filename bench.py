@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the Hyena convolution hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload mr|se|li|decode]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload mr|se|li|decode_mr|decode_se|decode_li|decode_stack]
 
 Default workload: Hyena-MR grouped causal FIR prefill, B=4, L=8192, D=4096, bf16 I/O with fp32
 accumulation, 128-tap filters shared by groups of 16 channels, featurizer and gates fused
@@ -44,6 +45,11 @@ WORKLOADS = {
                       name="hyena_se_decode B=64 D=4096 bf16 (one layer, one token: featurizer + 7-tap FIR caches)"),
     "decode_li": dict(B=64, L=1, D=4096, G=256, K=0, io="bf16", seed=3, decode=True,
                       name="hyena_li_decode B=64 D=4096 bf16 (one layer, one token: featurizer cache + 16 complex modal states)"),
+    # one token through the 27 Hyena layers of an Evo 2 7B-shaped stack (9 SE, 9 MR, 9 LI; the 5 attention layers, the
+    # projections and the MLPs are not part of the path): 27 launches per step, every layer with caches of its own
+    "decode_stack": dict(B=64, L=1, D=4096, G=256, K=-1, io="bf16", seed=3, decode=True, stack=True,
+                         name="hyena_decode_stack B=64 D=4096 bf16 (one token through 9 SE + 9 MR + 9 LI layers, "
+                              "reference cache layout: fp32 caches, 16 real modal states per channel)"),
 }
 
 
@@ -60,10 +66,14 @@ def make_inputs(w, device, dtype=torch.bfloat16):
     g = torch.Generator().manual_seed(w["seed"])
     B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
     p = {}
+    if w.get("stack"):
+        return make_stack(w, g, dtype)
     # generated in slices to bound host memory; values ~ N(0, 1)
     p["u"] = torch.empty(B, L, 3 * D, dtype=dtype)
     for b in range(B):
-        p["u"][b] = torch.randn(L, 3 * D, generator=g).to(dtype)
+        for t0 in range(0, L, 65536):
+            t1 = min(L, t0 + 65536)
+            p["u"][b, t0:t1] = torch.randn(t1 - t0, 3 * D, generator=g).to(dtype)
     p["w3"] = (torch.randn(3 * D, 1, 3, generator=g) / 3 ** 0.5).to(dtype)
     if K > 0:
         wt = torch.randn(G, 1, K, generator=g) / K ** 0.5
@@ -96,9 +106,39 @@ def make_inputs(w, device, dtype=torch.bfloat16):
     return p
 
 
+# layer kinds of the 27 Hyena layers in the order of the 7B block pattern (short, medium, long; attention left out)
+STACK_KINDS = ["se", "mr", "li"] * 9
+
+
+def make_stack(w, g, dtype):
+    """Parameters and caches of the Hyena layers of an Evo 2 7B-shaped stack, as a decode step finds them."""
+    B, D, G = w["B"], w["D"], w["G"]
+    p = {"u": torch.randn(B, 1, 3 * D, generator=g).to(dtype), "D": D, "layers": []}
+    for kind in STACK_KINDS:
+        c = {"kind": kind, "w3": (torch.randn(3 * D, 1, 3, generator=g) / 3 ** 0.5).to(dtype),
+             "fir_state": torch.randn(B, 3 * D, 2, generator=g)}
+        if kind == "li":
+            # the reference's live form: real poles and residues per channel, state [B, D, 16] fp32
+            c["log_poles"] = torch.log(0.9 + 0.099 * torch.rand(D, 16, generator=g))[..., None]
+            c["residues"] = torch.randn(D, 16, generator=g)
+            c["Dp"] = torch.randn(D, generator=g).to(dtype)
+            c["iir_state"] = torch.randn(B, D, 16, generator=g)
+        else:
+            K = 7 if kind == "se" else 128
+            wt = torch.randn(G, 1, K, generator=g) / K ** 0.5
+            c["h"] = wt.to(dtype)
+            c["Dp"] = torch.zeros(D, dtype=dtype) if kind == "mr" else None
+            c["inner_state"] = torch.randn(B, D, K - 1, generator=g)
+        p["layers"].append(c)
+    return p
+
+
 def decode_bytes(w):
     """Algorithmic HBM bytes of one decode launch: every cache element read and written once, plus the token."""
     B, D, K = w["B"], w["D"], w["K"]
+    if w.get("stack"):
+        per = {"se": B * D * 6 * 4, "mr": B * D * 127 * 4, "li": B * D * 16 * 4}
+        return sum(2 * (B * 3 * D * 2 * 4 + per[k]) + B * 3 * D * 2 + B * D * 2 for k in STACK_KINDS)
     cache = B * 3 * D * 2 * 4 + (B * D * (K - 1) * 4 if K > 0 else B * D * 16 * 2 * 4)
     return 2 * cache + B * 3 * D * 2 + B * D * 2
 
@@ -107,6 +147,16 @@ def run_block(name, pc, u=None):
     """One step through the public API; returns y [B, L, D]."""
     from vortex_b200 import hyena_ops, ops
     u = pc["u"] if u is None else u
+    if name == "decode_stack":
+        un = u[:, 0]
+        for c in pc["layers"]:
+            if c["kind"] == "li":
+                y = ops.decode_layer(un, c["w3"], None, c["fir_state"], pc["D"], log_poles=c["log_poles"],
+                                     residues=c["residues"], iir_state=c["iir_state"], bias=c["Dp"])[0]
+            else:
+                y = ops.decode_layer(un, c["w3"], None, c["fir_state"], pc["D"], h=c["h"], inner_state=c["inner_state"],
+                                     bias=c["Dp"], flip_filter=c["kind"] == "mr", gated_bias=c["kind"] == "mr")[0]
+        return y
     if name.startswith("decode"):
         un = u[:, 0]
         c = pc["sets"][pc["turn"][0] % len(pc["sets"])]
@@ -215,6 +265,7 @@ def main():
     ap.add_argument("--workload", default="mr", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small cases for profiling)")
     ap.add_argument("--seq", type=int, default=0, help="override the sequence length (small cases for profiling)")
+    ap.add_argument("--channels", type=int, default=0, help="override the hidden channels (the shard of one GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args()
@@ -226,13 +277,22 @@ def main():
     if a.seq > 0:
         w["L"] = a.seq
         w["name"] += f" [sequence length overridden to {a.seq}]"
+    if a.channels > 0:
+        w["G"] = max(1, w["G"] * a.channels // w["D"])
+        w["D"] = a.channels
+        w["name"] += f" [hidden channels overridden to {a.channels}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     tokens = w["B"] * w["L"]
+    step_bytes = decode_bytes(w) if w.get("decode") else 8 * w["B"] * w["D"] * w["L"]
     config = {"workload": w["name"], "seed": w["seed"], "qkv_layout": "interleaved",
-              "sharding": f"channel: each of {world} rank(s) owns {w['D']} hidden channels, no collective",
-              "l2": "inputs (805 MB per step at the default workload) are larger than the 126 MB L2"}
+              "sharding": (f"batch: each of {world} rank(s) owns {w['B']} sequences, no collective" if w.get("decode") else
+                           f"channel: each of {world} rank(s) owns {w['D']} hidden channels, no collective"),
+              "l2": (f"{step_bytes / 1e6:.0f} MB of caches and tokens per step" +
+                     (", caches rotate over sets larger than L2" if w.get("decode") and not w.get("stack") else "")
+                     if w.get("decode") else
+                     f"inputs and outputs ({step_bytes / 1e6:.0f} MB per step) are larger than the 126 MB L2")}
 
     if a.impl == "reference":
         if rank != 0:
@@ -264,8 +324,9 @@ def main():
 
     p = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), dev)
     pc = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
-    if "sets" in pc:
-        pc["sets"] = [{k: v.to(dev) for k, v in c.items()} for c in pc["sets"]]
+    for key in ("sets", "layers"):
+        if key in pc:
+            pc[key] = [{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in c.items()} for c in pc[key]]
     from vortex_b200 import ops
 
     for _ in range(a.warmup):
@@ -384,7 +445,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload (no cache outputs requested)
-LAUNCHES = {"mr": 1, "se": 1, "li": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1}
+LAUNCHES = {"mr": 1, "se": 1, "li": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9}   # small-case captures scaled by the units of a bench launch

@@ -212,30 +212,43 @@ int vtx_iir_fwd(const vtx_iir_params* p, void* stream);
 #define VTX_IIR_STATIC_SCRATCH_BYTES (16u << 20)
 int vtx_iir_fwd_noalloc(const vtx_iir_params* p, void* stream);
 
-/* Fused Hyena-LI block on the projection output, channel-last in and out (bf16 I/O, groups of 16 channels
- * sharing one modal system of up to 16 poles): featurizer (3 taps) -> q/k/v selection -> k*v -> modal long
- * convolution -> (+ bias*kv) -> q gate in ONE pass over HBM, as a chunked state-space scan whose Toeplitz,
- * state-input and state-update contractions run on tcgen05 tensor cores.  Fuses model.py:233-316
- * (HyenaCascade.parallel_forward for a long-filter layer: featurizer parallel_fir + parallel_iir with its FFT
- * branch, engine.py:262-353) -- the hyena_li_fwd entry point the reference imports but never defines
- * (vortex/model/layers.py:18-21).
+/* Fused Hyena-LI block on the projection output, channel-last in and out: featurizer (3 taps) -> q/k/v
+ * selection -> k*v -> modal long convolution -> (+ bias*kv) -> q gate in ONE pass over the rows (no [B,3D,L]
+ * intermediate).  Fuses model.py:233-316 (HyenaCascade.parallel_forward for a long-filter layer: featurizer
+ * parallel_fir + parallel_iir with its FFT branch, engine.py:262-353, and the end state of
+ * prefill_via_modal_fft, engine.py:525-559) -- the hyena_li_fwd entry point the reference imports but never
+ * defines (vortex/model/layers.py:18-21).  Two kernels, chosen by shape:
+ *   - bf16 I/O, modal systems of up to 16 poles shared by groups of 16 channels (G * 16 == D), no featurizer
+ *     bias, no carried-in state: a chunked state-space scan whose Toeplitz, state-input and state-update
+ *     contractions run on tcgen05 tensor cores;
+ *   - everything else (a modal system per channel as in Evo 2, configs/evo2-7b-8k.yml:11, any G dividing D,
+ *     fp32 / fp16 / bf16 I/O, featurizer bias, a call that continues an earlier one): the recurrence itself on
+ *     the fp32 pipe, time segments with a carry scan.
  *   u [B,L,3D] -> y [B,L,D]; state fp32 [B,D,S] (real poles) or [B,D,S,2] (complex) after the last token, or NULL.
+ * Chunked prefill (what generation.py:94-101 does token by token): state_in is the modal state and
+ * fir_state_in [B,3D,2] the featurizer cache (the last two projection rows, packed-channel order) that the
+ * call on the previous chunk returned; NULL = start of a sequence.
  * ------------------------------------------------------------------------ */
 typedef struct vtx_fused_iir_params {
     const void* u;       int64_t u_stride_b, u_stride_l;   /* channel stride 1 */
     const void* w3;      int64_t w3_dtype;     /* [3D,3] featurizer taps                  */
-    const void* b3;      int64_t b3_dtype;     /* must be NULL                            */
-    vtx_modal_params modal;                     /* G * 16 == D                             */
+    const void* b3;      int64_t b3_dtype;     /* [3D] featurizer bias or NULL            */
+    vtx_modal_params modal;                     /* G modal systems, G divides D            */
     const void* bias;    int64_t bias_dtype;   /* [D] skip term or NULL                   */
     void* y;             int64_t y_stride_b, y_stride_l;   /* channel stride 1 */
     float* state;                               /* or NULL                                 */
-    void* scratch;                              /* vtx_fused_iir_scratch_bytes(B,L,D) bytes, 16-byte aligned, or NULL:
-                                                   lets a sequence be cut into time slices that run on different SMs */
+    void* scratch;                              /* vtx_fused_iir_scratch_bytes(p) bytes, 16-byte aligned, or NULL:
+                                                   lets a sequence be cut into time segments that run on different
+                                                   SMs (without it every channel or group is walked by one thread
+                                                   or block from the first sample to the last) */
     int64_t B, L, D, K3;
     int64_t layout, num_heads, flip_x1x2;
     int64_t io_dtype;
+    const float* state_in;                      /* modal state to start from, layout of state, or NULL (zero) */
+    const void* fir_state_in; int64_t fir_state_dtype;   /* [B,3D,2] rows before the first one, or NULL (zero) */
 } vtx_fused_iir_params;
-int64_t vtx_fused_iir_scratch_bytes(int64_t B, int64_t L, int64_t D);
+/* Scratch the call described by p can use (p->scratch itself is not read); 0 = none needed. */
+int64_t vtx_fused_iir_scratch_bytes(const vtx_fused_iir_params* p);
 int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream);
 
 /* Hyena-X forward (vortex/ops/hyena_x/triton_indirect_fwd.py:262 hyena_x_bdl_fwd, reference :413-424):

@@ -61,12 +61,26 @@ def test_cpu_tensors_are_rejected():
 
 
 def test_fused_iir_scratch_plan():
-    """Host-side planning of the long-filter kernel's time slices (no GPU work): no scratch for short walks or many
-    walks, a few KB per walk once a launch has too few walks to fill the SMs evenly."""
+    """Host-side planning of the long-filter kernels (no GPU work).  Tensor-core shapes: no scratch for short walks
+    or many walks, a few KB per walk once a launch has too few walks to fill the SMs evenly.  Per-channel systems
+    (the recurrence kernel): one state per channel and time segment."""
     from vortex_b200 import _lib
     f = _lib.lib().vtx_fused_iir_scratch_bytes
-    assert f(1, 1000, 4096) == 0                       # 3 steps: nothing to slice
-    assert f(0, 1000, 4096) == 0 and f(1, 0, 4096) == 0
-    n = f(1, 131072, 4096)                             # 256 walks on 148 SMs: sliced
+
+    def q(B, L, D, G, S=16, cplx=False, io=_lib.BF16):
+        p = _lib.FusedIirParams(B=B, L=L, D=D, K3=3, io_dtype=io, y_stride_l=D, y_stride_b=L * D,
+                                u_stride_l=3 * D, u_stride_b=3 * D * L)
+        p.modal.G, p.modal.S = G, S
+        if cplx:
+            p.modal.theta = 16       # only tested against NULL
+        return f(C.byref(p))
+
+    assert q(1, 1000, 4096, 256) == 0                       # 3 steps: nothing to slice
+    assert q(0, 1000, 4096, 256) == 0 and q(1, 0, 4096, 256) == 0
+    n = q(1, 131072, 4096, 256)                             # 256 walks on 148 SMs: sliced
     assert n > 0 and n % (32 * 16 * 4 + 4) == 0
-    assert f(8, 131072, 4096 * 4) == 0                 # 8192 walks: whole rounds anyway
+    assert q(8, 131072, 4096 * 4, 1024) == 0                # 8192 walks: whole rounds anyway
+    n = q(1, 131072, 4096, 4096)                            # a modal system per channel: segments
+    assert n > 0 and n % (4096 * 16 * 4) == 0
+    assert q(1, 131072, 4096, 4096, cplx=True) == 2 * n
+    assert q(1, 40, 4096, 4096) == 0                        # too short to cut

@@ -54,7 +54,7 @@ class FusedIirParams(C.Structure):
                 ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
                 ("y", _p), ("y_stride_b", _i), ("y_stride_l", _i), ("state", _p), ("scratch", _p),
                 ("B", _i), ("L", _i), ("D", _i), ("K3", _i), ("layout", _i), ("num_heads", _i), ("flip_x1x2", _i),
-                ("io_dtype", _i)]
+                ("io_dtype", _i), ("state_in", _p), ("fir_state_in", _p), ("fir_state_dtype", _i)]
 
 
 class IirParams(C.Structure):
@@ -105,7 +105,7 @@ SYMBOLS = {
     "vtx_iir_fwd": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_iir_fwd_noalloc": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_fused_iir_fwd": (C.c_int, [C.POINTER(FusedIirParams), _p]),
-    "vtx_fused_iir_scratch_bytes": (_i, [_i, _i, _i]),
+    "vtx_fused_iir_scratch_bytes": (_i, [C.POINTER(FusedIirParams)]),
     "vtx_hyena_x_fwd": (C.c_int, [C.POINTER(HyenaXParams), _p]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),

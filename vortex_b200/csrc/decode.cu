@@ -372,6 +372,55 @@ __global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_p
     }
 }
 
+// Modal layer with real poles when the modal systems are not shared by whole tiles of 8 channels (Evo 2: one system
+// per channel): four lanes per row, each with four of the row's 16 states as one 16-byte load and store; the row's
+// poles and residues are read the same way.  Three of the four lanes do one packed channel of the featurizer each.
+template <typename T>
+__global__ void __launch_bounds__(256) decode_iir_quad_kernel(vtx_decode_layer_params p) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t row = tid >> 2;
+    const int part = (int)(tid & 3);
+    if (row >= p.B * p.D) return;                  // rows are whole quads: a quad leaves together
+    const unsigned mask = 0xfu << ((threadIdx.x & 31) & ~3);
+    const int64_t b = row / p.D, d = row % p.D, g = d / (p.D / p.modal.G);
+    // state and parameters first: the longest latencies
+    const float4 s = reinterpret_cast<const float4*>(p.iir_state_in + row * 16)[part];
+    const float4 lp = reinterpret_cast<const float4*>(static_cast<const float*>(p.modal.log_poles) + g * 16)[part];
+    const float4 rr = reinterpret_cast<const float4*>(static_cast<const float*>(p.modal.res_re) + g * 16)[part];
+    float z = 0.f;
+    if (part < 3) {
+        QkvMap map{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? p.D / p.num_heads : p.D};
+        int64_t ch[3];
+        map.get(d, ch[0], ch[1], ch[2]);
+        const int64_t c = part == 0 ? ch[0] : part == 1 ? ch[1] : ch[2], so = (b * 3 * p.D + c) * 2;
+        const float2 st = *reinterpret_cast<const float2*>(static_cast<const float*>(p.fir_state_in) + so);
+        const float x = to_f32<T>(static_cast<const T*>(p.u)[b * 3 * p.D + c]);
+        float acc = ld_param(p.w3, p.w3_dtype, c * 3 + 2) * x;
+        acc = fmaf(st.x, ld_param(p.w3, p.w3_dtype, c * 3), acc);
+        acc = fmaf(st.y, ld_param(p.w3, p.w3_dtype, c * 3 + 1), acc);
+        *reinterpret_cast<float2*>(p.fir_state_out + so) = make_float2(st.y, x);
+        if (p.b3) acc += ld_param(p.b3, p.b3_dtype, c);
+        z = round_io<T>(acc);
+    }
+    const float q = __shfl_sync(mask, z, 0, 4), k = __shfl_sync(mask, z, 1, 4), v = __shfl_sync(mask, z, 2, 4);
+    const float kv = round_io<T>(k * v);
+    float4 n;
+    n.x = fmaf(expf(lp.x), s.x, kv);
+    n.y = fmaf(expf(lp.y), s.y, kv);
+    n.z = fmaf(expf(lp.z), s.z, kv);
+    n.w = fmaf(expf(lp.w), s.w, kv);
+    reinterpret_cast<float4*>(p.iir_state_out + row * 16)[part] = n;
+    float sum = fmaf(rr.x, n.x, fmaf(rr.y, n.y, fmaf(rr.z, n.z, rr.w * n.w)));
+    sum += __shfl_xor_sync(mask, sum, 1, 4);
+    sum += __shfl_xor_sync(mask, sum, 2, 4);
+    if (part == 0) {
+        const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+        float skip = bias * kv;
+        if (p.bias && p.bias_dtype != VTX_F32) skip = round_io<T>(skip);
+        static_cast<T*>(p.y)[row] = from_f32<T>(q * (sum + skip));
+    }
+}
+
 }  // namespace vtx
 
 extern "C" int vtx_step_fir(const vtx_step_fir_params* p, void* stream) {
@@ -450,6 +499,12 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
         const int64_t tpg = cpg / 8;                    // tiles per group
         const bool tiled = p->K3 == 3 && p->fir_state_dtype == VTX_F32 && cpg % 8 == 0 && (tpg == 1 || tpg == 2 || tpg == 4 || tpg == 8 || tpg == 16);
         const bool cplx = p->modal.theta != nullptr;
+        // one system per channel (or per few): real poles, 16 states, four lanes per row
+        const bool quad = !cplx && p->modal.S == 16 && p->K3 == 3 && p->fir_state_dtype == VTX_F32 &&
+                          reinterpret_cast<uintptr_t>(p->iir_state_in) % 16 == 0 &&
+                          reinterpret_cast<uintptr_t>(p->iir_state_out) % 16 == 0 &&
+                          reinterpret_cast<uintptr_t>(p->modal.log_poles) % 16 == 0 &&
+                          reinterpret_cast<uintptr_t>(p->modal.res_re) % 16 == 0;
         VTX_DISPATCH_IO(p->io_dtype, T, {
             if (tiled) {
                 // a block = 16 tiles of one group: 16 / tpg batch elements share one evaluation of the group's poles
@@ -458,6 +513,8 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
                 const int64_t nblk = (p->modal.G / gpb) * ceil_div<int64_t>(p->B, bpb);
                 if (cplx) decode_iir_tile_kernel<T, 8, true><<<(unsigned)nblk, 256, 0, s>>>(*p, (int)tpg, gpb);
                 else decode_iir_tile_kernel<T, 8, false><<<(unsigned)nblk, 256, 0, s>>>(*p, (int)tpg, gpb);
+            } else if (quad) {
+                decode_iir_quad_kernel<T><<<(unsigned)ceil_div<int64_t>(rows * 4, 256), 256, 0, s>>>(*p);
             } else {
                 decode_layer_kernel<T, 16, 1><<<(unsigned)ceil_div<int64_t>(rows * 16, 256), 256, 0, s>>>(*p);
             }

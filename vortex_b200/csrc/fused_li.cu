@@ -613,12 +613,31 @@ static void plan_slices(int64_t walks, int64_t ntotal, int& nslice, int& spp) {
 }  // namespace li
 }  // namespace vtx
 
-extern "C" int64_t vtx_fused_iir_scratch_bytes(int64_t B, int64_t L, int64_t D) {
+namespace vtx {
+namespace licc {   // fused_li_cc.cu: the recurrence on the fp32 pipe (modal systems of any grouping, any I/O dtype)
+int64_t scratch_bytes(const vtx_fused_iir_params* p);
+int fwd(const vtx_fused_iir_params* p, cudaStream_t stream);
+}  // namespace licc
+
+// Shapes the tensor-core kernel takes; every other call runs the recurrence kernel.
+static bool li_tc_shape(const vtx_fused_iir_params* p) {
+    using namespace li;
+    return p->io_dtype == VTX_BF16 && p->D == p->modal.G * CH && p->modal.S <= NPOLE && p->K3 == 3 && !p->b3 &&
+           !p->state_in && !p->fir_state_in && (reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 &&
+           (p->y_stride_b % 16) == 0 && (reinterpret_cast<uintptr_t>(p->u) % 16) == 0 && (p->u_stride_l % 8) == 0 &&
+           (p->u_stride_b % 8) == 0 &&
+           (p->layout == VTX_QKV_INTERLEAVED || (p->D % 8) == 0) &&
+           (p->layout != VTX_QKV_COLUMN_SPLIT || (p->num_heads > 0 && p->D % p->num_heads == 0 && (p->D / p->num_heads) % CH == 0));
+}
+}  // namespace vtx
+
+extern "C" int64_t vtx_fused_iir_scratch_bytes(const vtx_fused_iir_params* p) {
     using namespace vtx::li;
-    if (B <= 0 || L <= 0 || D <= 0) return 0;
+    if (!p || p->B <= 0 || p->L <= 0 || p->D <= 0 || p->modal.G <= 0 || p->modal.S <= 0) return 0;
+    if (!vtx::li_tc_shape(p)) return vtx::licc::scratch_bytes(p);
     int nslice, spp;
-    plan_slices(B * (D / CH), (L + SUPER - 1) / SUPER, nslice, spp);
-    return (int64_t)B * (D / CH) * (nslice - 1) * (32 * 16 * 4 + 4);
+    plan_slices(p->B * (p->D / CH), (p->L + SUPER - 1) / SUPER, nslice, spp);
+    return (int64_t)p->B * (p->D / CH) * (nslice - 1) * (32 * 16 * 4 + 4);
 }
 
 extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
@@ -628,12 +647,7 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     VTX_REQUIRE(p && p->u && p->w3 && p->y && p->modal.log_poles && p->modal.res_re, VTX_ERR_BAD_ARG, "fused_iir: null pointer");
     VTX_REQUIRE(p->B > 0 && p->L > 0 && p->D > 0 && p->modal.G > 0 && p->modal.S > 0, VTX_ERR_BAD_ARG, "fused_iir: sizes must be positive");
     VTX_REQUIRE(!p->modal.res_im || p->modal.theta, VTX_ERR_BAD_ARG, "fused_iir: complex residues need complex poles");
-    VTX_REQUIRE(p->io_dtype == VTX_BF16, VTX_ERR_UNSUPPORTED, "fused_iir: bf16 I/O only");
-    VTX_REQUIRE(p->D == p->modal.G * CH, VTX_ERR_UNSUPPORTED, "fused_iir: needs modal systems shared by groups of %d channels", CH);
-    VTX_REQUIRE(p->modal.S <= NPOLE, VTX_ERR_UNSUPPORTED, "fused_iir: state size %lld > %d", (long long)p->modal.S, NPOLE);
-    VTX_REQUIRE(p->K3 == 3 && !p->b3, VTX_ERR_UNSUPPORTED, "fused_iir: needs a 3-tap featurizer without bias");
-    VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0,
-                VTX_ERR_ALIGNMENT, "fused_iir: y rows must be 32-byte aligned");
+    if (!li_tc_shape(p)) return licc::fwd(p, stream);
     VTX_REQUIRE(p->L < ((int64_t)1 << 30) && p->B <= 65535 && p->modal.G * p->B < ((int64_t)1 << 27), VTX_ERR_UNSUPPORTED,
                 "fused_iir: problem too large");
     Args a{};

@@ -1,0 +1,525 @@
+// Fused Hyena-LI block for modal systems that are NOT shared by groups of 16 channels (Evo 2 gives every channel
+// its own 16 real poles, configs/evo2-7b-8k.yml:11 `hcl_filter_groups: 4096`), any I/O dtype, channel-last in and
+// out:  featurizer (3 taps) -> q/k/v selection -> k*v -> modal recurrence -> (+ bias*kv) -> q gate.
+// Fuses model.py:233-316 (featurizer parallel_fir + parallel_iir, engine.py:262-353) and the end state of
+// engine.py:525-559 without the [B,3D,L] intermediate.
+//
+// A per-channel filter has no operand that tensor cores could share between channels, so the recurrence itself runs
+// on the fp32 pipe:  sigma_s[t] = p_s sigma_s[t-1] + kv[t],  y[t] = q[t] (sum_s R_s sigma_s[t] + bias kv[t]),
+// 32 FMA per sample and channel (real poles; issued as 16 packed fma.rn.f32x2).
+// Thread = (batch, channel, time segment), lane = channel, so that a warp reads 32 neighbouring channels of a row.
+// Segments make the parallelism batch*channels alone does not have; the carry between them takes three launches:
+//   A  end state of every segment from a zero start            (reads k, v rows)
+//   B  scan over the segments of a channel: start states        (tiny)
+//   C  recurrence from the true start state, writes y           (reads q, k, v rows)
+// Nothing between the input rows and the output is rounded to the I/O dtype (the reference rounds the featurizer
+// output, k*v and the convolution result, engine.py:208,159,230): the result is closer to the fp32 reference.
+// A call can continue an earlier one (chunked prefill): state_in is the modal state and fir_state_in the two
+// projection rows the earlier call ended with.
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace vtx {
+namespace licc {
+
+using umma::f32x2;
+using umma::fma2;
+using umma::pk2;
+using umma::up2;
+
+constexpr int NS = 16;         // states per thread (shorter systems are padded with p = R = 0)
+constexpr int THREADS = 128;
+#ifndef VTX_LICC_TB
+#define VTX_LICC_TB 4
+#endif
+#ifndef VTX_LICC_MINB
+#define VTX_LICC_MINB 4
+#endif
+constexpr int TB = VTX_LICC_TB;   // samples per software-pipeline block
+
+struct Plan {
+    int64_t nseg, seg_len;
+};
+
+// Segments per channel: about four rounds of resident threads over the SMs, segments of at least 64 samples.
+static Plan plan(int64_t B, int64_t L, int64_t D, bool have_scratch) {
+    Plan pl{1, L};
+    if (!have_scratch) return pl;
+    const int64_t rows = B * D, want = (int64_t)kNumSMs * 640 * 4;
+    int64_t nseg = ceil_div<int64_t>(want, rows);
+    if (nseg > L / 64) nseg = L / 64;
+    if (nseg < 1) nseg = 1;
+    int64_t seg = ceil_div<int64_t>(ceil_div<int64_t>(L, nseg), (int64_t)8) * 8;      // a multiple of both block sizes
+    pl.seg_len = seg;
+    pl.nseg = ceil_div<int64_t>(L, seg);
+    return pl;
+}
+
+struct Args {
+    const void* u; int64_t sb, sl;
+    const void* w3; int64_t w3_dtype;
+    const void* b3; int64_t b3_dtype;
+    vtx_modal_params m;
+    const void* bias; int64_t bias_dtype;
+    void* y; int64_t ysb, ysl;
+    float* state; const float* state_in;
+    const void* fs_in; int64_t fs_dtype;
+    float* scratch;
+    int64_t B, L, D;
+    QkvMap map;
+    Plan pl;
+};
+
+// scratch[(seg * SS + j) * rows + row]: component j of the state at the START of segment seg (after phase B)
+template <bool CPLX> constexpr int comps(int S) { return CPLX ? 2 * S : S; }
+
+template <bool CPLX>
+struct Modes {
+    float pr[NS], pi[CPLX ? NS : 1], rr[NS], ri[CPLX ? NS : 1];
+    __device__ __forceinline__ void load(const vtx_modal_params& m, int64_t g) {
+        const int S = (int)m.S;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            pr[s] = rr[s] = 0.f;
+            if constexpr (CPLX) pi[s] = ri[s] = 0.f;
+            if (s < S) {
+                const float mag = expf(static_cast<const float*>(m.log_poles)[g * S + s]);
+                rr[s] = static_cast<const float*>(m.res_re)[g * S + s];
+                if constexpr (CPLX) {
+                    float sn, cs;
+                    sincosf(static_cast<const float*>(m.theta)[g * S + s], &sn, &cs);
+                    pr[s] = mag * cs; pi[s] = mag * sn;
+                    ri[s] = m.res_im ? static_cast<const float*>(m.res_im)[g * S + s] : 0.f;
+                } else {
+                    pr[s] = mag;
+                }
+            }
+        }
+    }
+};
+
+// Real systems keep poles, residues and states as f32x2 pairs: one packed FMA advances two states.
+template <bool CPLX> struct Sys;
+
+template <>
+struct Sys<false> {
+    f32x2 p2[NS / 2], r2[NS / 2], s2[NS / 2];
+    __device__ __forceinline__ void init(const Modes<false>& m) {
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) {
+            p2[j] = pk2(m.pr[2 * j], m.pr[2 * j + 1]);
+            r2[j] = pk2(m.rr[2 * j], m.rr[2 * j + 1]);
+            s2[j] = pk2(0.f, 0.f);
+        }
+    }
+    // components j < n of a state vector stored with the given stride
+    __device__ __forceinline__ void load(const float* in, int64_t stride, int n) {
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) {
+            const float lo = 2 * j < n ? in[(2 * j) * stride] : 0.f;
+            const float hi = 2 * j + 1 < n ? in[(2 * j + 1) * stride] : 0.f;
+            s2[j] = pk2(lo, hi);
+        }
+    }
+    __device__ __forceinline__ void store(float* out, int64_t stride, int n) const {
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) {
+            float lo, hi;
+            up2(s2[j], lo, hi);
+            if (2 * j < n) out[(2 * j) * stride] = lo;
+            if (2 * j + 1 < n) out[(2 * j + 1) * stride] = hi;
+        }
+    }
+    __device__ __forceinline__ void advance(float x) {
+        const f32x2 x2 = pk2(x, x);
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) s2[j] = fma2(p2[j], s2[j], x2);
+    }
+    __device__ __forceinline__ float step(float x) {
+        const f32x2 x2 = pk2(x, x);
+        f32x2 a0 = pk2(0.f, 0.f), a1 = a0;
+#pragma unroll
+        for (int j = 0; j < NS / 2; j += 2) {
+            s2[j] = fma2(p2[j], s2[j], x2);
+            s2[j + 1] = fma2(p2[j + 1], s2[j + 1], x2);
+            a0 = fma2(r2[j], s2[j], a0);
+            a1 = fma2(r2[j + 1], s2[j + 1], a1);
+        }
+        float u0, u1, v0, v1;
+        up2(a0, u0, u1);
+        up2(a1, v0, v1);
+        return (u0 + v0) + (u1 + v1);
+    }
+};
+
+template <>
+struct Sys<true> {
+    float pr[NS], pi[NS], rr[NS], ri[NS], re[NS], im[NS];
+    __device__ __forceinline__ void init(const Modes<true>& m) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            pr[s] = m.pr[s]; pi[s] = m.pi[s]; rr[s] = m.rr[s]; ri[s] = m.ri[s];
+            re[s] = im[s] = 0.f;
+        }
+    }
+    // components (re, im interleaved) j < n of a state vector stored with the given stride
+    __device__ __forceinline__ void load(const float* in, int64_t stride, int n) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            re[s] = 2 * s < n ? in[(2 * s) * stride] : 0.f;
+            im[s] = 2 * s + 1 < n ? in[(2 * s + 1) * stride] : 0.f;
+        }
+    }
+    __device__ __forceinline__ void store(float* out, int64_t stride, int n) const {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            if (2 * s < n) out[(2 * s) * stride] = re[s];
+            if (2 * s + 1 < n) out[(2 * s + 1) * stride] = im[s];
+        }
+    }
+    __device__ __forceinline__ void advance(float x) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const float nr = fmaf(pr[s], re[s], fmaf(-pi[s], im[s], x));
+            const float ni = fmaf(pr[s], im[s], pi[s] * re[s]);
+            re[s] = nr; im[s] = ni;
+        }
+    }
+    __device__ __forceinline__ float step(float x) {
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const float nr = fmaf(pr[s], re[s], fmaf(-pi[s], im[s], x));
+            const float ni = fmaf(pr[s], im[s], pi[s] * re[s]);
+            re[s] = nr; im[s] = ni;
+            acc = fmaf(rr[s], nr, fmaf(-ri[s], ni, acc));
+        }
+        return acc;
+    }
+};
+
+struct Work {
+    int64_t b, d, row, seg, t0, t1;
+    bool valid;
+};
+// Segment index slowest, so that the lanes of a warp sit on neighbouring channels of one segment.
+__device__ __forceinline__ Work work_of(const Args& a) {
+    Work w;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t rows = a.B * a.D;
+    w.valid = i < rows * a.pl.nseg;
+    w.row = i % rows;
+    w.seg = i / rows;
+    w.b = w.row / a.D;
+    w.d = w.row % a.D;
+    w.t0 = w.seg * a.pl.seg_len;
+    w.t1 = w.t0 + a.pl.seg_len < a.L ? w.t0 + a.pl.seg_len : a.L;
+    return w;
+}
+
+// One packed channel of the featurizer: taps, bias and the two samples before the current one.
+template <typename T>
+struct Stream {
+    float w0, w1, w2, b;   // z[t] = w0 u[t-2] + w1 u[t-1] + w2 u[t] (+ b)
+    float u1, u2;          // u[t-1], u[t-2]
+    __device__ __forceinline__ void init(const Args& a, int64_t bidx, int64_t c, int64_t t0) {
+        const T* col = static_cast<const T*>(a.u) + bidx * a.sb + c;
+        w0 = ld_param(a.w3, a.w3_dtype, c * 3 + 0);
+        w1 = ld_param(a.w3, a.w3_dtype, c * 3 + 1);
+        w2 = ld_param(a.w3, a.w3_dtype, c * 3 + 2);
+        b = a.b3 ? ld_param(a.b3, a.b3_dtype, c) : 0.f;
+        u1 = hist(a, col, bidx, c, t0 - 1);
+        u2 = hist(a, col, bidx, c, t0 - 2);
+    }
+    // sample at time t < t0: this call's rows, else the rows the previous call ended with, else zero
+    __device__ __forceinline__ float hist(const Args& a, const T* col, int64_t bidx, int64_t c, int64_t t) const {
+        if (t >= 0) return to_f32<T>(col[t * a.sl]);
+        if (!a.fs_in) return 0.f;
+        return ld_param(a.fs_in, a.fs_dtype, (bidx * 3 * a.D + c) * 2 + (2 + t));
+    }
+    __device__ __forceinline__ float feat(float u0) {
+        const float z = fmaf(w2, u0, fmaf(w1, u1, fmaf(w0, u2, b)));
+        u2 = u1; u1 = u0;
+        return z;
+    }
+};
+
+// Rows a segment will read PF samples from now, asked into L2 once per block of NB samples by 3 * NB lanes of the warp
+// (NB rows x 3 pieces: the q, k, v columns of the warp's 32 channels, or the three thirds of their interleaved span).
+constexpr int PF = 48;
+template <typename T, int NB>
+struct Prefetch {
+    const T* piece;     // lane < 3 * NB: piece lane % 3 of the row PF + lane / 3 ahead of the block being computed
+    int64_t step;       // NB rows
+    int left;           // rows until the end of the tensor, counted from that row
+    // cq, ck, cv: the thread's columns in the first row of its segment.  All 32 lanes of the warp must be here.
+    __device__ __forceinline__ void init(const Args& a, const T* cq, const T* ck, const T* cv, int64_t t0) {
+        const int lane = threadIdx.x & 31, j = lane % 3, row = lane / 3;
+        const unsigned long long q0 = __shfl_sync(0xffffffffu, (unsigned long long)cq, 0);
+        const unsigned long long k0 = __shfl_sync(0xffffffffu, (unsigned long long)ck, 0);
+        const unsigned long long v0 = __shfl_sync(0xffffffffu, (unsigned long long)cv, 0);
+        const unsigned long long lo = q0 < k0 ? (q0 < v0 ? q0 : v0) : (k0 < v0 ? k0 : v0);
+        const bool inter = a.map.layout == VTX_QKV_INTERLEAVED;
+        piece = (inter ? reinterpret_cast<const T*>(lo) + 32 * j : reinterpret_cast<const T*>(j == 0 ? q0 : j == 1 ? k0 : v0)) +
+                (PF + row) * a.sl;
+        step = NB * a.sl;
+        const int64_t l = a.L - (t0 + PF + row);
+        left = lane < 3 * NB ? (int)(l < 0 ? 0 : l > 0x7fffffff ? 0x7fffffff : l) : 0;
+    }
+    __device__ __forceinline__ void ask() {
+        if (left > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(piece));
+        piece += step;
+        left -= NB;
+    }
+};
+
+template <typename T, bool CPLX>
+__device__ __forceinline__ void load_state(Sys<CPLX>& sys, const Args& a, const Work& w) {
+    const int SS = comps<CPLX>((int)a.m.S);
+    if (w.seg > 0) {
+        const int64_t rows = a.B * a.D;
+        sys.load(a.scratch + (w.seg * SS) * rows + w.row, rows, SS);
+    } else if (a.state_in) {
+        sys.load(a.state_in + w.row * SS, 1, SS);
+    }
+}
+
+// ---- phase A: end state of every segment but the last, from a zero start ------------------------------------------
+constexpr int TBA = 8;         // samples per software-pipeline block (every segment but the last is a multiple of it)
+template <typename T, bool CPLX>
+__global__ void __launch_bounds__(THREADS) licc_segment_state_kernel(Args a) {
+    const Work w = work_of(a);
+    if (!w.valid || w.seg == a.pl.nseg - 1) return;
+    Modes<CPLX> md;
+    md.load(a.m, w.d / (a.D / a.m.G));
+    Sys<CPLX> sys;
+    sys.init(md);
+    int64_t cq, ck, cv;
+    a.map.get(w.d, cq, ck, cv);
+    Stream<T> sk, sv;
+    sk.init(a, w.b, ck, w.t0);
+    sv.init(a, w.b, cv, w.t0);
+    const T* row0 = static_cast<const T*>(a.u) + w.b * a.sb + w.t0 * a.sl;      // first row of the segment
+    const bool use_pf = (a.B * a.D) % 32 == 0;       // whole warps on one segment
+    Prefetch<T, TBA> pf;
+    // interleaved rows hold q between k and v anyway; the other layouts read the k and v columns only
+    if (use_pf) pf.init(a, row0 + (a.map.layout == VTX_QKV_INTERLEAVED ? cq : ck), row0 + ck, row0 + cv, w.t0);
+    const T* pk = row0 + ck;        // running pointers of the loads, one block ahead of the arithmetic
+    const T* pv = row0 + cv;
+    const int64_t sl = a.sl;
+    T bk[2][TBA], bv[2][TBA];
+    auto fetch = [&](int which) {
+#pragma unroll
+        for (int i = 0; i < TBA; ++i) {
+            bk[which][i] = *pk; bv[which][i] = *pv;
+            pk += sl; pv += sl;
+        }
+    };
+    auto consume = [&](int which) {
+#pragma unroll
+        for (int i = 0; i < TBA; ++i) sys.advance(sk.feat(to_f32<T>(bk[which][i])) * sv.feat(to_f32<T>(bv[which][i])));
+    };
+    int64_t left = (w.t1 - w.t0) / TBA;      // blocks
+    fetch(0);
+    while (true) {
+        if (use_pf) pf.ask();
+        if (left > 1) fetch(1);
+        consume(0);
+        if (--left == 0) break;
+        if (use_pf) pf.ask();
+        if (left > 1) fetch(0);
+        consume(1);
+        if (--left == 0) break;
+    }
+    const int SS = comps<CPLX>((int)a.m.S);
+    const int64_t rows = a.B * a.D;
+    sys.store(a.scratch + (w.seg * SS) * rows + w.row, rows, SS);
+}
+
+// ---- phase B: scratch[seg] <- state at the START of segment seg ----------------------------------------------------
+template <bool CPLX>
+__global__ void licc_carry_kernel(Args a) {
+    const int S = (int)a.m.S, SS = comps<CPLX>(S);
+    const int64_t rows = a.B * a.D;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * S) return;
+    const int64_t row = i % rows;
+    const int s = (int)(i / rows);
+    const int64_t d = row % a.D, g = d / (a.D / a.m.G);
+    // p^seg_len in polar form
+    const float lam = static_cast<const float*>(a.m.log_poles)[g * S + s];
+    const float mag = expf(lam * (float)a.pl.seg_len);
+    float pr = mag, pi = 0.f;
+    if (CPLX) {
+        double ang = (double)static_cast<const float*>(a.m.theta)[g * S + s] * (double)a.pl.seg_len;
+        ang -= 6.283185307179586 * floor(ang / 6.283185307179586);
+        float sn, cs;
+        sincosf((float)ang, &sn, &cs);
+        pr = mag * cs; pi = mag * sn;
+    }
+    float cr = 0.f, ci = 0.f;
+    if (a.state_in) {
+        cr = a.state_in[row * SS + (CPLX ? 2 * s : s)];
+        if (CPLX) ci = a.state_in[row * SS + 2 * s + 1];
+    }
+    // the end states of CB segments are read together (independent loads), then scanned and overwritten
+    constexpr int CB = 8;
+    const int64_t nseg = a.pl.nseg, seg_stride = (int64_t)SS * rows;
+    float* e0 = a.scratch + (int64_t)(CPLX ? 2 * s : s) * rows + row;
+    for (int64_t sb = 0; sb < nseg; sb += CB) {
+        float er[CB], ei[CB];
+#pragma unroll
+        for (int k = 0; k < CB; ++k) {
+            er[k] = ei[k] = 0.f;
+            if (sb + k + 1 < nseg) {          // the last segment's end state is not a carry (phase A leaves it unwritten)
+                er[k] = e0[(sb + k) * seg_stride];
+                if (CPLX) ei[k] = e0[(sb + k) * seg_stride + rows];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < CB; ++k) {
+            if (sb + k < nseg) {
+                e0[(sb + k) * seg_stride] = cr;
+                if (CPLX) e0[(sb + k) * seg_stride + rows] = ci;
+                const float nr = pr * cr - pi * ci + er[k];
+                const float ni = pr * ci + pi * cr + ei[k];
+                cr = nr; ci = ni;
+            }
+        }
+    }
+}
+
+// ---- phase C: outputs --------------------------------------------------------------------------------------------
+// INTER: the three packed channels of a hidden channel are neighbours in a row (one running pointer, constant
+// offsets); streams are then kept by POSITION in the row and q / k picked after the featurizer (flip_x1x2 swaps them).
+template <typename T, bool CPLX, bool INTER>
+__global__ void __launch_bounds__(THREADS, VTX_LICC_MINB) licc_output_kernel(Args a) {
+    const Work w = work_of(a);
+    if (!w.valid) return;
+    Modes<CPLX> md;
+    md.load(a.m, w.d / (a.D / a.m.G));
+    Sys<CPLX> sys;
+    sys.init(md);
+    load_state<T, CPLX>(sys, a, w);
+    int64_t cq, ck, cv;
+    a.map.get(w.d, cq, ck, cv);
+    const bool swap01 = INTER && a.map.flip;      // position 0 holds k, position 1 holds q
+    if (swap01) { const int64_t t = cq; cq = ck; ck = t; }
+    Stream<T> s0, s1, s2;                         // INTER: by position; else q, k, v
+    s0.init(a, w.b, cq, w.t0);
+    s1.init(a, w.b, ck, w.t0);
+    s2.init(a, w.b, cv, w.t0);
+    const float bias = a.bias ? ld_param(a.bias, a.bias_dtype, w.d) : 0.f;
+    const T* row0 = static_cast<const T*>(a.u) + w.b * a.sb + w.t0 * a.sl;
+    const bool use_pf = (a.B * a.D) % 32 == 0;       // whole warps on one segment
+    Prefetch<T, TB> pf;
+    if (use_pf) pf.init(a, row0 + cq, row0 + ck, row0 + cv, w.t0);
+    const T* p0 = row0 + cq;        // running pointers of the loads, one block ahead of the arithmetic
+    const T* p1 = row0 + ck;
+    const T* p2 = row0 + cv;
+    T* yp = static_cast<T*>(a.y) + w.b * a.ysb + w.t0 * a.ysl + w.d;
+    const int64_t sl = a.sl, ysl = a.ysl;
+
+    auto sample = [&](float e0, float e1, float e2) {
+        const float z0 = s0.feat(e0), z1 = s1.feat(e1), v = s2.feat(e2);
+        const float q = swap01 ? z1 : z0, k = swap01 ? z0 : z1;
+        const float x = k * v;
+        const float z = fmaf(bias, x, sys.step(x));
+        *yp = from_f32<T>(z * q);
+        yp += ysl;
+    };
+    T b0[2][TB], b1[2][TB], b2[2][TB];
+    auto fetch = [&](int which) {
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+            if (INTER) {
+                b0[which][i] = p0[0]; b1[which][i] = p0[1]; b2[which][i] = p0[2];
+                p0 += sl;
+            } else {
+                b0[which][i] = *p0; b1[which][i] = *p1; b2[which][i] = *p2;
+                p0 += sl; p1 += sl; p2 += sl;
+            }
+        }
+    };
+    auto consume = [&](int which) {
+#pragma unroll
+        for (int i = 0; i < TB; ++i) sample(to_f32<T>(b0[which][i]), to_f32<T>(b1[which][i]), to_f32<T>(b2[which][i]));
+    };
+    int64_t left = (w.t1 - w.t0) / TB;       // whole blocks
+    const int ragged = (int)((w.t1 - w.t0) - left * TB);
+    if (left > 0) {
+        fetch(0);
+        while (true) {
+            if (use_pf) pf.ask();
+            if (left > 1) fetch(1);
+            consume(0);
+            if (--left == 0) break;
+            if (use_pf) pf.ask();
+            if (left > 1) fetch(0);
+            consume(1);
+            if (--left == 0) break;
+        }
+    }
+    for (int i = 0; i < ragged; ++i) {        // ragged end of the sequence (p0.. stand on its first row)
+        if (INTER) sample(to_f32<T>(p0[0]), to_f32<T>(p0[1]), to_f32<T>(p0[2]));
+        else sample(to_f32<T>(*p0), to_f32<T>(*p1), to_f32<T>(*p2));
+        p0 += sl; p1 += sl; p2 += sl;
+    }
+
+    if (a.state && w.seg == a.pl.nseg - 1) {
+        const int SS = comps<CPLX>((int)a.m.S);
+        sys.store(a.state + w.row * SS, 1, SS);
+    }
+}
+
+int64_t scratch_bytes(const vtx_fused_iir_params* p) {
+    const Plan pl = plan(p->B, p->L, p->D, true);
+    if (pl.nseg <= 1) return 0;
+    return p->B * p->D * pl.nseg * p->modal.S * (p->modal.theta ? 2 : 1) * (int64_t)sizeof(float);
+}
+
+int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
+    VTX_REQUIRE(p->K3 == 3, VTX_ERR_UNSUPPORTED, "fused_iir: needs a 3-tap featurizer (got %lld taps)", (long long)p->K3);
+    VTX_REQUIRE(p->modal.S <= NS, VTX_ERR_UNSUPPORTED, "fused_iir: state size %lld > %d", (long long)p->modal.S, NS);
+    VTX_REQUIRE(p->D % p->modal.G == 0, VTX_ERR_BAD_ARG, "fused_iir: D not a multiple of the number of modal systems");
+    VTX_REQUIRE(valid_dtype(p->w3_dtype) && (!p->b3 || valid_dtype(p->b3_dtype)) && (!p->bias || valid_dtype(p->bias_dtype)) &&
+                    (!p->fir_state_in || valid_dtype(p->fir_state_dtype)),
+                VTX_ERR_BAD_ARG, "fused_iir: bad parameter dtype");
+    Args a{};
+    a.u = p->u; a.sb = p->u_stride_b; a.sl = p->u_stride_l;
+    a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.b3 = p->b3; a.b3_dtype = p->b3_dtype;
+    a.m = p->modal; a.bias = p->bias; a.bias_dtype = p->bias_dtype;
+    a.y = p->y; a.ysb = p->y_stride_b; a.ysl = p->y_stride_l;
+    a.state = p->state; a.state_in = p->state_in; a.fs_in = p->fir_state_in; a.fs_dtype = p->fir_state_dtype;
+    a.scratch = static_cast<float*>(p->scratch);
+    a.B = p->B; a.L = p->L; a.D = p->D;
+    a.map.layout = (int)p->layout; a.map.flip = p->flip_x1x2 != 0; a.map.D = p->D; a.map.hd = p->D;
+    if (p->layout == VTX_QKV_COLUMN_SPLIT) {
+        VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_iir: bad num_heads");
+        a.map.hd = p->D / p->num_heads;
+    }
+    a.pl = plan(p->B, p->L, p->D, p->scratch != nullptr);
+    const bool cplx = p->modal.theta != nullptr;
+    const int64_t n = p->B * p->D * a.pl.nseg;
+    VTX_REQUIRE(ceil_div<int64_t>(n, THREADS) < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "fused_iir: problem too large");
+    const unsigned blocks = (unsigned)ceil_div<int64_t>(n, THREADS);
+    VTX_DISPATCH_IO(p->io_dtype, T, {
+        if (a.pl.nseg > 1) {
+            const unsigned ablocks = (unsigned)ceil_div<int64_t>(p->B * p->D * (a.pl.nseg - 1), THREADS);
+            if (cplx) licc_segment_state_kernel<T, true><<<ablocks, THREADS, 0, stream>>>(a);
+            else licc_segment_state_kernel<T, false><<<ablocks, THREADS, 0, stream>>>(a);
+            const int64_t nc = p->B * p->D * p->modal.S;
+            if (cplx) licc_carry_kernel<true><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);
+            else licc_carry_kernel<false><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);
+        }
+        const bool inter = p->layout == VTX_QKV_INTERLEAVED;
+        if (cplx && inter) licc_output_kernel<T, true, true><<<blocks, THREADS, 0, stream>>>(a);
+        else if (cplx) licc_output_kernel<T, true, false><<<blocks, THREADS, 0, stream>>>(a);
+        else if (inter) licc_output_kernel<T, false, true><<<blocks, THREADS, 0, stream>>>(a);
+        else licc_output_kernel<T, false, false><<<blocks, THREADS, 0, stream>>>(a);
+    });
+    return check_launch("fused_iir");
+}
+
+}  // namespace licc
+}  // namespace vtx

@@ -77,19 +77,26 @@ def hyena_mr_fwd(u, short_filter_weight, short_filter_bias, h, D_skip, *, layout
 
 
 def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues, D_skip, *, theta=None, res_im=None,
-                 layout="interleaved", num_heads=1, flip=False, want_state=False):
+                 layout="interleaved", num_heads=1, flip=False, want_state=False, state_in=None, fir_state_in=None):
     """Hyena-LI block (modal long filter).  u [B, L, 3D] -> y [B, L, D], featurizer cache, modal state
-    fp32 [B, D, S] (complex poles: [B, D, S, 2])."""
+    fp32 [B, D, S] (complex poles: [B, D, S, 2]).  ``state_in`` / ``fir_state_in``: the caches a call on the
+    preceding chunk of the same sequences returned (chunked prefill)."""
     D = u.shape[-1] // 3
-    if _li_tensor_core_ok(u, short_filter_weight, short_filter_bias, residues, layout, num_heads):
+    if short_filter_weight.shape[-1] == 3 and residues.shape[-1] <= 16:
+        # one pass over the rows; the library routes per-group-of-16 bf16 systems to the tensor-core kernel
         out = ops.fused_iir_fwd(u, short_filter_weight, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads,
-                                flip=flip, theta=theta, res_im=res_im, want_state=want_state)
+                                flip=flip, theta=theta, res_im=res_im, want_state=want_state, b3=short_filter_bias,
+                                state_in=state_in, fir_state_in=fir_state_in)
         if not want_state:
             return out, None, None
         # featurizer cache: the last two input rows, channel-first (a strided copy, no arithmetic)
         L = u.shape[1]
-        fs = u[:, max(L - 2, 0):, :].transpose(1, 2).contiguous()
-        return out[0], fs, out[1]
+        fs = u[:, max(L - 2, 0):, :].transpose(1, 2)
+        if L < 2 and fir_state_in is not None:
+            fs = torch.cat([fir_state_in[..., L:].to(u.dtype), fs], dim=-1)
+        return out[0], fs.contiguous(), out[1]
+    if state_in is not None or fir_state_in is not None:
+        raise NotImplementedError("chunked prefill needs a 3-tap featurizer and at most 16 poles")
     z, fs = ops.featurizer_fwd(u, short_filter_weight, short_filter_bias, None, want_state=want_state)
     y, st = ops.iir_fwd(z, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads, flip=flip, theta=theta,
                         res_im=res_im, want_state=want_state, round_kv=True)
@@ -97,8 +104,8 @@ def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues,
 
 
 def _li_tensor_core_ok(u, w3, b3, residues, layout, num_heads):
-    """Shapes the tcgen05 chunked-scan kernel takes: bf16 I/O, 3-tap featurizer without bias, one modal system of up
-    to 16 poles per group of 16 channels."""
+    """Shapes the tcgen05 chunked-scan kernel takes (the library checks the same): bf16 I/O, 3-tap featurizer without
+    bias, one modal system of up to 16 poles per group of 16 channels."""
     D = u.shape[-1] // 3
     if u.dtype != torch.bfloat16 or b3 is not None or w3.shape[-1] != 3:
         return False

@@ -227,29 +227,44 @@ def modal_filter(log_poles, residues, L: int, theta=None, res_im=None) -> torch.
 
 
 def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, layout="interleaved", num_heads=1,
-                  flip=False, theta=None, res_im=None, want_state=False):
-    """Channel-last fused long-filter block (tensor cores): u [B, L, 3D] bf16 -> y [B, L, D] and, on request, the
-    modal state after the last token (fp32 [B, D, S], complex poles [B, D, S, 2])."""
-    _need_cuda(u, w3, residues, bias)
+                  flip=False, theta=None, res_im=None, want_state=False, b3=None, state_in=None, fir_state_in=None):
+    """Channel-last fused long-filter block: u [B, L, 3D] -> y [B, L, D] and, on request, the modal state after the
+    last token (fp32 [B, D, S], complex poles [B, D, S, 2]).  The library picks the kernel: tensor cores for bf16
+    with one modal system per group of 16 channels, the fp32-pipe recurrence otherwise.  ``state_in`` /
+    ``fir_state_in`` ([B, 3D, 2]) continue an earlier call (chunked prefill)."""
+    _need_cuda(u, w3, residues, bias, b3, state_in, fir_state_in)
     if u.stride(2) != 1:
         u = u.contiguous()
     B, L, C3 = u.shape
     if C3 != 3 * D:
         raise ValueError(f"expected {3 * D} packed channels, got {C3}")
     w3 = _param(w3, u).reshape(C3, -1)
-    bias = _param(bias, u)
+    bias, b3 = _param(bias, u), _param(b3, u)
     m, keep = _modal(log_poles, residues, u, theta, res_im)
+    cplx = theta is not None
     y = torch.empty(B, L, D, device=u.device, dtype=u.dtype)
     st = None
     if want_state:
-        st = torch.empty((B, D, m.S, 2) if theta is not None else (B, D, m.S), device=u.device, dtype=torch.float32)
-    nscratch = _lib.lib().vtx_fused_iir_scratch_bytes(B, L, D)
-    scratch = torch.empty(nscratch, device=u.device, dtype=torch.uint8) if nscratch > 0 else None
+        st = torch.empty((B, D, m.S, 2) if cplx else (B, D, m.S), device=u.device, dtype=torch.float32)
+    if state_in is not None:
+        if tuple(state_in.shape) != ((B, D, m.S, 2) if cplx else (B, D, m.S)):
+            raise ValueError(f"state_in has shape {tuple(state_in.shape)}")
+        state_in = state_in.to(torch.float32).contiguous()
+    if fir_state_in is not None:
+        if tuple(fir_state_in.shape) != (B, C3, 2):
+            raise ValueError(f"fir_state_in has shape {tuple(fir_state_in.shape)}, expected {(B, C3, 2)}")
+        fir_state_in = fir_state_in.contiguous()
     p = _lib.FusedIirParams(
-        u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3), b3=None, b3_dtype=0,
+        u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3),
+        b3=_ptr(b3), b3_dtype=_code(b3) if b3 is not None else 0,
         modal=m, bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
-        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), scratch=_ptr(scratch), B=B, L=L, D=D, K3=w3.shape[1],
-        layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip), io_dtype=_code(u))
+        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), scratch=None, B=B, L=L, D=D, K3=w3.shape[1],
+        layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip), io_dtype=_code(u),
+        state_in=_ptr(state_in), fir_state_in=_ptr(fir_state_in),
+        fir_state_dtype=_code(fir_state_in) if fir_state_in is not None else 0)
+    nscratch = _lib.lib().vtx_fused_iir_scratch_bytes(C.byref(p))
+    scratch = torch.empty(nscratch, device=u.device, dtype=torch.uint8) if nscratch > 0 else None
+    p.scratch = _ptr(scratch)
     with _on(u):
         _lib.check(_lib.lib().vtx_fused_iir_fwd(C.byref(p), _stream(u)))
     del keep
