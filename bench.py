@@ -2,7 +2,7 @@
 """Benchmark of the Hyena convolution hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mr|se|li|decode_mr|decode_se|decode_li|decode_stack]
+                    [--workload mr|se|li|li_pc|decode_mr|decode_se|decode_li|decode_stack]
 
 Default workload: Hyena-MR grouped causal FIR prefill, B=4, L=8192, D=4096, bf16 I/O with fp32
 accumulation, 128-tap filters shared by groups of 16 channels, featurizer and gates fused
@@ -38,6 +38,11 @@ WORKLOADS = {
                name="hyena_se_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + 7-tap grouped FIR + gate)"),
     "li": dict(B=1, L=131072, D=4096, G=256, K=0, io="bf16", seed=2,
                name="hyena_li_prefill B=1 L=131072 D=4096 bf16 (featurizer3 + gate + 16-pole modal filter + gate)"),
+    # the long-filter layer as Evo 2 has it (configs/evo2-7b-8k.yml: hcl_filter_groups == hidden size): 16 real poles
+    # per CHANNEL, at the 7B prefill shape of configuration 2
+    "li_pc": dict(B=4, L=8192, D=4096, G=4096, K=0, io="bf16", seed=2, real_poles=True,
+                  name="hyena_li_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + modal long conv, 16 real poles per "
+                       "channel + skip, state after the last token)"),
     # one-token decode of one Hyena layer (one launch): a step = B tokens; fp32 caches as after the first decode step
     "decode_mr": dict(B=64, L=1, D=4096, G=256, K=128, io="bf16", seed=3, decode=True,
                       name="hyena_mr_decode B=64 D=4096 bf16 (one layer, one token: featurizer + 128-tap FIR caches)"),
@@ -84,9 +89,11 @@ def make_inputs(w, device, dtype=torch.bfloat16):
         p["Dp"] = torch.zeros(D, dtype=dtype) if K >= 128 else None
     else:
         p["log_poles"] = torch.log(0.9 + 0.099 * torch.rand(G, 16, generator=g))[..., None]
-        p["theta"] = torch.pi * torch.rand(G, 16, generator=g)
         p["residues"] = torch.randn(G, 16, generator=g)
-        p["res_im"] = torch.randn(G, 16, generator=g)
+        p["theta"] = p["res_im"] = None
+        if not w.get("real_poles"):
+            p["theta"] = torch.pi * torch.rand(G, 16, generator=g)
+            p["res_im"] = torch.randn(G, 16, generator=g)
         p["Dp"] = torch.randn(D, generator=g).to(dtype)
     if w.get("decode"):
         # caches as a decode step leaves them (fp32); several sets, used in turn, so that the timed steps stream
@@ -172,7 +179,7 @@ def run_block(name, pc, u=None):
     if name == "se":
         return hyena_ops.hyena_se_fwd(u, pc["w3"], None, pc["h"])[0]
     return hyena_ops.hyena_li_fwd(u, pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"], theta=pc["theta"],
-                                  res_im=pc["res_im"])[0]
+                                  res_im=pc["res_im"], want_state=name == "li_pc")[0]
 
 
 class ClockSampler:
@@ -219,7 +226,7 @@ def cpu_baseline(name, w, steps=1):
     """The reference's CPU path (oracle/torch_port.py) on a bounded channel slice, scaled to the full width."""
     from oracle import torch_port as TP
     torch.manual_seed(0)
-    Ds = {"mr": 256, "se": 256, "li": 64}[name]
+    Ds = {"mr": 256, "se": 256, "li": 64, "li_pc": 64}[name]
     B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
     Gs = max(1, G * Ds // D)
     dt = torch.bfloat16
@@ -445,7 +452,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload (no cache outputs requested)
-LAUNCHES = {"mr": 1, "se": 1, "li": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
+LAUNCHES = {"mr": 1, "se": 1, "li": 1, "li_pc": 3, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9}   # small-case captures scaled by the units of a bench launch

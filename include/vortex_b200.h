@@ -140,6 +140,11 @@ int vtx_gcg_fwd(const vtx_gcg_params* p, void* stream);
  * (persistent CTAs, Toeplitz operand in TMEM); other dtypes / group sizes with K <= 16 run on CUDA cores
  * with TMA-staged rows.
  * The base address and the row pitch of u and y must be 16-byte aligned.
+ * Chunked prefill (a long prompt in pieces; the reference forces it token by token, generation.py:94-101):
+ * u_hist_rows = H > 0 says that the H rows BEFORE u[b][0] in memory (same row pitch) are the projection rows
+ * that precede this chunk in the sequence; the kernels then read them as the halo of the first outputs
+ * instead of zeros.  H must be at least K + 1 (K - 1 taps back plus the 2 rows of the featurizer).  The caches
+ * written are then always full: fir_state [B,3D,2], inner_state [B,D,K-1].
  * ------------------------------------------------------------------------ */
 typedef struct vtx_fused_fir_params {
     const void* u;       int64_t u_stride_b, u_stride_l;   /* channel stride 1 */
@@ -154,6 +159,7 @@ typedef struct vtx_fused_fir_params {
     int64_t layout, num_heads, flip_x1x2;
     int64_t taps, bias_mode;
     int64_t io_dtype;
+    int64_t u_hist_rows;                        /* 0, or >= K + 1 valid rows before u[b][0]  */
 } vtx_fused_fir_params;
 int vtx_fused_fir_fwd(const vtx_fused_fir_params* p, void* stream);
 

@@ -368,3 +368,54 @@ def test_fused_li_chunked_prefill_carries_state(io, cplx, cuts):
     assert rel_l2(st, st_all) <= 1e-5
     ref, _ = _li_cc_oracle(p, L, D, G, cplx, io, "interleaved", 1, False, None)
     assert rel_l2(y, ref) <= (1e-4 if io == "f32" else TOL["bf16"])
+
+
+# io, D, G, K, layout, chunk boundaries
+FIR_CHUNK_CASES = [
+    ("bf16", 64, 4, 128, "interleaved", (0, 1000, 1130, 2500)),     # 128 taps on tensor cores, a chunk of K + 2 rows
+    ("bf16", 128, 8, 7, "interleaved", (0, 300, 308, 900)),         # 7 taps on tensor cores
+    ("f32", 64, 4, 7, "split", (0, 260, 700)),                      # CUDA-core kernel, plane layout
+]
+
+
+@pytest.mark.parametrize("io,D,G,K,layout,cuts", FIR_CHUNK_CASES)
+def test_fused_fir_chunked_prefill(io, D, G, K, layout, cuts):
+    """A prompt prefilled in chunks: (a) chunks that are views of the whole projection buffer, every call told that
+    K + 1 earlier rows precede its view; (b) the same through the PrefillChunks staging buffer (one chunk shorter than
+    the history it keeps).  Output and final caches equal those of one call over the whole prompt."""
+    from vortex_b200 import hyena_ops, ops
+    B, L = 2, cuts[-1]
+    p = make_block(59, B, L, D, G, K, io)
+    pc = cuda(p)
+
+    def call(u, hist, want_state=True):
+        if K >= 128:
+            return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"], layout=layout, want_state=want_state,
+                                          hist_rows=hist)
+        return hyena_ops.hyena_se_fwd(u, pc["w3"], None, pc["h"], layout=layout, want_state=want_state, hist_rows=hist)
+
+    y_all, fs_all, st_all = call(pc["u"], 0)
+    tol = 1e-6 if io == "f32" else 1e-3          # the 128-row tiles of a chunk start elsewhere: other summation order
+    # (a) views
+    ys = []
+    for t0, t1 in zip(cuts[:-1], cuts[1:]):
+        yc, fs, st = call(pc["u"][:, t0:t1], K + 1 if t0 else 0)
+        ys.append(yc)
+    ops.device_status()
+    assert rel_l2(torch.cat(ys, dim=1), y_all) <= tol
+    assert torch.equal(fs, fs_all) and torch.equal(st, st_all)
+    # (b) staging buffer; chunks: the cuts, then the rest one short chunk at a time
+    hist = K + 3
+    stage = hyena_ops.PrefillChunks(B, max(b - a for a, b in zip(cuts[:-1], cuts[1:])), 3 * D, hist, device="cuda",
+                                    dtype=pc["u"].dtype)
+    ys = []
+    for t0, t1 in zip(cuts[:-1], cuts[1:]):
+        stage.rows(t1 - t0).copy_(pc["u"][:, t0:t1])        # stands for the projection GEMM of the chunk
+        yc, fs, st = call(stage.rows(t1 - t0), stage.hist_rows)
+        ys.append(yc)
+        stage.advance(t1 - t0)
+    ops.device_status()
+    assert rel_l2(torch.cat(ys, dim=1), y_all) <= tol
+    assert torch.equal(fs, fs_all) and torch.equal(st, st_all)
+    with pytest.raises(ValueError):
+        call(pc["u"][:, 200:300], K)                         # fewer history rows than the filter reaches back

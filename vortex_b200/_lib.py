@@ -41,7 +41,7 @@ GcgParams = _struct("GcgParams", """
 FusedFirParams = _struct("FusedFirParams", """
     p:u i:u_stride_b i:u_stride_l p:w3 i:w3_dtype p:b3 i:b3_dtype p:h i:h_dtype p:bias i:bias_dtype
     p:y i:y_stride_b i:y_stride_l p:fir_state p:inner_state
-    i:B i:L i:D i:G i:K3 i:K i:layout i:num_heads i:flip_x1x2 i:taps i:bias_mode i:io_dtype""")
+    i:B i:L i:D i:G i:K3 i:K i:layout i:num_heads i:flip_x1x2 i:taps i:bias_mode i:io_dtype i:u_hist_rows""")
 
 ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G i:S")
 

@@ -37,6 +37,7 @@ struct FusedArgs {
     int64_t nslab, nseg, seg_len;
     int layout, flip, taps, bias_mode;
     int64_t hd;       // channels per head (column split)
+    int64_t hist;     // rows before u[b][0] that hold the sequence's earlier samples (chunked prefill), 0 or >= K + 1
 };
 
 // Packed-column base of the q, k, v planes of a slab (plane layouts only).
@@ -89,6 +90,7 @@ __global__ void __launch_bounds__(32) fused_fir_kernel(const __grid_constant__ C
     const int64_t te = ts + a.seg_len < a.L ? ts + a.seg_len : a.L;
     const int64_t row0 = ts - halo;
     const int nstages = (int)((te - row0 + ROWS - 1) / ROWS);
+    const int64_t tmin = a.hist > 2 ? -(a.hist - 2) : 0;      // first sample whose featurizer output is complete
 
     int64_t pcol[3] = {0, 0, 0};
     if (!INTERLEAVED) plane_cols(a, d0, pcol);
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(32) fused_fir_kernel(const __grid_constant__ C
         const int slot = s % FF_STAGES;
         const uint32_t bar = smem_u32(&bars[slot]);
         const uint32_t dst = smem_u32(base + slot * FF_STAGE_BYTES);
-        const int r = (int)(row0 + (int64_t)s * ROWS);
+        const int r = (int)(row0 + (int64_t)s * ROWS + a.hist);      // the tensor map starts a.hist rows before u
         mbar_expect_tx(bar, FF_STAGE_BYTES);
         if (INTERLEAVED) {
             tma_load_3d(dst, &tmap, bar, (int)(3 * d0), r, (int)b);
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(32) fused_fir_kernel(const __grid_constant__ C
                     z[sx] = acc;
                 }
                 const float zq = swap_qk ? z[1] : z[0], zk = swap_qk ? z[0] : z[1];
-                float kv = t >= 0 ? zk * z[2] : 0.f;
+                float kv = t >= tmin ? zk * z[2] : 0.f;
                 float acc = h[c][KMAX - 1] * kv;
 #pragma unroll
                 for (int m = 0; m < KMAX - 1; ++m) acc = fmaf(h[c][m], kvw[c][m], acc);
@@ -231,14 +233,15 @@ __global__ void fused_state_kernel(const T* __restrict__ u, int64_t u_stride_b, 
     int64_t pc[3];
     map.get(d, pc[0], pc[1], pc[2]);
     const T* ub = u + b * u_stride_b;
+    // with history rows before u the caches are always full (negative times index those rows)
     if (fir_state) {
-        const int64_t n3 = a.L < FF_K3 - 1 ? a.L : FF_K3 - 1;
+        const int64_t n3 = (a.hist > 0 || a.L >= FF_K3 - 1) ? FF_K3 - 1 : a.L;
         for (int s = 0; s < 3; ++s)
             for (int64_t j = 0; j < n3; ++j)
                 fir_state[(b * 3 * a.D + pc[s]) * n3 + j] = ub[(a.L - n3 + j) * u_stride_l + pc[s]];
     }
     if (inner_state) {
-        const int64_t ns = a.L < a.K - 1 ? a.L : a.K - 1;
+        const int64_t ns = (a.hist > 0 || a.L >= a.K - 1) ? a.K - 1 : a.L;
         for (int64_t j = 0; j < ns; ++j) {
             const int64_t t = a.L - ns + j;
             float z[3];
@@ -246,7 +249,7 @@ __global__ void fused_state_kernel(const T* __restrict__ u, int64_t u_stride_b, 
                 float acc = a.b3 ? ld_param(a.b3, a.b3_dtype, pc[s]) : 0.f;
                 for (int jj = 0; jj < FF_K3; ++jj) {
                     int64_t tt = t - (FF_K3 - 1) + jj;
-                    if (tt >= 0) acc = fmaf(ld_param(a.w3, a.w3_dtype, pc[s] * FF_K3 + jj), to_f32<T>(ub[tt * u_stride_l + pc[s]]), acc);
+                    if (tt >= -a.hist) acc = fmaf(ld_param(a.w3, a.w3_dtype, pc[s] * FF_K3 + jj), to_f32<T>(ub[tt * u_stride_l + pc[s]]), acc);
                 }
                 z[s] = acc;
             }
@@ -280,6 +283,7 @@ int launch_fused_state_bf16(const vtx_fused_fir_params* p, cudaStream_t s) {
     a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0;
     a.hd = p->layout == VTX_QKV_COLUMN_SPLIT ? p->D / p->num_heads : p->D;
+    a.hist = p->u_hist_rows;
     using T = __nv_bfloat16;
     fused_state_kernel<T><<<(unsigned)ceil_div<int64_t>(a.B * a.D, 128), 128, 0, s>>>(
         static_cast<const T*>(p->u), p->u_stride_b, p->u_stride_l, a, static_cast<T*>(p->fir_state),
@@ -298,6 +302,8 @@ extern "C" int vtx_fused_fir_fwd(const vtx_fused_fir_params* p, void* stream) {
     VTX_REQUIRE(p->K3 == FF_K3, VTX_ERR_UNSUPPORTED, "fused_fir: featurizer length %lld (only 3 is fused)",
                 (long long)p->K3);
     VTX_REQUIRE(valid_dtype(p->io_dtype), VTX_ERR_BAD_ARG, "fused_fir: bad io dtype");
+    VTX_REQUIRE(p->u_hist_rows == 0 || p->u_hist_rows >= p->K + 1, VTX_ERR_BAD_ARG,
+                "fused_fir: u_hist_rows must be 0 or at least K + 1 = %lld", (long long)(p->K + 1));
     VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || p->bias, VTX_ERR_BAD_ARG, "fused_fir: bias mode set without a bias");
     VTX_REQUIRE(p->B <= 65535, VTX_ERR_UNSUPPORTED, "fused_fir: batch too large");
     // Kernel choice: the tensor-core kernel (bf16, groups of 16 channels, up to 128 taps) is the faster one for every
@@ -315,6 +321,7 @@ extern "C" int vtx_fused_fir_fwd(const vtx_fused_fir_params* p, void* stream) {
     a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps; a.bias_mode = (int)p->bias_mode;
     a.hd = p->D;
+    a.hist = p->u_hist_rows;
     if (p->layout == VTX_QKV_COLUMN_SPLIT) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG,
                     "fused_fir: column split needs num_heads dividing D");
@@ -338,7 +345,9 @@ extern "C" int vtx_fused_fir_fwd(const vtx_fused_fir_params* p, void* stream) {
 
     const bool inter = p->layout == VTX_QKV_INTERLEAVED;
     CUtensorMap tmap;
-    if (int rc = make_tmap_3d(&tmap, p->u, p->io_dtype, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
+    // the tensor map starts at the first history row
+    const char* u_first = static_cast<const char*>(p->u) - p->u_hist_rows * p->u_stride_l * es;
+    if (int rc = make_tmap_3d(&tmap, u_first, p->io_dtype, 3 * p->D, p->L + p->u_hist_rows, p->B, p->u_stride_l, p->u_stride_b,
                               inter ? 3 * FF_CH : FF_CH, rows, 0, "fused_fir"))
         return rc;
     cudaStream_t s = (cudaStream_t)stream;

@@ -114,6 +114,7 @@ struct Args {
     int64_t nquad, nitems;                 // stream quads per group; work items (group x quad) of the launch
     int layout, flip, taps, has_bias;
     int64_t hd;
+    int hist;        // rows before u[b][0] that hold the sequence's earlier samples (the tensor map starts there)
     int pf;          // chunks of L2 prefetch distance (0 = off)
     int dbg;         // diagnostic builds only: knock out parts of the kernel to time the rest
     unsigned long long* trace;   // diagnostic builds only
@@ -643,7 +644,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
                 for (int s = 0; s < NS; ++s) {
                     const Stream st = stream_of(a, item_quad(t), s);
-                    row_base[s] = (int)st.ts - CHUNK - 2 - s;
+                    row_base[s] = (int)st.ts - CHUNK - 2 - s + a.hist;
                     bidx[s] = (int)st.b;
                 }
                 for (int hh = 0; hh < 2 * nchunk; ++hh, ++nh) {
@@ -700,6 +701,7 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
     a.hd = p->D;
+    a.hist = (int)p->u_hist_rows;
     a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 0;
     a.dbg = getenv("VTX_MR_DBG") ? atoi(getenv("VTX_MR_DBG")) : 0;
     a.trace = getenv("VTX_MR_TRACE_PTR") ? (unsigned long long*)strtoull(getenv("VTX_MR_TRACE_PTR"), nullptr, 0) : nullptr;
@@ -729,7 +731,9 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
 
     const bool inter = p->layout == VTX_QKV_INTERLEAVED;
     CUtensorMap tmap;
-    if (int rc = make_tmap_3d(&tmap, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
+    // the tensor map starts at the first history row (chunked prefill), else at u
+    const __nv_bfloat16* u_first = static_cast<const __nv_bfloat16*>(p->u) - p->u_hist_rows * p->u_stride_l;
+    if (int rc = make_tmap_3d(&tmap, u_first, VTX_BF16, 3 * p->D, p->L + p->u_hist_rows, p->B, p->u_stride_l, p->u_stride_b,
                               inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_fir(mr)"))
         return rc;
     const int variant = !inter ? 0 : (a.flip ? 2 : 1);

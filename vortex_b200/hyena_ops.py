@@ -50,30 +50,65 @@ def _tensor_core_ok(u, b3, h, layout, num_heads):
     return True
 
 
-def _fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state):
+def _fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state, hist_rows=0):
     """Kernel choice per workload: tcgen05 blocked-Toeplitz kernel for bf16 I/O with groups of 16 channels and up
     to 128 taps, single-pass CUDA-core kernel for other dtypes / group sizes up to 16 taps, two-launch general path
     otherwise (the choice between the first two is made inside vtx_fused_fir_fwd)."""
     D = u.shape[-1] // 3
     if _fused_ok(u, h, layout, num_heads) or _tensor_core_ok(u, b3, h, layout, num_heads):
         return ops.fused_fir_fwd(u, w3, b3, h, D_skip, D, taps=taps, bias_mode=bias_mode, layout=layout,
-                                 num_heads=num_heads, flip=flip, want_state=want_state)
+                                 num_heads=num_heads, flip=flip, want_state=want_state, hist_rows=hist_rows)
+    if hist_rows:
+        raise NotImplementedError("chunked prefill (hist_rows) needs a shape the single-pass kernels take")
     return _general_fir_block(u, w3, b3, h, D_skip, taps, bias_mode, layout, num_heads, flip, want_state)
 
 
 def hyena_se_fwd(u, short_filter_weight, short_filter_bias, h, *, layout="interleaved", num_heads=1, flip=False,
-                 want_state=False):
+                 want_state=False, hist_rows=0):
     """Hyena-SE block (inner filter shorter than 128 taps, cross-correlation taps, no skip term).
-    u [B, L, 3D] -> y [B, L, D] (+ featurizer cache [B, 3D, 2], inner cache [B, D, K-1])."""
+    u [B, L, 3D] -> y [B, L, D] (+ featurizer cache [B, 3D, 2], inner cache [B, D, K-1]).
+    ``hist_rows``: see PrefillChunks (the rows before ``u`` in memory are the sequence's earlier rows)."""
     return _fir_block(u, short_filter_weight, short_filter_bias, h, None, TAPS_XCORR, BIAS_NONE, layout, num_heads,
-                      flip, want_state)
+                      flip, want_state, hist_rows)
 
 
 def hyena_mr_fwd(u, short_filter_weight, short_filter_bias, h, D_skip, *, layout="interleaved", num_heads=1,
-                 flip=False, want_state=False):
+                 flip=False, want_state=False, hist_rows=0):
     """Hyena-MR block (128-tap grouped filter, convolution taps, per-channel skip term D_skip)."""
     return _fir_block(u, short_filter_weight, short_filter_bias, h, D_skip, TAPS_CONV, BIAS_GATED, layout, num_heads,
-                      flip, want_state)
+                      flip, want_state, hist_rows)
+
+
+class PrefillChunks:
+    """Staging buffer for prefilling a long prompt in chunks through the FIR blocks (what the reference does token
+    by token when it forces a prompt, generation.py:94-101).
+
+    The projection GEMM of a chunk writes its [B, Lc, 3D] output into ``rows(Lc)``; the ``hist`` rows in front of
+    it hold the end of the previous chunk, so that ``hyena_se_fwd / hyena_mr_fwd(..., hist_rows=chunks.hist_rows)``
+    see the samples their first outputs reach back to.  ``advance(Lc)`` then moves the last ``hist`` rows to the
+    front for the next chunk (a copy of hist x 3D elements per sequence).  ``hist`` must be at least K + 1 for the
+    longest FIR filter that reads the buffer (130 for the 128-tap filter)."""
+
+    def __init__(self, B, max_chunk, D3, hist, *, device, dtype):
+        self.hist, self.max_chunk = int(hist), int(max_chunk)
+        self.buf = torch.zeros(B, self.hist + self.max_chunk, D3, device=device, dtype=dtype)
+        self.seen = 0            # samples of the sequence consumed so far
+
+    @property
+    def hist_rows(self):
+        """What to pass as ``hist_rows``: 0 for the first chunk (nothing precedes it), ``hist`` afterwards."""
+        return self.hist if self.seen > 0 else 0
+
+    def rows(self, Lc):
+        if Lc > self.max_chunk:
+            raise ValueError(f"chunk of {Lc} rows > max_chunk {self.max_chunk}")
+        return self.buf[:, self.hist:self.hist + Lc]
+
+    def advance(self, Lc):
+        # the last `hist` rows seen so far (of this chunk and, for a short chunk, of the history before it)
+        tail = self.buf[:, Lc:Lc + self.hist].clone()
+        self.buf[:, :self.hist] = tail
+        self.seen += Lc
 
 
 def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues, D_skip, *, theta=None, res_im=None,

@@ -173,10 +173,15 @@ def gcg_fwd_bdl(q, k, v, h, bias=None, *, taps=TAPS_XCORR, bias_mode=BIAS_NONE, 
 
 
 def fused_fir_fwd(u: torch.Tensor, w3, b3, h, bias, D: int, *, taps: int, bias_mode: int, layout="interleaved",
-                  num_heads=1, flip=False, want_state=True):
-    """Channel-last fused block: u [B, L, 3D] -> y [B, L, D], fir_state [B, 3D, min(L,2)], inner [B, D, min(L,K-1)]."""
+                  num_heads=1, flip=False, want_state=True, hist_rows=0):
+    """Channel-last fused block: u [B, L, 3D] -> y [B, L, D], fir_state [B, 3D, min(L,2)], inner [B, D, min(L,K-1)].
+
+    ``hist_rows`` = H > 0 (chunked prefill): ``u`` is a view whose H preceding rows in memory (same row pitch) hold
+    the sequence's earlier projection rows, H >= K + 1; the caches returned are then always full."""
     _need_cuda(u, w3, b3, h, bias)
     if u.stride(2) != 1:
+        if hist_rows:
+            raise ValueError("hist_rows needs u with unit channel stride (a view into the buffer that holds the history)")
         u = u.contiguous()
     B, L, C3 = u.shape
     if C3 != 3 * D:
@@ -188,8 +193,11 @@ def fused_fir_fwd(u: torch.Tensor, w3, b3, h, bias, D: int, *, taps: int, bias_m
     K, K3 = h.shape[1], w3.shape[1]
     b3, bias = _param(b3, u), _param(bias, u)
     y = torch.empty(B, L, D, device=u.device, dtype=u.dtype)
-    fs = torch.empty(B, C3, min(L, K3 - 1), device=u.device, dtype=u.dtype) if want_state else None
-    ist = torch.empty(B, D, min(L, K - 1), device=u.device, dtype=u.dtype) if want_state else None
+    if hist_rows and u.storage_offset() < hist_rows * u.stride(1):
+        raise ValueError(f"hist_rows={hist_rows}: u starts {u.storage_offset() // max(u.stride(1), 1)} rows into its storage")
+    n3, ns = (K3 - 1, K - 1) if hist_rows else (min(L, K3 - 1), min(L, K - 1))
+    fs = torch.empty(B, C3, n3, device=u.device, dtype=u.dtype) if want_state else None
+    ist = torch.empty(B, D, ns, device=u.device, dtype=u.dtype) if want_state else None
     p = _lib.FusedFirParams(
         u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3),
         b3=_ptr(b3), b3_dtype=_code(b3) if b3 is not None else 0, h=_ptr(h), h_dtype=_code(h),
@@ -198,7 +206,7 @@ def fused_fir_fwd(u: torch.Tensor, w3, b3, h, bias, D: int, *, taps: int, bias_m
         fir_state=_ptr(fs) if (fs is not None and fs.numel()) else None,
         inner_state=_ptr(ist) if (ist is not None and ist.numel()) else None,
         B=B, L=L, D=D, G=G, K3=K3, K=K, layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip),
-        taps=taps, bias_mode=bias_mode if bias is not None else BIAS_NONE, io_dtype=_code(u))
+        taps=taps, bias_mode=bias_mode if bias is not None else BIAS_NONE, io_dtype=_code(u), u_hist_rows=hist_rows)
     with _on(u):
         _lib.check(_lib.lib().vtx_fused_fir_fwd(C.byref(p), _stream(u)))
     return y, fs, ist
