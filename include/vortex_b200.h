@@ -257,6 +257,46 @@ typedef struct vtx_fused_iir_params {
 int64_t vtx_fused_iir_scratch_bytes(const vtx_fused_iir_params* p);
 int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream);
 
+/* Short depthwise causal convolution of the reference's conv extension (its pybind module
+ * local_causal_conv1d_cuda, vortex/ops/conv/csrc/causal_conv1d.cpp:473-477):
+ *   vtx_causal_conv1d_fwd    replaces causal_conv1d_fwd    (causal_conv1d.cpp:130-236, causal_conv1d_fwd.cu)
+ *   vtx_causal_conv1d_update replaces causal_conv1d_update (causal_conv1d.cpp:382-470, causal_conv1d_update.cu)
+ * x, out [B,D,L] of the I/O dtype with element strides (time-contiguous or channel-contiguous, as the reference
+ * accepts), weight [D,W] contiguous with W in 2..4, optional bias [D], optional SiLU.
+ * fwd: seq_idx int32 [B,L] contiguous (packed sequences: a tap counts only if it has the same index as the
+ * output sample), initial_states [B,D,W-1] (samples before the first), final_states [B,D,W-1] written when given.
+ * update: conv_state [rows,D,state_len] updated in place; cache_seqlens int32 [B] makes it a circular buffer
+ * written at cache_seqlens[b] + i (mod state_len); conv_state_indices int32 [B] picks the row of conv_state
+ * per batch element (continuous batching).
+ * ------------------------------------------------------------------------ */
+typedef struct vtx_causal_conv1d_params {
+    const void* x;       int64_t x_stride_b, x_stride_d, x_stride_l;
+    const void* weight;  int64_t weight_dtype;
+    const void* bias;    int64_t bias_dtype;       /* or NULL */
+    const int32_t* seq_idx;                         /* or NULL */
+    const void* initial_states; int64_t is_stride_b, is_stride_d, is_stride_l;   /* or NULL */
+    void* final_states;  int64_t fs_stride_b, fs_stride_d, fs_stride_l;          /* or NULL */
+    void* out;           int64_t out_stride_b, out_stride_d, out_stride_l;
+    int64_t B, D, L, W;
+    int64_t silu;
+    int64_t io_dtype;
+} vtx_causal_conv1d_params;
+int vtx_causal_conv1d_fwd(const vtx_causal_conv1d_params* p, void* stream);
+
+typedef struct vtx_causal_conv1d_update_params {
+    const void* x;       int64_t x_stride_b, x_stride_d, x_stride_l;
+    void* conv_state;    int64_t cs_stride_b, cs_stride_d, cs_stride_l; int64_t state_len;
+    const void* weight;  int64_t weight_dtype;
+    const void* bias;    int64_t bias_dtype;       /* or NULL */
+    const int32_t* cache_seqlens;                   /* or NULL */
+    const int32_t* conv_state_indices;              /* or NULL */
+    void* out;           int64_t out_stride_b, out_stride_d, out_stride_l;
+    int64_t B, D, L, W;
+    int64_t silu;
+    int64_t io_dtype;
+} vtx_causal_conv1d_update_params;
+int vtx_causal_conv1d_update(const vtx_causal_conv1d_update_params* p, void* stream);
+
 /* Hyena-X forward (vortex/ops/hyena_x/triton_indirect_fwd.py:262 hyena_x_bdl_fwd, reference :413-424):
  * o = fir(h[0:D], q) * fir(h[D:2D], k) * fir(h[2D:3D], v), depthwise causal filters of Lh <= 16 taps
  * (cross-correlation order), q, k, v, o [B,D,L] contiguous, h [3D,Lh]. */

@@ -213,6 +213,75 @@ def hyena_x(qkv, h, io="f32", mirror=True):
     return _maybe(_maybe(q * k, io, mirror) * v, io, mirror)
 
 
+def causal_conv1d(x, weight, bias=None, initial_states=None, seq_idx=None, silu=False, io="f32", mirror=False):
+    """Short depthwise causal convolution of the reference's conv extension
+    (vortex/ops/conv/local_causal_conv1d/causal_conv1d_interface.py:187-222 causal_conv1d_ref; kernel
+    csrc/causal_conv1d_fwd.cu:300-330 for seq_idx):
+    out[b,d,t] = bias[d] + sum_w weight[d,w] * xx[b,d,t-(W-1)+w], xx = [initial_states | x] (zeros without initial
+    states); with seq_idx a tap counts only if its position lies in this call (t' >= 0) and seq_idx[b,t'] ==
+    seq_idx[b,t]; optional SiLU; result rounded to the I/O dtype.  Also returns the final states: the last W-1
+    samples of xx.  x [B,D,L], weight [D,W] -> ([B,D,L], [B,D,W-1]).
+    mirror=True rounds the convolution result to the I/O dtype before the SiLU, as the PyTorch reference function
+    does (its conv1d returns the narrow dtype); the CUDA kernel keeps fp32 up to the final cast (mirror=False)."""
+    x = round_io(x, io)
+    w = np.asarray(weight, dtype=np.float64)
+    B, D, L = x.shape
+    W = w.shape[1]
+    ini = np.zeros((B, D, W - 1)) if initial_states is None else round_io(initial_states, io)
+    xx = np.concatenate([ini, x], axis=-1)
+    out = np.zeros((B, D, L))
+    if bias is not None:
+        out += np.asarray(bias, dtype=np.float64)[None, :, None]
+    for j in range(W):
+        term = w[None, :, j, None] * xx[..., j:j + L]                    # position t - (W-1) + j
+        if seq_idx is not None:
+            sid = np.asarray(seq_idx)
+            pos = np.arange(L) - (W - 1) + j
+            same = np.zeros((B, L), dtype=bool)
+            ok = pos >= 0
+            same[:, ok] = sid[:, pos[ok]] == sid[:, ok]
+            term = term * same[:, None, :]
+        out += term
+    if mirror:
+        out = round_io(out, io)
+    if silu:
+        out = out / (1.0 + np.exp(-out))
+    return round_io(out, io), xx[..., xx.shape[-1] - (W - 1):]
+
+
+def causal_conv1d_update(x, conv_state, weight, bias=None, silu=False, cache_seqlens=None, io="f32"):
+    """Decode-time update of the same convolution (causal_conv1d_interface.py:250-282, kernel
+    csrc/causal_conv1d_update.cu): x [B,D,Lq] new samples, conv_state [B,D,state_len] (state_len >= W-1).
+    Without cache_seqlens the state is a shift register (new state = last state_len samples of [state | x]); with it
+    a circular buffer: the W-1 samples before position cache_seqlens[b] are read, x is written at positions
+    cache_seqlens[b] + i (mod state_len).  Returns (out [B,D,Lq], new conv_state)."""
+    x = round_io(x, io)
+    st = np.array(round_io(conv_state, io))
+    w = np.asarray(weight, dtype=np.float64)
+    B, D, Lq = x.shape
+    W, SL = w.shape[1], st.shape[-1]
+    if cache_seqlens is None:
+        xn = np.concatenate([st, x], axis=-1)
+        new = xn[..., -SL:]
+    else:
+        cs = np.asarray(cache_seqlens).astype(np.int64)
+        widx = (np.arange(-(W - 1), 0)[None, :] + cs[:, None]) % SL                       # [B, W-1]
+        hist = np.take_along_axis(st, np.broadcast_to(widx[:, None, :], (B, D, W - 1)), axis=2)
+        xn = np.concatenate([hist, x], axis=-1)
+        new = st.copy()
+        cidx = (np.arange(Lq)[None, :] + cs[:, None]) % SL
+        np.put_along_axis(new, np.broadcast_to(cidx[:, None, :], (B, D, Lq)), x, axis=2)
+    n = xn.shape[-1]
+    out = np.zeros((B, D, Lq))
+    if bias is not None:
+        out += np.asarray(bias, dtype=np.float64)[None, :, None]
+    for j in range(W):
+        out += w[None, :, j, None] * xn[..., n - Lq - (W - 1) + j:n - (W - 1) + j]
+    if silu:
+        out = out / (1.0 + np.exp(-out))
+    return round_io(out, io), new
+
+
 def modal_filter(log_poles, residues, L):
     """HyenaCascade.compute_filter (model.py:390-398): real modal form,
     h[g, t] = sum_s R[g, s] * exp(lambda[g, s] * t), float32 arithmetic.

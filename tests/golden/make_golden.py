@@ -194,6 +194,27 @@ def main(ref_root):
             k = f"hx_{io}_Lh{Lh}"
             out[k + "_qkv"], out[k + "_h"], out[k + "_y"] = np32(qkv), np32(h), np32(hyena_x_fwd_ref(qkv, h))
 
+    # ---- causal_conv1d reference (width 2..4 depthwise conv, bias, initial / final states, SiLU) --------------
+    # the interface module imports its CUDA extension at import time; the reference function itself is pure PyTorch
+    sys.modules.setdefault("local_causal_conv1d_cuda", types.ModuleType("local_causal_conv1d_cuda"))
+    sys.path.insert(0, os.path.join(ref_root, "vortex", "ops", "conv", "local_causal_conv1d"))
+    from causal_conv1d_interface import causal_conv1d_ref
+    for io, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        for W in (2, 3, 4):
+            for L in (1, 2, 37):
+                g = torch.Generator().manual_seed(8000 + 10 * W + L)
+                B, D = 2, 12
+                x = torch.randn(B, D, L, generator=g).to(dt)
+                w = torch.randn(D, W, generator=g).to(dt)
+                b = torch.randn(D, generator=g).to(dt)
+                ini = torch.randn(B, D, W - 1, generator=g).to(dt)
+                k = f"cc1d_{io}_W{W}_L{L}"
+                out[k + "_x"], out[k + "_w"], out[k + "_b"], out[k + "_ini"] = np32(x), np32(w), np32(b), np32(ini)
+                y0, f0 = causal_conv1d_ref(x, w, None, None, True, None, None)
+                y1, f1 = causal_conv1d_ref(x, w, b, ini, True, None, "silu")
+                out[k + "_y_plain"], out[k + "_fs_plain"] = np32(y0), np32(f0)
+                out[k + "_y_full"], out[k + "_fs_full"] = np32(y1), np32(f1)
+
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

@@ -323,3 +323,88 @@ def test_hyena_x_vs_oracle(io, B, D, L, Lh):
     assert rel_l2(y, ref) <= {"f32": 2e-6, "bf16": 2.5e-3, "f16": 1e-3}[io]
     q, k, v = qkv.cuda().split([D, D, D], dim=1)
     assert torch.equal(hyena_ops.hyena_x_bdl_fwd(q, k, v, h.cuda()), y)
+
+
+# ------------------------------------------------------------------ short causal convolution of the conv extension
+CC_TOL = {"f32": 2e-6, "bf16": 2.5e-3, "f16": 1e-3}
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("L", [1, 2, 37])
+def test_golden_causal_conv1d(golden, io, W, L):
+    """The reference's causal_conv1d_ref vectors: plain, and bias + initial states + SiLU; final states bit-exact."""
+    from vortex_b200 import hyena_ops
+    k = f"cc1d_{io}_W{W}_L{L}"
+    x, w, b, ini = (T(golden[k + s], io) for s in ("_x", "_w", "_b", "_ini"))
+    y = hyena_ops.causal_conv1d_fn(x, w)
+    assert y.shape == x.shape and y.dtype == DT[io]
+    assert rel_l2(y, golden[k + "_y_plain"]) <= CC_TOL[io]
+    xl = x.transpose(1, 2).contiguous().transpose(1, 2)               # channel-last, as initial states require
+    il = ini.transpose(1, 2).contiguous().transpose(1, 2)
+    fs = torch.empty_like(il)
+    y = hyena_ops.causal_conv1d_fn(xl, w, b, None, il, fs, "silu")
+    assert y.stride() == xl.stride()
+    assert rel_l2(y, golden[k + "_y_full"]) <= 2 * CC_TOL[io]         # the reference rounds once more before the SiLU
+    assert np.array_equal(to_np(fs), golden[k + "_fs_full"])
+
+
+@pytest.mark.parametrize("io,B,D,L,W,cl", [("bf16", 2, 64, 1000, 4, True), ("bf16", 3, 40, 513, 3, False),
+                                            ("f32", 1, 8, 9, 2, True), ("f16", 2, 24, 130, 4, False),
+                                            ("bf16", 1, 4096, 2048, 4, True)])
+def test_causal_conv1d_vs_oracle(io, B, D, L, W, cl):
+    """Both layouts, packed sequences (seq_idx), initial and final states, against the oracle (kernel rounding)."""
+    from vortex_b200 import hyena_ops
+    g = torch.Generator().manual_seed(900 + L)
+    x = torch.randn(B, D, L, generator=g).to(DT[io])
+    w = (torch.randn(D, W, generator=g) / W ** 0.5).to(DT[io])
+    b = torch.randn(D, generator=g).to(DT[io])
+    ini = torch.randn(B, D, W - 1, generator=g).to(DT[io])
+    cuts = torch.sort(torch.randint(1, max(L, 2), (B, 3), generator=g), dim=1).values
+    sid = (torch.arange(L)[None, :, None] >= cuts[:, None, :]).sum(-1).to(torch.int32)
+
+    def lay(t):
+        t = t.cuda()
+        return t.transpose(1, 2).contiguous().transpose(1, 2) if cl else t
+    xd = lay(x)
+    fs = torch.empty_like(lay(ini))
+    y = hyena_ops.causal_conv1d_fn(xd, w.cuda(), b.cuda(), None, lay(ini), fs, "silu")
+    ref, rfs = O.causal_conv1d(to_np(x), to_np(w), bias=to_np(b), initial_states=to_np(ini), silu=True, io=io)
+    assert y.stride() == xd.stride() and rel_l2(y, ref) <= CC_TOL[io]
+    assert np.array_equal(to_np(fs), rfs.astype(np.float32))
+    y = hyena_ops.causal_conv1d_fn(xd, w.cuda(), None, sid.cuda(), None, None, None)
+    ref, _ = O.causal_conv1d(to_np(x), to_np(w), seq_idx=sid.numpy(), io=io)
+    assert rel_l2(y, ref) <= CC_TOL[io]
+    with pytest.raises(NotImplementedError):
+        hyena_ops.causal_conv1d_fn(xd, w.cuda(), activation="gelu")
+    with pytest.raises(NotImplementedError):
+        hyena_ops.causal_conv1d_fn(xd, torch.randn(D, 5).to(DT[io]).cuda())
+
+
+@pytest.mark.parametrize("io,B,D,Lq,W,SL", [("bf16", 4, 64, 1, 4, 3), ("bf16", 2, 40, 3, 3, 6), ("f32", 3, 8, 1, 2, 1),
+                                             ("f16", 2, 16, 5, 4, 4), ("bf16", 8, 4096, 1, 4, 3)])
+def test_causal_conv1d_update_vs_oracle(io, B, D, Lq, W, SL):
+    """Shift-register state, circular state (cache_seqlens) and indirect rows (conv_state_indices)."""
+    from vortex_b200 import hyena_ops
+    g = torch.Generator().manual_seed(950 + D)
+    x = torch.randn(B, D, Lq, generator=g).to(DT[io])
+    st = torch.randn(B, D, SL, generator=g).to(DT[io])
+    w = (torch.randn(D, W, generator=g) / W ** 0.5).to(DT[io])
+    b = torch.randn(D, generator=g).to(DT[io])
+    ref, rst = O.causal_conv1d_update(to_np(x), to_np(st), to_np(w), bias=to_np(b), silu=True, io=io)
+    s = st.cuda()
+    y = hyena_ops.causal_conv1d_update(x.cuda() if Lq > 1 else x[..., 0].cuda(), s, w.cuda(), b.cuda(), "silu")
+    assert y.shape == (x.shape if Lq > 1 else x.shape[:2])
+    assert rel_l2(y.reshape(B, D, Lq), ref) <= CC_TOL[io]
+    assert np.array_equal(to_np(s), rst.astype(np.float32))
+    if Lq <= SL:
+        cs = torch.tensor([7 + 5 * i for i in range(B)], dtype=torch.int32)
+        ref, rst = O.causal_conv1d_update(to_np(x), to_np(st), to_np(w), cache_seqlens=cs.numpy(), io=io)
+        # indirect rows: the states live in a pool of 2B rows, batch element i uses row 2B-1-2i
+        pool = torch.zeros(2 * B, D, SL, dtype=DT[io]).cuda()
+        rows = torch.tensor([2 * B - 1 - 2 * i for i in range(B)], dtype=torch.int32)
+        pool[rows.long().cuda()] = st.cuda()
+        y = hyena_ops.causal_conv1d_update(x.cuda(), pool, w.cuda(), None, None, cs.cuda(), rows.cuda())
+        assert rel_l2(y, ref) <= CC_TOL[io]
+        assert np.array_equal(to_np(pool[rows.long().cuda()]), rst.astype(np.float32))
+        assert float(pool[(rows.long() - 1).cuda()].abs().sum()) == 0.0

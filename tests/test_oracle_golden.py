@@ -144,3 +144,37 @@ def test_hyena_x(golden, io, Lh):
     k = f"hx_{io}_Lh{Lh}"
     y = O.hyena_x(golden[k + "_qkv"], golden[k + "_h"], io=io)
     close(y, golden[k + "_y"], io, scale=2.0)
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("L", [1, 2, 37])
+def test_causal_conv1d(golden, io, W, L):
+    """The reference's causal_conv1d_ref: plain, and with bias + initial states + SiLU; final states bit-exact."""
+    k = f"cc1d_{io}_W{W}_L{L}"
+    x, w, b, ini = (golden[k + s] for s in ("_x", "_w", "_b", "_ini"))
+    y, fs = O.causal_conv1d(x, w, io=io)
+    close(y, golden[k + "_y_plain"], io)
+    assert np.array_equal(fs.astype(np.float32), golden[k + "_fs_plain"])
+    ym, fs = O.causal_conv1d(x, w, bias=b, initial_states=ini, silu=True, io=io, mirror=True)
+    close(ym, golden[k + "_y_full"], io)
+    assert np.array_equal(fs.astype(np.float32), golden[k + "_fs_full"])
+    y, _ = O.causal_conv1d(x, w, bias=b, initial_states=ini, silu=True, io=io)      # the kernel's rounding
+    # update form == the convolution's last samples, shift-register and circular state
+    st0 = np.concatenate([np.zeros_like(ini[..., :1]), ini], axis=-1)          # state_len = W: one spare slot
+    yu, st1 = O.causal_conv1d_update(x, st0, w, bias=b, silu=True, io=io)
+    assert np.array_equal(yu, y)
+    assert np.array_equal(st1[..., -(W - 1):], fs)
+    B = x.shape[0]
+    cs = np.array([5 + 3 * i for i in range(B)])
+    SL = W + 2
+    circ = np.zeros(ini.shape[:2] + (SL,))
+    for i in range(B):
+        for j in range(W - 1):
+            circ[i, :, (cs[i] - (W - 1) + j) % SL] = ini[i, :, j]
+    if L <= SL:
+        yc, circ1 = O.causal_conv1d_update(x, circ, w, bias=b, silu=True, cache_seqlens=cs, io=io)
+        assert np.array_equal(yc, y)
+        for i in range(B):
+            for t in range(L):
+                assert np.array_equal(circ1[i, :, (cs[i] + t) % SL], O.round_io(x, io)[i, :, t])

@@ -49,6 +49,17 @@ ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G 
 HyenaXParams = _struct("HyenaXParams", "p:q p:k p:v p:h i:h_dtype p:y i:B i:D i:L i:Lh i:io_dtype")
 
 
+CausalConv1dParams = _struct("CausalConv1dParams", """
+    p:x i:x_stride_b i:x_stride_d i:x_stride_l p:weight i:weight_dtype p:bias i:bias_dtype p:seq_idx
+    p:initial_states i:is_stride_b i:is_stride_d i:is_stride_l p:final_states i:fs_stride_b i:fs_stride_d i:fs_stride_l
+    p:out i:out_stride_b i:out_stride_d i:out_stride_l i:B i:D i:L i:W i:silu i:io_dtype""")
+
+CausalConv1dUpdateParams = _struct("CausalConv1dUpdateParams", """
+    p:x i:x_stride_b i:x_stride_d i:x_stride_l p:conv_state i:cs_stride_b i:cs_stride_d i:cs_stride_l i:state_len
+    p:weight i:weight_dtype p:bias i:bias_dtype p:cache_seqlens p:conv_state_indices
+    p:out i:out_stride_b i:out_stride_d i:out_stride_l i:B i:D i:L i:W i:silu i:io_dtype""")
+
+
 class FusedIirParams(C.Structure):
     _fields_ = [("u", _p), ("u_stride_b", _i), ("u_stride_l", _i), ("w3", _p), ("w3_dtype", _i),
                 ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
@@ -89,7 +100,7 @@ class DecodeLayerParams(C.Structure):
 
 
 STRUCTS = [FeaturizerParams, GcgParams, FusedFirParams, ModalParams, IirParams, StepFirParams, StepIirParams,
-           DecodeLayerParams, FusedIirParams, HyenaXParams]
+           DecodeLayerParams, FusedIirParams, HyenaXParams, CausalConv1dParams, CausalConv1dUpdateParams]
 
 # name -> (restype, argtypes); every symbol include/vortex_b200.h declares
 SYMBOLS = {
@@ -107,6 +118,8 @@ SYMBOLS = {
     "vtx_fused_iir_fwd": (C.c_int, [C.POINTER(FusedIirParams), _p]),
     "vtx_fused_iir_scratch_bytes": (_i, [C.POINTER(FusedIirParams)]),
     "vtx_hyena_x_fwd": (C.c_int, [C.POINTER(HyenaXParams), _p]),
+    "vtx_causal_conv1d_fwd": (C.c_int, [C.POINTER(CausalConv1dParams), _p]),
+    "vtx_causal_conv1d_update": (C.c_int, [C.POINTER(CausalConv1dUpdateParams), _p]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),
     "vtx_decode_layer": (C.c_int, [C.POINTER(DecodeLayerParams), _p]),

@@ -108,6 +108,8 @@ extern "C" int64_t vtx_struct_size(int64_t which) {
         case 7: return sizeof(vtx_decode_layer_params);
         case 8: return sizeof(vtx_fused_iir_params);
         case 9: return sizeof(vtx_hyena_x_params);
+        case 10: return sizeof(vtx_causal_conv1d_params);
+        case 11: return sizeof(vtx_causal_conv1d_update_params);
         default: return -1;
     }
 }

@@ -1,0 +1,168 @@
+// Short depthwise causal convolution (2..4 taps) of the reference's conv extension, forward and decode update:
+// causal_conv1d_fwd (vortex/ops/conv/csrc/causal_conv1d.cpp:130-236, causal_conv1d_fwd.cu:44-135,208-346) and
+// causal_conv1d_update (causal_conv1d.cpp:382-470, causal_conv1d_update.cu:24-100).
+//   out[b,d,t] = act(bias[d] + sum_w weight[d,w] * xx[b,d,t-(W-1)+w]),   xx = [initial_states | x]
+// Both tensor layouts of the reference go through one kernel each, by strides: with time contiguous a thread owns TS
+// consecutive samples of one channel (lanes along time), with channels contiguous a lane owns a channel and walks TS
+// samples (lanes along channels); either way a warp's accesses are contiguous.  fp32 arithmetic, one final rounding.
+#include "common.cuh"
+
+namespace vtx {
+namespace cc1d {
+
+constexpr int TS = 8;          // samples per thread
+constexpr int MAXW = 4;
+
+template <typename T, bool CHANNEL_LAST>
+__global__ void __launch_bounds__(256) fwd_kernel(vtx_causal_conv1d_params p) {
+    const int64_t nblk = ceil_div<int64_t>(p.L, (int64_t)TS);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.B * p.D * nblk) return;
+    int64_t b, d, tb;
+    if (CHANNEL_LAST) { d = i % p.D; tb = (i / p.D) % nblk; b = i / (p.D * nblk); }
+    else { tb = i % nblk; d = (i / nblk) % p.D; b = i / (nblk * p.D); }
+    const int W = (int)p.W;
+    const int64_t t0 = tb * TS;
+    const T* x = static_cast<const T*>(p.x) + b * p.x_stride_b + d * p.x_stride_d;
+    const T* ini = p.initial_states ? static_cast<const T*>(p.initial_states) + b * p.is_stride_b + d * p.is_stride_d : nullptr;
+    const int32_t* sid = p.seq_idx ? p.seq_idx + b * p.L : nullptr;
+    float w[MAXW];
+#pragma unroll
+    for (int j = 0; j < MAXW; ++j) w[j] = j < W ? ld_param(p.weight, p.weight_dtype, d * W + j) : 0.f;
+    const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+    // window xx[t0-(W-1) .. t0+TS): negative times come from the initial states (or are zero)
+    float xv[TS + MAXW - 1];
+    int sv[TS + MAXW - 1];
+#pragma unroll
+    for (int k = 0; k < TS + MAXW - 1; ++k) {
+        const int64_t t = t0 - (MAXW - 1) + k;
+        float v = 0.f;
+        int s = -1;
+        if (t >= 0 && t < p.L) {
+            v = to_f32<T>(x[t * p.x_stride_l]);
+            if (sid) s = sid[t];
+        } else if (t < 0 && t >= -(W - 1) && ini) {
+            v = to_f32<T>(ini[(W - 1 + t) * p.is_stride_l]);
+        }
+        xv[k] = v; sv[k] = s;
+    }
+    T* out = static_cast<T*>(p.out) + b * p.out_stride_b + d * p.out_stride_d;
+#pragma unroll
+    for (int k = 0; k < TS; ++k) {
+        const int64_t t = t0 + k;
+        if (t >= p.L) break;
+        float acc = bias;
+#pragma unroll
+        for (int j = 0; j < MAXW; ++j) {
+            // tap j of W reaches back W-1-j samples: window slot k + (MAXW-1) - (W-1-j)
+            if (j < W) {
+                const int slot = k + (MAXW - 1) - (W - 1 - j);
+                const bool on = !sid || sv[slot] == sv[k + MAXW - 1];
+                acc = on ? fmaf(w[j], xv[slot], acc) : acc;
+            }
+        }
+        if (p.silu) acc = acc / (1.f + expf(-acc));
+        out[t * p.out_stride_l] = from_f32<T>(acc);
+    }
+    // final states: the last W-1 samples of [initial_states | x]; written by the thread that owns the last block
+    if (p.final_states && tb == nblk - 1) {
+        T* fs = static_cast<T*>(p.final_states) + b * p.fs_stride_b + d * p.fs_stride_d;
+        for (int j = 0; j < W - 1; ++j) {
+            const int64_t t = p.L - (W - 1) + j;
+            float v = 0.f;
+            if (t >= 0) v = to_f32<T>(x[t * p.x_stride_l]);
+            else if (ini && t >= -(W - 1)) v = to_f32<T>(ini[(W - 1 + t) * p.is_stride_l]);
+            fs[j * p.fs_stride_l] = from_f32<T>(v);
+        }
+    }
+}
+
+// Decode update: thread = (batch, channel); the new samples are few (usually one).
+template <typename T>
+__global__ void __launch_bounds__(128) update_kernel(vtx_causal_conv1d_update_params p) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.B * p.D) return;
+    const int64_t b = i / p.D, d = i % p.D;
+    const int W = (int)p.W;
+    const int64_t SL = p.state_len, Lq = p.L;
+    const int64_t sb = p.conv_state_indices ? (int64_t)p.conv_state_indices[b] : b;
+    T* st = static_cast<T*>(p.conv_state) + sb * p.cs_stride_b + d * p.cs_stride_d;
+    const T* x = static_cast<const T*>(p.x) + b * p.x_stride_b + d * p.x_stride_d;
+    T* out = static_cast<T*>(p.out) + b * p.out_stride_b + d * p.out_stride_d;
+    float w[MAXW];
+#pragma unroll
+    for (int j = 0; j < MAXW; ++j) w[j] = j < W ? ld_param(p.weight, p.weight_dtype, d * W + j) : 0.f;
+    const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+    // the W-1 samples before the first new one
+    float h[MAXW - 1] = {0.f, 0.f, 0.f};
+    const int64_t pos = p.cache_seqlens ? (int64_t)p.cache_seqlens[b] : 0;
+#pragma unroll
+    for (int j = 0; j < MAXW - 1; ++j) {
+        if (j < W - 1) {
+            int64_t idx = p.cache_seqlens ? (((pos - (W - 1) + j) % SL) + SL) % SL : SL - (W - 1) + j;
+            h[(MAXW - 1) - (W - 1) + j] = to_f32<T>(st[idx * p.cs_stride_l]);
+        }
+    }
+    if (!p.cache_seqlens && Lq < SL) {
+        // shift register: keep the last SL - Lq old samples (read before written: the walk goes forward)
+        for (int64_t k = 0; k < SL - Lq; ++k) st[k * p.cs_stride_l] = st[(k + Lq) * p.cs_stride_l];
+    }
+    for (int64_t t = 0; t < Lq; ++t) {
+        const T xt = x[t * p.x_stride_l];
+        const float xf = to_f32<T>(xt);
+        float acc = bias;
+        // h holds the MAXW-1 samples before xf; tap j of W reaches back W-1-j
+#pragma unroll
+        for (int j = 0; j < MAXW; ++j) {
+            if (j < W) {
+                const int back = W - 1 - j;
+                const float v = back == 0 ? xf : h[(MAXW - 1) - back];
+                acc = fmaf(w[j], v, acc);
+            }
+        }
+        h[0] = h[1]; h[1] = h[2]; h[2] = xf;
+        if (p.silu) acc = acc / (1.f + expf(-acc));
+        out[t * p.out_stride_l] = from_f32<T>(acc);
+        if (p.cache_seqlens) st[((pos + t) % SL) * p.cs_stride_l] = xt;
+        else if (t >= Lq - SL) st[(SL - Lq + t) * p.cs_stride_l] = xt;
+    }
+}
+
+}  // namespace cc1d
+}  // namespace vtx
+
+extern "C" int vtx_causal_conv1d_fwd(const vtx_causal_conv1d_params* p, void* stream) {
+    using namespace vtx;
+    using namespace vtx::cc1d;
+    VTX_REQUIRE(p && p->x && p->weight && p->out, VTX_ERR_BAD_ARG, "causal_conv1d: null pointer");
+    VTX_REQUIRE(p->B > 0 && p->D > 0 && p->L > 0, VTX_ERR_BAD_ARG, "causal_conv1d: sizes must be positive");
+    VTX_REQUIRE(p->W >= 2 && p->W <= MAXW, VTX_ERR_UNSUPPORTED, "causal_conv1d: only widths between 2 and 4 (got %lld)", (long long)p->W);
+    VTX_REQUIRE(valid_dtype(p->weight_dtype) && (!p->bias || valid_dtype(p->bias_dtype)), VTX_ERR_BAD_ARG,
+                "causal_conv1d: bad parameter dtype");
+    const bool cl = p->x_stride_d == 1 && p->x_stride_l != 1;
+    VTX_REQUIRE(!p->seq_idx || cl || p->L == 1 || p->x_stride_l == 1, VTX_ERR_BAD_ARG, "causal_conv1d: bad strides");
+    const int64_t n = p->B * p->D * ceil_div<int64_t>(p->L, (int64_t)TS);
+    VTX_REQUIRE(ceil_div<int64_t>(n, 256) < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "causal_conv1d: problem too large");
+    const unsigned blocks = (unsigned)ceil_div<int64_t>(n, 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    VTX_DISPATCH_IO(p->io_dtype, T, {
+        if (cl) fwd_kernel<T, true><<<blocks, 256, 0, s>>>(*p);
+        else fwd_kernel<T, false><<<blocks, 256, 0, s>>>(*p);
+    });
+    return check_launch("causal_conv1d_fwd");
+}
+
+extern "C" int vtx_causal_conv1d_update(const vtx_causal_conv1d_update_params* p, void* stream) {
+    using namespace vtx;
+    using namespace vtx::cc1d;
+    VTX_REQUIRE(p && p->x && p->weight && p->out && p->conv_state, VTX_ERR_BAD_ARG, "causal_conv1d_update: null pointer");
+    VTX_REQUIRE(p->B > 0 && p->D > 0 && p->L > 0, VTX_ERR_BAD_ARG, "causal_conv1d_update: sizes must be positive");
+    VTX_REQUIRE(p->W >= 2 && p->W <= MAXW, VTX_ERR_UNSUPPORTED, "causal_conv1d_update: only widths between 2 and 4 (got %lld)", (long long)p->W);
+    VTX_REQUIRE(p->state_len >= p->W - 1, VTX_ERR_BAD_ARG, "causal_conv1d_update: conv_state shorter than width - 1");
+    VTX_REQUIRE(valid_dtype(p->weight_dtype) && (!p->bias || valid_dtype(p->bias_dtype)), VTX_ERR_BAD_ARG,
+                "causal_conv1d_update: bad parameter dtype");
+    const unsigned blocks = (unsigned)ceil_div<int64_t>(p->B * p->D, 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    VTX_DISPATCH_IO(p->io_dtype, T, { update_kernel<T><<<blocks, 128, 0, s>>>(*p); });
+    return check_launch("causal_conv1d_update");
+}

@@ -182,3 +182,17 @@ def hyena_x_fwd(qkv, h):
     """The packed form of the reference's ``hyena_x_fwd_ref``: qkv [B, 3D, L] -> [B, D, L]."""
     D = qkv.shape[1] // 3
     return ops.hyena_x_fwd(qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:], h)
+
+
+def causal_conv1d_fn(x, weight, bias=None, seq_idx=None, initial_states=None, final_states_out=None, activation=None):
+    """``causal_conv1d_fn`` of the reference's conv package
+    (``vortex/ops/conv/local_causal_conv1d/causal_conv1d_interface.py:84-112``; math ``causal_conv1d_ref``, ``:187-222``):
+    x (b, d, l), weight (d, hl), bias (d,), seq_idx (b, l), initial_states / final_states_out (b, d, hl - 1) -> (b, d, l)."""
+    return ops.causal_conv1d_fwd(x, weight, bias, seq_idx, initial_states, final_states_out, activation)
+
+
+def causal_conv1d_update(x, conv_state, weight, bias=None, activation=None, cache_seqlens=None,
+                         conv_state_indices=None):
+    """``causal_conv1d_update`` of the same package (``causal_conv1d_interface.py:225-252``): one or a few new samples
+    against a cached window; conv_state is updated in place."""
+    return ops.causal_conv1d_update(x, conv_state, weight, bias, activation, cache_seqlens, conv_state_indices)

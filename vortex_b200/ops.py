@@ -295,6 +295,92 @@ def hyena_x_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, h) -> torch.T
     return y
 
 
+def _act_flag(activation) -> int:
+    if activation not in (None, "silu", "swish"):
+        raise NotImplementedError("activation must be None, silu, or swish")
+    return int(activation is not None)
+
+
+def causal_conv1d_fwd(x: torch.Tensor, weight: torch.Tensor, bias=None, seq_idx=None, initial_states=None,
+                      final_states_out=None, activation=None) -> torch.Tensor:
+    """Depthwise causal convolution of 2..4 taps (the reference extension's ``causal_conv1d_fwd``,
+    ``vortex/ops/conv/csrc/causal_conv1d.cpp:130-236``): x [B, D, L] with time or channels contiguous, weight [D, W],
+    bias [D], seq_idx int32 [B, L], initial_states / final_states_out [B, D, W-1] -> out shaped and strided like x."""
+    _need_cuda(x, weight, bias, seq_idx, initial_states, final_states_out)
+    if x.dim() != 3 or weight.dim() != 2 or weight.shape[0] != x.shape[1]:
+        raise ValueError(f"x {tuple(x.shape)} / weight {tuple(weight.shape)}: expected [B, D, L] and [D, W]")
+    B, D, L = x.shape
+    W = weight.shape[1]
+    silu = _act_flag(activation)
+    if x.stride(2) != 1 and x.stride(1) != 1:
+        x = x.contiguous()
+    weight, bias = _param(weight, x), _param(bias, x)
+    if bias is not None and tuple(bias.shape) != (D,):
+        raise ValueError(f"bias has shape {tuple(bias.shape)}, expected {(D,)}")
+    if seq_idx is not None:
+        if seq_idx.dtype != torch.int32 or tuple(seq_idx.shape) != (B, L):
+            raise ValueError("seq_idx must be int32 of shape [B, L]")
+        seq_idx = seq_idx.contiguous()
+    for name, t in (("initial_states", initial_states), ("final_states_out", final_states_out)):
+        if t is not None and (tuple(t.shape) != (B, D, W - 1) or t.dtype != x.dtype):
+            raise ValueError(f"{name} must be [B, D, W-1] of x's dtype")
+    out = torch.empty_like(x)              # keeps x's layout (dense time-last or channel-last)
+    if out.stride() != x.stride():
+        out = torch.empty_strided(x.shape, x.stride(), device=x.device, dtype=x.dtype) if x.is_non_overlapping_and_dense() \
+            else torch.empty(x.shape, device=x.device, dtype=x.dtype)
+    ini, fs = initial_states, final_states_out
+    p = _lib.CausalConv1dParams(
+        x=_ptr(x), x_stride_b=x.stride(0), x_stride_d=x.stride(1), x_stride_l=x.stride(2),
+        weight=_ptr(weight), weight_dtype=_code(weight), bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        seq_idx=_ptr(seq_idx), initial_states=_ptr(ini),
+        is_stride_b=ini.stride(0) if ini is not None else 0, is_stride_d=ini.stride(1) if ini is not None else 0,
+        is_stride_l=ini.stride(2) if ini is not None else 0, final_states=_ptr(fs),
+        fs_stride_b=fs.stride(0) if fs is not None else 0, fs_stride_d=fs.stride(1) if fs is not None else 0,
+        fs_stride_l=fs.stride(2) if fs is not None else 0,
+        out=_ptr(out), out_stride_b=out.stride(0), out_stride_d=out.stride(1), out_stride_l=out.stride(2),
+        B=B, D=D, L=L, W=W, silu=silu, io_dtype=_code(x))
+    with _on(x):
+        _lib.check(_lib.lib().vtx_causal_conv1d_fwd(C.byref(p), _stream(x)))
+    return out
+
+
+def causal_conv1d_update(x: torch.Tensor, conv_state: torch.Tensor, weight: torch.Tensor, bias=None, activation=None,
+                         cache_seqlens=None, conv_state_indices=None) -> torch.Tensor:
+    """Decode-time update of the same convolution (``causal_conv1d.cpp:382-470``): x [B, D] or [B, D, Lq],
+    conv_state [rows, D, state_len] updated in place (shift register, or circular with cache_seqlens int32 [B];
+    conv_state_indices int32 [B] picks the state row per batch element) -> out shaped like x."""
+    _need_cuda(x, conv_state, weight, bias, cache_seqlens, conv_state_indices)
+    silu = _act_flag(activation)
+    squeeze = x.dim() == 2
+    if squeeze:
+        x = x.unsqueeze(-1)
+    B, D, L = x.shape
+    W = weight.shape[1]
+    if conv_state.dtype != x.dtype:
+        raise TypeError("conv_state must have x's dtype")
+    rows = conv_state.shape[0]
+    if conv_state.dim() != 3 or conv_state.shape[1] != D or (conv_state_indices is None and rows != B):
+        raise ValueError(f"conv_state has shape {tuple(conv_state.shape)}")
+    if tuple(weight.shape) != (D, W):
+        raise ValueError(f"weight has shape {tuple(weight.shape)}, expected {(D, W)}")
+    weight, bias = _param(weight, x), _param(bias, x)
+    for name, t in (("cache_seqlens", cache_seqlens), ("conv_state_indices", conv_state_indices)):
+        if t is not None and (t.dtype != torch.int32 or tuple(t.shape) != (B,) or t.stride(0) != 1):
+            raise ValueError(f"{name} must be a dense int32 vector of length B")
+    out = torch.empty_like(x)
+    p = _lib.CausalConv1dUpdateParams(
+        x=_ptr(x), x_stride_b=x.stride(0), x_stride_d=x.stride(1), x_stride_l=x.stride(2),
+        conv_state=_ptr(conv_state), cs_stride_b=conv_state.stride(0), cs_stride_d=conv_state.stride(1),
+        cs_stride_l=conv_state.stride(2), state_len=conv_state.shape[2],
+        weight=_ptr(weight), weight_dtype=_code(weight), bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        cache_seqlens=_ptr(cache_seqlens), conv_state_indices=_ptr(conv_state_indices),
+        out=_ptr(out), out_stride_b=out.stride(0), out_stride_d=out.stride(1), out_stride_l=out.stride(2),
+        B=B, D=D, L=L, W=W, silu=silu, io_dtype=_code(x))
+    with _on(x):
+        _lib.check(_lib.lib().vtx_causal_conv1d_update(C.byref(p), _stream(x)))
+    return out.squeeze(-1) if squeeze else out
+
+
 def iir_fwd(z_pre: torch.Tensor, log_poles, residues, bias, D: int, *, layout="split", num_heads=1, flip=False,
             theta=None, res_im=None, want_state=True, round_kv=True):
     """Gate -> modal long convolution -> gate.  z_pre [B, 3D, L] -> y [B, D, L] (contiguous), state fp32
