@@ -297,6 +297,20 @@ typedef struct vtx_causal_conv1d_update_params {
 } vtx_causal_conv1d_update_params;
 int vtx_causal_conv1d_update(const vtx_causal_conv1d_update_params* p, void* stream);
 
+/* Conv states of packed sequences (vortex/ops/conv/local_causal_conv1d/causal_conv1d_varlen.py:42-75
+ * causal_conv1d_varlen_states): x [total, dim] holds the sequences back to back, cu_seqlens int32 [batch+1] their
+ * boundaries; states[b, :, state_len-n:] = the last n = min(state_len, length_b) rows of sequence b, zeros before.
+ * states is addressed by element strides (the reference returns memory [batch, state_len, dim] viewed as
+ * [batch, dim, state_len]). */
+typedef struct vtx_varlen_states_params {
+    const void* x;       int64_t x_stride_t, x_stride_c;
+    const int32_t* cu_seqlens;
+    void* states;        int64_t st_stride_b, st_stride_c, st_stride_l;
+    int64_t total, batch, dim, state_len;
+    int64_t io_dtype;
+} vtx_varlen_states_params;
+int vtx_causal_conv1d_varlen_states(const vtx_varlen_states_params* p, void* stream);
+
 /* Hyena-X forward (vortex/ops/hyena_x/triton_indirect_fwd.py:262 hyena_x_bdl_fwd, reference :413-424):
  * o = fir(h[0:D], q) * fir(h[D:2D], k) * fir(h[2D:3D], v), depthwise causal filters of Lh <= 16 taps
  * (cross-correlation order), q, k, v, o [B,D,L] contiguous, h [3D,Lh]. */

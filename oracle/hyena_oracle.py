@@ -282,6 +282,22 @@ def causal_conv1d_update(x, conv_state, weight, bias=None, silu=False, cache_seq
     return round_io(out, io), new
 
 
+def causal_conv1d_varlen_states(x, cu_seqlens, state_len):
+    """causal_conv1d_varlen_states_ref (vortex/ops/conv/local_causal_conv1d/causal_conv1d_varlen.py:78-97): x [total, dim]
+    holds packed sequences, cu_seqlens [batch+1] their boundaries -> states [batch, dim, state_len] = the last
+    min(state_len, length) rows of each sequence, right-aligned, zeros before.  A pure copy."""
+    x = np.asarray(x)
+    cu = np.asarray(cu_seqlens).astype(np.int64)
+    batch, dim = len(cu) - 1, x.shape[1]
+    st = np.zeros((batch, dim, state_len), dtype=x.dtype)
+    for i in range(batch):
+        end = cu[i + 1]
+        start = max(cu[i], end - state_len)
+        if end > start:
+            st[i, :, state_len - (end - start):] = x[start:end].T
+    return st
+
+
 def modal_filter(log_poles, residues, L):
     """HyenaCascade.compute_filter (model.py:390-398): real modal form,
     h[g, t] = sum_s R[g, s] * exp(lambda[g, s] * t), float32 arithmetic.

@@ -215,6 +215,16 @@ def main(ref_root):
                 out[k + "_y_plain"], out[k + "_fs_plain"] = np32(y0), np32(f0)
                 out[k + "_y_full"], out[k + "_fs_full"] = np32(y1), np32(f1)
 
+    # ---- states of packed sequences (pure copy; the module's Triton import needs no GPU) ----------------------
+    from causal_conv1d_varlen import causal_conv1d_varlen_states_ref
+    for n, (lens, dim, sl) in enumerate([((5, 1, 9, 3), 12, 3), ((2, 40), 7, 6), ((17,), 33, 16)]):
+        g = torch.Generator().manual_seed(8500 + n)
+        cu = torch.tensor((0,) + tuple(np.cumsum(lens)), dtype=torch.int32)
+        x = torch.randn(int(cu[-1]), dim, generator=g)
+        k = f"vls_{n}"
+        out[k + "_x"], out[k + "_cu"] = np32(x), cu.numpy()
+        out[k + "_st"] = np32(causal_conv1d_varlen_states_ref(x, cu, sl))
+
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")

@@ -408,3 +408,27 @@ def test_causal_conv1d_update_vs_oracle(io, B, D, Lq, W, SL):
         assert rel_l2(y, ref) <= CC_TOL[io]
         assert np.array_equal(to_np(pool[rows.long().cuda()]), rst.astype(np.float32))
         assert float(pool[(rows.long() - 1).cuda()].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("n", [0, 1, 2])
+def test_golden_varlen_states(golden, n):
+    from vortex_b200 import hyena_ops
+    k = f"vls_{n}"
+    want = golden[k + "_st"]
+    st = hyena_ops.causal_conv1d_varlen_states(T(golden[k + "_x"], "f32"), torch.from_numpy(golden[k + "_cu"]).cuda(),
+                                               want.shape[-1])
+    assert st.shape == want.shape and st.stride(1) == 1 and np.array_equal(to_np(st), want)
+
+
+@pytest.mark.parametrize("io,lens,dim,sl", [("bf16", (8192, 1, 0, 300, 2), 4096, 3), ("f16", (3, 3, 3), 40, 127),
+                                             ("f32", (1,), 5, 1)])
+def test_varlen_states_vs_oracle(io, lens, dim, sl):
+    """Evo 2 width (bf16, 4096 channels), sequences shorter than the state, an empty sequence; bit-exact."""
+    from vortex_b200 import hyena_ops
+    g = torch.Generator().manual_seed(40 + dim)
+    cu = torch.tensor((0,) + tuple(np.cumsum(lens)), dtype=torch.int32)
+    x = torch.randn(int(cu[-1]), dim, generator=g).to(DT[io])
+    st = hyena_ops.causal_conv1d_varlen_states(x.cuda(), cu.cuda(), sl)
+    assert np.array_equal(to_np(st), O.causal_conv1d_varlen_states(to_np(x), cu.numpy(), sl))
+    with pytest.raises(TypeError):
+        hyena_ops.causal_conv1d_varlen_states(x.cuda(), cu.long().cuda(), sl)

@@ -178,3 +178,12 @@ def test_causal_conv1d(golden, io, W, L):
         for i in range(B):
             for t in range(L):
                 assert np.array_equal(circ1[i, :, (cs[i] + t) % SL], O.round_io(x, io)[i, :, t])
+
+
+@pytest.mark.parametrize("n", [0, 1, 2])
+def test_varlen_states(golden, n):
+    """causal_conv1d_varlen_states_ref: the last rows of each packed sequence, bit-exact."""
+    k = f"vls_{n}"
+    want = golden[k + "_st"]
+    st = O.causal_conv1d_varlen_states(golden[k + "_x"], golden[k + "_cu"], want.shape[-1])
+    assert st.shape == want.shape and np.array_equal(st, want)

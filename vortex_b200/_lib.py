@@ -60,6 +60,11 @@ CausalConv1dUpdateParams = _struct("CausalConv1dUpdateParams", """
     p:out i:out_stride_b i:out_stride_d i:out_stride_l i:B i:D i:L i:W i:silu i:io_dtype""")
 
 
+VarlenStatesParams = _struct("VarlenStatesParams", """
+    p:x i:x_stride_t i:x_stride_c p:cu_seqlens p:states i:st_stride_b i:st_stride_c i:st_stride_l
+    i:total i:batch i:dim i:state_len i:io_dtype""")
+
+
 class FusedIirParams(C.Structure):
     _fields_ = [("u", _p), ("u_stride_b", _i), ("u_stride_l", _i), ("w3", _p), ("w3_dtype", _i),
                 ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
@@ -100,7 +105,8 @@ class DecodeLayerParams(C.Structure):
 
 
 STRUCTS = [FeaturizerParams, GcgParams, FusedFirParams, ModalParams, IirParams, StepFirParams, StepIirParams,
-           DecodeLayerParams, FusedIirParams, HyenaXParams, CausalConv1dParams, CausalConv1dUpdateParams]
+           DecodeLayerParams, FusedIirParams, HyenaXParams, CausalConv1dParams, CausalConv1dUpdateParams,
+           VarlenStatesParams]
 
 # name -> (restype, argtypes); every symbol include/vortex_b200.h declares
 SYMBOLS = {
@@ -120,6 +126,7 @@ SYMBOLS = {
     "vtx_hyena_x_fwd": (C.c_int, [C.POINTER(HyenaXParams), _p]),
     "vtx_causal_conv1d_fwd": (C.c_int, [C.POINTER(CausalConv1dParams), _p]),
     "vtx_causal_conv1d_update": (C.c_int, [C.POINTER(CausalConv1dUpdateParams), _p]),
+    "vtx_causal_conv1d_varlen_states": (C.c_int, [C.POINTER(VarlenStatesParams), _p]),
     "vtx_step_fir": (C.c_int, [C.POINTER(StepFirParams), _p]),
     "vtx_step_iir": (C.c_int, [C.POINTER(StepIirParams), _p]),
     "vtx_decode_layer": (C.c_int, [C.POINTER(DecodeLayerParams), _p]),

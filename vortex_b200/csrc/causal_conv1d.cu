@@ -128,8 +128,36 @@ __global__ void __launch_bounds__(128) update_kernel(vtx_causal_conv1d_update_pa
     }
 }
 
+// States of packed sequences (causal_conv1d_varlen.py:8-39): states[b, c, state_len - 1 - r] = x[end_b - 1 - r, c]
+// for the last state_len rows of sequence b, zero where that row belongs to an earlier sequence.  Thread = (b, s, c)
+// with c fastest: rows of x and of the reference's [batch, state_len, dim] memory are read and written contiguously.
+template <typename T>
+__global__ void __launch_bounds__(256) varlen_states_kernel(vtx_varlen_states_params p) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.batch * p.state_len * p.dim) return;
+    const int64_t c = i % p.dim, s = (i / p.dim) % p.state_len, b = i / (p.dim * p.state_len);
+    const int64_t end = p.cu_seqlens[b + 1], begin = p.cu_seqlens[b];
+    const int64_t row = end - p.state_len + s;
+    T v = from_f32<T>(0.f);
+    if (row >= begin && row >= 0 && row < p.total) v = static_cast<const T*>(p.x)[row * p.x_stride_t + c * p.x_stride_c];
+    static_cast<T*>(p.states)[b * p.st_stride_b + c * p.st_stride_c + s * p.st_stride_l] = v;
+}
+
 }  // namespace cc1d
 }  // namespace vtx
+
+extern "C" int vtx_causal_conv1d_varlen_states(const vtx_varlen_states_params* p, void* stream) {
+    using namespace vtx;
+    using namespace vtx::cc1d;
+    VTX_REQUIRE(p && p->x && p->cu_seqlens && p->states, VTX_ERR_BAD_ARG, "varlen_states: null pointer");
+    VTX_REQUIRE(p->batch > 0 && p->dim > 0 && p->state_len > 0 && p->total >= 0, VTX_ERR_BAD_ARG,
+                "varlen_states: sizes must be positive");
+    const int64_t n = p->batch * p->state_len * p->dim;
+    VTX_REQUIRE(ceil_div<int64_t>(n, 256) < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "varlen_states: problem too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    VTX_DISPATCH_IO(p->io_dtype, T, { varlen_states_kernel<T><<<(unsigned)ceil_div<int64_t>(n, 256), 256, 0, s>>>(*p); });
+    return check_launch("causal_conv1d_varlen_states");
+}
 
 extern "C" int vtx_causal_conv1d_fwd(const vtx_causal_conv1d_params* p, void* stream) {
     using namespace vtx;

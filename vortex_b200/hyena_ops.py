@@ -196,3 +196,9 @@ def causal_conv1d_update(x, conv_state, weight, bias=None, activation=None, cach
     """``causal_conv1d_update`` of the same package (``causal_conv1d_interface.py:225-252``): one or a few new samples
     against a cached window; conv_state is updated in place."""
     return ops.causal_conv1d_update(x, conv_state, weight, bias, activation, cache_seqlens, conv_state_indices)
+
+
+def causal_conv1d_varlen_states(x, cu_seqlens, state_len):
+    """``causal_conv1d_varlen_states`` (``vortex/ops/conv/local_causal_conv1d/causal_conv1d_varlen.py:42-75``):
+    x (total_tokens, dim), cu_seqlens (batch + 1) int32 -> states (batch, dim, state_len)."""
+    return ops.causal_conv1d_varlen_states(x, cu_seqlens, state_len)

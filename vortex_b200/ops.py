@@ -381,6 +381,30 @@ def causal_conv1d_update(x: torch.Tensor, conv_state: torch.Tensor, weight: torc
     return out.squeeze(-1) if squeeze else out
 
 
+def causal_conv1d_varlen_states(x: torch.Tensor, cu_seqlens: torch.Tensor, state_len: int) -> torch.Tensor:
+    """x [total_tokens, dim] (sequences back to back), cu_seqlens int32 [batch + 1] -> states [batch, dim, state_len]
+    (memory [batch, state_len, dim] like the reference's, ``causal_conv1d_varlen.py:42-75``): the last rows of each
+    sequence, zeros where a sequence is shorter than state_len."""
+    _need_cuda(x, cu_seqlens)
+    if x.dim() != 2 or cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2:
+        raise ValueError("x must be [total_tokens, dim] and cu_seqlens [batch + 1]")
+    if cu_seqlens.dtype != torch.int32:
+        raise TypeError("cu_seqlens must be int32")
+    if int(state_len) < 1:
+        raise ValueError("state_len must be positive")
+    cu_seqlens = cu_seqlens.contiguous()
+    total, dim = x.shape
+    batch = cu_seqlens.numel() - 1
+    states = torch.empty(batch, state_len, dim, dtype=x.dtype, device=x.device).transpose(1, 2)
+    p = _lib.VarlenStatesParams(
+        x=_ptr(x), x_stride_t=x.stride(0), x_stride_c=x.stride(1), cu_seqlens=_ptr(cu_seqlens), states=_ptr(states),
+        st_stride_b=states.stride(0), st_stride_c=states.stride(1), st_stride_l=states.stride(2),
+        total=total, batch=batch, dim=dim, state_len=int(state_len), io_dtype=_code(x))
+    with _on(x):
+        _lib.check(_lib.lib().vtx_causal_conv1d_varlen_states(C.byref(p), _stream(x)))
+    return states
+
+
 def iir_fwd(z_pre: torch.Tensor, log_poles, residues, bias, D: int, *, layout="split", num_heads=1, flip=False,
             theta=None, res_im=None, want_state=True, round_kv=True):
     """Gate -> modal long convolution -> gate.  z_pre [B, 3D, L] -> y [B, D, L] (contiguous), state fp32
