@@ -225,7 +225,8 @@ int vtx_iir_fwd_noalloc(const vtx_iir_params* p, void* stream);
  * prefill_via_modal_fft, engine.py:525-559) -- the hyena_li_fwd entry point the reference imports but never
  * defines (vortex/model/layers.py:18-21).  Two kernels, chosen by shape:
  *   - bf16 I/O, modal systems of up to 16 poles shared by groups of 16 channels (G * 16 == D), no featurizer
- *     bias, no carried-in state: a chunked state-space scan whose Toeplitz, state-input and state-update
+ *     bias; a call that continues an earlier one only when L is a multiple of 384 and its history comes as
+ *     u_hist_rows (not fir_state_in): a chunked state-space scan whose Toeplitz, state-input and state-update
  *     contractions run on tcgen05 tensor cores;
  *   - everything else (a modal system per channel as in Evo 2, configs/evo2-7b-8k.yml:11, any G dividing D,
  *     fp32 / fp16 / bf16 I/O, featurizer bias, a call that continues an earlier one): the recurrence itself on
@@ -252,6 +253,9 @@ typedef struct vtx_fused_iir_params {
     int64_t io_dtype;
     const float* state_in;                      /* modal state to start from, layout of state, or NULL (zero) */
     const void* fir_state_in; int64_t fir_state_dtype;   /* [B,3D,2] rows before the first one, or NULL (zero) */
+    int64_t u_hist_rows;                        /* 0, or >= 2: that many rows in front of u in memory (same row pitch)
+                                                   are the sequence's preceding projection rows and take the place
+                                                   of fir_state_in (which must then be NULL), as in vtx_fused_fir_params */
 } vtx_fused_iir_params;
 /* Scratch the call described by p can use (p->scratch itself is not read); 0 = none needed. */
 int64_t vtx_fused_iir_scratch_bytes(const vtx_fused_iir_params* p);

@@ -370,6 +370,32 @@ def test_fused_li_chunked_prefill_carries_state(io, cplx, cuts):
     assert rel_l2(y, ref) <= (1e-4 if io == "f32" else TOL["bf16"])
 
 
+@pytest.mark.parametrize("cplx,cuts", [(True, (0, 768, 1152, 1920)), (False, (0, 384, 2304)), (True, (0, 1000, 1384))])
+def test_fused_li_tensor_core_chunked_prefill(cplx, cuts):
+    """Grouped bf16 systems (the tensor-core kernel): chunks that are views of the whole projection buffer, each call
+    told that earlier rows precede its view and given the modal state the previous call returned.  Chunks of a
+    multiple of 384 rows stay on the tensor-core kernel; the result equals one call over the whole prompt."""
+    from vortex_b200 import hyena_ops, ops
+    B, D, G, S = 2, 64, 4, 16
+    L = cuts[-1]
+    p = make_block(61, B, L, D, G, 0, "bf16", modal=True, S=S, complex_poles=cplx)
+    pc = cuda(p)
+    kw = dict(theta=pc.get("theta"), res_im=pc.get("res_im"), want_state=True)
+    y_all, fs_all, st_all = hyena_ops.hyena_li_fwd(pc["u"], pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"], **kw)
+    ys, st = [], None
+    for t0, t1 in zip(cuts[:-1], cuts[1:]):
+        yc, fs, st = hyena_ops.hyena_li_fwd(pc["u"][:, t0:t1], pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"],
+                                            state_in=st, hist_rows=min(t0, 5), **kw)
+        ys.append(yc)
+    ops.device_status()
+    y = torch.cat(ys, dim=1)
+    assert rel_l2(y, y_all) <= 1e-3
+    assert torch.equal(fs, fs_all)
+    assert rel_l2(st, st_all) <= 1e-4
+    ref, _ = _li_cc_oracle(p, L, D, G, cplx, "bf16", "interleaved", 1, False, None)
+    assert rel_l2(y, ref) <= TOL["bf16"]
+
+
 # io, D, G, K, layout, chunk boundaries
 FIR_CHUNK_CASES = [
     ("bf16", 64, 4, 128, "interleaved", (0, 1000, 1130, 2500)),     # 128 taps on tensor cores, a chunk of K + 2 rows

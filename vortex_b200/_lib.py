@@ -70,7 +70,8 @@ class FusedIirParams(C.Structure):
                 ("b3", _p), ("b3_dtype", _i), ("modal", ModalParams), ("bias", _p), ("bias_dtype", _i),
                 ("y", _p), ("y_stride_b", _i), ("y_stride_l", _i), ("state", _p), ("scratch", _p),
                 ("B", _i), ("L", _i), ("D", _i), ("K3", _i), ("layout", _i), ("num_heads", _i), ("flip_x1x2", _i),
-                ("io_dtype", _i), ("state_in", _p), ("fir_state_in", _p), ("fir_state_dtype", _i)]
+                ("io_dtype", _i), ("state_in", _p), ("fir_state_in", _p), ("fir_state_dtype", _i),
+                ("u_hist_rows", _i)]
 
 
 class IirParams(C.Structure):

@@ -6,6 +6,7 @@
 // consecutive samples of one channel (lanes along time), with channels contiguous a lane owns a channel and walks TS
 // samples (lanes along channels); either way a warp's accesses are contiguous.  fp32 arithmetic, one final rounding.
 #include "common.cuh"
+#include <initializer_list>
 
 namespace vtx {
 namespace cc1d {
@@ -74,6 +75,189 @@ __global__ void __launch_bounds__(256) fwd_kernel(vtx_causal_conv1d_params p) {
             else if (ini && t >= -(W - 1)) v = to_f32<T>(ini[(W - 1 + t) * p.is_stride_l]);
             fs[j * p.fs_stride_l] = from_f32<T>(v);
         }
+    }
+}
+
+
+// ---- vectorised kernels: 16-byte accesses; taken when sizes, strides and addresses allow (else the kernel above) ----
+template <typename T> struct Vec16 {
+    static constexpr int N = 16 / (int)sizeof(T);
+    T e[N];
+};
+template <typename T> __device__ __forceinline__ void ld16(const T* p, float (&f)[16 / sizeof(T)]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    Vec16<T> v;
+    *reinterpret_cast<uint4*>(&v) = raw;
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) f[i] = to_f32<T>(v.e[i]);
+}
+template <typename T> __device__ __forceinline__ void st16(T* p, const float (&f)[16 / sizeof(T)]) {
+    Vec16<T> v;
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) v.e[i] = from_f32<T>(f[i]);
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&v);
+}
+__device__ __forceinline__ float act(float a, bool silu) { return silu ? __fdividef(a, 1.f + __expf(-a)) : a; }
+
+// Channel-last: a thread owns V = 16 bytes of channels and walks CLT samples with the W-1 rows before them in
+// registers; a warp reads and writes 512 contiguous bytes per row.
+constexpr int CLT = 16;
+template <typename T, int W, bool SEQ>
+__global__ void __launch_bounds__(256, 2) fwd_cl_kernel(vtx_causal_conv1d_params p) {
+    constexpr int V = Vec16<T>::N;
+    const int64_t nv = p.D / V, nblk = ceil_div<int64_t>(p.L, (int64_t)CLT);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.B * nblk * nv) return;
+    const int64_t d = (i % nv) * V, tb = (i / nv) % nblk, b = i / (nv * nblk);
+    const int64_t t0 = tb * CLT;
+    const T* x = static_cast<const T*>(p.x) + b * p.x_stride_b + d;
+    T* out = static_cast<T*>(p.out) + b * p.out_stride_b + d;
+    const int32_t* sid = SEQ ? p.seq_idx + b * p.L : nullptr;
+    float w[W][V], bias[V];
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) w[j][c] = ld_param(p.weight, p.weight_dtype, (d + c) * W + j);
+        bias[c] = p.bias ? ld_param(p.bias, p.bias_dtype, d + c) : 0.f;
+    }
+    // rows t0-(W-1) .. t0-1
+    float h[W - 1][V];
+    int hs[W - 1];
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {
+        const int64_t t = t0 - (W - 1) + j;
+        hs[j] = -1;
+        if (t >= 0) {
+            ld16<T>(x + t * p.x_stride_l, h[j]);
+            if (SEQ) hs[j] = sid[t];
+        } else {
+#pragma unroll
+            for (int c = 0; c < V; ++c)
+                h[j][c] = p.initial_states ? to_f32<T>(static_cast<const T*>(p.initial_states)[b * p.is_stride_b + (d + c) * p.is_stride_d + (W - 1 + t) * p.is_stride_l]) : 0.f;
+        }
+    }
+    const bool silu = p.silu != 0;
+    const int nt = (int)((p.L - t0) < CLT ? (p.L - t0) : CLT);
+    constexpr int U = V == 8 ? 2 : 4;          // rows in flight
+    for (int k0 = 0; k0 < nt; k0 += U) {
+        float xr[U][V];
+        int xs[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            xs[u] = 0;
+            if (k0 + u < nt) {
+                ld16<T>(x + (t0 + k0 + u) * p.x_stride_l, xr[u]);
+                if (SEQ) xs[u] = sid[t0 + k0 + u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (k0 + u < nt) {
+                float y[V];
+#pragma unroll
+                for (int c = 0; c < V; ++c) {
+                    float acc = fmaf(w[W - 1][c], xr[u][c], bias[c]);
+#pragma unroll
+                    for (int j = 0; j < W - 1; ++j) {
+                        const bool on = !SEQ || hs[j] == xs[u];
+                        acc = on ? fmaf(w[j][c], h[j][c], acc) : acc;
+                    }
+                    y[c] = act(acc, silu);
+                }
+                st16<T>(out + (t0 + k0 + u) * p.out_stride_l, y);
+#pragma unroll
+                for (int j = 0; j + 1 < W - 1; ++j) {
+                    hs[j] = hs[j + 1];
+#pragma unroll
+                    for (int c = 0; c < V; ++c) h[j][c] = h[j + 1][c];
+                }
+                hs[W - 2] = xs[u];
+#pragma unroll
+                for (int c = 0; c < V; ++c) h[W - 2][c] = xr[u][c];
+            }
+        }
+    }
+    // after the walk h holds the last W-1 samples of [initial_states | x] when this is the last block
+    if (p.final_states && tb == nblk - 1) {
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+            for (int c = 0; c < V; ++c)
+                static_cast<T*>(p.final_states)[b * p.fs_stride_b + (d + c) * p.fs_stride_d + j * p.fs_stride_l] = from_f32<T>(h[j][c]);
+    }
+}
+
+// Time-last: a thread owns V = 16 bytes of consecutive samples of one channel; the W-1 samples before them come from
+// the previous lane by shuffle (lane 0, and the first vector of a row, fetch them).  No seq_idx on this path.
+template <typename T, int W>
+__global__ void __launch_bounds__(256) fwd_tl_kernel(vtx_causal_conv1d_params p) {
+    constexpr int V = Vec16<T>::N;
+    const int64_t nv = p.L / V;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = i < p.B * p.D * nv;
+    const int64_t ii = live ? i : 0;
+    const int64_t tv = ii % nv, d = (ii / nv) % p.D, b = ii / (nv * p.D);
+    const T* x = static_cast<const T*>(p.x) + b * p.x_stride_b + d * p.x_stride_d;
+    float xv[V + W - 1];                       // [W-1 samples before | V own samples]
+    {
+        float own[V];
+        ld16<T>(x + tv * V, own);
+#pragma unroll
+        for (int c = 0; c < V; ++c) xv[W - 1 + c] = own[c];
+    }
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {
+        const float up = __shfl_up_sync(0xffffffffu, xv[W - 1 + V - (W - 1) + j], 1);
+        float v = up;
+        if (tv == 0) {
+            v = p.initial_states ? to_f32<T>(static_cast<const T*>(p.initial_states)[b * p.is_stride_b + d * p.is_stride_d + j * p.is_stride_l]) : 0.f;
+        } else if (lane == 0) {
+            v = to_f32<T>(x[tv * V - (W - 1) + j]);
+        }
+        xv[j] = v;
+    }
+    if (!live) return;
+    float w[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) w[j] = ld_param(p.weight, p.weight_dtype, d * W + j);
+    const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+    const bool silu = p.silu != 0;
+    float y[V];
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+        float acc = bias;
+#pragma unroll
+        for (int j = 0; j < W; ++j) acc = fmaf(w[j], xv[c + j], acc);
+        y[c] = act(acc, silu);
+    }
+    st16<T>(static_cast<T*>(p.out) + b * p.out_stride_b + d * p.out_stride_d + tv * V, y);
+    if (p.final_states && tv == nv - 1) {
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j)
+            static_cast<T*>(p.final_states)[b * p.fs_stride_b + d * p.fs_stride_d + j * p.fs_stride_l] = from_f32<T>(xv[V + j]);
+    }
+}
+
+template <typename T>
+static bool vec_ok(const void* ptr, std::initializer_list<int64_t> strides) {
+    constexpr int64_t V = 16 / sizeof(T);
+    if (reinterpret_cast<uintptr_t>(ptr) % 16) return false;
+    for (int64_t s : strides) if (s % V) return false;
+    return true;
+}
+
+template <typename T, int W>
+static void launch_fast(const vtx_causal_conv1d_params& p, bool cl, cudaStream_t s) {
+    constexpr int64_t V = 16 / sizeof(T);
+    if (cl) {
+        const int64_t n = p.B * ceil_div<int64_t>(p.L, (int64_t)CLT) * (p.D / V);
+        const unsigned blocks = (unsigned)ceil_div<int64_t>(n, 256);
+        if (p.seq_idx) fwd_cl_kernel<T, W, true><<<blocks, 256, 0, s>>>(p);
+        else fwd_cl_kernel<T, W, false><<<blocks, 256, 0, s>>>(p);
+    } else {
+        const int64_t n = p.B * p.D * (p.L / V);
+        fwd_tl_kernel<T, W><<<(unsigned)ceil_div<int64_t>(n, 256), 256, 0, s>>>(p);
     }
 }
 
@@ -174,8 +358,20 @@ extern "C" int vtx_causal_conv1d_fwd(const vtx_causal_conv1d_params* p, void* st
     const unsigned blocks = (unsigned)ceil_div<int64_t>(n, 256);
     cudaStream_t s = (cudaStream_t)stream;
     VTX_DISPATCH_IO(p->io_dtype, T, {
-        if (cl) fwd_kernel<T, true><<<blocks, 256, 0, s>>>(*p);
-        else fwd_kernel<T, false><<<blocks, 256, 0, s>>>(*p);
+        constexpr int64_t V = 16 / sizeof(T);
+        const bool fast_cl = cl && p->out_stride_d == 1 && p->D % V == 0 && p->B * p->L * (p->D / V) < ((int64_t)1 << 38) &&
+                             vec_ok<T>(p->x, {p->x_stride_b, p->x_stride_l}) && vec_ok<T>(p->out, {p->out_stride_b, p->out_stride_l});
+        const bool fast_tl = !cl && p->x_stride_l == 1 && p->out_stride_l == 1 && !p->seq_idx && p->L % V == 0 &&
+                             vec_ok<T>(p->x, {p->x_stride_b, p->x_stride_d}) && vec_ok<T>(p->out, {p->out_stride_b, p->out_stride_d});
+        if (fast_cl || fast_tl) {
+            if (p->W == 2) launch_fast<T, 2>(*p, cl, s);
+            else if (p->W == 3) launch_fast<T, 3>(*p, cl, s);
+            else launch_fast<T, 4>(*p, cl, s);
+        } else if (cl) {
+            fwd_kernel<T, true><<<blocks, 256, 0, s>>>(*p);
+        } else {
+            fwd_kernel<T, false><<<blocks, 256, 0, s>>>(*p);
+        }
     });
     return check_launch("causal_conv1d_fwd");
 }

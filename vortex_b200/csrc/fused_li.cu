@@ -83,7 +83,8 @@ struct Args {
     const void* bias; int64_t bias_dtype;
     const float* log_poles; const float* theta; const float* res_re; const float* res_im;
     __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
-    float* state;
+    float* state; const float* state_in;   // state after the last token (out), state before the first (in, or null)
+    int hist;                      // rows in front of u covered by the tensor map (the sequence's earlier samples)
     float* carry; int* flags;      // [walk][slice][32][16] states handed from slice to slice, arrival counters
     int64_t L, D, G, S, B;
     int spp, nslice;               // steps per slice, slices per walk
@@ -433,6 +434,19 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
         float S[8];                                            // this component of the state at a chunk start
 #pragma unroll
         for (int c = 0; c < 8; ++c) S[c] = 0.f;
+        if (slice == 0 && a.state_in && (jj >> 1) < (int)a.S) {
+            // a call that continues an earlier one starts from that call's end state (same layout as a.state);
+            // the walk then has no padding in front (the host only routes such calls here when L % SUPER == 0)
+            const bool cplx = a.theta != nullptr;
+            if (cplx || !(jj & 1)) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int64_t d = g * CH + 8 * half + c;
+                    const int64_t idx = (b * a.D + d) * a.S + (jj >> 1);
+                    S[c] = a.state_in[cplx ? 2 * idx + (jj & 1) : idx];
+                }
+            }
+        }
         if (slice > 0) {
             // wait (bounded) for both state warps of the previous slice, then take its final state over
             const int64_t prev = walk * (a.nslice - 1) + (slice - 1);
@@ -575,7 +589,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 for (int s = 0; s < NS; ++s) {
                     if (s % NTMA != tw) continue;
                     const uint32_t dst = sm_u + (uint32_t)(stg * STAGE_BYTES + s * BOX_STRIDE);
-                    const int row = (NS * (kbase + k) + s) * CHUNK + h * HROWS - 2 - s - pad;      // stream s is staged s rows early
+                    const int row = (NS * (kbase + k) + s) * CHUNK + h * HROWS - 2 - s - pad + a.hist;      // stream s is staged s rows early
                     if (INTERLEAVED) {
                         tma_load_3d(dst, &tmap, bar, col[0], row, (int)b);
                     } else {
@@ -623,7 +637,8 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream);
 static bool li_tc_shape(const vtx_fused_iir_params* p) {
     using namespace li;
     return p->io_dtype == VTX_BF16 && p->D == p->modal.G * CH && p->modal.S <= NPOLE && p->K3 == 3 && !p->b3 &&
-           !p->state_in && !p->fir_state_in && (reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 &&
+           !p->fir_state_in && ((!p->state_in && p->u_hist_rows == 0) || (p->L % SUPER == 0 && (p->u_hist_rows == 0 || p->u_hist_rows >= 2))) &&
+           (reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 &&
            (p->y_stride_b % 16) == 0 && (reinterpret_cast<uintptr_t>(p->u) % 16) == 0 && (p->u_stride_l % 8) == 0 &&
            (p->u_stride_b % 8) == 0 &&
            (p->layout == VTX_QKV_INTERLEAVED || (p->D % 8) == 0) &&
@@ -655,7 +670,7 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     a.log_poles = static_cast<const float*>(p->modal.log_poles); a.theta = static_cast<const float*>(p->modal.theta);
     a.res_re = static_cast<const float*>(p->modal.res_re); a.res_im = static_cast<const float*>(p->modal.res_im);
     a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
-    a.state = p->state;
+    a.state = p->state; a.state_in = p->state_in; a.hist = (int)p->u_hist_rows;
     a.L = p->L; a.D = p->D; a.G = p->modal.G; a.S = p->modal.S; a.B = p->B;
     const int64_t walks = p->B * p->modal.G, ntotal = (p->L + SUPER - 1) / SUPER;
     a.nslice = 1; a.spp = (int)ntotal;
@@ -680,7 +695,8 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
                 "fused_iir: D*itemsize must be a multiple of 16 bytes for this q/k/v layout");
     const bool inter = p->layout == VTX_QKV_INTERLEAVED;
     CUtensorMap tmap;
-    if (int rc = make_tmap_3d(&tmap, p->u, VTX_BF16, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b,
+    const __nv_bfloat16* u_first = static_cast<const __nv_bfloat16*>(p->u) - p->u_hist_rows * p->u_stride_l;
+    if (int rc = make_tmap_3d(&tmap, u_first, VTX_BF16, 3 * p->D, p->L + p->u_hist_rows, p->B, p->u_stride_l, p->u_stride_b,
                               inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_iir"))
         return rc;
     const int variant = !inter ? 0 : (a.flip ? 2 : 1);

@@ -64,6 +64,7 @@ struct Args {
     void* y; int64_t ysb, ysl;
     float* state; const float* state_in;
     const void* fs_in; int64_t fs_dtype;
+    int64_t hist_rows;             // rows in front of u that hold the sequence's earlier samples
     float* scratch;
     int64_t B, L, D;
     QkvMap map;
@@ -233,7 +234,7 @@ struct Stream {
     }
     // sample at time t < t0: this call's rows, else the rows the previous call ended with, else zero
     __device__ __forceinline__ float hist(const Args& a, const T* col, int64_t bidx, int64_t c, int64_t t) const {
-        if (t >= 0) return to_f32<T>(col[t * a.sl]);
+        if (t >= -a.hist_rows) return to_f32<T>(col[t * a.sl]);
         if (!a.fs_in) return 0.f;
         return ld_param(a.fs_in, a.fs_dtype, (bidx * 3 * a.D + c) * 2 + (2 + t));
     }
@@ -482,6 +483,8 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
     VTX_REQUIRE(p->K3 == 3, VTX_ERR_UNSUPPORTED, "fused_iir: needs a 3-tap featurizer (got %lld taps)", (long long)p->K3);
     VTX_REQUIRE(p->modal.S <= NS, VTX_ERR_UNSUPPORTED, "fused_iir: state size %lld > %d", (long long)p->modal.S, NS);
     VTX_REQUIRE(p->D % p->modal.G == 0, VTX_ERR_BAD_ARG, "fused_iir: D not a multiple of the number of modal systems");
+    VTX_REQUIRE(p->u_hist_rows == 0 || (p->u_hist_rows >= 2 && !p->fir_state_in), VTX_ERR_BAD_ARG,
+                "fused_iir: u_hist_rows must be 0 or >= 2, and excludes fir_state_in");
     VTX_REQUIRE(valid_dtype(p->w3_dtype) && (!p->b3 || valid_dtype(p->b3_dtype)) && (!p->bias || valid_dtype(p->bias_dtype)) &&
                     (!p->fir_state_in || valid_dtype(p->fir_state_dtype)),
                 VTX_ERR_BAD_ARG, "fused_iir: bad parameter dtype");
@@ -491,6 +494,7 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
     a.m = p->modal; a.bias = p->bias; a.bias_dtype = p->bias_dtype;
     a.y = p->y; a.ysb = p->y_stride_b; a.ysl = p->y_stride_l;
     a.state = p->state; a.state_in = p->state_in; a.fs_in = p->fir_state_in; a.fs_dtype = p->fir_state_dtype;
+    a.hist_rows = p->u_hist_rows;
     a.scratch = static_cast<float*>(p->scratch);
     a.B = p->B; a.L = p->L; a.D = p->D;
     a.map.layout = (int)p->layout; a.map.flip = p->flip_x1x2 != 0; a.map.D = p->D; a.map.hd = p->D;

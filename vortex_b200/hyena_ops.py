@@ -112,25 +112,31 @@ class PrefillChunks:
 
 
 def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues, D_skip, *, theta=None, res_im=None,
-                 layout="interleaved", num_heads=1, flip=False, want_state=False, state_in=None, fir_state_in=None):
+                 layout="interleaved", num_heads=1, flip=False, want_state=False, state_in=None, fir_state_in=None,
+                 hist_rows=0):
     """Hyena-LI block (modal long filter).  u [B, L, 3D] -> y [B, L, D], featurizer cache, modal state
     fp32 [B, D, S] (complex poles: [B, D, S, 2]).  ``state_in`` / ``fir_state_in``: the caches a call on the
-    preceding chunk of the same sequences returned (chunked prefill)."""
+    preceding chunk of the same sequences returned (chunked prefill).  ``hist_rows`` (see PrefillChunks) replaces
+    ``fir_state_in`` when the rows before ``u`` in memory are the sequence's earlier rows; chunks of a multiple of
+    384 rows then run on the tensor-core kernel."""
     D = u.shape[-1] // 3
     if short_filter_weight.shape[-1] == 3 and residues.shape[-1] <= 16:
         # one pass over the rows; the library routes per-group-of-16 bf16 systems to the tensor-core kernel
         out = ops.fused_iir_fwd(u, short_filter_weight, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads,
                                 flip=flip, theta=theta, res_im=res_im, want_state=want_state, b3=short_filter_bias,
-                                state_in=state_in, fir_state_in=fir_state_in)
+                                state_in=state_in, fir_state_in=fir_state_in, hist_rows=hist_rows)
         if not want_state:
             return out, None, None
+        if hist_rows:
+            ext = u.as_strided((u.shape[0], u.shape[1] + 2, u.shape[2]), u.stride(), u.storage_offset() - 2 * u.stride(1))
+            return out[0], ext[:, -2:].transpose(1, 2).contiguous(), out[1]
         # featurizer cache: the last two input rows, channel-first (a strided copy, no arithmetic)
         L = u.shape[1]
         fs = u[:, max(L - 2, 0):, :].transpose(1, 2)
         if L < 2 and fir_state_in is not None:
             fs = torch.cat([fir_state_in[..., L:].to(u.dtype), fs], dim=-1)
         return out[0], fs.contiguous(), out[1]
-    if state_in is not None or fir_state_in is not None:
+    if state_in is not None or fir_state_in is not None or hist_rows:
         raise NotImplementedError("chunked prefill needs a 3-tap featurizer and at most 16 poles")
     z, fs = ops.featurizer_fwd(u, short_filter_weight, short_filter_bias, None, want_state=want_state)
     y, st = ops.iir_fwd(z, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads, flip=flip, theta=theta,

@@ -235,14 +235,24 @@ def modal_filter(log_poles, residues, L: int, theta=None, res_im=None) -> torch.
 
 
 def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, layout="interleaved", num_heads=1,
-                  flip=False, theta=None, res_im=None, want_state=False, b3=None, state_in=None, fir_state_in=None):
+                  flip=False, theta=None, res_im=None, want_state=False, b3=None, state_in=None, fir_state_in=None,
+                  hist_rows=0):
     """Channel-last fused long-filter block: u [B, L, 3D] -> y [B, L, D] and, on request, the modal state after the
     last token (fp32 [B, D, S], complex poles [B, D, S, 2]).  The library picks the kernel: tensor cores for bf16
     with one modal system per group of 16 channels, the fp32-pipe recurrence otherwise.  ``state_in`` /
-    ``fir_state_in`` ([B, 3D, 2]) continue an earlier call (chunked prefill)."""
+    ``fir_state_in`` ([B, 3D, 2]) continue an earlier call (chunked prefill).  ``hist_rows`` = H >= 2 instead of
+    ``fir_state_in``: ``u`` is a view whose H preceding rows in memory (same row pitch) hold the sequence's earlier
+    projection rows; with it, and L a multiple of 384, a continued call stays on the tensor-core kernel."""
     _need_cuda(u, w3, residues, bias, b3, state_in, fir_state_in)
     if u.stride(2) != 1:
+        if hist_rows:
+            raise ValueError("hist_rows needs u with unit channel stride (a view into the buffer that holds the history)")
         u = u.contiguous()
+    if hist_rows:
+        if hist_rows < 2 or fir_state_in is not None:
+            raise ValueError("hist_rows must be >= 2 and excludes fir_state_in")
+        if u.storage_offset() < hist_rows * u.stride(1):
+            raise ValueError(f"hist_rows={hist_rows}: u starts {u.storage_offset() // max(u.stride(1), 1)} rows into its storage")
     B, L, C3 = u.shape
     if C3 != 3 * D:
         raise ValueError(f"expected {3 * D} packed channels, got {C3}")
@@ -269,7 +279,7 @@ def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, lay
         y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), scratch=None, B=B, L=L, D=D, K3=w3.shape[1],
         layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip), io_dtype=_code(u),
         state_in=_ptr(state_in), fir_state_in=_ptr(fir_state_in),
-        fir_state_dtype=_code(fir_state_in) if fir_state_in is not None else 0)
+        fir_state_dtype=_code(fir_state_in) if fir_state_in is not None else 0, u_hist_rows=int(hist_rows))
     nscratch = _lib.lib().vtx_fused_iir_scratch_bytes(C.byref(p))
     scratch = torch.empty(nscratch, device=u.device, dtype=torch.uint8) if nscratch > 0 else None
     p.scratch = _ptr(scratch)
