@@ -100,8 +100,9 @@ template <typename T> __device__ __forceinline__ void st16(T* p, const float (&f
 __device__ __forceinline__ float act(float a, bool silu) { return silu ? __fdividef(a, 1.f + __expf(-a)) : a; }
 
 // Channel-last: a thread owns V = 16 bytes of channels and walks CLT samples with the W-1 rows before them in
-// registers; a warp reads and writes 512 contiguous bytes per row.
-constexpr int CLT = 16;
+// registers; a warp reads and writes 512 contiguous bytes per row.  Rows stay in their I/O dtype while in flight (U
+// rows of 16 bytes per thread) and are widened at use, which keeps enough loads in flight for the memory system.
+constexpr int CLT = 32;
 template <typename T, int W, bool SEQ>
 __global__ void __launch_bounds__(256, 2) fwd_cl_kernel(vtx_causal_conv1d_params p) {
     constexpr int V = Vec16<T>::N;
@@ -121,32 +122,33 @@ __global__ void __launch_bounds__(256, 2) fwd_cl_kernel(vtx_causal_conv1d_params
         bias[c] = p.bias ? ld_param(p.bias, p.bias_dtype, d + c) : 0.f;
     }
     // rows t0-(W-1) .. t0-1
-    float h[W - 1][V];
+    Vec16<T> h[W - 1];
     int hs[W - 1];
 #pragma unroll
     for (int j = 0; j < W - 1; ++j) {
         const int64_t t = t0 - (W - 1) + j;
         hs[j] = -1;
         if (t >= 0) {
-            ld16<T>(x + t * p.x_stride_l, h[j]);
+            *reinterpret_cast<uint4*>(&h[j]) = *reinterpret_cast<const uint4*>(x + t * p.x_stride_l);
             if (SEQ) hs[j] = sid[t];
         } else {
 #pragma unroll
             for (int c = 0; c < V; ++c)
-                h[j][c] = p.initial_states ? to_f32<T>(static_cast<const T*>(p.initial_states)[b * p.is_stride_b + (d + c) * p.is_stride_d + (W - 1 + t) * p.is_stride_l]) : 0.f;
+                h[j].e[c] = p.initial_states ? static_cast<const T*>(p.initial_states)[b * p.is_stride_b + (d + c) * p.is_stride_d + (W - 1 + t) * p.is_stride_l]
+                                             : from_f32<T>(0.f);
         }
     }
     const bool silu = p.silu != 0;
     const int nt = (int)((p.L - t0) < CLT ? (p.L - t0) : CLT);
-    constexpr int U = V == 8 ? 2 : 4;          // rows in flight
+    constexpr int U = 8;                       // rows in flight
     for (int k0 = 0; k0 < nt; k0 += U) {
-        float xr[U][V];
+        Vec16<T> xr[U];
         int xs[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             xs[u] = 0;
             if (k0 + u < nt) {
-                ld16<T>(x + (t0 + k0 + u) * p.x_stride_l, xr[u]);
+                *reinterpret_cast<uint4*>(&xr[u]) = *reinterpret_cast<const uint4*>(x + (t0 + k0 + u) * p.x_stride_l);
                 if (SEQ) xs[u] = sid[t0 + k0 + u];
             }
         }
@@ -156,34 +158,40 @@ __global__ void __launch_bounds__(256, 2) fwd_cl_kernel(vtx_causal_conv1d_params
                 float y[V];
 #pragma unroll
                 for (int c = 0; c < V; ++c) {
-                    float acc = fmaf(w[W - 1][c], xr[u][c], bias[c]);
+                    float acc = fmaf(w[W - 1][c], to_f32<T>(xr[u].e[c]), bias[c]);
 #pragma unroll
                     for (int j = 0; j < W - 1; ++j) {
-                        const bool on = !SEQ || hs[j] == xs[u];
-                        acc = on ? fmaf(w[j][c], h[j][c], acc) : acc;
+                        // the row W-1-j samples back: an earlier row of this batch, else the carried window
+                        const int back = W - 1 - j;
+                        const float v = to_f32<T>(u - back >= 0 ? xr[u - back >= 0 ? u - back : 0].e[c] : h[u + j < W - 1 ? u + j : 0].e[c]);
+                        const int vs = u - back >= 0 ? xs[u - back >= 0 ? u - back : 0] : hs[u + j < W - 1 ? u + j : 0];
+                        const bool on = !SEQ || vs == xs[u];
+                        acc = on ? fmaf(w[j][c], v, acc) : acc;
                     }
                     y[c] = act(acc, silu);
                 }
                 st16<T>(out + (t0 + k0 + u) * p.out_stride_l, y);
-#pragma unroll
-                for (int j = 0; j + 1 < W - 1; ++j) {
-                    hs[j] = hs[j + 1];
-#pragma unroll
-                    for (int c = 0; c < V; ++c) h[j][c] = h[j + 1][c];
-                }
-                hs[W - 2] = xs[u];
-#pragma unroll
-                for (int c = 0; c < V; ++c) h[W - 2][c] = xr[u][c];
             }
         }
-    }
-    // after the walk h holds the last W-1 samples of [initial_states | x] when this is the last block
-    if (p.final_states && tb == nblk - 1) {
+        // the window for the next batch: the last W-1 rows of this one (a full batch unless the walk ends here)
+        if (k0 + U < nt) {
 #pragma unroll
-        for (int j = 0; j < W - 1; ++j)
+            for (int j = 0; j < W - 1; ++j) { h[j] = xr[U - (W - 1) + j]; hs[j] = xs[U - (W - 1) + j]; }
+        } else if (p.final_states && tb == nblk - 1) {
+            // last W-1 samples of [initial_states | x]: row L-(W-1)+j is batch row r = nt-k0-(W-1)+j, or window row W-1+r
 #pragma unroll
-            for (int c = 0; c < V; ++c)
-                static_cast<T*>(p.final_states)[b * p.fs_stride_b + (d + c) * p.fs_stride_d + j * p.fs_stride_l] = from_f32<T>(h[j][c]);
+            for (int j = 0; j < W - 1; ++j) {
+                const int r = nt - k0 - (W - 1) + j;
+                Vec16<T> v = h[0];
+#pragma unroll
+                for (int q = 0; q < W - 1; ++q) if (r + (W - 1) == q) v = h[q];
+#pragma unroll
+                for (int q = 0; q < U; ++q) if (r == q) v = xr[q];
+#pragma unroll
+                for (int c = 0; c < V; ++c)
+                    static_cast<T*>(p.final_states)[b * p.fs_stride_b + (d + c) * p.fs_stride_d + j * p.fs_stride_l] = v.e[c];
+            }
+        }
     }
 }
 
