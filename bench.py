@@ -2,7 +2,7 @@
 """Benchmark of the Hyena convolution hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mr|se|li|li_pc|decode_mr|decode_se|decode_li|decode_stack]
+                    [--workload mr|se|li|li_pc|cc1d|decode_mr|decode_se|decode_li|decode_stack]
 
 Default workload: Hyena-MR grouped causal FIR prefill, B=4, L=8192, D=4096, bf16 I/O with fp32
 accumulation, 128-tap filters shared by groups of 16 channels, featurizer and gates fused
@@ -43,6 +43,10 @@ WORKLOADS = {
     "li_pc": dict(B=4, L=8192, D=4096, G=4096, K=0, io="bf16", seed=2, real_poles=True,
                   name="hyena_li_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + modal long conv, 16 real poles per "
                        "channel + skip, state after the last token)"),
+    # the featurizer as the conv extension's operator runs it (causal_conv1d_fn on the channel-last view [B,3D,L] of
+    # the projection rows, width 3, no activation): 2 bytes in + 2 bytes out per packed channel and token
+    "cc1d": dict(B=4, L=8192, D=4096, G=256, K=3, io="bf16", seed=1, cc1d=True,
+                 name="causal_conv1d_fwd B=4 L=8192 channels=12288 bf16 channel-last (width-3 depthwise causal conv)"),
     # one-token decode of one Hyena layer (one launch): a step = B tokens; fp32 caches as after the first decode step
     "decode_mr": dict(B=64, L=1, D=4096, G=256, K=128, io="bf16", seed=3, decode=True,
                       name="hyena_mr_decode B=64 D=4096 bf16 (one layer, one token: featurizer + 128-tap FIR caches)"),
@@ -174,6 +178,8 @@ def run_block(name, pc, u=None):
                                     res_im=pc["res_im"], bias=pc["Dp"])[0]
         return ops.decode_layer(un, pc["w3"], None, c["fir_state"], pc["D"], h=pc["h"], inner_state=c["inner_state"],
                                 bias=pc["Dp"], flip_filter=name == "decode_mr", gated_bias=name == "decode_mr")[0]
+    if name == "cc1d":
+        return hyena_ops.causal_conv1d_fn(u.transpose(1, 2), pc["w3"].reshape(-1, 3))
     if name == "mr":
         return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"])[0]
     if name == "se":
@@ -226,13 +232,16 @@ def cpu_baseline(name, w, steps=1):
     """The reference's CPU path (oracle/torch_port.py) on a bounded channel slice, scaled to the full width."""
     from oracle import torch_port as TP
     torch.manual_seed(0)
-    Ds = {"mr": 256, "se": 256, "li": 64, "li_pc": 64}[name]
+    Ds = {"mr": 256, "se": 256, "li": 64, "li_pc": 64, "cc1d": 256}[name]
     B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
     Gs = max(1, G * Ds // D)
     dt = torch.bfloat16
     u = torch.randn(B, L, 3 * Ds).to(dt)
     w3 = (torch.randn(3 * Ds, 1, 3) / 3 ** 0.5).to(dt)
-    if K > 0:
+    if w.get("cc1d"):
+        def step():
+            return TP.featurizer(u, w3)[0]
+    elif K > 0:
         h = (torch.randn(Gs, 1, K) / K ** 0.5).to(dt)
         Dp = torch.zeros(Ds, dtype=dt)
 
@@ -292,7 +301,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     tokens = w["B"] * w["L"]
-    step_bytes = decode_bytes(w) if w.get("decode") else 8 * w["B"] * w["D"] * w["L"]
+    step_bytes = decode_bytes(w) if w.get("decode") else (12 if w.get("cc1d") else 8) * w["B"] * w["D"] * w["L"]
     config = {"workload": w["name"], "seed": w["seed"], "qkv_layout": "interleaved",
               "sharding": (f"batch: each of {world} rank(s) owns {w['B']} sequences, no collective" if w.get("decode") else
                            f"channel: each of {world} rank(s) owns {w['D']} hidden channels, no collective"),
@@ -429,7 +438,7 @@ def main():
         return
     peak, peak_kind = _peaks()
     # prefill: 3 reads + 1 write of 2-byte elements per channel and token; decode: the caches, read and written once
-    algo_bytes = decode_bytes(w) if w.get("decode") else 8 * w["B"] * w["D"] * w["L"]
+    algo_bytes = decode_bytes(w) if w.get("decode") else (12 if w.get("cc1d") else 8) * w["B"] * w["D"] * w["L"]
     launches_per_step = LAUNCHES.get(a.workload, 1)
     achieved = algo_bytes / (ms_step * 1e-3) / 1e9
     line = {
@@ -452,10 +461,10 @@ def main():
 
 
 # kernel launches of ours per step of each workload (no cache outputs requested)
-LAUNCHES = {"mr": 1, "se": 1, "li": 1, "li_pc": 3, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
+LAUNCHES = {"mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
-NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9}   # small-case captures scaled by the units of a bench launch
+NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch
 
 if __name__ == "__main__":
     main()
