@@ -354,7 +354,8 @@ def test_golden_causal_conv1d(golden, io, W, L):
                                             ("bf16", 1, 4096, 2048, 4, True), ("bf16", 2, 24, 1024, 4, False),
                                             ("f32", 2, 5, 36, 3, False), ("bf16", 2, 12, 37, 3, True),
                                             ("f16", 2, 16, 19, 2, True), ("f32", 1, 4, 3, 4, True),
-                                            ("bf16", 3, 7, 8, 4, False)])
+                                            ("bf16", 3, 7, 8, 4, False), ("bf16", 1, 3, 8256, 4, False),
+                                            ("f32", 2, 2, 1028, 2, False)])
 def test_causal_conv1d_vs_oracle(io, B, D, L, W, cl):
     """Both layouts, packed sequences (seq_idx), initial and final states, against the oracle (kernel rounding)."""
     from vortex_b200 import hyena_ops

@@ -121,21 +121,20 @@ __global__ void __launch_bounds__(256, 2) fwd_cl_kernel(vtx_causal_conv1d_params
         for (int j = 0; j < W; ++j) w[j][c] = ld_param(p.weight, p.weight_dtype, (d + c) * W + j);
         bias[c] = p.bias ? ld_param(p.bias, p.bias_dtype, d + c) : 0.f;
     }
-    // rows t0-(W-1) .. t0-1
-    Vec16<T> h[W - 1];
+    // rows t0-(W-1) .. t0-1, widened once
+    float h[W - 1][V];
     int hs[W - 1];
 #pragma unroll
     for (int j = 0; j < W - 1; ++j) {
         const int64_t t = t0 - (W - 1) + j;
         hs[j] = -1;
         if (t >= 0) {
-            *reinterpret_cast<uint4*>(&h[j]) = *reinterpret_cast<const uint4*>(x + t * p.x_stride_l);
+            ld16<T>(x + t * p.x_stride_l, h[j]);
             if (SEQ) hs[j] = sid[t];
         } else {
 #pragma unroll
             for (int c = 0; c < V; ++c)
-                h[j].e[c] = p.initial_states ? static_cast<const T*>(p.initial_states)[b * p.is_stride_b + (d + c) * p.is_stride_d + (W - 1 + t) * p.is_stride_l]
-                                             : from_f32<T>(0.f);
+                h[j][c] = p.initial_states ? to_f32<T>(static_cast<const T*>(p.initial_states)[b * p.is_stride_b + (d + c) * p.is_stride_d + (W - 1 + t) * p.is_stride_l]) : 0.f;
         }
     }
     const bool silu = p.silu != 0;
@@ -155,95 +154,107 @@ __global__ void __launch_bounds__(256, 2) fwd_cl_kernel(vtx_causal_conv1d_params
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (k0 + u < nt) {
-                float y[V];
+                float cur[V], y[V];
 #pragma unroll
                 for (int c = 0; c < V; ++c) {
-                    float acc = fmaf(w[W - 1][c], to_f32<T>(xr[u].e[c]), bias[c]);
+                    cur[c] = to_f32<T>(xr[u].e[c]);
+                    float acc = fmaf(w[W - 1][c], cur[c], bias[c]);
 #pragma unroll
                     for (int j = 0; j < W - 1; ++j) {
-                        // the row W-1-j samples back: an earlier row of this batch, else the carried window
-                        const int back = W - 1 - j;
-                        const float v = to_f32<T>(u - back >= 0 ? xr[u - back >= 0 ? u - back : 0].e[c] : h[u + j < W - 1 ? u + j : 0].e[c]);
-                        const int vs = u - back >= 0 ? xs[u - back >= 0 ? u - back : 0] : hs[u + j < W - 1 ? u + j : 0];
-                        const bool on = !SEQ || vs == xs[u];
-                        acc = on ? fmaf(w[j][c], v, acc) : acc;
+                        const bool on = !SEQ || hs[j] == xs[u];
+                        acc = on ? fmaf(w[j][c], h[j][c], acc) : acc;
                     }
                     y[c] = act(acc, silu);
                 }
                 st16<T>(out + (t0 + k0 + u) * p.out_stride_l, y);
+#pragma unroll
+                for (int j = 0; j + 1 < W - 1; ++j) {
+                    hs[j] = hs[j + 1];
+#pragma unroll
+                    for (int c = 0; c < V; ++c) h[j][c] = h[j + 1][c];
+                }
+                hs[W - 2] = xs[u];
+#pragma unroll
+                for (int c = 0; c < V; ++c) h[W - 2][c] = cur[c];
             }
         }
-        // the window for the next batch: the last W-1 rows of this one (a full batch unless the walk ends here)
-        if (k0 + U < nt) {
+    }
+    // after the walk h holds the last W-1 samples of [initial_states | x] when this is the last block
+    if (p.final_states && tb == nblk - 1) {
 #pragma unroll
-            for (int j = 0; j < W - 1; ++j) { h[j] = xr[U - (W - 1) + j]; hs[j] = xs[U - (W - 1) + j]; }
-        } else if (p.final_states && tb == nblk - 1) {
-            // last W-1 samples of [initial_states | x]: row L-(W-1)+j is batch row r = nt-k0-(W-1)+j, or window row W-1+r
+        for (int j = 0; j < W - 1; ++j)
 #pragma unroll
-            for (int j = 0; j < W - 1; ++j) {
-                const int r = nt - k0 - (W - 1) + j;
-                Vec16<T> v = h[0];
-#pragma unroll
-                for (int q = 0; q < W - 1; ++q) if (r + (W - 1) == q) v = h[q];
-#pragma unroll
-                for (int q = 0; q < U; ++q) if (r == q) v = xr[q];
-#pragma unroll
-                for (int c = 0; c < V; ++c)
-                    static_cast<T*>(p.final_states)[b * p.fs_stride_b + (d + c) * p.fs_stride_d + j * p.fs_stride_l] = v.e[c];
-            }
-        }
+            for (int c = 0; c < V; ++c)
+                static_cast<T*>(p.final_states)[b * p.fs_stride_b + (d + c) * p.fs_stride_d + j * p.fs_stride_l] = from_f32<T>(h[j][c]);
     }
 }
 
-// Time-last: a thread owns V = 16 bytes of consecutive samples of one channel; the W-1 samples before them come from
-// the previous lane by shuffle (lane 0, and the first vector of a row, fetch them).  No seq_idx on this path.
+// Time-last: a warp owns TLV x 32 consecutive 16-byte vectors of one channel's row; a thread takes the vectors
+// lane, lane + 32, ... (coalesced 512-byte accesses, TLV loads in flight).  The W-1 samples before a vector come from
+// the previous lane by shuffle (lane 31 hands over its previous vector); only the first lane of a warp fetches them
+// from memory, and the first vector of a row takes the initial states.  No seq_idx on this path.
+constexpr int TLV = 4;
 template <typename T, int W>
 __global__ void __launch_bounds__(256) fwd_tl_kernel(vtx_causal_conv1d_params p) {
     constexpr int V = Vec16<T>::N;
-    const int64_t nv = p.L / V;
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool live = i < p.B * p.D * nv;
-    const int64_t ii = live ? i : 0;
-    const int64_t tv = ii % nv, d = (ii / nv) % p.D, b = ii / (nv * p.D);
-    const T* x = static_cast<const T*>(p.x) + b * p.x_stride_b + d * p.x_stride_d;
-    float xv[V + W - 1];                       // [W-1 samples before | V own samples]
-    {
-        float own[V];
-        ld16<T>(x + tv * V, own);
-#pragma unroll
-        for (int c = 0; c < V; ++c) xv[W - 1 + c] = own[c];
-    }
+    const int64_t nv = p.L / V, nch = ceil_div<int64_t>(nv, (int64_t)(32 * TLV));
+    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    if (wid >= p.B * p.D * nch) return;                  // whole warps leave together
     const int lane = threadIdx.x & 31;
+    const int64_t ch = wid % nch, d = (wid / nch) % p.D, b = wid / (nch * p.D);
+    const T* x = static_cast<const T*>(p.x) + b * p.x_stride_b + d * p.x_stride_d;
+    T* out = static_cast<T*>(p.out) + b * p.out_stride_b + d * p.out_stride_d;
+    const int64_t v0 = ch * (32 * TLV) + lane;           // this thread's vectors: v0 + 32 k
+    Vec16<T> raw[TLV];
 #pragma unroll
-    for (int j = 0; j < W - 1; ++j) {
-        const float up = __shfl_up_sync(0xffffffffu, xv[W - 1 + V - (W - 1) + j], 1);
-        float v = up;
-        if (tv == 0) {
-            v = p.initial_states ? to_f32<T>(static_cast<const T*>(p.initial_states)[b * p.is_stride_b + d * p.is_stride_d + j * p.is_stride_l]) : 0.f;
-        } else if (lane == 0) {
-            v = to_f32<T>(x[tv * V - (W - 1) + j]);
-        }
-        xv[j] = v;
-    }
-    if (!live) return;
+    for (int k = 0; k < TLV; ++k)
+        if (v0 + 32 * k < nv) *reinterpret_cast<uint4*>(&raw[k]) = *reinterpret_cast<const uint4*>(x + (v0 + 32 * k) * V);
+        else *reinterpret_cast<uint4*>(&raw[k]) = make_uint4(0, 0, 0, 0);
     float w[W];
 #pragma unroll
     for (int j = 0; j < W; ++j) w[j] = ld_param(p.weight, p.weight_dtype, d * W + j);
     const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
     const bool silu = p.silu != 0;
-    float y[V];
+    // samples before the warp's first vector
+    float first[W - 1];
 #pragma unroll
-    for (int c = 0; c < V; ++c) {
-        float acc = bias;
-#pragma unroll
-        for (int j = 0; j < W; ++j) acc = fmaf(w[j], xv[c + j], acc);
-        y[c] = act(acc, silu);
+    for (int j = 0; j < W - 1; ++j) {
+        first[j] = 0.f;
+        if (lane == 0) {
+            if (ch > 0) first[j] = to_f32<T>(x[v0 * V - (W - 1) + j]);
+            else if (p.initial_states)
+                first[j] = to_f32<T>(static_cast<const T*>(p.initial_states)[b * p.is_stride_b + d * p.is_stride_d + j * p.is_stride_l]);
+        }
     }
-    st16<T>(static_cast<T*>(p.out) + b * p.out_stride_b + d * p.out_stride_d + tv * V, y);
-    if (p.final_states && tv == nv - 1) {
 #pragma unroll
-        for (int j = 0; j < W - 1; ++j)
-            static_cast<T*>(p.final_states)[b * p.fs_stride_b + d * p.fs_stride_d + j * p.fs_stride_l] = from_f32<T>(xv[V + j]);
+    for (int k = 0; k < TLV; ++k) {
+        float xv[V + W - 1];
+#pragma unroll
+        for (int c = 0; c < V; ++c) xv[W - 1 + c] = to_f32<T>(raw[k].e[c]);
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j) {
+            // what the next lane needs: the tail of this vector; lane 31 hands over the tail of its previous vector
+            const float mine = to_f32<T>(raw[k].e[V - (W - 1) + j]);
+            const float prev = k > 0 ? to_f32<T>(raw[k > 0 ? k - 1 : 0].e[V - (W - 1) + j]) : 0.f;
+            const float got = __shfl_sync(0xffffffffu, lane == 31 ? prev : mine, (lane + 31) & 31);
+            xv[j] = (lane == 0 && k == 0) ? first[j] : got;
+        }
+        if (v0 + 32 * k < nv) {
+            float y[V];
+#pragma unroll
+            for (int c = 0; c < V; ++c) {
+                float acc = bias;
+#pragma unroll
+                for (int j = 0; j < W; ++j) acc = fmaf(w[j], xv[c + j], acc);
+                y[c] = act(acc, silu);
+            }
+            st16<T>(out + (v0 + 32 * k) * V, y);
+            if (p.final_states && v0 + 32 * k == nv - 1) {
+#pragma unroll
+                for (int j = 0; j < W - 1; ++j)
+                    static_cast<T*>(p.final_states)[b * p.fs_stride_b + d * p.fs_stride_d + j * p.fs_stride_l] = from_f32<T>(xv[V + j]);
+            }
+        }
     }
 }
 
@@ -264,8 +275,8 @@ static void launch_fast(const vtx_causal_conv1d_params& p, bool cl, cudaStream_t
         if (p.seq_idx) fwd_cl_kernel<T, W, true><<<blocks, 256, 0, s>>>(p);
         else fwd_cl_kernel<T, W, false><<<blocks, 256, 0, s>>>(p);
     } else {
-        const int64_t n = p.B * p.D * (p.L / V);
-        fwd_tl_kernel<T, W><<<(unsigned)ceil_div<int64_t>(n, 256), 256, 0, s>>>(p);
+        const int64_t warps = p.B * p.D * ceil_div<int64_t>(p.L / V, (int64_t)(32 * TLV));
+        fwd_tl_kernel<T, W><<<(unsigned)ceil_div<int64_t>(warps, 8), 256, 0, s>>>(p);
     }
 }
 
@@ -370,6 +381,7 @@ extern "C" int vtx_causal_conv1d_fwd(const vtx_causal_conv1d_params* p, void* st
         const bool fast_cl = cl && p->out_stride_d == 1 && p->D % V == 0 && p->B * p->L * (p->D / V) < ((int64_t)1 << 38) &&
                              vec_ok<T>(p->x, {p->x_stride_b, p->x_stride_l}) && vec_ok<T>(p->out, {p->out_stride_b, p->out_stride_l});
         const bool fast_tl = !cl && p->x_stride_l == 1 && p->out_stride_l == 1 && !p->seq_idx && p->L % V == 0 &&
+                             p->B * p->D * (p->L / V) < ((int64_t)1 << 38) &&
                              vec_ok<T>(p->x, {p->x_stride_b, p->x_stride_d}) && vec_ok<T>(p->out, {p->out_stride_b, p->out_stride_d});
         if (fast_cl || fast_tl) {
             if (p->W == 2) launch_fast<T, 2>(*p, cl, s);
