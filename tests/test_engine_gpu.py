@@ -436,3 +436,31 @@ def test_varlen_states_vs_oracle(io, lens, dim, sl):
     assert np.array_equal(to_np(st), O.causal_conv1d_varlen_states(to_np(x), cu.numpy(), sl))
     with pytest.raises(TypeError):
         hyena_ops.causal_conv1d_varlen_states(x.cuda(), cu.long().cuda(), sl)
+
+
+@pytest.mark.parametrize("io,B,G,dg,L,K", [("bf16", 2, 4, 16, 300, 7), ("f32", 1, 3, 4, 65, 4), ("f16", 2, 2, 8, 128, 32)])
+def test_inner_hyena_se_layouts(io, B, G, dg, L, K):
+    """The reference interface's wrappers over the gate-conv-gate kernel: every input / output layout gives the same
+    numbers as the oracle's y = q * conv(h, k * x) with blocked filter groups."""
+    from vortex_b200 import hyena_ops
+    g = torch.Generator().manual_seed(31 + K)
+    D = G * dg
+    x, k, q = ((torch.rand(B, D, L, generator=g) - 0.5).to(DT[io]) for _ in range(3))
+    h = (torch.randn(G, 1, K, generator=g) / K ** 0.5).to(DT[io])
+    # inner_hyena_se_ref in the I/O dtype: k*x, the convolution and the gate each round to it
+    kx = O.round_io(to_np(k).astype(np.float64) * to_np(x), io)
+    conv = O.round_io(O.causal_fir(kx, O.expand_groups(to_np(h), D), "xcorr"), io)
+    ref = O.round_io(to_np(q) * conv, io)
+    xc, kc, qc = x.cuda(), k.cuda(), q.cuda()
+    y = hyena_ops.inner_hyena_se(xc, kc, qc, h.cuda())
+    assert y.shape == (B, D, L) and rel_l2(y, ref) <= TOL[io]
+    blgdg = lambda t: t.transpose(1, 2).reshape(B, L, G, dg).contiguous()  # noqa: E731
+    bgdgl = lambda t: t.reshape(B, G, dg, L)  # noqa: E731
+    y2 = hyena_ops.inner_hyena_se(blgdg(xc), blgdg(kc), blgdg(qc), h.cuda(), input_layout="blgdg", output_layout="blgdg")
+    assert y2.shape == (B, L, G, dg) and torch.equal(y2, blgdg(y))
+    y3 = hyena_ops.inner_hyena_se(bgdgl(xc), bgdgl(kc), bgdgl(qc), h.cuda()[:, 0], input_layout="bgdgl", output_layout="bld")
+    assert torch.equal(y3, y.transpose(1, 2))
+    y4 = hyena_ops.two_pass_chunked_gate_conv_gate(blgdg(xc), blgdg(kc), blgdg(qc), h.cuda(), schedule="default", autotune=True)
+    assert torch.equal(y4, y2)
+    with pytest.raises(NotImplementedError):
+        hyena_ops.inner_hyena_se(xc, kc, qc, h.cuda(), output_layout="lbd")

@@ -178,6 +178,60 @@ def hyena_se_bdl(x, k, q, h, bias=None, gated_bias=False):
     return y
 
 
+def _to_bdl(t, layout, G):
+    """One operand in 'bdl' (b, d, l), 'blgdg' (b, l, g, dg) or 'bgdgl' (b, g, dg, l) layout -> (b, d, l); channels of
+    a group are consecutive in d (vortex/ops/hyena_se/interface.py:272-319 reshape_inputs)."""
+    if layout == "bdl":
+        return t
+    if layout == "blgdg":
+        b, l, g, dg = t.shape
+        if g != G:
+            raise ValueError("number of groups in feature groups and filter must match")
+        return t.reshape(b, l, g * dg).transpose(1, 2)
+    if layout == "bgdgl":
+        b, g, dg, l = t.shape
+        if g != G:
+            raise ValueError("number of groups in feature groups and filter must match")
+        return t.reshape(b, g * dg, l)
+    raise NotImplementedError("input_layout must be bdl, blgdg or bgdgl")
+
+
+def inner_hyena_se(x, k, q, h, bias=None, input_layout="bdl", output_layout="bdl", inner_layout="blgdg",
+                   apply_gated_bias=False, **kernel_options):
+    """``inner_hyena_se`` of the reference's hyena_ops interface (``vortex/ops/hyena_se/interface.py:400-443``; math
+    ``inner_hyena_se_ref``, ``:342-397``): y = q * causal_conv(h, k * x) with h (g, 1, hl) shared by the dg consecutive
+    channels of a group.  ``input_layout``: 'bdl', 'blgdg' or 'bgdgl'; ``output_layout``: 'bdl', 'bld', 'blgdg' or
+    'bgdgl'.  The reference's scheduling arguments (schedule, autotune, fwd_kernel_cfg, bwd_kernel_cfg,
+    use_fast_causal_conv1d, kernel_path) are accepted and ignored: there is one kernel, and ``inner_layout`` does not
+    change the result."""
+    if h.dim() == 2:
+        h = h.unsqueeze(1)
+    G = h.shape[0]
+    if not (x.shape == k.shape == q.shape):
+        raise ValueError("feature groups must have the same shape")
+    xb, kb, qb = (_to_bdl(t, input_layout, G) for t in (x, k, q))
+    y = hyena_se_bdl(xb, kb, qb, h, bias, apply_gated_bias)             # (b, d, l)
+    b, d, l = y.shape
+    if output_layout == "bdl":
+        return y
+    if output_layout == "bld":
+        return y.transpose(1, 2)
+    if output_layout == "blgdg":
+        return y.transpose(1, 2).reshape(b, l, G, d // G)
+    if output_layout == "bgdgl":
+        return y.reshape(b, G, d // G, l)
+    raise NotImplementedError("output_layout must be bdl, bld, blgdg or bgdgl")
+
+
+def two_pass_chunked_gate_conv_gate(x, B, C, h, return_toeplitz=False, **kernel_options):
+    """Forward of the reference's ``two_pass_chunked_gate_conv_gate`` (``vortex/ops/hyena_se/interface.py:170-204``;
+    kernel ``two_pass_fwd_grouped``, ``fwd.py:17``): y = C * xcorr(h_g, B * x) on (bs, l, g, dg) tensors.  The chunking
+    and autotuning arguments are accepted and ignored; no Toeplitz matrices are returned (there is no backward)."""
+    if return_toeplitz:
+        raise NotImplementedError("return_toeplitz serves the backward pass, which is not built")
+    return gcg_fwd(x, B, C, h)
+
+
 def hyena_x_bdl_fwd(q, k, v, h):
     """Hyena-X forward with the reference's name and (b, d, l) operands
     (``vortex/ops/hyena_x/triton_indirect_fwd.py:262``; math ``hyena_x_fwd_ref``, ``:413-424``)."""
