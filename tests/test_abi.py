@@ -84,3 +84,37 @@ def test_fused_iir_scratch_plan():
     assert n > 0 and n % (4096 * 16 * 4) == 0
     assert q(1, 131072, 4096, 4096, cplx=True) == 2 * n
     assert q(1, 40, 4096, 4096) == 0                        # too short to cut
+
+
+def test_conv_extension_argument_checks():
+    """The conv extension's entry points report bad arguments by code before any launch, and the host wrappers
+    reject CPU tensors, unknown activations and wrong layouts."""
+    from vortex_b200 import hyena_ops
+    lib = _lib.lib()
+    assert lib.vtx_causal_conv1d_fwd(C.byref(_lib.CausalConv1dParams()), None) == -1
+    p = _lib.CausalConv1dParams(x=16, weight=16, out=16, B=1, D=8, L=8, W=5)
+    assert lib.vtx_causal_conv1d_fwd(C.byref(p), None) == -2 and "between 2 and 4" in _lib.last_error()
+    u = _lib.CausalConv1dUpdateParams(x=16, weight=16, out=16, conv_state=16, B=1, D=8, L=1, W=4, state_len=2)
+    assert lib.vtx_causal_conv1d_update(C.byref(u), None) == -1 and "shorter" in _lib.last_error()
+    assert lib.vtx_causal_conv1d_varlen_states(C.byref(_lib.VarlenStatesParams()), None) == -1
+    x, w = torch.zeros(1, 8, 8), torch.zeros(8, 3)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        hyena_ops.causal_conv1d_fn(x, w)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        hyena_ops.causal_conv1d_update(x[..., 0], torch.zeros(1, 8, 2), w)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        hyena_ops.causal_conv1d_varlen_states(torch.zeros(8, 4), torch.tensor([0, 8], dtype=torch.int32), 2)
+
+
+def test_interface_layouts_on_cpu():
+    """Layout plumbing of inner_hyena_se needs no GPU: every input layout maps to the same (b, d, l) view."""
+    from vortex_b200.hyena_ops import _to_bdl
+    B, G, dg, L = 2, 3, 4, 5
+    x = torch.arange(B * G * dg * L, dtype=torch.float32).reshape(B, G * dg, L)
+    assert torch.equal(_to_bdl(x, "bdl", G), x)
+    assert torch.equal(_to_bdl(x.transpose(1, 2).reshape(B, L, G, dg), "blgdg", G), x)
+    assert torch.equal(_to_bdl(x.reshape(B, G, dg, L), "bgdgl", G), x)
+    with pytest.raises(ValueError):
+        _to_bdl(x.reshape(B, G, dg, L), "bgdgl", G + 1)
+    with pytest.raises(NotImplementedError):
+        _to_bdl(x, "lbd", G)
