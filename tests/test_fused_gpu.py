@@ -370,7 +370,8 @@ def test_fused_li_chunked_prefill_carries_state(io, cplx, cuts):
     assert rel_l2(y, ref) <= (1e-4 if io == "f32" else TOL["bf16"])
 
 
-@pytest.mark.parametrize("cplx,cuts", [(True, (0, 768, 1152, 1920)), (False, (0, 384, 2304)), (True, (0, 1000, 1384))])
+@pytest.mark.parametrize("cplx,cuts", [(True, (0, 768, 1152, 1920)), (False, (0, 384, 2304)), (True, (0, 1000, 1384)),
+                                       (True, (0, 500, 1500, 1600, 2601)), (False, (0, 385, 1154))])
 def test_fused_li_tensor_core_chunked_prefill(cplx, cuts):
     """Grouped bf16 systems (the tensor-core kernel): chunks that are views of the whole projection buffer, each call
     told that earlier rows precede its view and given the modal state the previous call returned.  Chunks of a

@@ -111,6 +111,9 @@ class PrefillChunks:
         self.seen += Lc
 
 
+LI_STEP = 384      # rows per step of the tensor-core long-filter kernel (4 chunks of 96)
+
+
 def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues, D_skip, *, theta=None, res_im=None,
                  layout="interleaved", num_heads=1, flip=False, want_state=False, state_in=None, fir_state_in=None,
                  hist_rows=0):
@@ -120,6 +123,22 @@ def hyena_li_fwd(u, short_filter_weight, short_filter_bias, log_poles, residues,
     ``fir_state_in`` when the rows before ``u`` in memory are the sequence's earlier rows; chunks of a multiple of
     384 rows then run on the tensor-core kernel."""
     D = u.shape[-1] // 3
+    L = u.shape[1]
+    if (state_in is not None and hist_rows and L > LI_STEP and L % LI_STEP and
+            _li_tensor_core_ok(u, short_filter_weight, short_filter_bias, residues, layout, num_heads)):
+        # a continued call on the tensor-core kernel must be a multiple of its 384-row step (its walk is aligned to
+        # the end of the rows and a carried-in state must not decay over padding): the first L % 384 rows go through
+        # the recurrence kernel, the rest start from the state it leaves; both write into one output
+        r = L % LI_STEP
+        kw = dict(layout=layout, num_heads=num_heads, flip=flip, theta=theta, res_im=res_im, b3=short_filter_bias)
+        y = torch.empty(u.shape[0], L, D, device=u.device, dtype=u.dtype)
+        _, st = ops.fused_iir_fwd(u[:, :r], short_filter_weight, log_poles, residues, D_skip, D, want_state=True,
+                                  state_in=state_in, hist_rows=hist_rows, out=y[:, :r], **kw)
+        res = ops.fused_iir_fwd(u[:, r:], short_filter_weight, log_poles, residues, D_skip, D, want_state=want_state,
+                                state_in=st, hist_rows=hist_rows + r, out=y[:, r:], **kw)
+        if not want_state:
+            return y, None, None
+        return y, u[:, L - 2:].transpose(1, 2).contiguous(), res[1]
     if short_filter_weight.shape[-1] == 3 and residues.shape[-1] <= 16:
         # one pass over the rows; the library routes per-group-of-16 bf16 systems to the tensor-core kernel
         out = ops.fused_iir_fwd(u, short_filter_weight, log_poles, residues, D_skip, D, layout=layout, num_heads=num_heads,

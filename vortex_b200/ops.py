@@ -236,7 +236,7 @@ def modal_filter(log_poles, residues, L: int, theta=None, res_im=None) -> torch.
 
 def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, layout="interleaved", num_heads=1,
                   flip=False, theta=None, res_im=None, want_state=False, b3=None, state_in=None, fir_state_in=None,
-                  hist_rows=0):
+                  hist_rows=0, out=None):
     """Channel-last fused long-filter block: u [B, L, 3D] -> y [B, L, D] and, on request, the modal state after the
     last token (fp32 [B, D, S], complex poles [B, D, S, 2]).  The library picks the kernel: tensor cores for bf16
     with one modal system per group of 16 channels, the fp32-pipe recurrence otherwise.  ``state_in`` /
@@ -260,7 +260,12 @@ def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, lay
     bias, b3 = _param(bias, u), _param(b3, u)
     m, keep = _modal(log_poles, residues, u, theta, res_im)
     cplx = theta is not None
-    y = torch.empty(B, L, D, device=u.device, dtype=u.dtype)
+    if out is None:
+        y = torch.empty(B, L, D, device=u.device, dtype=u.dtype)
+    else:       # a [B, L, D] view with unit channel stride (e.g. a range of rows of a larger output)
+        if tuple(out.shape) != (B, L, D) or out.dtype != u.dtype or out.stride(2) != 1 or out.device != u.device:
+            raise ValueError("out must be a [B, L, D] tensor of u's dtype and device with unit channel stride")
+        y = out
     st = None
     if want_state:
         st = torch.empty((B, D, m.S, 2) if cplx else (B, D, m.S), device=u.device, dtype=torch.float32)
@@ -276,7 +281,7 @@ def fused_iir_fwd(u: torch.Tensor, w3, log_poles, residues, bias, D: int, *, lay
         u=_ptr(u), u_stride_b=u.stride(0), u_stride_l=u.stride(1), w3=_ptr(w3), w3_dtype=_code(w3),
         b3=_ptr(b3), b3_dtype=_code(b3) if b3 is not None else 0,
         modal=m, bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
-        y=_ptr(y), y_stride_b=L * D, y_stride_l=D, state=_ptr(st), scratch=None, B=B, L=L, D=D, K3=w3.shape[1],
+        y=_ptr(y), y_stride_b=y.stride(0), y_stride_l=y.stride(1), state=_ptr(st), scratch=None, B=B, L=L, D=D, K3=w3.shape[1],
         layout=LAYOUTS[layout], num_heads=num_heads, flip_x1x2=int(flip), io_dtype=_code(u),
         state_in=_ptr(state_in), fir_state_in=_ptr(fir_state_in),
         fir_state_dtype=_code(fir_state_in) if fir_state_in is not None else 0, u_hist_rows=int(hist_rows))
