@@ -58,7 +58,9 @@ enum { VTX_BIAS_NONE = 0, VTX_BIAS_ADD = 1, VTX_BIAS_GATED = 2 /* + bias[d] * kv
 
 /* Copies the message of the calling thread's last failed vtx_* call into buf. */
 size_t vtx_last_error(char* buf, size_t len);
-/* ABI version of this header: major * 1000 + minor. */
+/* ABI version of this header: major * 1000 + minor.  vtx_abi_version() returns the value the library was
+ * built with; a binding compares the two (same major, library minor >= the minor it was written for). */
+#define VTX_ABI_VERSION 1002
 int64_t vtx_abi_version(void);
 /* sizeof() of the parameter structs in declaration order (0 = vtx_featurizer_params, ...),
  * -1 past the end; lets a binding verify that its mirror of a struct has the same size. */
@@ -212,7 +214,11 @@ int vtx_iir_fwd(const vtx_iir_params* p, void* stream);
  * counterpart in the reference.  p->scratch is ignored: the segment carries live in an array of
  * VTX_IIR_STATIC_SCRATCH_BYTES that is part of the library image (each GPU that loads the library holds it
  * until exit).  Sizes needing more (see vtx_iir_scratch_bytes) return VTX_ERR_UNSUPPORTED.  The first call on
- * a device resolves the array's device address; make it before any stream capture.  All calls share the
+ * a device resolves the array's device address; make it before any stream capture.  With CUDA's default lazy
+ * module loading the array's bytes are reserved on a device when the library's long-convolution module is first
+ * used there (this first call, or the first vtx_iir_fwd / vtx_modal_filter), not when the library is loaded: make
+ * that call during start-up, BEFORE the host hands the rest of the device memory to its own pools, or the
+ * reservation itself can fail with an out-of-memory launch error.  All calls share the
  * array and it keeps the last call's contents (nothing needs clearing); calls that overlap on the GPU race.
  * Calls no cudaMalloc, cudaFree or other allocating routine. */
 #define VTX_IIR_STATIC_SCRATCH_BYTES (16u << 20)

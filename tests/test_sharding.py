@@ -69,3 +69,42 @@ def test_two_rank_channel_sharding_equals_unsharded(layout, K):
         pr.join(timeout=60)
         assert pr.exitcode == 0
     assert ok
+
+
+def _uneven_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    B, L, D, G = 2, 5, 64, 4                                   # 4 groups on 3 ranks: 1, 1 and 2 groups
+    full = torch.arange(B * L * D, dtype=torch.float32).reshape(B, L, D)
+    d0, d1 = sharding.channel_range(D, G, world, rank)
+    widths = [b - a for a, b in (sharding.channel_range(D, G, world, r) for r in range(world))]
+    ok = torch.equal(sharding.gather_channels(full[..., d0:d1]), full)                     # widths exchanged
+    ok = ok and torch.equal(sharding.gather_channels(full[..., d0:d1], widths=widths), full)   # widths given
+    try:
+        sharding.gather_channels(full[..., d0:d1], widths=[D // world] * world)
+        ok = False
+    except ValueError:
+        pass
+    out.put((rank, bool(ok), widths))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gather_of_uneven_channel_shards():
+    """channel_range hands out whole filter groups, so 4 groups on 3 ranks give shards of 16, 16 and 32 channels:
+    the boundary all-gather pads to the widest shard for the exchange and returns the exact concatenation."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_uneven_worker, args=(r, 3, port, out)) for r in range(3)]
+    for pr in procs:
+        pr.start()
+    got = [out.get(timeout=120) for _ in range(3)]
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    assert all(ok for _, ok, _ in got), got
+    assert got[0][2] == [16, 16, 32]

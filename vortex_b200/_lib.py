@@ -18,6 +18,17 @@ BIAS_NONE, BIAS_ADD, BIAS_GATED = 0, 1, 2
 _p, _i = C.c_void_p, C.c_int64
 
 
+def header_abi_version() -> int:
+    """VTX_ABI_VERSION of include/vortex_b200.h (major * 1000 + minor): the one place the number is written."""
+    import re
+    path = os.path.join(os.path.dirname(PKG), "include", "vortex_b200.h")
+    with open(path) as f:
+        m = re.search(r"#define\s+VTX_ABI_VERSION\s+(\d+)", f.read())
+    if not m:
+        raise RuntimeError(f"{path} does not define VTX_ABI_VERSION")
+    return int(m.group(1))
+
+
 def _struct(name, spec):
     """spec: 'ptr:a i:b ...' -> ctypes.Structure subclass with 8-byte fields only."""
     fields = []
@@ -149,6 +160,10 @@ def lib() -> C.CDLL:
         for name, (res, args) in SYMBOLS.items():
             fn = getattr(handle, name)  # AttributeError if the library does not export it
             fn.restype, fn.argtypes = res, args
+        want, got = header_abi_version(), handle.vtx_abi_version()
+        if got // 1000 != want // 1000 or got < want:
+            raise RuntimeError(f"libvortex_b200.so has ABI version {got}, include/vortex_b200.h {want}: rebuild it "
+                               "with `python -m vortex_b200.build`")
         for i, st in enumerate(STRUCTS):
             if handle.vtx_struct_size(i) != C.sizeof(st):
                 raise RuntimeError(f"ABI mismatch for {st.__name__}: C {handle.vtx_struct_size(i)} vs "

@@ -94,7 +94,7 @@ extern "C" size_t vtx_last_error(char* buf, size_t len) {
     return n;
 }
 
-extern "C" int64_t vtx_abi_version(void) { return 1001; }
+extern "C" int64_t vtx_abi_version(void) { return VTX_ABI_VERSION; }
 
 extern "C" int64_t vtx_struct_size(int64_t which) {
     switch (which) {

@@ -345,7 +345,10 @@ extern "C" int vtx_iir_fwd(const vtx_iir_params* p, void* stream) {
 //   with VTX_ERR_UNSUPPORTED; nothing is launched.
 // * The first call on a device looks the array's device address up (cudaGetSymbolAddress with that device
 //   current -- the array's name is only a host-side handle, never a pointer a kernel could use) and keeps it
-//   per device.  Make that first call outside any stream capture.
+//   per device.  Make that first call outside any stream capture -- and during start-up, before the host
+//   commits the rest of the device memory: with CUDA's default lazy module loading the array is reserved on a
+//   device when this file's module is first used there (this call, vtx_iir_fwd or vtx_modal_filter), not when
+//   the library is loaded.
 // * All calls share the one array and it keeps whatever the last call left in it.  Nothing in it has to be
 //   zero at the start: every word a call reads was written earlier by the same call, except the carry slot of
 //   the last segment, whose value is computed but never used.  Two calls that overlap on the GPU (different

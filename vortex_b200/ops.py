@@ -569,7 +569,20 @@ def iir_fwd_noalloc(z_pre: torch.Tensor, log_poles, residues, bias, D: int, y: t
             raise ValueError("modal parameters must be contiguous fp32 tensors (no conversion is done on this path)")
     if y.shape != (B, D, L) or not y.is_contiguous() or y.dtype != z_pre.dtype:
         raise ValueError("y must be a contiguous [B, D, L] tensor of the input dtype")
+    if residues.dim() != 2:
+        raise ValueError("residues must be [G, S]")
     G, S = residues.shape
+    cplx = theta is not None
+    if state is not None:
+        want = (B, D, S, 2) if cplx else (B, D, S)
+        if (state.dtype != torch.float32 or tuple(state.shape) != want or not state.is_contiguous()
+                or state.device != z_pre.device):
+            raise ValueError(f"state must be a contiguous fp32 {want} tensor on the device of z_pre (the kernel "
+                             "writes that many floats through the pointer)")
+    if y.device != z_pre.device:
+        raise ValueError("y must be on the device of z_pre")
+    if bias is not None and (tuple(bias.shape) != (D,) or not bias.is_contiguous() or bias.dtype not in _DT):
+        raise ValueError(f"bias must be a contiguous [{D}] tensor")
     (q, k, v), hd, (sh, sd) = _qkv_views(z_pre, D, layout, num_heads, flip)
     m = _lib.ModalParams(log_poles=_ptr(log_poles), theta=_ptr(theta), res_re=_ptr(residues), res_im=_ptr(res_im), G=G, S=S)
     p = _lib.IirParams(

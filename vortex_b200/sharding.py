@@ -77,13 +77,36 @@ def shard_block(params: Dict[str, Optional[torch.Tensor]], D: int, G: int, world
     return out
 
 
-def gather_channels(y_shard: torch.Tensor, group=None) -> torch.Tensor:
-    """All-gather the block outputs [B, L, D/W] of all ranks along the channel axis (the one collective at the
-    shard boundary; NCCL over NVLink on GPUs, gloo in the CPU tests)."""
+def gather_channels(y_shard: torch.Tensor, group=None, widths=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather the block outputs [B, L, D_r] of all ranks along the channel axis (the one collective at the
+    shard boundary; NCCL over NVLink on GPUs, gloo in the CPU tests).
+
+    ``widths``: the channel counts D_r of all ranks, e.g. from ``channel_range``; when omitted they are
+    exchanged first (a small collective plus a host read).  Equal shards are gathered in place; unequal ones
+    (``channel_range`` hands out whole filter groups, so G % world != 0 gives shards that differ by one group)
+    are padded to the widest shard for the exchange and cut back afterwards -- a collective with mismatched
+    sizes across ranks is undefined on NCCL.  ``out``: optional [world, B, L, D_max] receive buffer to reuse."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
     if world == 1:
         return y_shard
-    parts = [torch.empty_like(y_shard) for _ in range(world)]
-    dist.all_gather(parts, y_shard.contiguous(), group=group)
-    return torch.cat(parts, dim=-1)
+    if widths is None:
+        mine = torch.tensor([y_shard.shape[-1]], dtype=torch.int64, device=y_shard.device)
+        allw = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allw, mine, group=group)
+        widths = [int(w.item()) for w in allw]
+    widths = [int(w) for w in widths]
+    if len(widths) != world or widths[dist.get_rank(group)] != y_shard.shape[-1]:
+        raise ValueError(f"widths {widths} do not describe this group (this rank holds {y_shard.shape[-1]} channels)")
+    wmax = max(widths)
+    send = y_shard.contiguous()
+    if send.shape[-1] != wmax:
+        send = torch.nn.functional.pad(send, (0, wmax - send.shape[-1]))
+    shape = (world,) + tuple(send.shape)
+    if out is None:
+        out = torch.empty(shape, device=send.device, dtype=send.dtype)
+    elif tuple(out.shape) != shape or out.dtype != send.dtype or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {shape} tensor of the shard's dtype")
+    # (the receive buffer is handed over in its "concatenated along dim 0" form, which every backend accepts)
+    dist.all_gather_into_tensor(out.view((world * send.shape[0],) + tuple(send.shape[1:])), send, group=group)
+    return torch.cat([out[r, ..., :widths[r]] for r in range(world)], dim=-1)
