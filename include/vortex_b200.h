@@ -69,6 +69,12 @@ int64_t vtx_struct_size(int64_t which);
  * (mbarrier / TMA completion) ran out.  Synchronous (a small device-to-host copy); meant to be
  * called after the stream was synchronised.  Returns VTX_OK or VTX_ERR_DEVICE. */
 int vtx_device_status(void);
+/* Diagnostics: how often a kernel polls a global-memory flag written by another block (the hand-over between the
+ * time slices of one long-filter walk) before it gives up, sets the status word and carries on with what it has.
+ * 0 restores the default (2^21 polls with a short sleep each, far beyond any real wait).  A tiny value makes the
+ * give-up path observable: the launch still ends normally, its output is not valid, vtx_device_status() reports
+ * VTX_ERR_DEVICE.  Process-wide; applies to launches made after the call.  No counterpart in the reference. */
+int vtx_debug_set_flag_poll_limit(int64_t polls);
 
 /* ------------------------------------------------------------------------
  * Featurizer: depthwise causal FIR of length K <= 8 over the packed
@@ -208,6 +214,15 @@ typedef struct vtx_iir_params {
 } vtx_iir_params;
 int64_t vtx_iir_scratch_bytes(int64_t B, int64_t L, int64_t D, int64_t S, int64_t complex_poles);
 int vtx_iir_fwd(const vtx_iir_params* p, void* stream);
+
+/* The legacy recurrent prefill, HyenaInferenceEngine.prefill_via_direct_recurrence (engine.py:473-504; taken by
+ * parallel_iir with prefill_style="recurrence", engine.py:314-321): complex poles and residues as (re, im) pairs,
+ * the state held in the I/O dtype and updated in the reference's order (real part first, the imaginary part then
+ * reads the NEW real part), y = q * (sum_s Re(R_s) Re(sigma_s) + bias * kv).
+ *   modal.log_poles = Re(p), modal.theta = Im(p), modal.res_re = Re(R), fp32 [G,S]; modal.res_im is not read.
+ *   state fp32 [B,D,S,2] = (re, im) after the last token, or NULL.  scratch is not used.
+ * One thread per (batch, channel) row walks the sequence: a compatibility path, not a fast one. */
+int vtx_iir_recurrence_fwd(const vtx_iir_params* p, void* stream);
 
 /* Same operator for callers that cannot allocate device memory where they need it (a server that gave all
  * free HBM to its cache pool, a C host without a device allocator, a latency-critical loop).  It has no

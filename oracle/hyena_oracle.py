@@ -348,6 +348,58 @@ def long_conv_gate(z_pre, h, bias, D, io="f32", layout="split", num_heads=1,
     return y.transpose(0, 2, 1), kv
 
 
+def long_fir_gate(z_pre, h, bias, D, threshold, io="f32", layout="split", num_heads=1, flip_x1x2=False):
+    """engine.parallel_iir with ``long_fir_threshold`` (engine.py:339-353): the long filter cut to its first
+    ``threshold`` samples, rounded to the I/O dtype and handed to F.conv1d -- so it is applied as a
+    cross-correlation (the LAST kept sample of h meets the current input), whatever its length.  Then the skip
+    term and the gate as in the FFT branch.  z_pre [B, 3D, L], h [D, L] per channel -> y [B, L, D]."""
+    z = round_io(z_pre, io)
+    q, k, v = select_qkv(z, D, layout, num_heads, flip_x1x2)
+    kv = round_io(k * v, io)
+    h = np.asarray(h, dtype=np.float64)
+    if h.ndim == 3:
+        h = h[0]
+    hk = round_io(h[:, :threshold], io)
+    y = round_io(causal_fir(kv, hk, "xcorr"), io)
+    b = np.asarray(bias, dtype=np.float64)[None, :, None]
+    y = round_io(y + round_io(kv * b, io), io)
+    y = round_io(y * q, io)
+    return y.transpose(0, 2, 1)
+
+
+def recurrence_prefill(z_pre, poles_ri, residues_ri, bias, D, io="f32", layout="split", num_heads=1,
+                       flip_x1x2=False):
+    """engine.parallel_iir with prefill_style="recurrence" -> prefill_via_direct_recurrence (engine.py:314-321,
+    473-504), then the skip term and the gate (engine.py:351-353).
+
+    poles_ri, residues_ri [D, S, 2] as (re, im).  The loop is the reference's: the state lives in the I/O dtype
+    (it is built from x1*v), its real part is updated in place and the imaginary part then reads the NEW real
+    part (engine.py:497-498); every product, difference and sum is a float32 operation of its own; the output
+    keeps sum_s Re(R_s) * Re(state_s).  Returns y [B, L, D] and the state [B, D, S, 2] float32."""
+    f32 = np.float32
+    z = round_io(z_pre, io)
+    q, k, v = select_qkv(z, D, layout, num_heads, flip_x1x2)
+    x = round_io(k * v, io).astype(f32)                                   # x1v [B, D, L]
+    pr, pi = (np.asarray(poles_ri, dtype=f32)[None, ..., j] for j in (0, 1))      # [1, D, S]
+    rr = np.asarray(residues_ri, dtype=f32)[None, ..., 0]
+    B, _, L = x.shape
+    re = np.zeros((B, D, pr.shape[-1]), dtype=f32)
+    im = np.zeros_like(re)
+    rnd = lambda a: round_io(a, io).astype(f32)  # noqa: E731
+    out = np.zeros((B, D, L), dtype=f32)
+    for i in range(L):
+        re = rnd((pr * re - pi * im) + x[:, :, i, None])
+        im = rnd(pr * im + pi * re)
+        acc = np.zeros((B, D), dtype=f32)
+        for s in range(re.shape[-1]):
+            acc = acc + rr[..., s] * re[..., s]
+        out[:, :, i] = rnd(acc)
+    b = np.asarray(bias, dtype=np.float64)[None, :, None]
+    y = round_io(out.astype(np.float64) + round_io(x.astype(np.float64) * b, io), io)
+    y = round_io(y * q, io)
+    return y.transpose(0, 2, 1), np.stack([re, im], axis=-1)
+
+
 def modal_state(kv, log_poles_d):
     """IIR state after prefill: what prefill_via_modal_fft extracts at index
     L-1 (engine.py:552-559): state[b,d,s] = sum_j exp(lambda[d,s]*(L-1-j)) kv[b,d,j].

@@ -109,6 +109,44 @@ def main(ref_root):
                                                                             np32(residues), np32(Dp))
             out[k + "_h"], out[k + "_y"], out[k + "_state"] = np32(h), np32(y), np32(ip.state_dict[3])
 
+    # ---- long convolution, the two other branches of parallel_iir --------------
+    # prefill_style="recurrence" (engine.py:314-321,473-504): complex poles / residues as (re, im) pairs
+    for io, dt in DT.items():
+        g = torch.Generator().manual_seed(2500)
+        B, D, S, L = 2, 12, 16, 48
+        z_pre = torch.randn(B, 3 * D, L, generator=g).to(dt)
+        mag = 0.5 + 0.49 * torch.rand(D, S, generator=g)
+        ang = torch.pi * torch.rand(D, S, generator=g)
+        poles = torch.stack([mag * torch.cos(ang), mag * torch.sin(ang)], -1)[:, :, None]     # [D, S, 1, 2]
+        residues = torch.randn(D, S, 1, 2, generator=g)
+        Dp = torch.randn(D, generator=g).to(dt)
+        eng = HyenaInferenceEngine(layer_idx=5)
+        ip = _P()
+        y = eng.parallel_iir(z_pre, None, Dp, L, poles=poles, residues=residues, t=None, dims=(D, 1, D, S, D),
+                             layer_idx=5, inference_params=ip, prefill_style="recurrence")
+        k = f"iirrec_{io}"
+        out[k + "_z"], out[k + "_p"], out[k + "_R"], out[k + "_D"] = np32(z_pre), np32(poles), np32(residues), np32(Dp)
+        out[k + "_y"], out[k + "_state"] = np32(y), np32(ip.state_dict[5])
+    # long_fir_threshold (engine.py:339-349): the filter cut to its first samples and handed to F.conv1d; the
+    # reference can only run it without inference_params (its state prefill reads a spectrum this branch never makes)
+    for io, dt in DT.items():
+        for thr in (24, 160):
+            g = torch.Generator().manual_seed(2600 + thr)
+            B, D, S, L = 1, 16, 16, 200
+            z_pre = torch.randn(B, 3 * D, L, generator=g).to(dt)
+            log_poles = torch.log(0.9 + 0.099 * torch.rand(D, S, 1, generator=g))
+            residues = torch.randn(D, S, generator=g)
+            Dp = torch.randn(D, generator=g).to(dt)
+            t = torch.arange(L)[None, None]
+            h = (residues[..., None] * (log_poles * t).exp()).sum(1)[None]
+            eng = HyenaInferenceEngine()
+            y = eng.parallel_iir(z_pre, h, Dp, L, poles=log_poles, residues=residues, t=t, dims=(D, 1, D, S, D),
+                                 layer_idx=0, inference_params=None, long_fir_threshold=thr)
+            k = f"iirfir_{io}_thr{thr}"
+            out[k + "_z"], out[k + "_lp"], out[k + "_R"], out[k + "_D"] = (np32(z_pre), np32(log_poles),
+                                                                            np32(residues), np32(Dp))
+            out[k + "_h"], out[k + "_y"] = np32(h), np32(y)
+
     # ---- decode: step_fir ----------------------------------------------------
     for io, dt in DT.items():
         for K, c0, flip, gb in ((3, 2, False, False), (3, 1, False, False), (7, 6, False, False),

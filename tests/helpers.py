@@ -16,6 +16,12 @@ def rel_l2(a, b):
     return O.rel_l2(to_np(a) if torch.is_tensor(a) else a, to_np(b) if torch.is_tensor(b) else b)
 
 
+def check(label, err, tol):
+    """Assert err <= tol and leave the measured figure in the captured output (``pytest -s`` or ``-rP`` shows it)."""
+    print(f"PARITY {label}: {err:.3e} (tolerance {tol:.1e})")
+    assert err <= tol, f"{label}: {err:.3e} > {tol:.1e}"
+
+
 def make_block(seed, B, L, D, G, K, io, modal=False, S=16, complex_poles=False):
     """Random projection output u [B, L, 3D] and the parameters of one Hyena block (CPU tensors)."""
     g = torch.Generator().manual_seed(seed)

@@ -118,3 +118,16 @@ def test_interface_layouts_on_cpu():
         _to_bdl(x.reshape(B, G, dg, L), "bgdgl", G + 1)
     with pytest.raises(NotImplementedError):
         _to_bdl(x, "lbd", G)
+
+
+def test_status_codes_map_to_the_reference_exception_types():
+    """Bad argument -> ValueError, unsupported -> NotImplementedError, alignment -> ValueError, launch and device
+    errors -> RuntimeError (what TORCH_CHECK / assert / NotImplementedError sites of the reference raise)."""
+    for rc, exc in ((-1, ValueError), (-2, NotImplementedError), (-3, ValueError), (-4, RuntimeError),
+                    (-5, RuntimeError), (-99, RuntimeError)):
+        with pytest.raises(exc):
+            _lib.check(rc)
+    _lib.check(0)
+    lib = _lib.lib()
+    assert lib.vtx_debug_set_flag_poll_limit(-1) == -1
+    assert lib.vtx_debug_set_flag_poll_limit(0) == 0

@@ -187,3 +187,31 @@ def test_varlen_states(golden, n):
     want = golden[k + "_st"]
     st = O.causal_conv1d_varlen_states(golden[k + "_x"], golden[k + "_cu"], want.shape[-1])
     assert st.shape == want.shape and np.array_equal(st, want)
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+def test_recurrence_prefill(golden, io):
+    """prefill_style="recurrence" (engine.py:473-504): the oracle repeats the reference's loop, its update order and
+    its rounding of the state to the I/O dtype, so the cached state is reproduced bit for bit."""
+    k = f"iirrec_{io}"
+    y, st = O.recurrence_prefill(golden[k + "_z"], golden[k + "_p"][:, :, 0], golden[k + "_R"][:, :, 0],
+                                 golden[k + "_D"], 12, io=io)
+    close(y, golden[k + "_y"], io)
+    assert st.dtype == np.float32 and np.array_equal(st, golden[k + "_state"])
+    # the reference's update is not a complex product: the true recurrence sigma <- p sigma + x ends elsewhere
+    z = O.round_io(golden[k + "_z"], io)
+    _, kk, v = O.select_qkv(z, 12, "split")
+    p = golden[k + "_p"][:, :, 0, 0] + 1j * golden[k + "_p"][:, :, 0, 1]
+    true = O.modal_state_complex(O.round_io(kk * v, io), p)
+    got = st[..., 0] + 1j * st[..., 1]
+    assert np.linalg.norm(got - true) / np.linalg.norm(true) > 1e-2
+
+
+@pytest.mark.parametrize("io", ["f32", "bf16"])
+@pytest.mark.parametrize("thr", [24, 160])
+def test_long_fir_threshold(golden, io, thr):
+    """long_fir_threshold (engine.py:339-349): the truncated filter goes through F.conv1d, i.e. as a
+    cross-correlation, whatever its length."""
+    k = f"iirfir_{io}_thr{thr}"
+    y = O.long_fir_gate(golden[k + "_z"], golden[k + "_h"], golden[k + "_D"], 16, thr, io=io)
+    close(y, golden[k + "_y"], io)

@@ -126,6 +126,7 @@ SYMBOLS = {
     "vtx_abi_version": (_i, []),
     "vtx_struct_size": (_i, [_i]),
     "vtx_device_status": (C.c_int, []),
+    "vtx_debug_set_flag_poll_limit": (C.c_int, [_i]),
     "vtx_featurizer_fwd": (C.c_int, [C.POINTER(FeaturizerParams), _p]),
     "vtx_gcg_fwd": (C.c_int, [C.POINTER(GcgParams), _p]),
     "vtx_fused_fir_fwd": (C.c_int, [C.POINTER(FusedFirParams), _p]),
@@ -133,6 +134,7 @@ SYMBOLS = {
     "vtx_iir_scratch_bytes": (_i, [_i, _i, _i, _i, _i]),
     "vtx_iir_fwd": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_iir_fwd_noalloc": (C.c_int, [C.POINTER(IirParams), _p]),
+    "vtx_iir_recurrence_fwd": (C.c_int, [C.POINTER(IirParams), _p]),
     "vtx_fused_iir_fwd": (C.c_int, [C.POINTER(FusedIirParams), _p]),
     "vtx_fused_iir_scratch_bytes": (_i, [C.POINTER(FusedIirParams)]),
     "vtx_hyena_x_fwd": (C.c_int, [C.POINTER(HyenaXParams), _p]),

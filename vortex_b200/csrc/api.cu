@@ -22,6 +22,9 @@ int check_launch(const char* what) {
     return VTX_OK;
 }
 
+static int g_flag_poll_limit = 1 << 21;
+int flag_poll_limit() { return g_flag_poll_limit; }
+
 static StatusReader* g_readers = nullptr;
 void register_status_reader(StatusReader* r) {
     r->next = g_readers;
@@ -82,6 +85,12 @@ extern "C" int vtx_device_status(void) {
     }
     if (worst) vtx::fail(VTX_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", worst);
     return worst ? VTX_ERR_DEVICE : VTX_OK;
+}
+
+extern "C" int vtx_debug_set_flag_poll_limit(int64_t polls) {
+    if (polls < 0 || polls > (1 << 30)) return vtx::fail(VTX_ERR_BAD_ARG, "flag poll limit out of range");
+    vtx::g_flag_poll_limit = polls == 0 ? 1 << 21 : (int)polls;
+    return VTX_OK;
 }
 
 extern "C" size_t vtx_last_error(char* buf, size_t len) {

@@ -24,6 +24,10 @@ int check_launch(const char* what);         // cudaGetLastError -> VTX_ERR_LAUNC
 
 constexpr int kNumSMs = 148;
 
+// Polls (each followed by a short sleep) of a global-memory flag before a kernel that waits for another block gives
+// up, records a code in the device status word and carries on; vtx_debug_set_flag_poll_limit changes it.
+int flag_poll_limit();
+
 // ---- dtype helpers --------------------------------------------------------
 template <typename T> struct DTypeCode;
 template <> struct DTypeCode<float> { static constexpr int value = VTX_F32; };

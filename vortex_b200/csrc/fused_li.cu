@@ -88,6 +88,7 @@ struct Args {
     float* carry; int* flags;      // [walk][slice][32][16] states handed from slice to slice, arrival counters
     int64_t L, D, G, S, B;
     int spp, nslice;               // steps per slice, slices per walk
+    int poll_limit;                // polls of a slice's arrival counter before the next slice gives up
     int layout, flip;
     int64_t hd;
 };
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             // wait (bounded) for both state warps of the previous slice, then take its final state over
             const int64_t prev = walk * (a.nslice - 1) + (slice - 1);
             bool have = false;
-            for (int it = 0; it < (1 << 21) && !have; ++it) {
+            for (int it = 0; it < a.poll_limit && !have; ++it) {
                 int v;
                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.flags + prev) : "memory");
                 have = v >= 2;
@@ -674,6 +675,7 @@ extern "C" int vtx_fused_iir_fwd(const vtx_fused_iir_params* p, void* stream_) {
     a.L = p->L; a.D = p->D; a.G = p->modal.G; a.S = p->modal.S; a.B = p->B;
     const int64_t walks = p->B * p->modal.G, ntotal = (p->L + SUPER - 1) / SUPER;
     a.nslice = 1; a.spp = (int)ntotal;
+    a.poll_limit = flag_poll_limit();
     if (p->scratch) {       // without scratch every walk is one block
         plan_slices(walks, ntotal, a.nslice, a.spp);
         if (a.nslice > 1) {

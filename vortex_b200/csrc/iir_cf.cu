@@ -253,6 +253,56 @@ __global__ void __launch_bounds__(ITHREADS) iir_output_kernel(vtx_iir_params p, 
     }
 }
 
+// The reference's legacy recurrent prefill (vortex/model/engine.py:473-504), step for step: complex poles and
+// residues given as (re, im) pairs, the state kept in the I/O dtype (the reference builds it from x1*v, so with bf16
+// activations every update is rounded to bf16), and the real part updated in place BEFORE the imaginary part reads
+// it:   re' = pr re - pi im + x ;  im' = pr im + pi re'   (not a complex product: that is what the reference
+// computes, and its cached state continues from it).  Every product, difference and sum is rounded on its own, as
+// the reference's separate tensor operations are.  out[t] = sum_s Re(R_s) re_s[t] in the I/O dtype, then the same
+// skip term and gate as the FFT branch.  One thread walks one (batch, channel) row: a compatibility path.
+// modal.log_poles holds Re(p), modal.theta Im(p), modal.res_re Re(R), all fp32 [G, S].
+template <typename T>
+__global__ void __launch_bounds__(ITHREADS) iir_recurrence_kernel(vtx_iir_params p) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.B * p.D) return;
+    const int64_t b = i / p.D, d = i % p.D, g = d / (p.D / p.modal.G);
+    const int S = (int)p.modal.S;
+    float pr[IS], pi[IS], rr[IS], re[IS], im[IS];
+#pragma unroll
+    for (int s = 0; s < IS; ++s) {
+        pr[s] = pi[s] = rr[s] = re[s] = im[s] = 0.f;
+        if (s < S) {
+            pr[s] = static_cast<const float*>(p.modal.log_poles)[g * S + s];
+            pi[s] = static_cast<const float*>(p.modal.theta)[g * S + s];
+            rr[s] = static_cast<const float*>(p.modal.res_re)[g * S + s];
+        }
+    }
+    const int64_t hn = d / p.head_dim, hj = d % p.head_dim;
+    const T* q = static_cast<const T*>(p.q) + b * p.q_stride_b + hn * p.q_stride_h + hj * p.q_stride_d;
+    const T* k = static_cast<const T*>(p.k) + b * p.k_stride_b + hn * p.k_stride_h + hj * p.k_stride_d;
+    const T* v = static_cast<const T*>(p.v) + b * p.v_stride_b + hn * p.v_stride_h + hj * p.v_stride_d;
+    T* y = static_cast<T*>(p.y) + b * p.y_stride_b + d * p.y_stride_d;
+    const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+    for (int64_t t = 0; t < p.L; ++t) {
+        const float x = round_io<T>(to_f32<T>(k[t]) * to_f32<T>(v[t]));
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < IS; ++s) {
+            const float nr = round_io<T>(__fadd_rn(__fsub_rn(__fmul_rn(pr[s], re[s]), __fmul_rn(pi[s], im[s])), x));
+            const float ni = round_io<T>(__fadd_rn(__fmul_rn(pr[s], im[s]), __fmul_rn(pi[s], nr)));
+            re[s] = nr; im[s] = ni;
+            acc = __fadd_rn(acc, __fmul_rn(rr[s], nr));
+        }
+        const float conv = round_io<T>(acc);
+        const float z = round_io<T>(conv + round_io<T>(bias * x));
+        y[t * p.y_stride_l] = from_f32<T>(z * to_f32<T>(q[t]));
+    }
+    if (p.state) {
+        float* so = p.state + (b * p.D + d) * S * 2;
+        for (int s = 0; s < S; ++s) { so[2 * s] = re[s]; so[2 * s + 1] = im[s]; }
+    }
+}
+
 __global__ void modal_filter_kernel(vtx_modal_params m, float* h, int64_t L) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= m.G * L) return;
@@ -328,6 +378,21 @@ extern "C" int vtx_iir_fwd(const vtx_iir_params* p, void* stream) {
         else iir_output_kernel<T, false><<<blocks, ITHREADS, 0, s>>>(*p, pl);
     });
     return check_launch("iir");
+}
+
+extern "C" int vtx_iir_recurrence_fwd(const vtx_iir_params* p, void* stream) {
+    using namespace vtx;
+    VTX_REQUIRE(p && p->q && p->k && p->v && p->y, VTX_ERR_BAD_ARG, "iir(recurrence): null pointer");
+    VTX_REQUIRE(p->B > 0 && p->L > 0 && p->D > 0, VTX_ERR_BAD_ARG, "iir(recurrence): sizes must be positive");
+    VTX_REQUIRE(p->head_dim > 0 && p->D % p->head_dim == 0, VTX_ERR_BAD_ARG, "iir(recurrence): head_dim must divide D");
+    VTX_REQUIRE(p->modal.log_poles && p->modal.theta && p->modal.res_re, VTX_ERR_BAD_ARG,
+                "iir(recurrence): Re(p), Im(p) and Re(R) are needed");
+    VTX_REQUIRE(p->modal.G > 0 && p->modal.S > 0 && p->D % p->modal.G == 0, VTX_ERR_BAD_ARG,
+                "iir(recurrence): D not a multiple of the number of modal systems");
+    VTX_REQUIRE(p->modal.S <= IS, VTX_ERR_UNSUPPORTED, "iir(recurrence): state size %lld > %d", (long long)p->modal.S, IS);
+    const unsigned blocks = (unsigned)ceil_div<int64_t>(p->B * p->D, ITHREADS);
+    VTX_DISPATCH_IO(p->io_dtype, T, { iir_recurrence_kernel<T><<<blocks, ITHREADS, 0, (cudaStream_t)stream>>>(*p); });
+    return check_launch("iir(recurrence)");
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -135,17 +135,16 @@ class HyenaInferenceEngine:
         if want_state and prefill_style == "recurrence":
             # legacy complex-pole form (engine.py:473-504): poles/residues [D, S, 1, 2] as (re, im);
             # the output keeps sum_s R_re * Re(sigma_s) and the state is [B, D, S, 2]
-            p = poles[:, :, 0].float()
-            lam = torch.log(torch.hypot(p[..., 0], p[..., 1]))
-            theta = torch.atan2(p[..., 1], p[..., 0])
-            y, state = ops.iir_fwd(z_pre, lam, residues[:, :, 0, 0].float(), D, hidden_size, layout=layout,
-                                   num_heads=num_heads, flip=self.hyena_flip_x1x2, theta=theta, want_state=True)
+            # the kernel follows the reference's loop step for step (update order, state in the I/O dtype)
+            y, state = ops.iir_recurrence_fwd(z_pre, poles[:, :, 0], residues[:, :, 0], D, hidden_size, layout=layout,
+                                              num_heads=num_heads, flip=self.hyena_flip_x1x2)
             inference_params.state_dict[self.layer_idx] = state
             return y.permute(0, 2, 1)
 
         if long_fir_threshold is not None:
             assert h.shape[0] == 1, "batch size must be 1 for long_fir_threshold"
-            hk = h[0][:, None][..., :long_fir_threshold]      # [D, 1, thr], applied as F.conv1d does (engine.py:339-349)
+            # [D, 1, thr] in the I/O dtype, applied as F.conv1d applies it (engine.py:341-349)
+            hk = h[0][:, None][..., :long_fir_threshold].to(z_pre.dtype)
             y, _ = ops.gcg_fwd(z_pre, hk, D, hidden_size, taps=TAPS_XCORR, bias_mode=BIAS_GATED, layout=layout,
                                num_heads=num_heads, flip=self.hyena_flip_x1x2, want_state=False, round_kv=True)
             state = None

@@ -452,6 +452,38 @@ def iir_fwd(z_pre: torch.Tensor, log_poles, residues, bias, D: int, *, layout="s
     return y, state
 
 
+def iir_recurrence_fwd(z_pre: torch.Tensor, poles_ri, residues_ri, bias, D: int, *, layout="split", num_heads=1,
+                       flip=False):
+    """The reference's legacy recurrent prefill (engine.py:473-504): poles_ri / residues_ri [D, S, 2] as (re, im).
+    z_pre [B, 3D, L] -> y [B, D, L] and the state fp32 [B, D, S, 2] after the last token."""
+    _need_cuda(z_pre, poles_ri, residues_ri, bias)
+    if z_pre.stride(2) != 1:
+        z_pre = z_pre.contiguous()
+    B, C3, L = z_pre.shape
+    if C3 != 3 * D:
+        raise ValueError(f"expected {3 * D} packed channels, got {C3}")
+    if poles_ri.dim() != 3 or poles_ri.shape[-1] != 2 or poles_ri.shape != residues_ri.shape:
+        raise ValueError("poles and residues must be [D, S, 2] (re, im)")
+    G, S, _ = poles_ri.shape
+    f = lambda t: t.detach().to(device=z_pre.device, dtype=torch.float32).contiguous()  # noqa: E731
+    pre, pim, rre = f(poles_ri[..., 0]), f(poles_ri[..., 1]), f(residues_ri[..., 0])
+    (q, k, v), hd, (sh, sd) = _qkv_views(z_pre, D, layout, num_heads, flip)
+    bias = _param(bias, z_pre)
+    y = torch.empty(B, D, L, device=z_pre.device, dtype=z_pre.dtype)
+    state = torch.empty(B, D, S, 2, device=z_pre.device, dtype=torch.float32)
+    m = _lib.ModalParams(log_poles=_ptr(pre), theta=_ptr(pim), res_re=_ptr(rre), res_im=None, G=G, S=S)
+    p = _lib.IirParams(
+        q=_ptr(q), q_stride_b=z_pre.stride(0), q_stride_h=sh, q_stride_d=sd,
+        k=_ptr(k), k_stride_b=z_pre.stride(0), k_stride_h=sh, k_stride_d=sd,
+        v=_ptr(v), v_stride_b=z_pre.stride(0), v_stride_h=sh, v_stride_d=sd, head_dim=hd, modal=m,
+        bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0,
+        y=_ptr(y), y_stride_b=D * L, y_stride_d=L, y_stride_l=1, state=_ptr(state), scratch=None,
+        B=B, L=L, D=D, round_kv=1, io_dtype=_code(z_pre))
+    with _on(z_pre):
+        _lib.check(_lib.lib().vtx_iir_recurrence_fwd(C.byref(p), _stream(z_pre)))
+    return y, state
+
+
 # ----------------------------------------------------------------------------------------------
 def step_fir(u: torch.Tensor, fir_state: torch.Tensor, weight, bias=None, gated_bias=False, flip_filter=False):
     """One decode step of a depthwise FIR.  u [B, C]; fir_state [B, C, c]; weight [Gw, 1, K] / [Gw, K].
