@@ -1,6 +1,9 @@
 """GPU parity: the drop-in engine (CUDA kernels through the C ABI) against the reference's golden
 vectors and against the CPU oracle on seeded inputs.  Tolerances are the stated ones: relative L2
-<= 1e-4 for fp32 I/O, <= 2e-3 for bf16 I/O against the fp32 oracle; pure-copy caches bit-exact."""
+<= 1e-4 for fp32 I/O, <= 2e-3 for bf16 I/O against the reference's own path (its golden vectors, or the
+oracle with the reference's rounding points); pure-copy caches bit-exact.  The drop-in methods round where
+the reference does, so against its bf16 vectors they are bit-identical or differ in single last-place flips;
+the few wider bounds below compare quantities that are each rounded to bf16 on their own, and say so."""
 import numpy as np
 import pytest
 import torch
@@ -37,7 +40,7 @@ def test_golden_featurizer(golden, eng, io, L, tag):
                              T(golden[k + "_b"], io) if tag == "bias" else None, L, dims=(16, 1, 16, 16, 16),
                              gate=False, dim_last=True, fir_length=3, inference_params=True)
     assert z.shape == golden[k + "_z"].shape and z.dtype == DT[io]
-    check("test_engine_gpu.py:40 z, golden[k + '_z']", rel_l2(z, golden[k + "_z"]), (1e-6 if io == "f32" else 2.5e-3))
+    check("test_engine_gpu.py:40 z, golden[k + '_z']", rel_l2(z, golden[k + "_z"]), (1e-6 if io == "f32" else 2e-3))
     assert np.array_equal(to_np(st), golden[k + "_state"])
     z2, st2 = eng.parallel_fir(F.conv1d, T(golden[k + "_u"], io), T(golden[k + "_w"], io), None, L,
                                dims=(16, 1, 16, 16, 16), gate=False, inference_params=None)
@@ -66,7 +69,7 @@ def test_golden_gate_conv_gate(golden, io, K, L, layout):
                              column_split_hyena=layout == "column_split", fir_length=K, inference_params=True,
                              groups=G)
     assert y.shape == golden[k + "_y"].shape and y.dtype == DT[io]
-    check("test_engine_gpu.py:69 y, golden[k + '_y']", rel_l2(y, golden[k + "_y"]), (1e-5 if io == "f32" else 2.5e-3))
+    check("test_engine_gpu.py:69 y, golden[k + '_y']", rel_l2(y, golden[k + "_y"]), (1e-5 if io == "f32" else 2e-3))
     assert st.shape == golden[k + "_state"].shape
     assert np.array_equal(to_np(st), golden[k + "_state"])
 
@@ -84,7 +87,7 @@ def test_golden_long_conv(golden, eng, io, L, layout):
     y = eng.parallel_iir(z, T(golden[k + "_h"], "f32"), T(golden[k + "_D"], io), L, poles=lp, residues=R,
                          t=None, dims=(D, 1, D, S, D), layer_idx=3, inference_params=ip, prefill_style="fft")
     assert y.shape == (2, L, D) and y.dtype == DT[io]
-    check("test_engine_gpu.py:87 y, golden[k + '_y']", rel_l2(y, golden[k + "_y"]), (2e-5 if io == "f32" else 4e-3))
+    check("test_engine_gpu.py:87 y, golden[k + '_y']", rel_l2(y, golden[k + "_y"]), (2e-5 if io == "f32" else 2e-3))
     assert ip.state_dict[3].dtype == torch.float32 and ip.state_dict[3].shape == (2, D, S)
     check("test_engine_gpu.py:89 ip.state_dict[3], golden[k + '_state']", rel_l2(ip.state_dict[3], golden[k + "_state"]), 2e-5)
     y2 = eng.parallel_iir(z, None, T(golden[k + "_D"], io), L, poles=lp, residues=R, t=None,
@@ -144,7 +147,7 @@ def test_golden_step_fir(golden, eng, io, K, c0, flip, gb):
     for i in range(3):
         y, st = eng.step_fir(T(golden[f"{k}_u{i}"], io), st, w, bias=b, gated_bias=gb, flip_filter=flip)
         assert y.dtype == DT[io] and st.dtype == torch.float32
-        check(f"test_engine_gpu.py:147 y, golden[f'{k}_y{i}']", rel_l2(y, golden[f"{k}_y{i}"]), (2e-6 if io == "f32" else 2.5e-3))
+        check(f"test_engine_gpu.py:147 y, golden[f'{k}_y{i}']", rel_l2(y, golden[f"{k}_y{i}"]), (2e-6 if io == "f32" else 2e-3))
         assert st.shape == golden[f"{k}_state{i + 1}"].shape
         assert np.array_equal(to_np(st), golden[f"{k}_state{i + 1}"])   # cache layout and values bit-exact
 
@@ -258,7 +261,7 @@ def test_prefill_then_decode_matches_longer_prefill(eng, io, K):
                           gated_bias=K >= 128)
     y = y * q
     assert fs2.dtype == torch.float32 and st2.dtype == torch.float32 and st2.shape == st.shape
-    check("test_engine_gpu.py:261 y, full[:, L]", rel_l2(y, full[:, L]), (1e-5 if io == "f32" else 6e-3))
+    check("test_engine_gpu.py:261 y, full[:, L]", rel_l2(y, full[:, L]), (1e-5 if io == "f32" else 2e-3))
     assert torch.equal(st2[..., :-1], st[..., 1:].float()) and torch.equal(st2[..., -1], (k * v).float())
 
 
@@ -292,7 +295,7 @@ def test_long_conv_vs_oracle_and_decode(eng, io):
     z, _ = eng.step_fir(pc["u"][:, L], fs, pc["w3"])
     q, k, v = z[:, 0::3], z[:, 1::3], z[:, 2::3]
     y, st = eng.step_iir(q, k, v, pc["Dp"], pc["residues"], pc["log_poles"], ip.state_dict[3])
-    check("test_engine_gpu.py:295 y, y_full[:, L]", rel_l2(y, y_full[:, L]), (1e-4 if io == "f32" else 6e-3))
+    check("test_engine_gpu.py:295 y, y_full[:, L]", rel_l2(y, y_full[:, L]), (1e-4 if io == "f32" else 4e-3))   # bf16: step_iir returns fp32, the prefill output was rounded to bf16 after its own differently ordered sum: two roundings apart
 
 
 def test_long_conv_segmented_and_complex(eng):
@@ -361,13 +364,13 @@ def test_hyena_x_vs_oracle(io, B, D, L, Lh):
     y = hyena_ops.hyena_x_fwd(qkv.cuda(), h.cuda())
     ref = O.hyena_x(to_np(qkv), to_np(h), io=io)
     assert y.shape == (B, D, L) and y.dtype == DT[io]
-    check("test_engine_gpu.py:364 y, ref", rel_l2(y, ref), {"f32": 2e-6, "bf16": 2.5e-3, "f16": 1e-3}[io])
+    check("test_engine_gpu.py:364 y, ref", rel_l2(y, ref), {"f32": 2e-6, "bf16": 2e-3, "f16": 1e-3}[io])
     q, k, v = qkv.cuda().split([D, D, D], dim=1)
     assert torch.equal(hyena_ops.hyena_x_bdl_fwd(q, k, v, h.cuda()), y)
 
 
 # ------------------------------------------------------------------ short causal convolution of the conv extension
-CC_TOL = {"f32": 2e-6, "bf16": 2.5e-3, "f16": 1e-3}
+CC_TOL = {"f32": 2e-6, "bf16": 2e-3, "f16": 1e-3}
 
 
 @pytest.mark.parametrize("io", ["f32", "bf16"])
@@ -386,7 +389,9 @@ def test_golden_causal_conv1d(golden, io, W, L):
     fs = torch.empty_like(il)
     y = hyena_ops.causal_conv1d_fn(xl, w, b, None, il, fs, "silu")
     assert y.stride() == xl.stride()
-    check("test_engine_gpu.py:389 y, golden[k + '_y_full']", rel_l2(y, golden[k + "_y_full"]), 2 * CC_TOL[io])         # the reference rounds once more before the SiLU
+    check("test_engine_gpu.py:389 y, golden[k + '_y_full']", rel_l2(y, golden[k + "_y_full"]), 2.5 * CC_TOL[io])
+    # (wider: causal_conv1d_ref rounds to the I/O dtype BEFORE the SiLU and again after it, the extension's kernel --
+    # which this operator replaces -- rounds once; the vectors hold 12..444 numbers, so single flips weigh a lot)
     assert np.array_equal(to_np(fs), golden[k + "_fs_full"])
 
 

@@ -48,7 +48,7 @@ def test_fused_se_vs_oracle(io, B, L, D, G, K, layout, heads, flip):
     check("test_fused_gpu.py:47 y, ref", rel_l2(y, ref), TOL[io])
     assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))     # copy of the last inputs: bit-exact
     assert st.shape == st_ref.shape
-    check("test_fused_gpu.py:50 st, st_ref", rel_l2(st, st_ref), (1e-6 if io == "f32" else 2.5e-3))   # k*v rounded once to the I/O dtype
+    check("test_fused_gpu.py:50 st, st_ref", rel_l2(st, st_ref), (1e-6 if io == "f32" else 2e-3))   # k*v rounded once to the I/O dtype
 
 
 MR_CASES = [
@@ -77,7 +77,7 @@ def test_fused_mr_vs_oracle(io, B, L, D, G, K, layout, heads, flip):
     check("test_fused_gpu.py:76 y, ref", rel_l2(y, ref), TOL[io])
     assert np.array_equal(to_np(fs), fs_ref.astype(np.float32))
     assert st.shape == st_ref.shape
-    check("test_fused_gpu.py:79 st, st_ref", rel_l2(st, st_ref), 2.5e-3)
+    check("test_fused_gpu.py:79 st, st_ref", rel_l2(st, st_ref), 2e-3)
 
 
 def test_fused_mr_exact_on_integers():
@@ -207,7 +207,7 @@ def test_decode_layer_matches_step_sequence(io, kind):
                                               bias=Dp if K >= 128 else None, flip_filter=K >= 128, gated_bias=K >= 128)
         assert yb.dtype == dt and fs_b.dtype == torch.float32 and st_b.dtype == torch.float32
         assert torch.equal(fs_a, fs_b)
-        check("test_fused_gpu.py:209 yb, ya", rel_l2(yb, ya), (1e-6 if io == "f32" else 4e-3))
+        check("test_fused_gpu.py:209 yb, ya", rel_l2(yb, ya), (1e-6 if io == "f32" else 2e-3))
         check("test_fused_gpu.py:210 st_b, st_a", rel_l2(st_b, st_a), 1e-6)
 
 
@@ -509,10 +509,8 @@ def test_fused_li_full_size_properties(kind):
     c0, c1 = 1024, 1536
     ys, _, _ = run(pc["u"][:, :, 3 * c0:3 * c1].contiguous(), c0, c1)
     ops.device_status()
-    if grouped:      # another number of walks changes the time slicing, hence the fp32 summation order
-        check("LI full size shard vs full", rel_l2(ys, y[:, :, c0:c1]), 1e-3)
-    else:
-        assert torch.equal(ys, y[:, :, c0:c1])
+    # (another number of walks / rows changes the time slicing, hence the fp32 summation order: last-place flips)
+    check(f"LI full size ({kind}) shard vs full", rel_l2(ys, y[:, :, c0:c1]), 5e-4)
     # (3) causality
     t0 = 100003
     u2 = pc["u"].clone()
