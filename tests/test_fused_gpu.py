@@ -556,7 +556,9 @@ def test_engine_fused_prefill_then_fused_decode(io, kind):
     # ---- fused
     kw = dict(log_poles=p["log_poles"], residues=p["residues"]) if li else dict(h=p["h"])
     yb = eng.fused_prefill(u0, p["w3"], None, dims, D=p["Dp"], inference_params=cb, **kw)
-    tol = 1e-5 if io == "f32" else 4e-3        # bf16: two differently rounded bf16 results
+    # bf16: the two-call sequence rounds z, k*v and the filter output to bf16 (it sits ~4e-3 from the un-rounded
+    # evaluation, like the reference's own bf16 pipeline), the fused pass rounds once (1.7e-3): independent errors
+    tol = 1e-5 if io == "f32" else 6e-3
     check(f"fused_prefill vs two-call prefill ({kind}, {io})", rel_l2(yb, ya), tol)
     assert torch.equal(ca.fir_state_dict[4], cb.fir_state_dict[4])
     for step in range(3):

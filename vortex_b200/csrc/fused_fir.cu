@@ -276,21 +276,6 @@ static int launch_fused(const vtx_fused_fir_params* p, const FusedArgs& a, const
 
 int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream);   // fused_mr.cu (tcgen05 path)
 
-// Cache kernel alone (bf16), for the tensor-core path.
-int launch_fused_state_bf16(const vtx_fused_fir_params* p, cudaStream_t s) {
-    FusedArgs a{};
-    a.w3 = p->w3; a.w3_dtype = p->w3_dtype; a.b3 = p->b3; a.b3_dtype = p->b3_dtype;
-    a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
-    a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0;
-    a.hd = p->layout == VTX_QKV_COLUMN_SPLIT ? p->D / p->num_heads : p->D;
-    a.hist = p->u_hist_rows;
-    using T = __nv_bfloat16;
-    fused_state_kernel<T><<<(unsigned)ceil_div<int64_t>(a.B * a.D, 128), 128, 0, s>>>(
-        static_cast<const T*>(p->u), p->u_stride_b, p->u_stride_l, a, static_cast<T*>(p->fir_state),
-        static_cast<T*>(p->inner_state));
-    return check_launch("fused_fir state");
-}
-
 }  // namespace vtx
 
 extern "C" int vtx_fused_fir_fwd(const vtx_fused_fir_params* p, void* stream) {

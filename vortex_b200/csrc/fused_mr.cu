@@ -1,35 +1,37 @@
-// Hyena-MR fused block on tcgen05 / TMEM (bf16 I/O, filters of 17..128 taps, one per channel group of 16):
+// Hyena-MR / Hyena-SE fused block on tcgen05 / TMEM (bf16 I/O, filters of up to 128 taps, one per group of 16 channels):
 //   featurizer FIR (3 taps) -> q/k/v selection -> k*v -> grouped causal FIR -> (+ D*kv) -> q gate
-// in one pass over HBM, channel-last in and out.
+// in one pass over HBM, channel-last in and out; the prefill caches fall out of the same launch.
 //
 // The FIR is a blocked-Toeplitz contraction.  For a chunk of 128 output samples of one channel group
 //   Y[128 x N] = [T^ | T][128 x 256] * KV[256 x N],   [T^|T][i][j] = h[128 + i - j]  (0 outside 0..K-1)
 // where KV holds the previous and the current chunk of k*v.  The Toeplitz matrix depends on the group
 // only: it is expanded from the taps straight into tensor memory (A operand in TMEM, 128 lanes x 128 columns of
-// packed bf16) and every tcgen05.mma reads only the data tile from shared memory.  A work item is one group and
-// FOUR independent streams (a stream = one batch element and one segment of the time axis), so N = 4 x 16 channels;
-// k*v is split into a bf16 head and a bf16 remainder (the MMA's 128 columns are [head | remainder], summed in the
-// epilogue), which keeps the product exact to ~16 bits.  The skip term D[c]*kv is added in the epilogue from the
-// same tile.
+// packed fp16) and every tcgen05.mma reads only the data tile from shared memory.  A work item is one group and
+// FOUR independent streams (a stream = one batch element and one segment of the time axis), so N = 4 x 16 channels.
+//
+// Precision.  The output is rounded to bf16 once (1.7e-3 relative L2 on its own), so nothing else may lose more than
+// a few 1e-4: the featurizer runs in fp32, k*v and the gate q cross shared memory as fp16 (11 significant bits,
+// 2.8e-4 each; bf16 would cost 1.1e-3 each), bf16 taps are exact in fp16 (8 of its 11 bits) and the accumulation is
+// fp32.  fp16 has a narrow range, so k*v is carried scaled by 2^-6 (the featurizer taps of v are scaled when they are
+// staged, the Toeplitz operand and the skip parameter by 2^6: powers of two, exact): k*v up to 4e6 and down to 4e-6
+// keeps its bits, taps between 1e-6 and 1e3 keep theirs (smaller ones lose bits they contribute nothing with);
+// conversions saturate instead of overflowing, q beyond +-65504 is clamped.
 //
 // One persistent CTA per SM walks through its work items (blockIdx, blockIdx + gridDim, ...: at any time the CTAs of
 // the launch read neighbouring groups of the same rows).  Warp roles (16 warps): 0-7 front end (TMA-staged rows ->
-// featurizer -> k*v head/remainder and 24-bit q into the chunk's slot), 8-11 epilogue (tcgen05.ld -> skip -> q gate
-// -> bf16 -> global; they also expand the NEXT item's Toeplitz operand into the other half of a TMEM double buffer
-// while the current item streams), 12 MMA issue, 13-14 TMA issue.  A front-end lane owns one channel pair of one
-// stream and walks 16 rows per chunk in two register batches, the next batch fetched before the current one is
-// computed; the four streams of a warp are staged one row apart in shared memory, which makes every shared-memory
-// access of the front end bank-conflict free.  All waits are bounded.
-#include <cstdlib>
-
+// featurizer -> k*v and q as fp16 into the chunk's slot), 8-11 epilogue (tcgen05.ld -> skip -> q gate -> bf16 ->
+// global; they also expand the NEXT item's Toeplitz operand into the other half of a TMEM double buffer while the
+// current item streams), 12 MMA issue, 13-14 TMA issue, 15 prefill caches (the last two input rows and the last
+// K-1 samples of k*v of every sequence, re-evaluated from the rows themselves for the items whose streams end a
+// sequence).  A front-end lane owns one channel pair of one stream and walks 16 rows per chunk in two register
+// batches, the next batch fetched before the current one is computed; the four streams of a warp are staged one
+// row apart in shared memory so that the lanes of a warp read distinct banks.  All waits are bounded.
 #include "tma.cuh"
 #include "umma.cuh"
 
 namespace vtx {
 
 VTX_DEFINE_STATUS_READER()
-
-int launch_fused_state_bf16(const vtx_fused_fir_params* p, cudaStream_t s);   // fused_fir.cu
 
 namespace mr {
 
@@ -41,67 +43,55 @@ constexpr int CHUNK = 128;                 // output samples per MMA chunk
 #ifndef VTX_MR_NFE
 #define VTX_MR_NFE 8
 #endif
-constexpr int NFE = VTX_MR_NFE;                     // front-end warps (two per scheduler: the featurizer chain is latency-bound)
+constexpr int NFE = VTX_MR_NFE;            // front-end warps (two per scheduler: the featurizer chain is latency-bound)
 constexpr int WROWS = CHUNK / NFE;         // rows of a chunk owned by one front-end warp
-#ifndef VTX_MR_RB
-#define VTX_MR_RB 8
-#endif
-constexpr int RB = VTX_MR_RB;                     // rows a front-end lane fetches into registers at a time
+constexpr int RB = 8;                      // rows a front-end lane fetches into registers at a time
 constexpr int HROWS = 64;                  // rows per staged box: half a chunk, shared by two front-end warps
                                            // (the TMA unit retires ~12 boxes per microsecond and SM whatever their
                                            // size, so boxes are made as tall as the shared-memory budget allows)
 constexpr int BOX_ROWS = HROWS + 2 + (NS - 1);         // featurizer halo + stream skew
 constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;       // 6624
 constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;   // q | k | v planes of the non-interleaved layouts (TMA wants 128-byte aligned tiles)
-constexpr int BOX_STRIDE = 3 * IN_PLANE;               // 6912 >= BOX_BYTES
-#ifndef VTX_MR_IN_STAGES
-#define VTX_MR_IN_STAGES 4
-#endif
-constexpr int IN_STAGES = VTX_MR_IN_STAGES;            // ring of half-chunk stages (a stage is handed back as soon as its rows sit
-                                                       // in registers); HBM latency under load is ~2 us, so full bandwidth needs
-                                                       // ~100 KB in flight per SM: the ring gets all the shared memory that is left
-constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // one stage: the four streams' boxes of one half chunk
-// k*v tiles: [128 rows (time)][128 B = 64 channels] bf16 with the 128-byte swizzle (16-byte chunk c of row r is
-// stored at chunk c ^ (r & 7)); the tensor core fetches such rows whole, whereas the unswizzled form is fetched
-// 16 bytes at a time (measured: ~130 instead of ~32 cycles per MMA).  Tiles are 1024-byte aligned.
-constexpr int KV_TILE = CHUNK * 128;       // 16384
-// q tile: the gate is kept to 24 bits (sign, exponent, 15 mantissa bits: a bf16-rounded gate would by itself cost as
-// much accuracy as the rounding of the output).  Upper 16 bits in a tile shaped like a k*v tile (same swizzle, so the
-// front end reuses its store address), third byte in a [128 rows][64 B] tile whose 16-byte chunk c of row r sits at
-// chunk c ^ ((r >> 1) & 3) (conflict-free for the row-per-lane 16-byte reads of the epilogue).
-constexpr int QH_TILE = KV_TILE, QM_TILE = CHUNK * 64;
-constexpr int Q_BYTES = QH_TILE + QM_TILE;     // 24576
-constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE;   // (third bytes of q follow at QH_OFF + QH_TILE)
-constexpr int SLOT_BYTES = 2 * KV_TILE + Q_BYTES;      // one chunk: k*v head, k*v remainder, q upper halves, q third bytes
-constexpr int DIAG_BYTES = 2 * 64;         // skip parameters D[16] of the group, fp32; two buffers (this item, next item)
-constexpr int TAPS_BYTES = 2 * 384 * 2;    // zero-padded taps, bf16; two buffers
-constexpr int SMEM_IN = IN_STAGES * STAGE_BYTES;
-constexpr int SMEM_SLOTS = 2 * SLOT_BYTES;
-constexpr int OFF_SLOTS = SMEM_IN;
-constexpr int OFF_DIAG = OFF_SLOTS + SMEM_SLOTS;
-constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
-constexpr int W3S_BYTES = 3 * 3 * CH * 4;   // featurizer taps of a group as fp32 [q|k|v][tap][channel]; two buffers
-constexpr int OFF_W3S = OFF_TAPS + TAPS_BYTES;
-constexpr int OFF_BARS = OFF_W3S + 2 * W3S_BYTES;
-constexpr int NBARS = IN_STAGES * 2 + 2 * 6;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty, a_ready, taps_ready x2
-constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 48 + 1024;
-static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0, "k*v tiles must be 1024-byte aligned");
-constexpr int TMEM_COLS = 512;             // Toeplitz operand of item t at 128 (t & 1); accumulator buffer b at 256 + 128 b:
-                                           // [head part 64 | remainder part 64]
-constexpr int D_COL = 256;
-#ifndef VTX_MR_NTMA
-#define VTX_MR_NTMA 2
-#endif
-constexpr int NTMA = VTX_MR_NTMA;          // TMA issue warps: one thread issues a box of 96-byte rows every ~300 cycles only
-constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5;   // first epilogue warp (multiple of 4), MMA warp, first TMA warp
-constexpr int NWARPS = (NFE + 5 + NTMA + 3) / 4 * 4;    // whole warpgroups (register reallocation is per warpgroup)
-constexpr int THREADS = 32 * NWARPS;
-static_assert(NS % NTMA == 0 && THREADS <= 1024 && NFE % 8 == 0 && (CHUNK / NFE) % RB == 0, "warp roles");
+constexpr float KV_SCALE = 0.015625f, KV_UNSCALE = 64.f;      // k*v crosses shared memory as fp16 scaled by 2^-6
 
-// L2 prefetch of rows that will be staged later: keeps HBM requests in flight without shared memory
-// (full HBM bandwidth needs ~100 KB in flight per SM; the staging ring holds a third of that).
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// k*v and q tiles of a chunk: [128 rows (time)][128 B = 64 channels] fp16 with the 128-byte swizzle (16-byte chunk c of
+// row r is stored at chunk c ^ (r & 7)); the tensor core fetches such rows whole, whereas the unswizzled form is fetched
+// 16 bytes at a time (measured: ~130 instead of ~32 cycles per MMA).  Tiles are 1024-byte aligned.  The same swizzle
+// makes the row-per-lane 16-byte reads of the epilogue conflict-free.
+constexpr int KV_TILE = CHUNK * 128;       // 16384
+constexpr int Q_OFF = KV_TILE;
+constexpr int SLOT_BYTES = 2 * KV_TILE;    // one chunk: k*v tile, q tile
+constexpr int DIAG_BYTES = 2 * 64;         // skip parameters D[16] of the group (times 2^6), fp32; two buffers (this item, next item)
+constexpr int TAPS_BYTES = 2 * 384 * 2;    // zero-padded taps (times 2^6), fp16; two buffers
+constexpr int W3S_BYTES = 3 * 3 * CH * 4;  // featurizer taps of a group as fp32 [q|k|v][tap][channel]; two buffers
+
+// Shared-memory plan.  HBM latency under load is ~2 us, so full bandwidth needs ~100 KB in flight per SM: the ring of
+// half-chunk stages (a stage is handed back as soon as its rows sit in registers) gets all the memory the two chunk
+// slots leave.  The planar q | k | v layouts stage three 128-byte aligned planes per box, the interleaved layout one.
+template <bool INTERLEAVED>
+struct Lay {
+    static constexpr int BOX_STRIDE = INTERLEAVED ? (BOX_BYTES + 127) / 128 * 128 : 3 * IN_PLANE;   // 6656 : 6912
+    static constexpr int IN_STAGES = INTERLEAVED ? 6 : 5;
+    static constexpr int STAGE_BYTES = NS * BOX_STRIDE;           // the four streams' boxes of one half chunk
+    static constexpr int OFF_SLOTS = IN_STAGES * STAGE_BYTES;
+    static constexpr int OFF_DIAG = OFF_SLOTS + 2 * SLOT_BYTES;
+    static constexpr int OFF_TAPS = OFF_DIAG + DIAG_BYTES;
+    static constexpr int OFF_W3S = OFF_TAPS + TAPS_BYTES;
+    static constexpr int OFF_BARS = OFF_W3S + 2 * W3S_BYTES;
+    static constexpr int NBARS = IN_STAGES * 2 + 2 * 6;   // in_full/in_empty per stage; kv_full, slot_free, d_full, d_empty, a_ready, taps_ready x2
+    static constexpr int OFF_TSLOT = OFF_BARS + NBARS * 8;
+    static constexpr int SMEM_BYTES = OFF_TSLOT + 48 + 1024;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    static_assert(OFF_SLOTS % 1024 == 0, "k*v tiles must be 1024-byte aligned");
+    static_assert((BOX_STRIDE / 4) % 32 == 0 && BOX_STRIDE % 128 == 0, "stream boxes start on bank 0 and on a TMA boundary");
+};
+constexpr int TMEM_COLS = 512;             // Toeplitz operand of item t at 128 (t & 1); accumulator buffer b at 256 + 64 b
+constexpr int D_COL = 256;
+constexpr int NTMA = 2;                    // TMA issue warps: one thread issues a box of 96-byte rows every ~300 cycles only
+constexpr int W_EP = NFE, W_MMA = NFE + 4, W_TMA = NFE + 5, W_STATE = NFE + 5 + NTMA;   // first epilogue warp (multiple of 4), MMA, first TMA, cache warp
+constexpr int NWARPS = (W_STATE + 1 + 3) / 4 * 4;       // whole warpgroups
+constexpr int THREADS = 32 * NWARPS;
+static_assert(NS % NTMA == 0 && THREADS <= 1024 && NFE % 8 == 0 && WROWS == 2 * RB, "warp roles");
 
 struct Args {
     const void* w3; int64_t w3_dtype;
@@ -109,52 +99,14 @@ struct Args {
     const void* bias; int64_t bias_dtype;
     const __nv_bfloat16* u; int64_t u_stride_b, u_stride_l;
     __nv_bfloat16* y; int64_t y_stride_b, y_stride_l;
+    __nv_bfloat16* fir_state; __nv_bfloat16* inner_state;    // prefill caches, or null
     int64_t B, L, D, G, K;
     int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
     int64_t nquad, nitems;                 // stream quads per group; work items (group x quad) of the launch
     int layout, flip, taps, has_bias;
     int64_t hd;
     int hist;        // rows before u[b][0] that hold the sequence's earlier samples (the tensor map starts there)
-    int pf;          // chunks of L2 prefetch distance (0 = off)
-    int dbg;         // diagnostic builds only: knock out parts of the kernel to time the rest
-    unsigned long long* trace;   // diagnostic builds only
 };
-
-#ifdef VTX_MR_KNOCKOUT
-#define KO(bit) (a.dbg & (bit))
-#else
-#define KO(bit) false
-#endif
-
-#ifdef VTX_MR_LANE0_WAIT
-// One lane polls, the warp learns the outcome through a shuffle (the warp-level barrier inside it orders memory).
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int code) {
-    bool ok = true;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, code);
-    return __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-}
-#define WARP_WAIT warp_wait
-#else
-#define WARP_WAIT mbar_wait
-#endif
-#ifdef VTX_MR_SPIN
-#undef WARP_WAIT
-#define WARP_WAIT mbar_spin
-#define MBAR_WAIT mbar_spin
-#else
-#define MBAR_WAIT mbar_wait
-#endif
-
-// Diagnostic builds only (-DVTX_MR_TRACE): CTA 0 logs (event, clock) pairs per warp into a.trace[warp][256].
-#ifdef VTX_MR_TRACE
-#define TRACE(code)                                                                              \
-    do {                                                                                         \
-        if (blockIdx.x == 0 && lane == 0 && a.trace && trace_n < 256)                            \
-            a.trace[warp * 256 + trace_n++] = ((unsigned long long)(code) << 48) | (unsigned long long)(clock64() & 0xffffffffffffull); \
-    } while (0)
-#else
-#define TRACE(code) do {} while (0)
-#endif
 
 struct Stream {
     int64_t b, ts, te;   // batch, first row, one past the last row this stream stores
@@ -171,17 +123,109 @@ __device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) 
     return st;
 }
 
+// two fp32 -> packed fp16 (lo in bits [15:0]), saturating at +-65504
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// packed fp16 pair -> packed fp32 pair
+__device__ __forceinline__ f32x2 unpack_f16(uint32_t w) {
+    float lo, hi;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w));
+    return pk2(lo, hi);
+}
+// instruction descriptor: f32 accumulate, A fp16 (K-major, from TMEM), B fp16 (N-major).  Both operands have the same
+// format: a descriptor that asked for bf16 x fp16 raised "illegal instruction" on this part.
+__device__ __forceinline__ uint32_t instr_desc_f16(int M, int N) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (1u << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// taps and other parameters -> fp16 bits, clamped to the finite range
+__device__ __forceinline__ uint16_t f16_bits(float v) {
+    return __half_as_ushort(__float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f)));
+}
+
+// Prefill caches (one warp per CTA, beside the streaming roles): fir_state[b, c, :] = u[b, L-n3:L, c] (n3 = min(L, 2)),
+// inner_state[b, d, :] = bf16(kv[b, d, L-ns:L]) (ns = min(L, K-1)); with history rows in front of u both are always
+// full and negative times index those rows.  Exactly one stream of a (batch, group) ends its sequence; the CTA that
+// owns its item evaluates the caches here from the rows themselves (fp32 featurizer, unscaled taps).  Not inlined:
+// its registers are then allocated apart from the front end's, which runs at the limit.
+__device__ __noinline__ void write_caches(const Args& a, int nmine, int lane) {
+    const int c = lane % CH, hh = lane / CH;
+    const int ncta = (int)gridDim.x, K = (int)a.K;
+    const QkvMap map{a.layout, a.flip, a.D, a.hd};
+    const int64_t L = a.L;
+    const int64_t n3 = (a.hist > 0 || L >= 2) ? 2 : L;
+    const int64_t ns = (a.hist > 0 || L >= K - 1) ? K - 1 : L;
+    for (int t = 0; t < nmine; ++t) {
+        const int64_t item = (int64_t)blockIdx.x + (int64_t)t * ncta;
+        const int g = (int)(item % a.G);
+        const int64_t quad = item / a.G;
+        int64_t cq, ck, cv;
+        map.get((int64_t)g * CH + c, cq, ck, cv);
+        float wk[3], wv[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            wk[j] = ld_param(a.w3, a.w3_dtype, ck * 3 + j);
+            wv[j] = ld_param(a.w3, a.w3_dtype, cv * 3 + j);
+        }
+        for (int s = 0; s < NS; ++s) {
+            const Stream st = stream_of(a, quad, s);
+            if (!st.active || st.te != L) continue;
+            const __nv_bfloat16* ub = a.u + st.b * a.u_stride_b;
+            auto ld = [&](int64_t tt, int64_t col) {
+                return tt >= -(int64_t)a.hist ? __bfloat162float(ub[tt * a.u_stride_l + col]) : 0.f;
+            };
+            if (a.inner_state && ns > 0) {
+                // the two half-warps split the ns samples; lane = channel within the group
+                const int64_t per = (ns + 1) / 2, j0 = hh * per, j1 = j0 + per < ns ? j0 + per : ns;
+                __nv_bfloat16* dst = a.inner_state + (st.b * a.D + (int64_t)g * CH + c) * ns;
+                int64_t tt = L - ns + j0;
+                float k2 = ld(tt - 2, ck), k1 = ld(tt - 1, ck), v2 = ld(tt - 2, cv), v1 = ld(tt - 1, cv);
+                for (int64_t j = j0; j < j1; j += 4) {
+                    float kk[4], vv[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {      // (loads first: four rows in flight)
+                        const bool in = j + i < j1;
+                        kk[i] = in ? ld(tt + i, ck) : 0.f;
+                        vv[i] = in ? ld(tt + i, cv) : 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float zk = fmaf(wk[2], kk[i], fmaf(wk[1], k1, wk[0] * k2));
+                        const float zv = fmaf(wv[2], vv[i], fmaf(wv[1], v1, wv[0] * v2));
+                        if (j + i < j1) dst[j + i] = __float2bfloat16_rn(zk * zv);
+                        k2 = k1; k1 = kk[i]; v2 = v1; v1 = vv[i];
+                    }
+                    tt += 4;
+                }
+            }
+            if (a.fir_state && n3 > 0) {
+                for (int m = lane; m < 3 * CH; m += 32) {
+                    int64_t q0, q1, q2;
+                    map.get((int64_t)g * CH + m % CH, q0, q1, q2);
+                    const int64_t col = m < CH ? q0 : m < 2 * CH ? q1 : q2;
+                    for (int64_t j = 0; j < n3; ++j)
+                        a.fir_state[(st.b * 3 * a.D + col) * n3 + j] = ub[(L - n3 + j) * a.u_stride_l + col];
+                }
+            }
+        }
+    }
+}
+
 // SWAP: interleaved layout with the q and k roles exchanged (the planar layouts exchange their TMA columns instead).
 template <bool INTERLEAVED, bool SWAP>
-__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, Args a) {
+__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Args a) {
+    using LY = Lay<INTERLEAVED>;
+    constexpr int IN_STAGES = LY::IN_STAGES, BOX_STRIDE = LY::BOX_STRIDE, STAGE_BYTES = LY::STAGE_BYTES;
+    constexpr int OFF_SLOTS = LY::OFF_SLOTS, OFF_DIAG = LY::OFF_DIAG, OFF_TAPS = LY::OFF_TAPS, OFF_W3S = LY::OFF_W3S;
     extern __shared__ uint8_t smem_raw[];
     // Only the 32-bit shared-memory address of the (1024-byte aligned) buffer stays live; generic pointers are made
     // from it where a role needs one (the front end runs at the register limit).
     const uint32_t sm_u = (smem_u32(smem_raw) + 1023u) & ~1023u;
     auto smp = [&](uint32_t off) { return reinterpret_cast<uint8_t*>(__cvta_shared_to_generic(sm_u + off)); };
-    constexpr uint32_t OFF_TSLOT = OFF_BARS + NBARS * 8;
     // barrier addresses (32-bit shared-memory addresses: no generic pointer has to stay live in the role loops)
-    const uint32_t bar_u = sm_u + OFF_BARS;
+    const uint32_t bar_u = sm_u + LY::OFF_BARS;
     auto in_full = [&](int st) { return bar_u + 16u * (uint32_t)st; };
     auto in_empty = [&](int st) { return bar_u + 16u * (uint32_t)st + 8u; };
     constexpr uint32_t BB = IN_STAGES * 2;
@@ -195,11 +239,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     auto taps_ready = [&](int ab) { return bar_u + 8u * (BB + 10 + (uint32_t)ab); };  // taps of the next item in shared memory (4 epilogue warps)
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    int trace_n = 0;
-    (void)trace_n;
-    // Persistent CTA: work items (item = quad * G + group, as many as the launch has blocks apart: at any time the CTAs
+    // Persistent CTA: work items (item = quad * G + group) as many as the launch has blocks apart: at any time the CTAs
     // of the launch read neighbouring groups of the same rows, which keeps the concurrent reads inside few DRAM
-    // pages).  Every item has its own group, hence its own Toeplitz operand: the epilogue warps expand the operand
+    // pages.  Every item has its own group, hence its own Toeplitz operand: the epilogue warps expand the operand
     // of the NEXT item into the other half of a double buffer while the current item streams, so the roles run
     // through the items without draining.  Per-role running counters give the barrier phases.
     const int ncta = (int)gridDim.x;
@@ -219,14 +261,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         fence_mbar_init();
     }
     if (warp == W_MMA) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u + OFF_TSLOT), "r"(TMEM_COLS));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u + LY::OFF_TSLOT), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     uint32_t tmem;
-    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(sm_u + OFF_TSLOT) : "memory");
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(sm_u + LY::OFF_TSLOT) : "memory");
     uint32_t cc = 0;          // chunks this role has gone through (halo chunks included): slot = cc & 1
     uint32_t oc = 0;          // output chunks: accumulator buffer = oc & 1
 
@@ -239,7 +281,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         // featurizer taps of item t: staged in shared memory by the epilogue warps together with the item's Toeplitz
         // operand (a_ready); [feature][tap][channel] fp32, this lane's two channels as one 8-byte load
         auto load_w3 = [&](int t) {
-            if (!WARP_WAIT(a_ready(t & 1), (uint32_t)((t >> 1) & 1), 17)) return false;
+            if (!mbar_wait(a_ready(t & 1), (uint32_t)((t >> 1) & 1), 17)) return false;
             const uint32_t base = sm_u + OFF_W3S + (uint32_t)((t & 1) * W3S_BYTES) + 8u * (uint32_t)p;
 #pragma unroll
             for (int x = 0; x < 3; ++x)
@@ -248,13 +290,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     asm volatile("ld.shared.b64 %0, [%1];" : "=l"(w3[x][j]) : "r"(base + (uint32_t)((x * 3 + j) * CH * 4)));
             return true;
         };
-        // lane constants folded into three offsets: the lane's first staged word of a half chunk, its bf16 pair in row
-        // 16 w of a k*v tile (16-byte chunk 2 s + p / 4, bytes 4 (p % 4)), its two third-bytes in row 16 w of a q tile
+        // lane constants folded into two offsets: the lane's first staged word of a half chunk, and its fp16 pair in row
+        // 16 w of a k*v tile (16-byte chunk 2 s + p / 4, bytes 4 (p % 4))
         const uint32_t lane_box = (uint32_t)(s * BOX_STRIDE + ((w % (NFE / 2)) * WROWS + s) * (INTERLEAVED ? 96 : 32) + (INTERLEAVED ? 12 : 4) * p);
         const uint32_t lane_kv = (uint32_t)(((s * 2 + p / 4) << 4) + (p % 4) * 4 + w * WROWS * 128);
-        const uint32_t lane_qm = (uint32_t)((s << 4) + 2 * p + w * WROWS * 64);
         const uint32_t half = (uint32_t)(w / (NFE / 2));
-        static_assert(WROWS == 2 * RB, "the front end walks a chunk as two register batches");
         constexpr int ROWB = INTERLEAVED ? 96 : 32;             // bytes per staged row (per plane in the planar layouts)
         // shared-memory address of this lane's first word of batch hb of chunk k (the box row of the batch's first
         // sample minus the two featurizer history rows; stream s was staged s rows early)
@@ -268,12 +308,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 #pragma unroll
             for (int r = 0; r < RB + 2; ++r) {
 #pragma unroll
-                for (int j = 0; j < 3; ++j) {
-                    if (KO(2))
-                        raw[r][j] = 0x3f803f80u + r + lane;
-                    else
-                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw[r][j]) : "r"(addr + (uint32_t)(r * ROWB + (INTERLEAVED ? 4 * j : j * IN_PLANE))));
-                }
+                for (int j = 0; j < 3; ++j)
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw[r][j]) : "r"(addr + (uint32_t)(r * ROWB + (INTERLEAVED ? 4 * j : j * IN_PLANE))));
             }
         };
         // x[0..2] = q | k | v samples of the lane's channel pair (packed positions before any q/k swap)
@@ -287,23 +323,16 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 for (int pl = 0; pl < 3; ++pl) x[pl] = pk2(bf_lo(e[pl]), bf_hi(e[pl]));
             }
         };
-        // featurizer -> k*v head/remainder and q of RB rows, written into the chunk's slot
+        // featurizer -> k*v and q of RB rows as fp16, written into the chunk's slot
         auto compute = [&](int slot, int hb, const uint32_t (&raw)[RB + 2][3]) {
-            const uint32_t slot_u = sm_u + OFF_SLOTS + slot * SLOT_BYTES;
             // Tiles are 1024-byte aligned, so the swizzle (16-byte chunk index XOR row phase) is one XOR on the address
             // of the lane's element in row 0; row offsets are compile-time immediates of the stores.
-            const uint32_t kv_a0 = slot_u + lane_kv + (uint32_t)(hb * RB * 128);
-            const uint32_t qh_a0 = kv_a0 + QH_OFF;
-            const uint32_t qm_a0 = slot_u + QH_OFF + QH_TILE + lane_qm + (uint32_t)(hb * RB * 64);
+            const uint32_t kv_a0 = sm_u + OFF_SLOTS + slot * SLOT_BYTES + lane_kv + (uint32_t)(hb * RB * 128);
             f32x2 x1[3], x2[3];
             unpack(raw[0], x2);
             unpack(raw[1], x1);
 #pragma unroll
             for (int i = 0; i < RB; ++i) {
-                if (KO(16)) {
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(kv_a0 + i * 128), "r"(raw[i + 2][0]));
-                    continue;
-                }
                 f32x2 x0[3], z[3];
                 unpack(raw[i + 2], x0);
 #pragma unroll
@@ -312,25 +341,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     x2[x] = x1[x];
                     x1[x] = x0[x];
                 }
-                const f32x2 q = SWAP ? z[1] : z[0];
-                const f32x2 kv = mul2(SWAP ? z[0] : z[1], z[2]);          // rows before the sequence start are zeros
-                float kv0, kv1;
-                up2(kv, kv0, kv1);
-                const uint32_t hi = pack_bf16(kv0, kv1);
-                float r0, r1;
-                up2(sub2(kv, pk2(bf_lo(hi), bf_hi(hi))), r0, r1);
-                const uint32_t lo = pack_bf16(r0, r1);
+                // (the staged taps of v carry the 2^-6 of the k*v tile; rows before the sequence start are zeros)
+                float kv0, kv1, q0, q1;
+                up2(mul2(SWAP ? z[0] : z[1], z[2]), kv0, kv1);
+                up2(SWAP ? z[1] : z[0], q0, q1);
                 // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
                 const uint32_t kaddr = kv_a0 ^ (uint32_t)((i & 7) << 4);
-                if (KO(1) && hi != 0x12345678u) continue;
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (HI_OFF + i * 128)), "r"(hi));
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (LO_OFF + i * 128)), "r"(lo));
-                float q0, q1;
-                up2(q, q0, q1);
-                const uint32_t qh = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x7632);   // upper halves
-                const uint32_t qm = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5151);   // third bytes
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"((qh_a0 ^ (uint32_t)((i & 7) << 4)) + i * 128), "r"(qh));
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)(((i >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + i * 128), "r"(pack_f16(kv0, kv1)));
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + (Q_OFF + i * 128)), "r"(pack_f16(q0, q1)));
             }
         };
         auto stage_of = [&](uint32_t k) { return (int)((2 * k + half) % IN_STAGES); };
@@ -341,17 +359,15 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         uint32_t rawA[RB + 2][3], rawB[RB + 2][3];
         uint32_t c_end = (uint32_t)nmine * (uint32_t)nchunk;
         int kin = 0, t = 0;       // chunk within the item, item
-        if (!WARP_WAIT(in_full(stage_of(cc)), stage_parity(cc), 4)) c_end = cc;     // (gave up: nothing to do)
+        if (!mbar_wait(in_full(stage_of(cc)), stage_parity(cc), 4)) c_end = cc;     // (gave up: nothing to do)
         fetch(box_addr(cc, 0), rawA);
         for (; cc < c_end; ++cc) {
             const int slot = cc & 1;
             if (kin == 0 && !load_w3(t)) break;         // a new item: its group's featurizer taps
             if (++kin == nchunk) { kin = 0; ++t; }
-            TRACE(0);
             fetch(box_addr(cc, 1), rawB);
             // slot reuse: the MMAs that read chunk cc-2 and the epilogue that read its k*v rows and q tile are done
-            if (cc >= 2 && !WARP_WAIT(slot_free(slot), ((cc - 2) >> 1) & 1u, 2)) break;
-            TRACE(1);
+            if (cc >= 2 && !mbar_wait(slot_free(slot), ((cc - 2) >> 1) & 1u, 2)) break;
             compute(slot, 0, rawA);
             // Every row this warp needs from the stage now sits in registers: hand the stage back to the TMA warp (HBM
             // latency under load is ~2 us, so as much of the ring as possible should be in flight).  The empty asm
@@ -360,38 +376,32 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             for (int r = 0; r < RB + 2; ++r) asm volatile("" ::"r"(rawB[r][0]), "r"(rawB[r][1]), "r"(rawB[r][2]));
             __syncwarp();
             if (lane == 0) mbar_arrive(in_empty(stage_of(cc)));
-            TRACE(3);
             if (cc + 1 < c_end) {
-                if (!WARP_WAIT(in_full(stage_of(cc + 1)), stage_parity(cc + 1), 4)) break;
+                if (!mbar_wait(in_full(stage_of(cc + 1)), stage_parity(cc + 1), 4)) break;
                 fetch(box_addr(cc + 1, 0), rawA);
             }
-            TRACE(2);
             compute(slot, 1, rawB);
-            TRACE(4);
             fence_proxy_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(kv_full(slot));
-            TRACE(5);
         }
     } else if (warp < W_EP + 4) {
         // ======== epilogue: thread = output row (TMEM lane) ========================================
         const int e = warp - W_EP, r = e * 32 + lane;
-        // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
-        // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
         const int64_t chunk_pitch = (int64_t)CHUNK * a.y_stride_l;
-        // Toeplitz operand of item t -> TMEM buffer t & 1: the group's taps (zero padded: tp[m] = tap at lag m - 128) and
-        // skip parameters go through shared memory, then lane i writes row i of [T^|T].  Runs while the item before
-        // streams; the four epilogue warps meet on a barrier of their own (bounded wait) between the two steps.
+        // Toeplitz operand of item t -> TMEM buffer t & 1: the group's taps (zero padded: tp[m] = tap at lag m - 128,
+        // times 2^6) and skip parameters go through shared memory, then lane i writes row i of [T^|T].  Runs while the
+        // item before streams; the four epilogue warps meet on a barrier of their own (bounded wait) between the steps.
         auto expand = [&](int t) {
             const int g = item_group(t), ab = t & 1;
-            __nv_bfloat16* tp = reinterpret_cast<__nv_bfloat16*>(smp(OFF_TAPS + ab * 768));
+            uint16_t* tp = reinterpret_cast<uint16_t*>(smp(OFF_TAPS + ab * 768));
             for (int m = r; m < 384; m += 128) {
                 const int l = m - 128;
                 float v = 0.f;
-                if (l >= 0 && l < K) v = ld_param(a.h, a.h_dtype, (int64_t)g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
-                tp[m] = __float2bfloat16_rn(v);
+                if (l >= 0 && l < K) v = KV_UNSCALE * ld_param(a.h, a.h_dtype, (int64_t)g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
+                tp[m] = f16_bits(v);
             }
-            if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? ld_param(a.bias, a.bias_dtype, (int64_t)g * CH + r) : 0.f;
+            if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? KV_UNSCALE * ld_param(a.bias, a.bias_dtype, (int64_t)g * CH + r) : 0.f;
             {   // featurizer taps of the group's 16 channels (the front end picks them up at the item's first chunk)
                 QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
                 float* w3s = reinterpret_cast<float*>(smp(OFF_W3S + ab * W3S_BYTES));
@@ -399,13 +409,13 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                     const int c = m % CH, j = (m / CH) % 3, x = m / (3 * CH);
                     int64_t pc[3];
                     map.get((int64_t)g * CH + c, pc[0], pc[1], pc[2]);
-                    w3s[m] = ld_param(a.w3, a.w3_dtype, pc[x] * 3 + j);
+                    w3s[m] = ld_param(a.w3, a.w3_dtype, pc[x] * 3 + j) * (x == 2 ? KV_SCALE : 1.f);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(taps_ready(ab));
-            if (!WARP_WAIT(taps_ready(ab), (uint32_t)((t >> 1) & 1), 16)) return false;
-            const uint16_t* tpr = reinterpret_cast<const uint16_t*>(tp);
+            if (!mbar_wait(taps_ready(ab), (uint32_t)((t >> 1) & 1), 16)) return false;
+            const uint16_t* tpr = tp;
             for (int c0 = 0; c0 < 128; c0 += 16) {
                 uint32_t v[16];
 #pragma unroll
@@ -424,196 +434,152 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         };
         bool ok = expand(0);
         for (int t = 0; t < nmine && ok; ++t) {
-        const int g = item_group(t);
-        const float4* dsk = reinterpret_cast<const float4*>(smp(OFF_DIAG + (t & 1) * 64));    // skip parameters D[g*16 .. +16), fp32
-        bool has_skip = false;       // the skip parameter is all zeros at initialisation: then its term is not evaluated
+            const int g = item_group(t);
+            const float4* dsk = reinterpret_cast<const float4*>(smp(OFF_DIAG + (t & 1) * 64));    // 2^6 D[g*16 .. +16), fp32
+            bool has_skip = false;       // the skip parameter is all zeros at initialisation: then its term is not evaluated
 #pragma unroll
-        for (int c = 0; c < CH / 4; ++c) {
-            const float4 d = dsk[c];
-            has_skip = has_skip || d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f;
-        }
-        // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
-        // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
-        __nv_bfloat16* yrow[NS];
-        int nleft[NS];
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const Stream st = stream_of(a, item_quad(t), s);
-            yrow[s] = a.y + st.b * a.y_stride_b + (st.ts + r) * a.y_stride_l + (int64_t)g * CH;
-            nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
-        }
-        if (lane == 0) mbar_arrive(slot_free(cc & 1));      // the item's halo chunk has no epilogue
-        ++cc;
-        for (int k = 1; k < nchunk; ++k, ++cc, ++oc) {
-            const int slot = cc & 1, dbuf = oc & 1;
-            TRACE(10);
-            if (!WARP_WAIT(d_full(dbuf), (oc >> 1) & 1u, 5)) { ok = false; break; }
-            TRACE(11);
-            tc_fence_after();
-            __syncwarp();
-            const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + D_COL + dbuf * 128;
-            const uint8_t* slot_p = smp(OFF_SLOTS + slot * SLOT_BYTES);
-            const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
-            const uint8_t* qm_p = qh_p + QH_TILE - r * 64;
-            const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
-            // One stream at a time (16 channels: head and remainder accumulators -> gate -> 32 bytes of output), with the
-            // accumulators of the next stream already on their way from TMEM: at most two streams' values are live, so
-            // nothing spills (a spilled value is reloaded from L2 here: L1 is almost entirely carved out as shared memory).
-#ifdef VTX_MR_EP_UNROLLED
-            uint32_t acc[2][2][16];
-            tmem_ld16(taddr, acc[0][0]);
-            tmem_ld16(taddr + 64, acc[0][1]);
+            for (int c = 0; c < CH / 4; ++c) {
+                const float4 d = dsk[c];
+                has_skip = has_skip || d.x != 0.f || d.y != 0.f || d.z != 0.f || d.w != 0.f;
+            }
+            // per stream: pointer to this thread's first output row and the number of rows of the segment from there on
+            // (<= 0: nothing to store).  Kept as one pointer and one int per stream to save registers.
+            __nv_bfloat16* yrow[NS];
+            int nleft[NS];
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
-                uint32_t (&ah)[16] = acc[s & 1][0];
-                uint32_t (&al)[16] = acc[s & 1][1];
-                tmem_ld_wait(ah, al);
-                if (s + 1 < NS) {
-                    tmem_ld16(taddr + (s + 1) * 16, acc[(s + 1) & 1][0]);
-                    tmem_ld16(taddr + 64 + (s + 1) * 16, acc[(s + 1) & 1][1]);
-                } else {
-#else
-            // (rolled over the streams: keeps the instruction-cache footprint of this role small)
+                const Stream st = stream_of(a, item_quad(t), s);
+                yrow[s] = a.y + st.b * a.y_stride_b + (st.ts + r) * a.y_stride_l + (int64_t)g * CH;
+                nleft[s] = st.active ? (int)(st.te - st.ts) - r : 0;
+            }
+            if (lane == 0) mbar_arrive(slot_free(cc & 1));      // the item's halo chunk has no epilogue
+            ++cc;
+            for (int k = 1; k < nchunk; ++k, ++cc, ++oc) {
+                const int slot = cc & 1, dbuf = oc & 1;
+                if (!mbar_wait(d_full(dbuf), (oc >> 1) & 1u, 5)) { ok = false; break; }
+                tc_fence_after();
+                __syncwarp();
+                const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + D_COL + dbuf * 64;
+                const uint8_t* kv_p = smp(OFF_SLOTS + slot * SLOT_BYTES) + r * 128;     // this row of the k*v tile; q: + Q_OFF
+                const int64_t yoff = (int64_t)(k - 1) * chunk_pitch;
+                // One stream at a time (16 channels: accumulators -> skip -> gate -> 32 bytes of output), rolled over the
+                // streams: keeps the instruction-cache footprint of this role small and nothing spills (a spilled value
+                // is reloaded from L2 here: L1 is almost entirely carved out as shared memory).
 #pragma unroll 1
-            for (int s = 0; s < NS; ++s) {
-                uint32_t ah[16], al[16];
-                tmem_ld16(taddr + s * 16, ah);
-                tmem_ld16(taddr + 64 + s * 16, al);
-                tmem_ld_wait(ah, al);
-                if (s + 1 == NS) {
-#endif
-                    // every accumulator of this chunk has left TMEM: hand the buffer back to the MMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(d_empty(dbuf));
-                    TRACE(12);
-                }
-                // this stream's output pointer and row count (selects, not indexed arrays: the loop may be rolled)
-                __nv_bfloat16* ys = yrow[0];
-                int nl = nleft[0];
+                for (int s = 0; s < NS; ++s) {
+                    uint32_t acc[16];
+                    tmem_ld16(taddr + s * 16, acc);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_ld_touch(acc);
+                    if (s + 1 == NS) {
+                        // every accumulator of this chunk has left TMEM: hand the buffer back to the MMA warp
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(d_empty(dbuf));
+                    }
+                    // this stream's output pointer and row count (selects, not indexed arrays: the loop is rolled)
+                    __nv_bfloat16* ys = yrow[0];
+                    int nl = nleft[0];
 #pragma unroll
-                for (int t = 1; t < NS; ++t)
-                    if (s == t) { ys = yrow[t]; nl = nleft[t]; }
-                f32x2 y[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    y[i] = add2(pk2(__uint_as_float(ah[2 * i]), __uint_as_float(ah[2 * i + 1])),
-                                pk2(__uint_as_float(al[2 * i]), __uint_as_float(al[2 * i + 1])));
-                if (has_skip) {
-                    // skip term D[c] * kv[t, c] from this row of the k*v tile (head + remainder)
+                    for (int tt = 1; tt < NS; ++tt)
+                        if (s == tt) { ys = yrow[tt]; nl = nleft[tt]; }
+                    uint32_t o[8];
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
-                        const uint32_t off = (uint32_t)(r * 128) + (uint32_t)(((2 * s + hf) ^ (r & 7)) << 4);
-                        const uint4 h4 = *reinterpret_cast<const uint4*>(slot_p + HI_OFF + off);
-                        const uint4 l4 = *reinterpret_cast<const uint4*>(slot_p + LO_OFF + off);
-                        const float4 d0 = dsk[2 * hf], d1 = dsk[2 * hf + 1];
-                        f32x2* yy = &y[4 * hf];
-                        yy[0] = fma2(pk2(d0.x, d0.y), add2(pk2(bf_lo(h4.x), bf_hi(h4.x)), pk2(bf_lo(l4.x), bf_hi(l4.x))), yy[0]);
-                        yy[1] = fma2(pk2(d0.z, d0.w), add2(pk2(bf_lo(h4.y), bf_hi(h4.y)), pk2(bf_lo(l4.y), bf_hi(l4.y))), yy[1]);
-                        yy[2] = fma2(pk2(d1.x, d1.y), add2(pk2(bf_lo(h4.z), bf_hi(h4.z)), pk2(bf_lo(l4.z), bf_hi(l4.z))), yy[2]);
-                        yy[3] = fma2(pk2(d1.z, d1.w), add2(pk2(bf_lo(h4.w), bf_hi(h4.w)), pk2(bf_lo(l4.w), bf_hi(l4.w))), yy[3]);
-                    }
-                }
-                if (KO(32)) continue;
-                uint32_t o[8];
-                const uint4 qm4 = *reinterpret_cast<const uint4*>(qm_p + ((s ^ ((r >> 1) & 3)) << 4));
-                const uint32_t qm[4] = {qm4.x, qm4.y, qm4.z, qm4.w};
+                        const uint32_t off = (uint32_t)(((2 * s + hf) ^ (r & 7)) << 4);
+                        f32x2 y[4];
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const uint4 qh4 = *reinterpret_cast<const uint4*>(qh_p + (((2 * s + hf) ^ (r & 7)) << 4));
-                    const uint32_t qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+                        for (int j = 0; j < 4; ++j) y[j] = pk2(__uint_as_float(acc[8 * hf + 2 * j]), __uint_as_float(acc[8 * hf + 2 * j + 1]));
+                        if (has_skip) {
+                            // skip term D[c] * kv[t, c] from this row of the k*v tile (both carry their power of two)
+                            const uint4 k4 = *reinterpret_cast<const uint4*>(kv_p + off);
+                            const float4 d0 = dsk[2 * hf], d1 = dsk[2 * hf + 1];
+                            y[0] = fma2(pk2(d0.x, d0.y), unpack_f16(k4.x), y[0]);
+                            y[1] = fma2(pk2(d0.z, d0.w), unpack_f16(k4.y), y[1]);
+                            y[2] = fma2(pk2(d1.x, d1.y), unpack_f16(k4.z), y[2]);
+                            y[3] = fma2(pk2(d1.z, d1.w), unpack_f16(k4.w), y[3]);
+                        }
+                        const uint4 q4 = *reinterpret_cast<const uint4*>(kv_p + Q_OFF + off);
+                        const uint32_t qw[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {          // channels 8 hf + 2 j, + 1: third bytes 2 (j % 2), + 1 of word 2 hf + j / 2
-                        const uint32_t mw = qm[2 * hf + j / 2];
-                        const uint32_t qa = __byte_perm(qh[j], mw, (j % 2) ? 0x1066 : 0x1044);
-                        const uint32_t qb = __byte_perm(qh[j], mw, (j % 2) ? 0x3277 : 0x3255);
-                        float o0, o1;
-                        up2(mul2(y[4 * hf + j], pk2(__uint_as_float(qa), __uint_as_float(qb))), o0, o1);
-                        o[4 * hf + j] = pack_bf16(o0, o1);
+                        for (int j = 0; j < 4; ++j) {
+                            float o0, o1;
+                            up2(mul2(y[j], unpack_f16(qw[j])), o0, o1);
+                            o[4 * hf + j] = pack_bf16(o0, o1);
+                        }
                     }
-                }
-                // (no "memory" clobber: nothing in this kernel reads y, and the shared-memory reads of the next stream
-                // may then be scheduled above this store)
+                    // (no "memory" clobber: nothing in this kernel reads y, and the shared-memory reads of the next stream
+                    // may then be scheduled above this store)
 #ifdef VTX_MR_CHECK
-                {   // diagnostic builds: a store outside y is recorded and skipped
-                    const int64_t off = (ys + yoff) - a.y;
-                    if ((k - 1) * CHUNK < nl && (off < 0 || off + 16 > a.B * a.y_stride_b)) {
-                        atomicCAS(&g_device_status, 0, 21);
-                        continue;
+                    {   // diagnostic builds: a store outside y is recorded and skipped
+                        const int64_t off = (ys + yoff) - a.y;
+                        if ((k - 1) * CHUNK < nl && (off < 0 || off + 16 > a.B * a.y_stride_b)) {
+                            atomicCAS(&g_device_status, 0, 21);
+                            continue;
+                        }
                     }
-                }
 #endif
-                if ((k - 1) * CHUNK < nl && !(KO(4) && o[0] != 0x12345678u))
-                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ys + yoff), "r"(o[0]),
-                                 "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
+                    if ((k - 1) * CHUNK < nl)
+                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ys + yoff), "r"(o[0]),
+                                     "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
+                }
+                // every shared-memory read of this chunk is done: its k*v slot and q tile may be rewritten
+                __syncwarp();
+                if (lane == 0) mbar_arrive(slot_free(slot));
+                if (k == 1 && t + 1 < nmine && !expand(t + 1)) { ok = false; break; }
             }
-            // every shared-memory read of this chunk is done: its k*v slot and q tile may be rewritten
-            __syncwarp();
-            if (lane == 0) mbar_arrive(slot_free(slot));
-            TRACE(13);
-            if (k == 1 && t + 1 < nmine && !expand(t + 1)) { ok = false; break; }
-        }
         }
     } else if (warp == W_MMA) {
         // ======== MMA issue =========================================================================
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(128, 2 * NS * CH, 1);
+            const uint32_t idesc = instr_desc_f16(128, NS * CH);
             // An output chunk accumulates  prev = T^ * kv(chunk before)  and  cur = T * kv(chunk)  into one buffer.
             // The prev half of the NEXT chunk is issued right behind cur, long before that chunk is staged, so a tile
             // is released (slot_free) one whole chunk before the front end needs its slot again.
             // Descriptors are built once; a K step of 16 rows moves the start-address field by 2048 B (128 units).
             // The issue loop is fully unrolled: the issuing thread is on the critical path of every chunk.
-            // B operand of one K step: 16 rows x [head tile | remainder tile] = N-major, two 64-channel atoms
-            // KV_TILE bytes apart (LBO), 8-row groups 1024 B apart (SBO), 128-byte swizzle.  N = 128 per MMA:
-            // narrower MMAs run at a fixed ~70 cycles each at this tile height, so both parts go into one.
+            // B operand of one K step: 16 rows x 64 channels, N-major, one 128-byte swizzle atom wide, 8-row groups
+            // 1024 B apart (SBO); the leading-dimension offset is not used with a single atom.
             uint64_t kv_desc[2];
 #pragma unroll
-            for (int sl = 0; sl < 2; ++sl) kv_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES + HI_OFF, KV_TILE, 1024, 2);
+            for (int sl = 0; sl < 2; ++sl) kv_desc[sl] = smem_desc(sm_u + OFF_SLOTS + sl * SLOT_BYTES, KV_TILE, 1024, 2);
             // one half of a chunk's contraction: T^ (cur == false) or T (cur == true) times the k*v tile in `slot`,
             // accumulated into buffer `dbuf`; the previous-chunk half comes first and overwrites the accumulator
             auto issue_half = [&](int abuf, int slot, int dbuf, bool cur) {
-                const uint32_t d = tmem + D_COL + dbuf * 128;
+                const uint32_t d = tmem + D_COL + dbuf * 64;
                 const uint32_t a0 = tmem + abuf * 128 + (cur ? 64 : 0);
                 const uint64_t dk = slot ? kv_desc[1] : kv_desc[0];
-                const int nj = KO(64) ? 0 : KO(8) ? 1 : 8;
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                    if (jj >= nj) continue;
+                for (int jj = 0; jj < 8; ++jj)
                     mma_ts(d, a0 + 8 * jj, dk + (uint64_t)(jj * (16 * 128 / 16)), idesc, (cur || jj > 0) ? 1u : 0u);
-                }
             };
             bool ok = true;
             for (int t = 0; t < nmine && ok; ++t) {
                 const int ab = t & 1;
                 // the item's Toeplitz operand (expanded by the epilogue warps while the item before was streaming)
-                if (!MBAR_WAIT(a_ready(ab), (uint32_t)((t >> 1) & 1), 10)) { ok = false; break; }
+                if (!mbar_wait(a_ready(ab), (uint32_t)((t >> 1) & 1), 10)) { ok = false; break; }
                 // halo chunk of the item: its tile only feeds the previous-chunk half of the first output chunk
-                if (!MBAR_WAIT(kv_full(cc & 1), (cc >> 1) & 1u, 7)) { ok = false; break; }
+                if (!mbar_wait(kv_full(cc & 1), (cc >> 1) & 1u, 7)) { ok = false; break; }
                 if (nchunk > 1) {
                     // the accumulator of output chunk oc was last read by the epilogue of output chunk oc - 2
-                    if (oc >= 2 && !MBAR_WAIT(d_empty(oc & 1), ((oc - 2) >> 1) & 1u, 8)) { ok = false; break; }
+                    if (oc >= 2 && !mbar_wait(d_empty(oc & 1), ((oc - 2) >> 1) & 1u, 8)) { ok = false; break; }
                     tc_fence_after();
                     issue_half(ab, cc & 1, oc & 1, false);
                 }
                 mma_commit(slot_free(cc & 1));
                 ++cc;
                 for (int k = 1; k < nchunk; ++k, ++cc, ++oc) {
-                    TRACE(20);
-                    if (!MBAR_WAIT(kv_full(cc & 1), (cc >> 1) & 1u, 6)) { ok = false; break; }
-                    TRACE(21);
+                    if (!mbar_wait(kv_full(cc & 1), (cc >> 1) & 1u, 6)) { ok = false; break; }
                     tc_fence_after();
                     issue_half(ab, cc & 1, oc & 1, true);
                     mma_commit(d_full(oc & 1));
-                    TRACE(22);
                     if (k + 1 < nchunk) {
                         // the next output chunk's accumulator was last read by the epilogue of output chunk oc - 1
-                        if (oc >= 1 && !MBAR_WAIT(d_empty((oc + 1) & 1), ((oc - 1) >> 1) & 1u, 8)) { ok = false; break; }
-                        TRACE(23);
+                        if (oc >= 1 && !mbar_wait(d_empty((oc + 1) & 1), ((oc - 1) >> 1) & 1u, 8)) { ok = false; break; }
                         tc_fence_after();
                         issue_half(ab, cc & 1, (oc + 1) & 1, false);
                     }
                     mma_commit(slot_free(cc & 1));
-                    TRACE(24);
                 }
             }
         }
@@ -649,8 +615,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 }
                 for (int hh = 0; hh < 2 * nchunk; ++hh, ++nh) {
                     const int stg = (int)(nh % IN_STAGES), k = hh / 2, h = hh % 2;
-                    if (nh >= IN_STAGES && !MBAR_WAIT(in_empty(stg), ((nh - IN_STAGES) / IN_STAGES) & 1u, 9)) { ok = false; break; }
-                    TRACE(30);
+                    if (nh >= IN_STAGES && !mbar_wait(in_empty(stg), ((nh - IN_STAGES) / IN_STAGES) & 1u, 9)) { ok = false; break; }
                     const uint32_t bar = in_full(stg);
                     mbar_expect_tx(bar, NS / NTMA * BOX_BYTES);
 #pragma unroll
@@ -669,6 +634,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 }
             }
         }
+    } else if (warp == W_STATE) {
+        if (a.fir_state || a.inner_state) write_caches(a, nmine, lane);
     }
 
     // ---------------- teardown -------------------------------------------------------------------
@@ -677,7 +644,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     if (warp == W_MMA) {
         __syncwarp();
         uint32_t tmem;
-        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(sm_u + OFF_TSLOT) : "memory");
+        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(sm_u + LY::OFF_TSLOT) : "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
     }
 }
@@ -698,13 +665,11 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     a.bias = p->bias; a.bias_dtype = p->bias_dtype; a.has_bias = p->bias_mode == VTX_BIAS_GATED;
     a.u = static_cast<const __nv_bfloat16*>(p->u); a.u_stride_b = p->u_stride_b; a.u_stride_l = p->u_stride_l;
     a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
+    a.fir_state = static_cast<__nv_bfloat16*>(p->fir_state); a.inner_state = static_cast<__nv_bfloat16*>(p->inner_state);
     a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
     a.hd = p->D;
     a.hist = (int)p->u_hist_rows;
-    a.pf = getenv("VTX_MR_PF") ? atoi(getenv("VTX_MR_PF")) : 0;
-    a.dbg = getenv("VTX_MR_DBG") ? atoi(getenv("VTX_MR_DBG")) : 0;
-    a.trace = getenv("VTX_MR_TRACE_PTR") ? (unsigned long long*)strtoull(getenv("VTX_MR_TRACE_PTR"), nullptr, 0) : nullptr;
     if (p->layout == VTX_QKV_COLUMN_SPLIT) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_fir: bad num_heads");
         a.hd = p->D / p->num_heads;
@@ -712,15 +677,12 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     }
     VTX_REQUIRE(p->layout == VTX_QKV_INTERLEAVED || (p->D * 2) % 16 == 0, VTX_ERR_ALIGNMENT,
                 "fused_fir: D*itemsize must be a multiple of 16 bytes for this q/k/v layout");
-    // segments: enough CTAs (group x stream quads) for ~7 rounds over the SMs, whole chunks each
+    // segments: enough work items (group x stream quads) for ~6 rounds over the SMs, whole chunks each
     const int64_t nchunks_total = ceil_div<int64_t>(p->L, CHUNK);
     int64_t nseg = 1;
     while (p->G * ceil_div<int64_t>(p->B * nseg, NS) < (int64_t)kNumSMs * 6 && nseg * 2 <= nchunks_total &&
            ceil_div<int64_t>(nchunks_total, nseg * 2) >= 8)
         nseg *= 2;
-#ifdef VTX_MR_KNOCKOUT
-    if (getenv("VTX_MR_NSEG")) nseg = atoi(getenv("VTX_MR_NSEG"));
-#endif
     a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
     a.nseg = ceil_div<int64_t>(p->L, a.seg_len);
     a.nstream = p->B * a.nseg;
@@ -738,32 +700,31 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
         return rc;
     const int variant = !inter ? 0 : (a.flip ? 2 : 1);
     auto kern = variant == 0 ? fused_mr_kernel<false, false> : variant == 1 ? fused_mr_kernel<true, false> : fused_mr_kernel<true, true>;
+    const int smem_bytes = inter ? Lay<true>::SMEM_BYTES : Lay<false>::SMEM_BYTES;
     // the opt-in is a per-device property of the function: remember it per device
     static bool attr_set[64][3] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[dev][variant]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev][variant] = true;
     }
-    // one persistent CTA per SM that can hold one (the shared-memory footprint allows no more), each with a contiguous
-    // range of items.  The CTA count must not exceed what is resident at once: a second round would double the time.
+    // One persistent CTA per SM (the shared-memory footprint allows no more), each walking the items blockIdx,
+    // blockIdx + gridDim, ...  The CTA count must not exceed what is resident at once: a second round would double the time.
     static int resident[64][3] = {};
     int nres = (dev >= 0 && dev < 64) ? resident[dev][variant] : 0;
     if (nres == 0) {
         int sms = 0, per_sm = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, SMEM_BYTES);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem_bytes);
         nres = sms * per_sm;
         if (nres <= 0) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): the kernel does not fit an SM (%d SMs, %d blocks each)", sms, per_sm);
         if (dev >= 0 && dev < 64) resident[dev][variant] = nres;
     }
     const int64_t ncta = a.nitems < nres ? a.nitems : nres;
-    kern<<<(unsigned)ncta, THREADS, SMEM_BYTES, stream>>>(tmap, a);
-    if (int rc = check_launch("fused_fir(mr)")) return rc;
-    if (p->fir_state || p->inner_state) return launch_fused_state_bf16(p, stream);
-    return VTX_OK;
+    kern<<<(unsigned)ncta, THREADS, smem_bytes, stream>>>(tmap, a);
+    return check_launch("fused_fir(mr)");
 }
 
 }  // namespace vtx
