@@ -5,10 +5,13 @@
                     [--workload mr|se|li|li_pc|cc1d|decode_mr|decode_se|decode_li|decode_stack]
 
 Default workload: Hyena-MR grouped causal FIR prefill, B=4, L=8192, D=4096, bf16 I/O with fp32
-accumulation, 128-tap filters shared by groups of 16 channels, featurizer and gates fused
-(seeded synthetic data).  A step is one pass of the fused block over the whole batch.  With N > 1
-every rank owns one 4096-channel shard of a hidden dimension of 4096*N (channels are independent,
-so there is no collective on the data path) and `value` adds up the tokens of all shards.
+accumulation, 128-tap filters shared by groups of 16 channels, featurizer and gates fused, prefill
+caches written (seeded synthetic data).  A step is one pass of the fused block over the whole batch.
+With N > 1 the SAME problem is cut into N channel shards (strong scaling: rank r owns the hidden channels
+`sharding.channel_range(D, G, N, r)`; decode workloads cut the batch instead).  Channels are independent, so
+the block itself needs no exchange; the step then all-gathers the block output over NCCL (the boundary a
+replicated output projection needs) inside the timed region, and the line reports the kernel-only and the
+collective's share next to it.  `--scaling weak` gives every rank a full-width problem of its own instead.
 
 Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM; `e2e` goes
 through the public API with pinned host buffers, host<->device copies inside the timed region.
@@ -154,6 +157,22 @@ def decode_bytes(w):
     return 2 * cache + B * 3 * D * 2 + B * D * 2
 
 
+def algorithmic_bytes(w):
+    """HBM bytes one step has to move.  Prefill: 3 reads + 1 write of 2-byte elements per hidden channel and token, plus
+    the caches when they are written (featurizer rows, and the inner FIR samples or the fp32 modal state); the conv
+    extension's operator: 2 in + 2 out per packed channel; decode: every cache element read and written once."""
+    if w.get("decode"):
+        return decode_bytes(w)
+    B, L, D, K = w["B"], w["L"], w["D"], w["K"]
+    if w.get("cc1d"):
+        return 12 * B * D * L
+    n = 8 * B * D * L
+    if w.get("caches"):
+        n += B * 3 * D * 2 * 2
+        n += B * D * (K - 1) * 2 if K > 0 else B * D * 16 * 4 * (1 if w.get("real_poles") else 2)
+    return n
+
+
 def run_block(name, pc, u=None):
     """One step through the public API; returns y [B, L, D]."""
     from vortex_b200 import hyena_ops, ops
@@ -180,12 +199,13 @@ def run_block(name, pc, u=None):
                                 bias=pc["Dp"], flip_filter=name == "decode_mr", gated_bias=name == "decode_mr")[0]
     if name == "cc1d":
         return hyena_ops.causal_conv1d_fn(u.transpose(1, 2), pc["w3"].reshape(-1, 3))
+    caches = bool(pc.get("caches"))
     if name == "mr":
-        return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"])[0]
+        return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"], want_state=caches)[0]
     if name == "se":
-        return hyena_ops.hyena_se_fwd(u, pc["w3"], None, pc["h"])[0]
+        return hyena_ops.hyena_se_fwd(u, pc["w3"], None, pc["h"], want_state=caches)[0]
     return hyena_ops.hyena_li_fwd(u, pc["w3"], None, pc["log_poles"], pc["residues"], pc["Dp"], theta=pc["theta"],
-                                  res_im=pc["res_im"], want_state=name == "li_pc")[0]
+                                  res_im=pc["res_im"], want_state=caches)[0]
 
 
 class ClockSampler:
@@ -228,7 +248,7 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-def cpu_baseline(name, w, steps=1):
+def cpu_baseline(name, w, steps=1, warmup=1, cap_s=25.0):
     """The reference's CPU path (oracle/torch_port.py) on a bounded channel slice, scaled to the full width."""
     from oracle import torch_port as TP
     # all the host threads this process may use (a launcher such as torchrun presets OMP_NUM_THREADS=1)
@@ -262,18 +282,23 @@ def cpu_baseline(name, w, steps=1):
             z, _ = TP.featurizer(u, w3)
             hh = TP.modal_filter(lp, R, L)
             return TP.long_conv_gate(z, hh, Dp, Ds, layout="interleaved")[0]
-    step()
-    best = float("inf")
+    for _ in range(max(1, warmup)):
+        step()
+    # every step timed; the figure is the mean over the steps (a 25 s cap keeps the default run short)
+    times = []
     t_all = time.perf_counter()
     for _ in range(max(1, steps)):
         t0 = time.perf_counter()
         step()
-        best = min(best, time.perf_counter() - t0)
-        if time.perf_counter() - t_all > 25:
+        times.append(time.perf_counter() - t0)
+        if cap_s and time.perf_counter() - t_all > cap_s:
             break
+    best = sum(times) / len(times)
     full = best * (D / Ds)
     return {"value": B * L / full, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{Ds} of {D} channels (B={B}, L={L}), best of up to {steps} passes, scaled by {D // Ds}x; "
+            "extrapolated": True, "slice_ms": best * 1e3, "slice_channels": Ds, "scale": D / Ds,
+            "sample": f"{Ds} of {D} channels (B={B}, L={L}) measured ({best * 1e3:.1f} ms, mean of {len(times)} passes) "
+                      f"and scaled by {D // Ds}x (channels are independent); "
                       f"torch {torch.__version__} F.conv1d/torch.fft on {os.cpu_count()} host cpus"}, full
 
 
@@ -284,6 +309,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mr", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: strong = one problem cut into N channel (prefill) or batch (decode) shards, block output "
+                         "all-gathered inside the timed region; weak = a full-size problem per rank, no collective")
+    ap.add_argument("--no-caches", action="store_true", help="prefill workloads: do not write the prefill caches")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small cases for profiling)")
     ap.add_argument("--seq", type=int, default=0, help="override the sequence length (small cases for profiling)")
     ap.add_argument("--channels", type=int, default=0, help="override the hidden channels (the shard of one GPU)")
@@ -305,24 +334,50 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    tokens = w["B"] * w["L"]
-    step_bytes = decode_bytes(w) if w.get("decode") else (12 if w.get("cc1d") else 8) * w["B"] * w["D"] * w["L"]
-    config = {"workload": w["name"], "seed": w["seed"], "qkv_layout": "interleaved",
-              "sharding": (f"batch: each of {world} rank(s) owns {w['B']} sequences, no collective" if w.get("decode") else
-                           f"channel: each of {world} rank(s) owns {w['D']} hidden channels, no collective"),
-              "l2": (f"{step_bytes / 1e6:.0f} MB of caches and tokens per step" +
-                     (", caches rotate over sets larger than L2" if w.get("decode") and not w.get("stack") else "")
+    prefill = not w.get("decode") and not w.get("cc1d")
+    w["caches"] = prefill and not a.no_caches
+    strong = world > 1 and a.scaling == "strong"
+    full = dict(w)                      # the whole problem; w becomes this rank's share of it
+    from vortex_b200 import sharding
+    if strong:
+        if w.get("decode"):
+            b0, b1 = sharding.batch_range(full["B"], world, rank)
+            w["B"] = b1 - b0
+        else:
+            d0, d1 = sharding.channel_range(full["D"], full["G"], world, rank)
+            w["D"], w["G"] = d1 - d0, (d1 - d0) // (full["D"] // full["G"])
+    tokens = full["B"] * full["L"] if strong else world * w["B"] * w["L"]      # whole-job tokens per step
+    step_bytes = algorithmic_bytes(w)
+    if world == 1:
+        how = "one GPU holds the whole problem"
+    elif not strong:
+        how = f"weak: each of {world} ranks runs a full-size problem of its own, no collective"
+    elif w.get("decode"):
+        how = (f"strong, batch shards: the {full['B']} sequences are cut into {world} shards of {w['B']}; every cache is "
+               "per sequence, so there is no collective on the data path")
+    else:
+        how = (f"strong, channel shards: the {full['D']} hidden channels are cut into {world} shards of whole filter "
+               f"groups ({w['D']} on this rank); the block needs no exchange, the step then all-gathers y over NCCL")
+    config = {"workload": full["name"], "seed": full["seed"], "qkv_layout": "interleaved", "sharding": how,
+              "caches": bool(w["caches"]),
+              "l2": (f"{step_bytes / 1e6:.0f} MB of caches and tokens per step and rank" +
+                     (", caches rotate over sets larger than L2" if not w.get("stack") else "")
                      if w.get("decode") else
-                     f"inputs and outputs ({step_bytes / 1e6:.0f} MB per step) are larger than the 126 MB L2")}
+                     f"inputs and outputs of a rank ({step_bytes / 1e6:.0f} MB per step) " +
+                     ("are larger than the 126 MB L2" if step_bytes > 2 * 126e6 else
+                      "fit the 126 MB L2: a buffer larger than L2 is written between timed steps"))}
 
     if a.impl == "reference":
         if rank != 0:
             return
-        cb, full = cpu_baseline(a.workload, w, steps=max(1, a.steps))
+        # the reference's CPU path on the host cores: every step is one pass over a bounded channel slice of the
+        # whole (un-sharded) workload; throughput is scaled to the full width
+        cb, _ = cpu_baseline(a.workload, full, steps=max(1, a.steps), warmup=max(1, a.warmup), cap_s=0)
         line = {"impl": "reference", "metric": "hyena_prefill_throughput", "value": cb["value"], "unit": "tok/s",
-                "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": full * 1e3,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic", "config": config, "cpu_baseline": cb,
+                "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": cb["slice_ms"],
+                "ms_per_step_full_width": cb["slice_ms"] * cb["scale"], "extrapolated": True,
+                "higher_is_better": True, "scaling": "strong" if strong or world == 1 else "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic", "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -343,15 +398,47 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    p = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), dev)
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if strong and prefill:
+        # every rank builds the same seeded problem and keeps its own channels (contiguous copies of the slices)
+        pfull = make_inputs(full, dev)
+        p = sharding.shard_block({k: v for k, v in pfull.items() if torch.is_tensor(v) or v is None},
+                                 full["D"], full["G"], world, rank, layout="interleaved")
+        p = {k: (v.contiguous() if torch.is_tensor(v) else v) for k, v in p.items()}
+        del pfull
+    else:
+        p = make_inputs(dict(w, seed=w["seed"] + (1000 * rank if world > 1 else 0)), dev)
     pc = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
     for key in ("sets", "layers"):
         if key in pc:
             pc[key] = [{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in c.items()} for c in pc[key]]
+    pc["caches"] = w["caches"]
     from vortex_b200 import ops
 
-    for _ in range(a.warmup):
+    gather = None
+    if strong and prefill:
+        widths = [hi - lo for lo, hi in (sharding.channel_range(full["D"], full["G"], world, r) for r in range(world))]
+        recv = torch.empty(world, w["B"], w["L"], max(widths), device=dev, dtype=torch.bfloat16)
+
+        def gather(y):
+            return sharding.gather_channels(y, widths=widths, out=recv, concat=False)
+
+    flush = None
+    if not w.get("decode") and step_bytes <= 2 * 126e6:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # written between steps: evicts the 126 MB L2
+
+    def step():
         y = run_block(a.workload, pc)
+        return gather(y) if gather is not None else y
+
+    for _ in range(a.warmup):
+        y = step()
     ops.device_status()
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -369,29 +456,56 @@ def main():
         torch.cuda.current_stream().wait_stream(side)
         graph.replay()
         torch.cuda.synchronize()
+
+    def timed(fn, n):
+        """n calls of fn between two events on the current stream; with a flush buffer every call is timed on its own
+        (the flush in between is not counted)."""
+        if flush is None:
+            barrier()
+            ev0.record()
+            for _ in range(n):
+                fn()
+            ev1.record()
+            barrier()
+            return max_over_ranks(ev0.elapsed_time(ev1))
+        total = 0.0
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        barrier()
+        for e0, e1 in evs:
+            flush.fill_(1)
+            e0.record()
+            fn()
+            e1.record()
+        barrier()
+        for e0, e1 in evs:
+            total += e0.elapsed_time(e1)
+        return max_over_ranks(total)
+
     with ClockSampler(local) as cs:
-        barrier()
-        ev0.record()
         if graph is not None:
-            graph.replay()
+            ms = timed(graph.replay, 1)
         else:
-            for _ in range(a.steps):
-                y = run_block(a.workload, pc)
-        ev1.record()
-        barrier()
-    ms = ev0.elapsed_time(ev1)
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+            ms = timed(step, a.steps)
     ms_step = ms / a.steps
-    value = world * tokens / (ms_step * 1e-3)
+    value = tokens / (ms_step * 1e-3)
+    kernel_only, collective = None, None
+    if gather is not None:
+        # the same steps without the collective, and the collective alone (same buffers)
+        ms_k = timed(lambda: run_block(a.workload, pc), a.steps) / a.steps
+        y_sh = run_block(a.workload, pc)
+        ms_c = timed(lambda: gather(y_sh), a.steps) / a.steps
+        kernel_only = {"ms_per_step": ms_k, "value": tokens / (ms_k * 1e-3), "unit": "tok/s",
+                       "frac_of_hbm_peak_per_rank": step_bytes / (ms_k * 1e-3) / 1e9 / _peaks()[0]}
+        collective = {"op": "all_gather", "backend": "nccl", "bytes_received_per_rank": recv.numel() * 2 * (world - 1) // world,
+                      "ms": ms_c, "overlapped": False,
+                      "limiter": "collective" if ms_c > ms_k else "kernel"}
 
     # ---- end to end: pinned host input -> device -> kernel -> pinned host output, every step
     e2e = None
     if not a.no_e2e and not w.get("decode"):
         hu = p["u"].pin_memory()
-        hy = [torch.empty(y.shape, dtype=y.dtype).pin_memory() for _ in range(2)]
+        y1 = run_block(a.workload, pc)
+        hy = [torch.empty(y1.shape, dtype=y1.dtype).pin_memory() for _ in range(2)]
         du = [torch.empty_like(pc["u"]) for _ in range(2)]
         main_s, s_in, s_out = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
         ev_in = [torch.cuda.Event() for _ in range(2)]
@@ -400,7 +514,8 @@ def main():
 
         def e2e_steps(n):
             # every step: pinned host input -> device (copy stream), kernel (main stream), output -> pinned host (copy
-            # stream); two buffers, so the copies of neighbouring steps overlap the kernel and each other
+            # stream); two buffers, so the copies of neighbouring steps overlap the kernel and each other.  With
+            # channel shards every rank moves its own columns in and its own slice of y out: the host assembles.
             for i in range(n):
                 j = i % 2
                 with torch.cuda.stream(s_in):
@@ -428,44 +543,44 @@ def main():
         e2e_steps(n_e2e)
         ev1.record()
         barrier()
-        ms_e = ev0.elapsed_time(ev1)
-        if dist is not None:
-            t = torch.tensor([ms_e], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_e = float(t.item())
-        e2e = {"value": world * tokens / (ms_e / n_e2e * 1e-3), "unit": "tok/s",
+        ms_e = max_over_ranks(ev0.elapsed_time(ev1))
+        e2e = {"value": tokens / (ms_e / n_e2e * 1e-3), "unit": "tok/s",
                "h2d_bytes_per_step": hu.numel() * hu.element_size(), "d2h_bytes_per_step": hy[0].numel() * hy[0].element_size(),
-               "steps": n_e2e}
+               "bytes_are": "per rank", "steps": n_e2e}
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
     peak, peak_kind = _peaks()
-    # prefill: 3 reads + 1 write of 2-byte elements per channel and token; decode: the caches, read and written once
-    algo_bytes = decode_bytes(w) if w.get("decode") else (12 if w.get("cc1d") else 8) * w["B"] * w["D"] * w["L"]
     launches_per_step = LAUNCHES.get(a.workload, 1)
-    achieved = algo_bytes / (ms_step * 1e-3) / 1e9
+    ms_kernel = kernel_only["ms_per_step"] if kernel_only else ms_step
+    achieved = step_bytes / (ms_kernel * 1e-3) / 1e9
+    traffic = NCU_TRAFFIC.get(a.workload)
+    if traffic is not None:
+        traffic = traffic * step_bytes / algorithmic_bytes(dict(WORKLOADS[a.workload], caches=w["caches"]))
     line = {
         "metric": "hyena_decode_throughput" if w.get("decode") else "hyena_prefill_throughput", "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
-        "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
+        "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak" if (world > 1 and not strong) else "strong", "vs_baseline": None,
+        "dtype": w.get("io_name", "bf16"), "data": "synthetic", "config": config, "clocks": cs.summary(),
         "gpu_launches": launches_per_step * a.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC.get(a.workload), "peak_kind": f"of {peak_kind}",
-                     "algorithmic_bytes_per_launch": algo_bytes,
-                     "note": "achieved = algorithmic bytes / (timed region / steps); one step = "
-                             f"{launches_per_step} kernel launch(es)"},
+                     "traffic": traffic, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": step_bytes,
+                     "note": "per rank: achieved = algorithmic bytes of the rank's share / kernel time per step (the "
+                             f"collective, if any, is reported apart); one step = {launches_per_step} kernel launch(es)"},
+        "kernel_only": kernel_only, "collective": collective,
         "e2e": e2e,
     }
     if not a.no_cpu_baseline and world == 1 and not w.get("decode"):
-        line["cpu_baseline"] = cpu_baseline(a.workload, w, steps=3)[0]
+        line["cpu_baseline"] = cpu_baseline(a.workload, full, steps=3)[0]
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
 
-# kernel launches of ours per step of each workload (no cache outputs requested)
+# kernel launches of ours per step of each workload
 LAUNCHES = {"mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)

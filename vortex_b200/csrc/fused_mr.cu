@@ -21,9 +21,8 @@
 // the launch read neighbouring groups of the same rows).  Warp roles (16 warps): 0-7 front end (TMA-staged rows ->
 // featurizer -> k*v and q as fp16 into the chunk's slot), 8-11 epilogue (tcgen05.ld -> skip -> q gate -> bf16 ->
 // global; they also expand the NEXT item's Toeplitz operand into the other half of a TMEM double buffer while the
-// current item streams), 12 MMA issue, 13-14 TMA issue, 15 prefill caches (the last two input rows and the last
-// K-1 samples of k*v of every sequence, re-evaluated from the rows themselves for the items whose streams end a
-// sequence).  A front-end lane owns one channel pair of one stream and walks 16 rows per chunk in two register
+// current item streams), 12 MMA issue, 13-14 TMA issue, 15 prefill caches (the last two input rows of every sequence,
+// and its last K-1 samples of k*v read back from the tiles the front end publishes).  A front-end lane owns one channel pair of one stream and walks 16 rows per chunk in two register
 // batches, the next batch fetched before the current one is computed; the four streams of a warp are staged one
 // row apart in shared memory so that the lanes of a warp read distinct banks.  All waits are bounded.
 #include "tma.cuh"
@@ -145,74 +144,6 @@ __device__ __forceinline__ uint16_t f16_bits(float v) {
     return __half_as_ushort(__float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f)));
 }
 
-// Prefill caches (one warp per CTA, beside the streaming roles): fir_state[b, c, :] = u[b, L-n3:L, c] (n3 = min(L, 2)),
-// inner_state[b, d, :] = bf16(kv[b, d, L-ns:L]) (ns = min(L, K-1)); with history rows in front of u both are always
-// full and negative times index those rows.  Exactly one stream of a (batch, group) ends its sequence; the CTA that
-// owns its item evaluates the caches here from the rows themselves (fp32 featurizer, unscaled taps).  Not inlined:
-// its registers are then allocated apart from the front end's, which runs at the limit.
-__device__ __noinline__ void write_caches(const Args& a, int nmine, int lane) {
-    const int c = lane % CH, hh = lane / CH;
-    const int ncta = (int)gridDim.x, K = (int)a.K;
-    const QkvMap map{a.layout, a.flip, a.D, a.hd};
-    const int64_t L = a.L;
-    const int64_t n3 = (a.hist > 0 || L >= 2) ? 2 : L;
-    const int64_t ns = (a.hist > 0 || L >= K - 1) ? K - 1 : L;
-    for (int t = 0; t < nmine; ++t) {
-        const int64_t item = (int64_t)blockIdx.x + (int64_t)t * ncta;
-        const int g = (int)(item % a.G);
-        const int64_t quad = item / a.G;
-        int64_t cq, ck, cv;
-        map.get((int64_t)g * CH + c, cq, ck, cv);
-        float wk[3], wv[3];
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            wk[j] = ld_param(a.w3, a.w3_dtype, ck * 3 + j);
-            wv[j] = ld_param(a.w3, a.w3_dtype, cv * 3 + j);
-        }
-        for (int s = 0; s < NS; ++s) {
-            const Stream st = stream_of(a, quad, s);
-            if (!st.active || st.te != L) continue;
-            const __nv_bfloat16* ub = a.u + st.b * a.u_stride_b;
-            auto ld = [&](int64_t tt, int64_t col) {
-                return tt >= -(int64_t)a.hist ? __bfloat162float(ub[tt * a.u_stride_l + col]) : 0.f;
-            };
-            if (a.inner_state && ns > 0) {
-                // the two half-warps split the ns samples; lane = channel within the group
-                const int64_t per = (ns + 1) / 2, j0 = hh * per, j1 = j0 + per < ns ? j0 + per : ns;
-                __nv_bfloat16* dst = a.inner_state + (st.b * a.D + (int64_t)g * CH + c) * ns;
-                int64_t tt = L - ns + j0;
-                float k2 = ld(tt - 2, ck), k1 = ld(tt - 1, ck), v2 = ld(tt - 2, cv), v1 = ld(tt - 1, cv);
-                for (int64_t j = j0; j < j1; j += 4) {
-                    float kk[4], vv[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {      // (loads first: four rows in flight)
-                        const bool in = j + i < j1;
-                        kk[i] = in ? ld(tt + i, ck) : 0.f;
-                        vv[i] = in ? ld(tt + i, cv) : 0.f;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float zk = fmaf(wk[2], kk[i], fmaf(wk[1], k1, wk[0] * k2));
-                        const float zv = fmaf(wv[2], vv[i], fmaf(wv[1], v1, wv[0] * v2));
-                        if (j + i < j1) dst[j + i] = __float2bfloat16_rn(zk * zv);
-                        k2 = k1; k1 = kk[i]; v2 = v1; v1 = vv[i];
-                    }
-                    tt += 4;
-                }
-            }
-            if (a.fir_state && n3 > 0) {
-                for (int m = lane; m < 3 * CH; m += 32) {
-                    int64_t q0, q1, q2;
-                    map.get((int64_t)g * CH + m % CH, q0, q1, q2);
-                    const int64_t col = m < CH ? q0 : m < 2 * CH ? q1 : q2;
-                    for (int64_t j = 0; j < n3; ++j)
-                        a.fir_state[(st.b * 3 * a.D + col) * n3 + j] = ub[(L - n3 + j) * a.u_stride_l + col];
-                }
-            }
-        }
-    }
-}
-
 // SWAP: interleaved layout with the q and k roles exchanged (the planar layouts exchange their TMA columns instead).
 template <bool INTERLEAVED, bool SWAP>
 __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Args a) {
@@ -230,8 +161,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     auto in_empty = [&](int st) { return bar_u + 16u * (uint32_t)st + 8u; };
     constexpr uint32_t BB = IN_STAGES * 2;
     auto kv_full = [&](int sl) { return bar_u + 8u * (BB + (uint32_t)sl); };
-    // slot_free: the chunk in this slot is no longer needed.  Five arrivals: the four epilogue warps (k*v rows of the skip
-    // term and the q tile read) and the MMA warp's commit behind the MMAs of the next chunk that read the k*v tile.
+    // slot_free: the chunk in this slot is no longer needed.  Six arrivals: the four epilogue warps (k*v rows of the skip
+    // term and the q tile read), the cache warp, and the MMA warp's commit behind the MMAs of the next chunk that read
+    // the k*v tile.
     auto slot_free = [&](int sl) { return bar_u + 8u * (BB + 2 + (uint32_t)sl); };
     auto d_full = [&](int sl) { return bar_u + 8u * (BB + 4 + (uint32_t)sl); };
     auto d_empty = [&](int sl) { return bar_u + 8u * (BB + 6 + (uint32_t)sl); };
@@ -255,7 +187,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     if (tid == 0) {
         for (int st = 0; st < IN_STAGES; ++st) { mbar_init(in_full(st), NTMA); mbar_init(in_empty(st), NFE / 2); }
         for (int sl = 0; sl < 2; ++sl) {
-            mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 5); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
+            mbar_init(kv_full(sl), NFE); mbar_init(slot_free(sl), 6); mbar_init(d_full(sl), 1); mbar_init(d_empty(sl), 4);
             mbar_init(a_ready(sl), 4); mbar_init(taps_ready(sl), 4);
         }
         fence_mbar_init();
@@ -635,7 +567,100 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             }
         }
     } else if (warp == W_STATE) {
-        if (a.fir_state || a.inner_state) write_caches(a, nmine, lane);
+        // ======== prefill caches ======================================================================
+        // fir_state[b, c, :] = u[b, L-n3:L, c] (n3 = min(L, 2)): a copy of a few input words, made when the item starts.
+        // inner_state[b, d, :] = bf16(kv[b, d, L-ns:L]) (ns = min(L, K-1)): read back from the k*v tiles the front end
+        // publishes -- this warp takes part in every chunk's hand-over (it waits for the tile and is one of the
+        // arrivals that free its slot) and touches only the chunks that hold the last ns rows of a sequence, the halo
+        // chunk included.  With history rows in front of u both caches are always full.  Exactly one stream of a
+        // (batch, group) ends its sequence.  lane = row of the tile: the stores of a channel run along time.
+        const int64_t L = a.L;
+        const int ns = (a.hist > 0 || L >= K - 1) ? K - 1 : (int)L;
+        const int n3 = (a.hist > 0 || L >= 2) ? 2 : (int)L;
+        bool ok = true;
+        for (int t = 0; t < nmine && ok; ++t) {
+            const int g = item_group(t);
+            int tr1[NS];          // rows [tr1 - ns, tr1), relative to the stream's first row, feed inner_state
+            int sb[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                const Stream st = stream_of(a, item_quad(t), s);
+                sb[s] = (int)st.b;
+                tr1[s] = (st.active && st.te == L) ? (int)(L - st.ts) : -(1 << 29);
+            }
+            // the input words of fir_state are requested now (volatile: issued where they stand) and stored after the
+            // item's first hand-over, so that the round trip to memory never holds up a slot
+            uint16_t fsv[NS][3];
+            auto fs_col = [&](int m) {      // m-th of the group's 3 x 16 packed columns times n3 rows -> packed column
+                const QkvMap map{a.layout, 0, a.D, a.hd};
+                int64_t pc[3];
+                map.get((int64_t)g * CH + (m / n3) % CH, pc[0], pc[1], pc[2]);
+                return m / n3 < CH ? pc[0] : m / n3 < 2 * CH ? pc[1] : pc[2];
+            };
+            if (a.fir_state && n3 > 0) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    if (tr1[s] <= 0) continue;
+                    const uint16_t* ub = reinterpret_cast<const uint16_t*>(a.u) + (int64_t)sb[s] * a.u_stride_b;
+#pragma unroll
+                    for (int i = 0; i < 3; ++i) {
+                        const int m = lane + 32 * i;
+                        fsv[s][i] = 0;
+                        if (m < 3 * CH * n3)
+                            asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(fsv[s][i]) : "l"(ub + (L - n3 + m % n3) * a.u_stride_l + fs_col(m)));
+                    }
+                }
+            }
+            for (int k = 0; k < nchunk; ++k, ++cc) {
+                const int slot = cc & 1;
+                if (!mbar_wait(kv_full(slot), (cc >> 1) & 1u, 18)) { ok = false; break; }
+                const int rel0 = (k - 1) * CHUNK;
+                if (a.inner_state) {
+#pragma unroll 1
+                    for (int s = 0; s < NS; ++s) {
+                        int t1 = tr1[0], b1 = sb[0];
+#pragma unroll
+                        for (int x = 1; x < NS; ++x)
+                            if (s == x) { t1 = tr1[x]; b1 = sb[x]; }
+                        if (rel0 + CHUNK <= t1 - ns || rel0 >= t1) continue;
+                        __nv_bfloat16* dst = a.inner_state + ((int64_t)b1 * a.D + (int64_t)g * CH) * ns;
+#pragma unroll 1
+                        for (int r = lane; r < CHUNK; r += 32) {
+                            const int rel = rel0 + r;
+                            if (rel < t1 - ns || rel >= t1) continue;
+                            const uint8_t* row = smp(OFF_SLOTS + slot * SLOT_BYTES) + r * 128;
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const uint4 k4 = *reinterpret_cast<const uint4*>(row + (((2 * s + hf) ^ (r & 7)) << 4));
+                                const uint32_t kw[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float v0, v1;
+                                    up2(unpack_f16(kw[j]), v0, v1);
+                                    __nv_bfloat16* d0 = dst + (int64_t)(8 * hf + 2 * j) * ns + (rel - (t1 - ns));
+                                    d0[0] = __float2bfloat16_rn(v0 * KV_UNSCALE);
+                                    d0[ns] = __float2bfloat16_rn(v1 * KV_UNSCALE);
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(slot_free(slot));
+                if (k == 0 && a.fir_state && n3 > 0) {
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) {
+                        if (tr1[s] <= 0) continue;
+                        uint16_t* fs = reinterpret_cast<uint16_t*>(a.fir_state) + (int64_t)sb[s] * 3 * a.D * n3;
+#pragma unroll
+                        for (int i = 0; i < 3; ++i) {
+                            const int m = lane + 32 * i;
+                            if (m < 3 * CH * n3) fs[fs_col(m) * n3 + m % n3] = fsv[s][i];
+                        }
+                    }
+                }
+            }
+        }
     }
 
     // ---------------- teardown -------------------------------------------------------------------

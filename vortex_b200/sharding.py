@@ -77,19 +77,22 @@ def shard_block(params: Dict[str, Optional[torch.Tensor]], D: int, G: int, world
     return out
 
 
-def gather_channels(y_shard: torch.Tensor, group=None, widths=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gather_channels(y_shard: torch.Tensor, group=None, widths=None, out: Optional[torch.Tensor] = None,
+                    concat: bool = True) -> torch.Tensor:
     """All-gather the block outputs [B, L, D_r] of all ranks along the channel axis (the one collective at the
     shard boundary; NCCL over NVLink on GPUs, gloo in the CPU tests).
 
     ``widths``: the channel counts D_r of all ranks, e.g. from ``channel_range``; when omitted they are
-    exchanged first (a small collective plus a host read).  Equal shards are gathered in place; unequal ones
-    (``channel_range`` hands out whole filter groups, so G % world != 0 gives shards that differ by one group)
-    are padded to the widest shard for the exchange and cut back afterwards -- a collective with mismatched
-    sizes across ranks is undefined on NCCL.  ``out``: optional [world, B, L, D_max] receive buffer to reuse."""
+    exchanged first (a small collective plus a host read).  Unequal shards (``channel_range`` hands out whole filter
+    groups, so G % world != 0 gives shards that differ by one group) are padded to the widest shard for the
+    exchange and cut back afterwards -- a collective with mismatched sizes across ranks is undefined on NCCL.
+    ``out``: optional [world, B, L, D_max] receive buffer to reuse.  ``concat=False`` returns that rank-major
+    buffer as it arrived (no further copy; a replicated projection can contract it block by block, and only
+    ``[r, ..., :widths[r]]`` of each block is meaningful); the default concatenates to [B, L, D]."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
     if world == 1:
-        return y_shard
+        return y_shard if concat else y_shard[None]
     if widths is None:
         mine = torch.tensor([y_shard.shape[-1]], dtype=torch.int64, device=y_shard.device)
         allw = [torch.empty_like(mine) for _ in range(world)]
@@ -109,4 +112,6 @@ def gather_channels(y_shard: torch.Tensor, group=None, widths=None, out: Optiona
         raise ValueError(f"out must be a contiguous {shape} tensor of the shard's dtype")
     # (the receive buffer is handed over in its "concatenated along dim 0" form, which every backend accepts)
     dist.all_gather_into_tensor(out.view((world * send.shape[0],) + tuple(send.shape[1:])), send, group=group)
+    if not concat:
+        return out
     return torch.cat([out[r, ..., :widths[r]] for r in range(world)], dim=-1)
