@@ -9,9 +9,10 @@ accumulation, 128-tap filters shared by groups of 16 channels, featurizer and ga
 caches written (seeded synthetic data).  A step is one pass of the fused block over the whole batch.
 With N > 1 the SAME problem is cut into N channel shards (strong scaling: rank r owns the hidden channels
 `sharding.channel_range(D, G, N, r)`; decode workloads cut the batch instead).  Channels are independent, so
-the block itself needs no exchange; the step then all-gathers the block output over NCCL (the boundary a
-replicated output projection needs) inside the timed region, and the line reports the kernel-only and the
-collective's share next to it.  `--scaling weak` gives every rank a full-width problem of its own instead.
+the block itself needs no exchange and its output stays sharded, as a row-parallel output projection
+consumes it; the all-gather over NCCL that a replicated projection would need instead is measured in the
+same run and reported under `collective`, alone and behind the kernel.  `--scaling weak` gives every rank a
+full-width problem of its own instead.
 
 Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM; `e2e` goes
 through the public API with pinned host buffers, host<->device copies inside the timed region.
@@ -41,6 +42,17 @@ WORKLOADS = {
                name="hyena_se_prefill B=4 L=8192 D=4096 bf16 (featurizer3 + gate + 7-tap grouped FIR + gate)"),
     "li": dict(B=1, L=131072, D=4096, G=256, K=0, io="bf16", seed=2,
                name="hyena_li_prefill B=1 L=131072 D=4096 bf16 (featurizer3 + gate + 16-pole modal filter + gate)"),
+    # the same block through the drop-in engine, as the reference's HyenaCascade.parallel_forward calls it
+    # (model.py:233-291): parallel_fir(gate=False) -> z [B, 3D, L], then parallel_fir(gate=True) on it -> y [B, D, L].
+    # Per hidden channel and token: featurizer 6 bytes in + 6 out, gate-conv-gate 6 in + 2 out.  Plain q | k | v split
+    # (a model with config.interleave adds its own interleave() copy between the two calls).
+    "mr_dropin": dict(B=4, L=8192, D=4096, G=256, K=128, io="bf16", seed=1, dropin=True,
+                      name="hyena_mr_prefill through the drop-in engine B=4 L=8192 D=4096 bf16 (parallel_fir featurizer + "
+                           "parallel_fir gate / 128-tap grouped FIR / gate, z [B,3D,L] materialised between them)"),
+    # configuration 1: the reference's own CPU-runnable case, fp32, small enough for L2 (25 MB per step): the steps
+    # replay from a CUDA graph with a buffer larger than L2 written between them
+    "se_cfg1": dict(B=1, L=2048, D=768, G=48, K=7, io="f32", seed=0, layout="split",
+                    name="hyena_se_prefill B=1 L=2048 D=768 fp32 (configuration 1: featurizer3 + gate + 7-tap grouped FIR + gate)"),
     # the long-filter layer as Evo 2 has it (configs/evo2-7b-8k.yml: hcl_filter_groups == hidden size): 16 real poles
     # per CHANNEL, at the 7B prefill shape of configuration 2
     "li_pc": dict(B=4, L=8192, D=4096, G=4096, K=0, io="bf16", seed=2, real_poles=True,
@@ -74,7 +86,8 @@ def _peaks():
     return 6650.0, "fallback"
 
 
-def make_inputs(w, device, dtype=torch.bfloat16):
+def make_inputs(w, device, dtype=None):
+    dtype = dtype or (torch.float32 if w.get("io") == "f32" else torch.bfloat16)
     g = torch.Generator().manual_seed(w["seed"])
     B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
     p = {}
@@ -166,7 +179,9 @@ def algorithmic_bytes(w):
     B, L, D, K = w["B"], w["L"], w["D"], w["K"]
     if w.get("cc1d"):
         return 12 * B * D * L
-    n = 8 * B * D * L
+    if w.get("dropin"):
+        return 20 * B * D * L + (B * 3 * D * 2 * 2 + B * D * (K - 1) * 2 if w.get("caches") else 0)
+    n = (16 if w.get("io") == "f32" else 8) * B * D * L
     if w.get("caches"):
         n += B * 3 * D * 2 * 2
         n += B * D * (K - 1) * 2 if K > 0 else B * D * 16 * 4 * (1 if w.get("real_poles") else 2)
@@ -200,6 +215,17 @@ def run_block(name, pc, u=None):
     if name == "cc1d":
         return hyena_ops.causal_conv1d_fn(u.transpose(1, 2), pc["w3"].reshape(-1, 3))
     caches = bool(pc.get("caches"))
+    if name == "mr_dropin":
+        import torch.nn.functional as F
+        eng, D, G = pc["engine"], pc["u"].shape[-1] // 3, pc["h"].shape[0]
+        dims = (D, 1, D, 16, G)
+        ip = True if caches else None
+        z, _ = eng.parallel_fir(F.conv1d, u, pc["w3"], None, u.shape[1], dims=dims, gate=False, inference_params=ip)
+        y, _ = eng.parallel_fir(F.conv1d, z, pc["hx"], pc["Dp"], u.shape[1], dims=dims, gate=True, gated_bias=True,
+                                dim_last=False, fir_length=pc["h"].shape[-1], inference_params=ip, groups=G)
+        return y
+    if name == "se_cfg1":
+        return hyena_ops.hyena_se_fwd(u, pc["w3"], None, pc["h"], layout="split", want_state=caches)[0]
     if name == "mr":
         return hyena_ops.hyena_mr_fwd(u, pc["w3"], None, pc["h"], pc["Dp"], want_state=caches)[0]
     if name == "se":
@@ -257,10 +283,10 @@ def cpu_baseline(name, w, steps=1, warmup=1, cap_s=25.0):
     except (AttributeError, RuntimeError):
         pass
     torch.manual_seed(0)
-    Ds = {"mr": 256, "se": 256, "li": 64, "li_pc": 64, "cc1d": 256}[name]
+    Ds = min(w["D"], {"mr": 256, "se": 256, "li": 64, "li_pc": 64, "cc1d": 256, "mr_dropin": 256, "se_cfg1": 768}[name])
     B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
     Gs = max(1, G * Ds // D)
-    dt = torch.bfloat16
+    dt = torch.float32 if w.get("io") == "f32" else torch.bfloat16
     u = torch.randn(B, L, 3 * Ds).to(dt)
     w3 = (torch.randn(3 * Ds, 1, 3) / 3 ** 0.5).to(dt)
     if w.get("cc1d"):
@@ -296,7 +322,7 @@ def cpu_baseline(name, w, steps=1, warmup=1, cap_s=25.0):
     best = sum(times) / len(times)
     full = best * (D / Ds)
     return {"value": B * L / full, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-            "extrapolated": True, "slice_ms": best * 1e3, "slice_channels": Ds, "scale": D / Ds,
+            "extrapolated": Ds != D, "slice_ms": best * 1e3, "slice_channels": Ds, "scale": D / Ds,
             "sample": f"{Ds} of {D} channels (B={B}, L={L}) measured ({best * 1e3:.1f} ms, mean of {len(times)} passes) "
                       f"and scaled by {D // Ds}x (channels are independent); "
                       f"torch {torch.__version__} F.conv1d/torch.fft on {os.cpu_count()} host cpus"}, full
@@ -310,8 +336,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mr", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
-                    help="N > 1: strong = one problem cut into N channel (prefill) or batch (decode) shards, block output "
-                         "all-gathered inside the timed region; weak = a full-size problem per rank, no collective")
+                    help="N > 1: strong = one problem cut into N channel (prefill) or batch (decode) shards (the all-gather "
+                         "of the block output is measured apart); weak = a full-size problem per rank")
     ap.add_argument("--no-caches", action="store_true", help="prefill workloads: do not write the prefill caches")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small cases for profiling)")
     ap.add_argument("--seq", type=int, default=0, help="override the sequence length (small cases for profiling)")
@@ -357,7 +383,8 @@ def main():
                "per sequence, so there is no collective on the data path")
     else:
         how = (f"strong, channel shards: the {full['D']} hidden channels are cut into {world} shards of whole filter "
-               f"groups ({w['D']} on this rank); the block needs no exchange, the step then all-gathers y over NCCL")
+               f"groups ({w['D']} on this rank); the block needs no exchange and y stays sharded for a row-parallel "
+               "output projection (the all-gather a replicated projection would need is measured under `collective`)")
     config = {"workload": full["name"], "seed": full["seed"], "qkv_layout": "interleaved", "sharding": how,
               "caches": bool(w["caches"]),
               "l2": (f"{step_bytes / 1e6:.0f} MB of caches and tokens per step and rank" +
@@ -375,7 +402,7 @@ def main():
         cb, _ = cpu_baseline(a.workload, full, steps=max(1, a.steps), warmup=max(1, a.warmup), cap_s=0)
         line = {"impl": "reference", "metric": "hyena_prefill_throughput", "value": cb["value"], "unit": "tok/s",
                 "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": cb["slice_ms"],
-                "ms_per_step_full_width": cb["slice_ms"] * cb["scale"], "extrapolated": True,
+                "ms_per_step_full_width": cb["slice_ms"] * cb["scale"], "extrapolated": cb["extrapolated"],
                 "higher_is_better": True, "scaling": "strong" if strong or world == 1 else "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic", "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -420,6 +447,10 @@ def main():
             pc[key] = [{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in c.items()} for c in pc[key]]
     pc["caches"] = w["caches"]
     from vortex_b200 import ops
+    if w.get("dropin"):
+        from vortex_b200 import HyenaInferenceEngine
+        pc["engine"] = HyenaInferenceEngine()
+        pc["hx"] = pc["h"].repeat_interleave(w["D"] // w["G"], 0)       # what the caller hands over (model.py:261-262)
 
     gather = None
     if strong and prefill:
@@ -434,8 +465,10 @@ def main():
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # written between steps: evicts the 126 MB L2
 
     def step():
-        y = run_block(a.workload, pc)
-        return gather(y) if gather is not None else y
+        return run_block(a.workload, pc)
+
+    def step_gathered():
+        return gather(run_block(a.workload, pc))
 
     for _ in range(a.warmup):
         y = step()
@@ -488,17 +521,23 @@ def main():
             ms = timed(step, a.steps)
     ms_step = ms / a.steps
     value = tokens / (ms_step * 1e-3)
-    kernel_only, collective = None, None
+    collective = None
     if gather is not None:
-        # the same steps without the collective, and the collective alone (same buffers)
-        ms_k = timed(lambda: run_block(a.workload, pc), a.steps) / a.steps
+        # The block output stays sharded in `value`: a row-parallel output projection consumes its rank's channels as
+        # they are, and the exchange that follows (an all-reduce of the projection's result) belongs to that GEMM.  The
+        # other boundary -- a replicated projection, which needs y gathered on every rank -- is measured here on the
+        # same buffers: the all-gather alone, and the step with the all-gather behind the kernel.
+        step_gathered()
+        ms_g = timed(step_gathered, a.steps) / a.steps
         y_sh = run_block(a.workload, pc)
         ms_c = timed(lambda: gather(y_sh), a.steps) / a.steps
-        kernel_only = {"ms_per_step": ms_k, "value": tokens / (ms_k * 1e-3), "unit": "tok/s",
-                       "frac_of_hbm_peak_per_rank": step_bytes / (ms_k * 1e-3) / 1e9 / _peaks()[0]}
-        collective = {"op": "all_gather", "backend": "nccl", "bytes_received_per_rank": recv.numel() * 2 * (world - 1) // world,
-                      "ms": ms_c, "overlapped": False,
-                      "limiter": "collective" if ms_c > ms_k else "kernel"}
+        nrecv = recv.numel() * 2 * (world - 1) // world
+        collective = {"op": "all_gather", "backend": "nccl", "in_value": False, "bytes_received_per_rank": nrecv,
+                      "ms": ms_c, "recv_GBps_per_rank": nrecv / (ms_c * 1e-3) / 1e9,
+                      "ms_per_step_kernel_then_collective": ms_g, "value_with_collective": tokens / (ms_g * 1e-3),
+                      "limiter": "collective" if ms_c > ms_step else "kernel",
+                      "note": "every rank has to receive (N-1)/N of y: at 770 GB/s per direction that alone takes "
+                              f"{nrecv / 770e9 * 1e3:.3f} ms per step, against {ms_step:.3f} ms of kernel"}
 
     # ---- end to end: pinned host input -> device -> kernel -> pinned host output, every step
     e2e = None
@@ -554,8 +593,7 @@ def main():
         return
     peak, peak_kind = _peaks()
     launches_per_step = LAUNCHES.get(a.workload, 1)
-    ms_kernel = kernel_only["ms_per_step"] if kernel_only else ms_step
-    achieved = step_bytes / (ms_kernel * 1e-3) / 1e9
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
     traffic = NCU_TRAFFIC.get(a.workload)
     if traffic is not None:
         traffic = traffic * step_bytes / algorithmic_bytes(dict(WORKLOADS[a.workload], caches=w["caches"]))
@@ -563,14 +601,14 @@ def main():
         "metric": "hyena_decode_throughput" if w.get("decode") else "hyena_prefill_throughput", "value": value, "unit": "tok/s", "n_gpus": world, "steps": a.steps,
         "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak" if (world > 1 and not strong) else "strong", "vs_baseline": None,
-        "dtype": w.get("io_name", "bf16"), "data": "synthetic", "config": config, "clocks": cs.summary(),
+        "dtype": "f32" if w.get("io") == "f32" else "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
         "gpu_launches": launches_per_step * a.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": step_bytes,
                      "note": "per rank: achieved = algorithmic bytes of the rank's share / kernel time per step (the "
                              f"collective, if any, is reported apart); one step = {launches_per_step} kernel launch(es)"},
-        "kernel_only": kernel_only, "collective": collective,
+        "collective": collective,
         "e2e": e2e,
     }
     if not a.no_cpu_baseline and world == 1 and not w.get("decode"):
@@ -581,7 +619,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload
-LAUNCHES = {"mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
+LAUNCHES = {"mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch

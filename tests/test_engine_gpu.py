@@ -510,3 +510,121 @@ def test_inner_hyena_se_layouts(io, B, G, dg, L, K):
     assert torch.equal(y4, y2)
     with pytest.raises(NotImplementedError):
         hyena_ops.inner_hyena_se(xc, kc, qc, h.cuda(), output_layout="lbd")
+
+
+# ------------------------------------------------------------------ drop-in parallel_fir on the tensor-core kernel
+# B, L, D, G, K, layout, heads, flip, bias
+TC_CASES = [
+    (4, 1000, 256, 16, 128, "split", 1, False, True),        # one box per operand covers the four batch elements
+    (3, 2048, 64, 4, 128, "split", 1, False, True),          # batch quad with an idle stream
+    (5, 520, 128, 8, 7, "split", 1, True, False),            # two batch quads, the second mostly idle; q/k swapped
+    (1, 8192, 64, 4, 128, "split", 1, False, True),          # one sequence: streams are time segments
+    (2, 1504, 128, 8, 64, "column_split", 4, False, True),   # per-head column split (head size 32)
+    (2, 8, 32, 2, 7, "split", 1, False, False),              # shortest length the path takes
+    (1, 136, 32, 1, 128, "split", 1, False, True),           # L barely longer than the filter; 32 channels per filter
+    (2, 96, 32, 2, 128, "split", 1, False, True),            # L < K
+]
+
+
+@pytest.mark.parametrize("B,L,D,G,K,layout,heads,flip,with_bias", TC_CASES)
+def test_parallel_fir_tensor_core_path(B, L, D, G, K, layout, heads, flip, with_bias):
+    """engine.parallel_fir(gate=True) with bf16 operands and filters shared by blocks of 16 channels runs on tcgen05
+    (the caller's per-channel expansion of the filters is undone from its ``groups`` argument).  It rounds where the
+    reference rounds, so it has to agree with the oracle's mirrored evaluation like the general kernel does -- and
+    with that kernel itself (taken here by handing the taps over in fp32) up to last-place flips."""
+    from vortex_b200 import HyenaInferenceEngine, ops
+    p = make_block(81, B, L, D, G, K, "bf16")
+    g = torch.Generator().manual_seed(3)
+    z_pre = torch.randn(B, 3 * D, L, generator=g).bfloat16()
+    Dp = (0.5 * torch.randn(D, generator=g)).bfloat16() if with_bias else None
+    eng = HyenaInferenceEngine(hyena_flip_x1x2=flip)
+    dims = (D, heads, D // heads, 16, G)
+    hx = p["h"].repeat_interleave(D // G, 0).cuda()
+    kw = dict(dims=dims, gate=True, gated_bias=K >= 128 or with_bias, dim_last=False,
+              column_split_hyena=layout == "column_split", fir_length=K, inference_params=True)
+    y, st = eng.parallel_fir(F.conv1d, z_pre.cuda(), hx, None if Dp is None else Dp.cuda(), L, groups=G, **kw)
+    ops.device_status()
+    ref, st_ref = O.gate_conv_gate(to_np(z_pre), to_np(p["h"]), None if Dp is None else to_np(Dp), D, K, io="bf16",
+                                   layout=layout, num_heads=heads, flip_x1x2=flip, gated_bias=K >= 128 or with_bias)
+    assert y.shape == (B, D, L) and y.dtype == torch.bfloat16
+    check(f"tensor-core parallel_fir vs mirrored oracle (B={B} L={L} K={K} {layout})", rel_l2(y, ref), TOL["bf16"])
+    assert st.shape == st_ref.shape and np.array_equal(to_np(st), st_ref.astype(np.float32))
+    # the general kernel on the same data (fp32 taps keep it off the tensor-core path)
+    y2, st2 = eng.parallel_fir(F.conv1d, z_pre.cuda(), hx.float(), None if Dp is None else Dp.cuda(), L, groups=G, **kw)
+    check(f"tensor-core vs general kernel (B={B} L={L} K={K})", rel_l2(y, y2), 2e-4)
+    assert torch.equal(st, st2)
+    # without the groups hint the expanded filters are taken as they come (one filter per channel: general kernel)
+    y3, _ = eng.parallel_fir(F.conv1d, z_pre.cuda(), hx, None if Dp is None else Dp.cuda(), L, **kw)
+    assert torch.equal(y3, y2)
+    # rows that differ inside a block: the hint is not trusted
+    hbad = hx.clone()
+    hbad[1] += 1
+    y4, _ = eng.parallel_fir(F.conv1d, z_pre.cuda(), hbad, None if Dp is None else Dp.cuda(), L, groups=G, **kw)
+    y5, _ = eng.parallel_fir(F.conv1d, z_pre.cuda(), hbad.float(), None if Dp is None else Dp.cuda(), L, **kw)
+    assert torch.equal(y4, y5)
+
+
+def test_parallel_fir_tensor_core_full_size():
+    """Configuration 2 through the drop-in call (B=4, L=8192, D=4096, 128 taps): oracle on a slice of channels, and
+    exact integer data over the whole tensor (pins Toeplitz expansion, segment seams, box geometry, channel maps)."""
+    from vortex_b200 import HyenaInferenceEngine, ops
+    B, L, D, G, K = 4, 8192, 4096, 256, 128
+    g = torch.Generator().manual_seed(12)
+    eng = HyenaInferenceEngine()
+    dims = (D, 1, D, 16, G)
+    kw = dict(dims=dims, gate=True, gated_bias=True, dim_last=False, fir_length=K, inference_params=True, groups=G)
+    z = torch.randint(-2, 3, (B, 3 * D, L), generator=g).bfloat16()
+    h = torch.zeros(G, 1, K)
+    for pos in (0, 1, 77, K - 1):
+        h[:, 0, pos] = torch.randint(0, 2, (G,), generator=g).float() * 2 - 1
+    Dp = torch.randint(-1, 2, (D,), generator=g).bfloat16()
+    hx = h.bfloat16().repeat_interleave(D // G, 0).cuda()
+    y, st = eng.parallel_fir(F.conv1d, z.cuda(), hx, Dp.cuda(), L, **kw)
+    ops.device_status()
+    for d0 in (0, 2000, 4080):
+        sl = slice(d0, d0 + 16)
+        zz = torch.cat([z[:, d0:d0 + 16], z[:, D + d0:D + d0 + 16], z[:, 2 * D + d0:2 * D + d0 + 16]], 1)
+        ref, st_ref = O.gate_conv_gate(to_np(zz), to_np(h[d0 // 16:d0 // 16 + 1]), to_np(Dp[sl]), 16, K, io="bf16",
+                                       gated_bias=True)
+        assert np.array_equal(to_np(y[:, sl]), ref.astype(np.float32)), d0
+        assert np.array_equal(to_np(st[:, sl]), st_ref.astype(np.float32))
+    p = make_block(1, B, 8, D, G, K, "bf16")          # only the filters of the benchmark configuration are taken
+    zr = torch.randn(B, 3 * D, L, generator=g).bfloat16()
+    hx = p["h"].repeat_interleave(D // G, 0).cuda()
+    y, _ = eng.parallel_fir(F.conv1d, zr.cuda(), hx, Dp.cuda(), L, **kw)
+    d0 = 1024
+    zz = torch.cat([zr[::3, d0:d0 + 32], zr[::3, D + d0:D + d0 + 32], zr[::3, 2 * D + d0:2 * D + d0 + 32]], 1)
+    ref, _ = O.gate_conv_gate(to_np(zz), to_np(p["h"][d0 // 16:d0 // 16 + 2]), to_np(Dp[d0:d0 + 32]), 32, K, io="bf16",
+                              gated_bias=True)
+    check("tensor-core parallel_fir, configuration 2, vs mirrored oracle", rel_l2(y[::3, d0:d0 + 32], ref), TOL["bf16"])
+
+
+@pytest.mark.parametrize("io,B,L,C,K,with_bias,with_mask", [
+    ("bf16", 2, 264, 200, 3, True, True),      # channels not a multiple of the tile, ragged last time tile
+    ("bf16", 1, 8, 48, 3, False, False),       # one short tile
+    ("f16", 3, 1024, 192, 4, True, False),
+    ("bf16", 2, 4096, 96, 3, False, False),
+])
+def test_featurizer_tma_kernel(eng, io, B, L, C, K, with_bias, with_mask):
+    """The featurizer's 16-bit path (TMA box in, swizzled [channel][time] tile, TMA boxes out) against the mirrored
+    oracle, and against the general kernel on the same data (reached through a view whose rows are not 16-byte
+    aligned): same arithmetic, identical bits."""
+    g = torch.Generator().manual_seed(77)
+    u = torch.randn(B, L, C, generator=g).to(DT[io])
+    w = (torch.randn(C, 1, K, generator=g) / K ** 0.5).to(DT[io])
+    bias = torch.randn(C, generator=g).to(DT[io]) if with_bias else None
+    mask = (torch.rand(B, L, generator=g) > 0.2).to(DT[io]) if with_mask else None
+    cu = lambda t: None if t is None else t.cuda()  # noqa: E731
+    dims = (C // 3, 1, C // 3, 16, C // 3)
+    z, st = eng.parallel_fir(F.conv1d, cu(u), cu(w), cu(bias), L, dims=dims, gate=False, fir_length=K,
+                             inference_params=True, padding_mask=cu(mask))
+    ref, st_ref = O.featurizer(to_np(u), to_np(w), None if bias is None else to_np(bias), io=io,
+                               padding_mask=None if mask is None else to_np(mask))
+    assert z.shape == (B, C, L) and z.dtype == DT[io]
+    check(f"featurizer TMA kernel vs mirrored oracle ({io} L={L} C={C})", rel_l2(z, ref), 1e-4)
+    assert np.array_equal(to_np(st), st_ref.astype(np.float32))
+    wide = torch.zeros(B, L, C + 1, dtype=DT[io]).cuda()
+    wide[..., 1:] = cu(u)
+    z2, st2 = eng.parallel_fir(F.conv1d, wide[..., 1:], cu(w), cu(bias), L, dims=dims, gate=False, fir_length=K,
+                               inference_params=True, padding_mask=cu(mask))
+    assert torch.equal(z, z2) and torch.equal(st, st2)

@@ -75,6 +75,31 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int64_t dtype, int64_t cols
     return VTX_OK;
 }
 
+int make_tmap_bhdl(CUtensorMap* out, const void* base, int64_t dtype, int64_t L, int64_t head_dim, int64_t heads,
+                   int64_t batch, int64_t stride_d, int64_t stride_h, int64_t stride_b, int box_cols, int box_rows,
+                   int box_batch, const char* who) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(VTX_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled entry point unavailable", who);
+    const int64_t es = dtype_size(dtype);
+    if (heads <= 1) { heads = 1; stride_h = stride_d * head_dim; }      // never stepped: any legal pitch
+    if (batch <= 1) { batch = 1; stride_b = stride_h * heads; }
+    if (reinterpret_cast<uintptr_t>(base) % 16 || (stride_d * es) % 16 || (stride_h * es) % 16 || (stride_b * es) % 16 ||
+        stride_d <= 0 || stride_h <= 0 || stride_b <= 0)
+        return fail(VTX_ERR_ALIGNMENT, "%s: base address and channel / head / batch pitch must be positive multiples of 16 bytes", who);
+    if (box_cols * es != 128) return fail(VTX_ERR_ALIGNMENT, "%s: a swizzled box row is 128 bytes", who);
+    CUtensorMapDataType dt = dtype == VTX_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : dtype == VTX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cuuint64_t dims[4] = {(cuuint64_t)L, (cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)(stride_d * es), (cuuint64_t)(stride_h * es), (cuuint64_t)(stride_b * es)};
+    cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, (cuuint32_t)box_batch};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(VTX_ERR_BAD_ARG, "%s: cuTensorMapEncodeTiled failed with CUresult %d", who, (int)r);
+    return VTX_OK;
+}
+
 }  // namespace vtx
 
 extern "C" int vtx_device_status(void) {

@@ -25,6 +25,8 @@
 // and its last K-1 samples of k*v read back from the tiles the front end publishes).  A front-end lane owns one channel pair of one stream and walks 16 rows per chunk in two register
 // batches, the next batch fetched before the current one is computed; the four streams of a warp are staged one
 // row apart in shared memory so that the lanes of a warp read distinct banks.  All waits are bounded.
+#include <cstdint>
+
 #include "tma.cuh"
 #include "umma.cuh"
 
@@ -702,12 +704,20 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     }
     VTX_REQUIRE(p->layout == VTX_QKV_INTERLEAVED || (p->D * 2) % 16 == 0, VTX_ERR_ALIGNMENT,
                 "fused_fir: D*itemsize must be a multiple of 16 bytes for this q/k/v layout");
-    // segments: enough work items (group x stream quads) for ~6 rounds over the SMs, whole chunks each
+    // Time segments: a sequence is cut into nseg segments of whole chunks, a work item is one group x four streams
+    // (batch element x segment), the items are dealt round-robin to one persistent CTA per SM.  Every item pays one
+    // halo chunk, and the launch lasts as long as the CTA with the most chunks: pick the segment length that makes
+    // that CTA's chunk count smallest (ties: fewer items).
     const int64_t nchunks_total = ceil_div<int64_t>(p->L, CHUNK);
-    int64_t nseg = 1;
-    while (p->G * ceil_div<int64_t>(p->B * nseg, NS) < (int64_t)kNumSMs * 6 && nseg * 2 <= nchunks_total &&
-           ceil_div<int64_t>(nchunks_total, nseg * 2) >= 8)
-        nseg *= 2;
+    int64_t nseg = 1, best_cost = INT64_MAX;
+    for (int64_t seg_chunks = nchunks_total; seg_chunks >= 1; --seg_chunks) {
+        const int64_t ns_ = ceil_div<int64_t>(nchunks_total, seg_chunks);
+        if (ceil_div<int64_t>(nchunks_total, ns_) != seg_chunks) continue;       // same plan as a shorter segment
+        const int64_t items = p->G * ceil_div<int64_t>(p->B * ns_, NS);
+        const int64_t cost = ceil_div<int64_t>(items, kNumSMs) * (seg_chunks + 1) * 64 + ns_;   // (+ a little per segment)
+        if (cost < best_cost) { best_cost = cost; nseg = ns_; }
+        if (seg_chunks <= 2 || items > (int64_t)kNumSMs * 64) break;            // shorter segments only add halo chunks
+    }
     a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
     a.nseg = ceil_div<int64_t>(p->L, a.seg_len);
     a.nstream = p->B * a.nseg;

@@ -104,6 +104,9 @@ __global__ void __launch_bounds__(GTHREADS) gcg_kernel(vtx_gcg_params p) {
     }
 }
 
+bool gcg_tc_shape(const vtx_gcg_params* p);                    // gcg_tc.cu (tcgen05 path)
+int gcg_tc_fwd(const vtx_gcg_params* p, cudaStream_t stream);
+
 }  // namespace vtx
 
 extern "C" int vtx_gcg_fwd(const vtx_gcg_params* p, void* stream) {
@@ -118,6 +121,9 @@ extern "C" int vtx_gcg_fwd(const vtx_gcg_params* p, void* stream) {
     VTX_REQUIRE(p->B <= 65535 && p->D <= 65535, VTX_ERR_UNSUPPORTED, "gcg: B or D too large for one launch");
     VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || p->bias, VTX_ERR_BAD_ARG, "gcg: bias mode set without a bias");
     VTX_REQUIRE(valid_dtype(p->h_dtype), VTX_ERR_BAD_ARG, "gcg: bad filter dtype");
+    // Kernel choice: bf16 I/O with bf16 filters of up to 128 taps shared by blocks of 16 channels (time-contiguous,
+    // 16-byte aligned operands) runs as a blocked-Toeplitz contraction on tensor cores; the kernel below takes the rest.
+    if (gcg_tc_shape(p)) return gcg_tc_fwd(p, (cudaStream_t)stream);
     const int Kp = (int)((p->K + GR - 1) / GR * GR);
     const size_t smem = sizeof(float) * (size_t)(Kp + GT + Kp + GR);
     dim3 grid((unsigned)ceil_div<int64_t>(p->L, GT), (unsigned)p->D, (unsigned)p->B);

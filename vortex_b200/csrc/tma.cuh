@@ -100,6 +100,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+// shared -> global tile store (bulk async group of the issuing thread); out-of-range elements are not written
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int x, int y, int z, int w) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -109,5 +126,12 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
 int make_tmap_3d(CUtensorMap* out, const void* base, int64_t dtype, int64_t cols, int64_t rows, int64_t batch,
                  int64_t row_stride, int64_t batch_stride, int box_cols, int box_rows, int swizzle_bytes,
                  const char* who);
+
+// Tensor map over a channel-first operand [batch, head, channel-in-head, time], time contiguous, the other three
+// dimensions by element strides; box = [box_batch, 1, box_rows, box_cols] with the 128-byte swizzle (box_cols * element
+// size must be 128 bytes).  Out-of-range box elements read as zero.
+int make_tmap_bhdl(CUtensorMap* out, const void* base, int64_t dtype, int64_t L, int64_t head_dim, int64_t heads,
+                   int64_t batch, int64_t stride_d, int64_t stride_h, int64_t stride_b, int box_cols, int box_rows,
+                   int box_batch, const char* who);
 
 }  // namespace vtx

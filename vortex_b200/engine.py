@@ -52,6 +52,26 @@ class HyenaInferenceEngine:
         self.ground_truth_activations_path = ground_truth_activations_path
         self.print_activations = print_activations
         self.hyena_flip_x1x2 = hyena_flip_x1x2
+        self._grouped = {}       # (storage pointer, version, shape, groups) -> bool: see _group_filters
+
+    def _group_filters(self, weight, hidden_size, groups):
+        """The caller expands grouped filters to one row per channel before the call (``repeat_interleave``,
+        model.py:261-262) and passes ``groups`` along, which the reference ignores.  The kernels want the filters
+        un-expanded -- the tensor-core path shares one Toeplitz operand among the channels of a group -- so when
+        ``groups`` says the rows repeat in blocks, and they do (checked once per weight tensor and version: one
+        device-to-host read, cached), every block is handed over as one row."""
+        if (groups is None or weight.dim() != 3 or weight.shape[0] != hidden_size or not 0 < groups < hidden_size
+                or hidden_size % groups):
+            return weight
+        key = (weight.data_ptr(), weight._version, tuple(weight.shape), int(groups))
+        ok = self._grouped.get(key)
+        if ok is None:
+            blocks = weight.detach().reshape(groups, hidden_size // groups, -1)
+            ok = bool((blocks == blocks[:, :1]).all().item())
+            if len(self._grouped) > 64:
+                self._grouped.clear()
+            self._grouped[key] = ok
+        return weight[:: hidden_size // groups] if ok else weight
 
     # ------------------------------------------------------------------ prefill: FIR paths
     def parallel_fir(
@@ -95,6 +115,7 @@ class HyenaInferenceEngine:
         else:
             taps = TAPS_XCORR
             bias_mode = BIAS_NONE if bias is None else (BIAS_GATED if gated_bias else BIAS_ADD)
+        weight = self._group_filters(weight, hidden_size, groups)
         return ops.gcg_fwd(z_pre, weight, bias, hidden_size, taps=taps, bias_mode=bias_mode,
                            layout=_layout(column_split_hyena), num_heads=num_heads, flip=self.hyena_flip_x1x2,
                            mask=padding_mask, want_state=want_state, round_kv=True)
