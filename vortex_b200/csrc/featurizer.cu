@@ -12,6 +12,7 @@
 // with the 128-byte swizzle (conflict-free for lanes on neighbouring channels), and two boxes of whole 128-byte
 // rows along time carry the tile out.  Six CTAs per SM keep ~200 KB in flight; both directions move full lines.
 #include "tma.cuh"
+#include "umma.cuh"
 
 namespace vtx {
 
@@ -79,7 +80,25 @@ constexpr int FT_OUT = FC * FTT * 2;                      // two [64 channels][6
 constexpr int FT_SMEM = 1024 + FT_OUT + (FT_IN + 127) / 128 * 128 + FC * FK * 4 + 16;
 static_assert(FT_SMEM <= 48 * 1024, "fits the default dynamic shared memory limit");
 
-template <typename T>
+// two 16-bit elements in one word <-> a packed fp32 pair (low half = first element)
+template <typename T> __device__ __forceinline__ umma::f32x2 unpack2(uint32_t w);
+template <> __device__ __forceinline__ umma::f32x2 unpack2<__nv_bfloat16>(uint32_t w) { return umma::pk2(umma::bf_lo(w), umma::bf_hi(w)); }
+template <> __device__ __forceinline__ umma::f32x2 unpack2<__half>(uint32_t w) {
+    float lo, hi;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w));
+    return umma::pk2(lo, hi);
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) { return umma::pack_bf16(lo, hi); }
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// PLAIN3: three taps, no bias, no mask (the featurizer of every shipped model configuration): a thread filters eight
+// samples of a channel PAIR with packed fp32 arithmetic, one rounding on the way out.
+template <typename T, bool PLAIN3>
 __global__ void __launch_bounds__(256) featurizer_tma_kernel(const __grid_constant__ CUtensorMap tm_in,
                                                             const __grid_constant__ CUtensorMap tm_out,
                                                             vtx_featurizer_params p) {
@@ -92,7 +111,8 @@ __global__ void __launch_bounds__(256) featurizer_tma_kernel(const __grid_consta
     const uint32_t bar = sm_u + OFF_BAR;
     const int K = (int)p.K, tid = threadIdx.x;
     const int64_t L = p.L, C = p.C;
-    const int64_t t0 = (int64_t)blockIdx.x * FTT, c0 = (int64_t)blockIdx.y * FC, b = blockIdx.z;
+    // (channel tiles are the fastest grid dimension: CTAs that run together read neighbouring pieces of the same rows)
+    const int64_t t0 = (int64_t)blockIdx.y * FTT, c0 = (int64_t)blockIdx.x * FC, b = blockIdx.z;
     if (tid == 0) {
         mbar_init(bar, 1);
         fence_mbar_init();
@@ -105,6 +125,35 @@ __global__ void __launch_bounds__(256) featurizer_tma_kernel(const __grid_consta
     }
     __syncthreads();
     if (!mbar_wait(bar, 0, 51)) return;
+    if (PLAIN3) {
+        // task = (channel pair, block of 8 samples); the lanes of a warp cover the 64 channels of a row
+        using namespace umma;
+#pragma unroll 1
+        for (int task = tid; task < (FC / 2) * (FTT / 8); task += 256) {
+            const int cp = task % (FC / 2), t8 = task / (FC / 2);
+            f32x2 wv[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) wv[j] = pk2(ws[(2 * cp) * FK + j], ws[(2 * cp + 1) * FK + j]);
+            const uint32_t src = sm_u + OFF_IN + (uint32_t)(t8 * 8 * FC * 2 + cp * 4);
+            f32x2 x[10];
+#pragma unroll
+            for (int i = 0; i < 10; ++i) {
+                uint32_t w;
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"(src + (uint32_t)(i * FC * 2)));
+                x[i] = unpack2<T>(w);
+            }
+            float lo[8], hi[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)        // same order of operations as the general kernel: identical bits
+                up2(fma2(wv[2], x[e + 2], fma2(wv[1], x[e + 1], mul2(wv[0], x[e]))), lo[e], hi[e]);
+            const uint32_t dst = sm_u + (uint32_t)((t8 / 8) * (FT_OUT / 2));
+            const int r0 = 2 * cp, r1 = 2 * cp + 1;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)(r0 * 128 + (((t8 % 8) ^ (r0 & 7)) << 4))),
+                         "r"(pack2<T>(lo[0], lo[1])), "r"(pack2<T>(lo[2], lo[3])), "r"(pack2<T>(lo[4], lo[5])), "r"(pack2<T>(lo[6], lo[7])) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)(r1 * 128 + (((t8 % 8) ^ (r1 & 7)) << 4))),
+                         "r"(pack2<T>(hi[0], hi[1])), "r"(pack2<T>(hi[2], hi[3])), "r"(pack2<T>(hi[4], hi[5])), "r"(pack2<T>(hi[6], hi[7])) : "memory");
+        }
+    } else
     // task = (channel, block of 8 samples); lanes run along channels
     for (int task = tid; task < FC * (FTT / 8); task += 256) {
         const int cc = task % FC, t8 = task / FC;
@@ -150,7 +199,7 @@ __global__ void __launch_bounds__(256) featurizer_tma_kernel(const __grid_consta
         for (int hf = 0; hf < 2; ++hf)
             if (t0 + hf * 64 < L) tma_store_3d(&tm_out, sm_u + hf * (FT_OUT / 2), (int)(t0 + hf * 64), (int)c0, (int)b);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the tile has left shared memory: the CTA may go
     }
 }
 
@@ -170,7 +219,7 @@ extern "C" int vtx_featurizer_fwd(const vtx_featurizer_params* p, void* stream) 
     const bool tma_ok = p->io_dtype != VTX_F32 && p->u_stride_c == 1 && reinterpret_cast<uintptr_t>(p->u) % 16 == 0 &&
                         p->u_stride_l % 8 == 0 && (p->B == 1 || p->u_stride_b % 8 == 0) && p->u_stride_l > 0 &&
                         reinterpret_cast<uintptr_t>(p->z) % 16 == 0 && p->L % 8 == 0 && p->L < ((int64_t)1 << 31) - 256 &&
-                        p->C < ((int64_t)1 << 31) && ceil_div<int64_t>(p->L, FTT) < ((int64_t)1 << 31);
+                        p->C < ((int64_t)1 << 31) && ceil_div<int64_t>(p->L, FTT) <= 65535;
     if (tma_ok) {
         CUtensorMap tm_in, tm_out;
         if (int rc = make_tmap_3d(&tm_in, p->u, p->io_dtype, p->C, p->L, p->B, p->u_stride_l, p->u_stride_b, FC,
@@ -178,11 +227,15 @@ extern "C" int vtx_featurizer_fwd(const vtx_featurizer_params* p, void* stream) 
             return rc;
         if (int rc = make_tmap_3d(&tm_out, p->z, p->io_dtype, p->L, p->C, p->B, p->L, p->C * p->L, 64, FC, 128, "featurizer"))
             return rc;
-        dim3 grid((unsigned)ceil_div<int64_t>(p->L, FTT), (unsigned)ceil_div<int64_t>(p->C, FC), (unsigned)p->B);
+        dim3 grid((unsigned)ceil_div<int64_t>(p->C, FC), (unsigned)ceil_div<int64_t>(p->L, FTT), (unsigned)p->B);
+        const bool plain3 = p->K == 3 && !p->bias && !p->mask;
+        cudaStream_t st = (cudaStream_t)stream;
         if (p->io_dtype == VTX_BF16) {
-            featurizer_tma_kernel<__nv_bfloat16><<<grid, 256, FT_SMEM, (cudaStream_t)stream>>>(tm_in, tm_out, *p);
+            if (plain3) featurizer_tma_kernel<__nv_bfloat16, true><<<grid, 256, FT_SMEM, st>>>(tm_in, tm_out, *p);
+            else featurizer_tma_kernel<__nv_bfloat16, false><<<grid, 256, FT_SMEM, st>>>(tm_in, tm_out, *p);
         } else {
-            featurizer_tma_kernel<__half><<<grid, 256, FT_SMEM, (cudaStream_t)stream>>>(tm_in, tm_out, *p);
+            if (plain3) featurizer_tma_kernel<__half, true><<<grid, 256, FT_SMEM, st>>>(tm_in, tm_out, *p);
+            else featurizer_tma_kernel<__half, false><<<grid, 256, FT_SMEM, st>>>(tm_in, tm_out, *p);
         }
         return check_launch("featurizer");
     }

@@ -178,7 +178,7 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                 bool tail = false;
 #pragma unroll
                 for (int s = 0; s < NS; ++s) tail = tail || (rel0 + CHUNK > tr1[s] - ns && rel0 < tr1[s]);
-#pragma unroll 2
+#pragma unroll 1
                 for (int i = 0; i < TILE / 16 / (NFE * 32); ++i) {
                     const int vi = tid + i * NFE * 32;
                     const uint4 kk = *reinterpret_cast<const uint4*>(kt + vi * 16);
@@ -284,7 +284,8 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
                     return (uint32_t)v;
                 };
-#pragma unroll
+                // (rolled over the streams: the unrolled form did not fit the instruction cache next to the other roles)
+#pragma unroll 1
                 for (int s = 0; s < NS; ++s) {
                     uint32_t acc[16];
                     tmem_ld16(taddr + s * 16, acc);
@@ -297,6 +298,7 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                     }
 #pragma unroll
                     for (int c = 0; c < CH; c += 2) {
+                        // (16 s + c) & 7 == c & 7: the swizzle term of a column does not depend on the stream
                         const uint32_t o0 = (uint32_t)((s * CH + c) * 128) + xo[c & 7], o1 = (uint32_t)((s * CH + c + 1) * 128) + xo[(c + 1) & 7];
                         f32x2 z = pk2(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]));
                         if (a.bias_mode == VTX_BIAS_GATED) {
