@@ -14,10 +14,11 @@
 // elements over the same time segment, fetched as ONE box [4 x 16 x 64] per operand and half chunk (mode A, batch of
 // three or more), or four (batch element, segment) pairs fetched box by box (mode B).
 //
-// One persistent CTA per SM, 12 warps: 0-3 front end (k*v of the staged k and v tiles into the chunk's slot, and the
-// inner FIR cache from the last K-1 products of a sequence), 4-7 epilogue (thread = output sample: TMEM -> skip ->
-// round -> gate, the result written over the q tile in place and stored by TMA in whole 128-byte rows along time;
-// they also expand the next item's Toeplitz operand), 8 MMA issue, 9 TMA issue for k and v, 10 TMA issue for q.  q
+// One persistent CTA per SM, 16 warps: 0-3 front end (k*v of the staged k and v tiles into the chunk's slot, and the
+// inner FIR cache from the last K-1 products of a sequence), 4-11 epilogue (thread = output sample, two warps per TMEM
+// lane quarter with two streams each: TMEM -> skip -> round -> gate, the result written over the q tile in place and
+// stored by TMA in whole 128-byte rows along time; the first four also expand the next item's Toeplitz operand),
+// 12 MMA issue, 13 TMA issue for k and v, 14 TMA issue for q.  q
 // never passes through the front end: its tiles stay in their ring until their chunk's outputs have left through
 // them.  All waits are bounded.
 #include <cstdint>
@@ -54,8 +55,8 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 static_assert(OFF_Q % 1024 == 0 && OFF_SLOTS % 1024 == 0, "tiles are 1024-byte aligned (swizzle atoms)");
 constexpr int TMEM_COLS = 512;                // Toeplitz operand of item t at 128 (t & 1); accumulator buffer b at 256 + 64 b
 constexpr int D_COL = 256;
-constexpr int NFE = 4, W_EP = 4, W_MMA = 8, W_TKV = 9, W_TQ = 10;
-constexpr int THREADS = 12 * 32;
+constexpr int NFE = 4, W_EP = 4, NEP = 8, W_MMA = 12, W_TKV = 13, W_TQ = 14;   // NEP epilogue warps: two per TMEM lane quarter
+constexpr int THREADS = 16 * 32;
 
 struct Args {
     const void* h;  int64_t h_dtype;
@@ -115,7 +116,7 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
     auto q_empty = [&](int i) { return bar_u + 8u * (uint32_t)(2 * NKV + NQ + i); };
     constexpr int BB = 2 * NKV + 2 * NQ;
     auto kv_full = [&](int i) { return bar_u + 8u * (uint32_t)(BB + i); };
-    // kv_free: five arrivals -- the four epilogue warps (skip term read) and the MMA warp's commit behind the last MMAs
+    // kv_free: nine arrivals -- the eight epilogue warps (skip term read) and the MMA warp's commit behind the last MMAs
     // that read the tile (the previous-chunk half of the NEXT chunk is issued right behind the chunk's own half)
     auto kv_free = [&](int i) { return bar_u + 8u * (uint32_t)(BB + NSLOT + i); };
     constexpr int BC = BB + 2 * NSLOT;
@@ -136,9 +137,9 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
     if (tid == 0) {
         for (int i = 0; i < NKV; ++i) { mbar_init(kvin_full(i), 1); mbar_init(kvin_empty(i), NFE); }
         for (int i = 0; i < NQ; ++i) { mbar_init(q_full(i), 1); mbar_init(q_empty(i), 1); }
-        for (int i = 0; i < NSLOT; ++i) { mbar_init(kv_full(i), NFE); mbar_init(kv_free(i), 5); }
+        for (int i = 0; i < NSLOT; ++i) { mbar_init(kv_full(i), NFE); mbar_init(kv_free(i), NEP + 1); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(d_full(i), 1); mbar_init(d_empty(i), 4); mbar_init(a_ready(i), 4); mbar_init(taps_ready(i), 4); mbar_init(y_ready(i), 4);
+            mbar_init(d_full(i), 1); mbar_init(d_empty(i), NEP); mbar_init(a_ready(i), 4); mbar_init(taps_ready(i), 4); mbar_init(y_ready(i), NEP);
         }
         fence_mbar_init();
     }
@@ -213,9 +214,10 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                 if (lane == 0) { mbar_arrive(kv_full(slot)); mbar_arrive(kvin_empty(stage)); }
             }
         }
-    } else if (warp < W_EP + 4) {
-        // ======== epilogue: thread = output sample (TMEM lane) =====================================
-        const int e = warp - W_EP, r = e * 32 + lane;
+    } else if (warp < W_EP + NEP) {
+        // ======== epilogue: thread = output sample (TMEM lane); warps e and e + 4 share a lane quarter and take two
+        // streams each (a single warp per scheduler leaves the latency of its shared-memory reads exposed) ========
+        const int e = (warp - W_EP) % 4, r = e * 32 + lane, sh = (warp - W_EP) / 4;
         // Toeplitz operand of item t -> TMEM buffer t & 1 (lane i writes row i of [T^|T]); the block's taps (zero padded:
         // tp[m] = tap at lag m - 128) and skip parameters go through shared memory.  Runs while the item before streams.
         auto expand = [&](int t) {
@@ -248,7 +250,7 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
             if (lane == 0) mbar_arrive(a_ready(ab));
             return true;
         };
-        bool ok = expand(0);
+        bool ok = sh == 0 ? expand(0) : true;      // (the first four warps expand the operands)
         int pending = -1;          // q stage whose tile of outputs the TMA unit may still be reading
         for (int t = 0; t < nmine && ok; ++t) {
             const int blk = item_blk(t);
@@ -286,12 +288,12 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                 };
                 // (rolled over the streams: the unrolled form did not fit the instruction cache next to the other roles)
 #pragma unroll 1
-                for (int s = 0; s < NS; ++s) {
+                for (int s = 2 * sh; s < 2 * sh + 2; ++s) {
                     uint32_t acc[16];
                     tmem_ld16(taddr + s * 16, acc);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     tmem_ld_touch(acc);
-                    if (s + 1 == NS) {
+                    if (s == 2 * sh + 1) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(d_empty(dbuf));
@@ -329,7 +331,7 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(kv_free(slot)); mbar_arrive(y_ready(oc & 1)); }
-                if (e == 0 && lane == 0 && mbar_wait(y_ready(oc & 1), (oc >> 1) & 1u, 42)) {
+                if (warp == W_EP && lane == 0 && mbar_wait(y_ready(oc & 1), (oc >> 1) & 1u, 42)) {
                     const uint32_t src = sm_u + OFF_Q + qs * TILE;
                     const int row = (int)(d0 % a.hdy), head = (int)(d0 / a.hdy);
 #pragma unroll
@@ -351,10 +353,10 @@ gcg_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ C
                     if (pending >= 0) mbar_arrive(q_empty(pending));
                     pending = qs;
                 }
-                if (k == 1 && t + 1 < nmine && !expand(t + 1)) { ok = false; break; }
+                if (sh == 0 && k == 1 && t + 1 < nmine && !expand(t + 1)) { ok = false; break; }
             }
         }
-        if (e == 0 && lane == 0) {
+        if (warp == W_EP && lane == 0) {
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             if (pending >= 0) mbar_arrive(q_empty(pending));
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");        // the last stores have landed before the CTA ends
