@@ -622,7 +622,7 @@ def main():
 LAUNCHES = {"mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
-NCU_TRAFFIC = {"mr": 1.004e9, "se": 1.004e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch
+NCU_TRAFFIC = {"mr": 1.026e9, "se": 1.024e9, "mr_dropin": 2.407e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch
 
 if __name__ == "__main__":
     main()
