@@ -74,6 +74,14 @@ WORKLOADS = {
     "decode_stack": dict(B=64, L=1, D=4096, G=256, K=-1, io="bf16", seed=3, decode=True, stack=True,
                          name="hyena_decode_stack B=64 D=4096 bf16 (one token through 9 SE + 9 MR + 9 LI layers, "
                               "reference cache layout: fp32 caches, 16 real modal states per channel)"),
+    # configuration 4's Hyena share end to end: the 27 Hyena layers of an Evo 2 7B-shaped stack prefill a prompt of 8192
+    # tokens for 64 sequences through engine.fused_prefill (which fills the reference's cache containers), then 512
+    # decode steps run through engine.fused_decode on those caches (attention, projections and MLPs are not part of
+    # the path).  One "step" of this workload is one decode step of the whole batch through the 27 layers.
+    "evo2_7b_hyena": dict(B=64, L=8192, D=4096, G=256, K=-1, io="bf16", seed=3, decode=True, stack=True, harness=True,
+                          name="Evo 2 7B-shaped Hyena stack (9 SE + 9 MR + 9 LI with 16 real poles per channel): prefill of "
+                               "64 x 8192 tokens through engine.fused_prefill, then decode steps through engine.fused_decode "
+                               "on the caches the prefill left"),
 }
 
 
@@ -158,6 +166,95 @@ def make_stack(w, g, dtype):
             c["inner_state"] = torch.randn(B, D, K - 1, generator=g)
         p["layers"].append(c)
     return p
+
+
+def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
+    """Configuration 4, Hyena share: prefill then cached decode through the engine's fused entry points on the
+    reference's cache containers, batch-sharded (every cache is per sequence: no collective)."""
+    from vortex_b200 import HyenaInferenceEngine, ops
+    from vortex_b200.cache import HyenaCascadeFIRInferenceParams, HyenaCascadeIIRInferenceParams
+    B, L, D, G = w["B"], w["L"], w["D"], w["G"]
+    g = torch.Generator(device=dev).manual_seed(w["seed"] + 1000 * rank)
+    gc = torch.Generator().manual_seed(w["seed"])
+    dims = (D, 1, D, 16, G)
+    layers = []
+    for i, kind in enumerate(STACK_KINDS):
+        c = {"kind": kind, "eng": HyenaInferenceEngine(layer_idx=i),
+             "w3": (torch.randn(3 * D, 1, 3, generator=gc) / 3 ** 0.5).bfloat16().to(dev)}
+        if kind == "li":
+            c["kw"] = dict(log_poles=torch.log(0.9 + 0.099 * torch.rand(D, 16, generator=gc))[..., None].to(dev),
+                           residues=torch.randn(D, 16, generator=gc).to(dev), D=torch.randn(D, generator=gc).bfloat16().to(dev))
+        else:
+            K = 7 if kind == "se" else 128
+            c["kw"] = dict(h=(torch.randn(G, 1, K, generator=gc) / K ** 0.5).bfloat16().to(dev),
+                           D=torch.zeros(D, dtype=torch.bfloat16, device=dev) if kind == "mr" else None)
+        layers.append(c)
+    fir_cache, iir_cache = HyenaCascadeFIRInferenceParams(), HyenaCascadeIIRInferenceParams()
+    # one projection output stands for every layer's (values do not matter to the kernels' speed)
+    u = torch.empty(B, L, 3 * D, device=dev, dtype=torch.bfloat16)
+    for b0 in range(0, B, 4):
+        u[b0:b0 + 4] = torch.randn(min(4, B - b0), L, 3 * D, device=dev, generator=g).bfloat16()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def prefill():
+        for c in layers:
+            ip = iir_cache if c["kind"] == "li" else fir_cache
+            y = c["eng"].fused_prefill(u, c["w3"], None, dims, inference_params=ip, **c["kw"])
+        return y
+
+    prefill()
+    ops.device_status()
+    barrier()
+    ev0.record()
+    y = prefill()
+    ev1.record()
+    barrier()
+    ms_prefill = max_over_ranks(ev0.elapsed_time(ev1))
+    assert bool(torch.isfinite(y.float()).all())
+    pre_bytes = sum(8 * B * D * L + B * 3 * D * 4 + (B * D * 16 * 4 if k == "li" else B * D * ((7 if k == "se" else 128) - 1) * 2)
+                    for k in STACK_KINDS)
+    del y
+    tok = torch.randn(B, 3 * D, device=dev, generator=g).bfloat16()
+
+    def decode_step():
+        for c in layers:
+            ip = iir_cache if c["kind"] == "li" else fir_cache
+            yd = c["eng"].fused_decode(tok, c["w3"], None, dims, ip, **c["kw"])
+        return yd
+
+    for _ in range(max(a.warmup, 3)):
+        decode_step()                       # (the first step turns the prefill's bf16 caches into fp32 ones)
+    ops.device_status()
+    with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as cs:
+        barrier()
+        ev0.record()
+        for _ in range(a.steps):
+            yd = decode_step()
+        ev1.record()
+        barrier()
+    ms = max_over_ranks(ev0.elapsed_time(ev1))
+    assert bool(torch.isfinite(yd.float()).all())
+    if rank != 0:
+        return None
+    peak, peak_kind = _peaks()
+    ms_step = ms / a.steps
+    step_bytes = decode_bytes(dict(w, stack=True))
+    tokens = full["B"]
+    return {
+        "metric": "hyena_decode_throughput", "value": tokens / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
+        "gpu_launches": len(STACK_KINDS) * a.steps,
+        "roofline": {"bound": "hbm", "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": step_bytes,
+                     "note": "per rank and decode step (27 launches from Python, no CUDA graph): every cache read and "
+                             "written once; host launch time is inside the figure"},
+        "prefill": {"ms": ms_prefill, "tokens_per_s": full["B"] * L / (ms_prefill * 1e-3),
+                    "frac_of_hbm_peak_per_rank": pre_bytes / (ms_prefill * 1e-3) / 1e9 / peak,
+                    "note": "27 layers, one fused launch each (three for the per-channel long filter), caches written"},
+        "collective": None, "e2e": None,
+    }
 
 
 def decode_bytes(w):
@@ -432,7 +529,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    if strong and prefill:
+    if w.get("harness"):
+        p, pc = {}, {}
+    elif strong and prefill:
         # every rank builds the same seeded problem and keeps its own channels (contiguous copies of the slices)
         pfull = make_inputs(full, dev)
         p = sharding.shard_block({k: v for k, v in pfull.items() if torch.is_tensor(v) or v is None},
@@ -445,6 +544,13 @@ def main():
     for key in ("sets", "layers"):
         if key in pc:
             pc[key] = [{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in c.items()} for c in pc[key]]
+    if w.get("harness"):
+        line = run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier)
+        if line is not None:
+            print(json.dumps(line))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     pc["caches"] = w["caches"]
     from vortex_b200 import ops
     if w.get("dropin"):
@@ -619,7 +725,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload
-LAUNCHES = {"mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
+LAUNCHES = {"evo2_7b_hyena": len(STACK_KINDS), "mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.026e9, "se": 1.024e9, "mr_dropin": 2.407e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch

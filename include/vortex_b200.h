@@ -60,7 +60,7 @@ enum { VTX_BIAS_NONE = 0, VTX_BIAS_ADD = 1, VTX_BIAS_GATED = 2 /* + bias[d] * kv
 size_t vtx_last_error(char* buf, size_t len);
 /* ABI version of this header: major * 1000 + minor.  vtx_abi_version() returns the value the library was
  * built with; a binding compares the two (same major, library minor >= the minor it was written for). */
-#define VTX_ABI_VERSION 1002
+#define VTX_ABI_VERSION 1003
 int64_t vtx_abi_version(void);
 /* sizeof() of the parameter structs in declaration order (0 = vtx_featurizer_params, ...),
  * -1 past the end; lets a binding verify that its mirror of a struct has the same size. */
@@ -134,6 +134,27 @@ typedef struct vtx_gcg_params {
     int64_t io_dtype;
 } vtx_gcg_params;
 int vtx_gcg_fwd(const vtx_gcg_params* p, void* stream);
+
+/* The same operator on three CHANNEL-LAST operands q, k, v [B,L,D] (channel stride 1) -- the layout of the reference's
+ * hyena_ops kernels, (bs, l, g, dg) with d = g*dg (vortex/ops/hyena_se/fwd.py:56-64).  Replaces two_pass_fwd_grouped
+ * (fwd.py:17-310, kernels fwd_kernels.py:268-626) and its reference gcg_fwd_ref_corrected (ref_fwd.py:80-127) for
+ * bf16 operands and bf16 filters of up to 128 taps shared by a multiple of 16 channels: one launch of the tcgen05
+ * blocked-Toeplitz kernel (no featurizer in front), k*v and the filter output rounded to bf16 where the reference
+ * materialises them.  bias_mode: VTX_BIAS_NONE or VTX_BIAS_GATED.  state [B,D,min(L,K-1)] (channel-first, as the
+ * caches are) or NULL.  Bases and row pitches 16-byte aligned, y rows 32-byte aligned. */
+typedef struct vtx_gcg_cl_params {
+    const void* q;  int64_t q_stride_b, q_stride_l;
+    const void* k;  int64_t k_stride_b, k_stride_l;
+    const void* v;  int64_t v_stride_b, v_stride_l;
+    const void* h;       int64_t h_dtype;      /* [G,K] contiguous                        */
+    const void* bias;    int64_t bias_dtype;   /* [D] or NULL                             */
+    void* y;             int64_t y_stride_b, y_stride_l;
+    void* state;                                /* or NULL                                 */
+    int64_t B, L, D, G, K;
+    int64_t taps, bias_mode;
+    int64_t io_dtype;
+} vtx_gcg_cl_params;
+int vtx_gcg_cl_fwd(const vtx_gcg_cl_params* p, void* stream);
 
 /* ------------------------------------------------------------------------
  * Fused Hyena FIR block on the projection output, channel-last in and out:

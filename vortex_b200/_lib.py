@@ -54,6 +54,11 @@ FusedFirParams = _struct("FusedFirParams", """
     p:y i:y_stride_b i:y_stride_l p:fir_state p:inner_state
     i:B i:L i:D i:G i:K3 i:K i:layout i:num_heads i:flip_x1x2 i:taps i:bias_mode i:io_dtype i:u_hist_rows""")
 
+GcgClParams = _struct("GcgClParams", """
+    p:q i:q_stride_b i:q_stride_l p:k i:k_stride_b i:k_stride_l p:v i:v_stride_b i:v_stride_l
+    p:h i:h_dtype p:bias i:bias_dtype p:y i:y_stride_b i:y_stride_l p:state
+    i:B i:L i:D i:G i:K i:taps i:bias_mode i:io_dtype""")
+
 ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G i:S")
 
 
@@ -118,7 +123,7 @@ class DecodeLayerParams(C.Structure):
 
 STRUCTS = [FeaturizerParams, GcgParams, FusedFirParams, ModalParams, IirParams, StepFirParams, StepIirParams,
            DecodeLayerParams, FusedIirParams, HyenaXParams, CausalConv1dParams, CausalConv1dUpdateParams,
-           VarlenStatesParams]
+           VarlenStatesParams, GcgClParams]
 
 # name -> (restype, argtypes); every symbol include/vortex_b200.h declares
 SYMBOLS = {
@@ -129,6 +134,7 @@ SYMBOLS = {
     "vtx_debug_set_flag_poll_limit": (C.c_int, [_i]),
     "vtx_featurizer_fwd": (C.c_int, [C.POINTER(FeaturizerParams), _p]),
     "vtx_gcg_fwd": (C.c_int, [C.POINTER(GcgParams), _p]),
+    "vtx_gcg_cl_fwd": (C.c_int, [C.POINTER(GcgClParams), _p]),
     "vtx_fused_fir_fwd": (C.c_int, [C.POINTER(FusedFirParams), _p]),
     "vtx_modal_filter": (C.c_int, [C.POINTER(ModalParams), _p, _i, _p]),
     "vtx_iir_scratch_bytes": (_i, [_i, _i, _i, _i, _i]),

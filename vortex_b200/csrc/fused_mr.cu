@@ -107,6 +107,7 @@ struct Args {
     int layout, flip, taps, has_bias;
     int64_t hd;
     int hist;        // rows before u[b][0] that hold the sequence's earlier samples (the tensor map starts there)
+    int64_t dg;      // channels that share a filter (a multiple of 16): the filter of group g is h[16 g / dg]
 };
 
 struct Stream {
@@ -147,8 +148,14 @@ __device__ __forceinline__ uint16_t f16_bits(float v) {
 }
 
 // SWAP: interleaved layout with the q and k roles exchanged (the planar layouts exchange their TMA columns instead).
-template <bool INTERLEAVED, bool SWAP>
-__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Args a) {
+// FEAT = false: the gate-conv-gate operator on its own, on three channel-last operands q, k, v [B, L, D] that are
+// already featurised (the hyena_ops (bs, l, g, dg) convention, vortex/ops/hyena_se/fwd.py:56-64): no featurizer in
+// the front end, one tensor map per operand (planes of the planar staging), and the reference's rounding points --
+// k*v and the filter output are rounded to bf16 where ref_fwd.py:80-127 materialises them.
+template <bool INTERLEAVED, bool SWAP, bool FEAT>
+__global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_k,
+                                                              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ Args a) {
+    static_assert(FEAT || (!INTERLEAVED && !SWAP), "the operator-only variant stages three planes");
     using LY = Lay<INTERLEAVED>;
     constexpr int IN_STAGES = LY::IN_STAGES, BOX_STRIDE = LY::BOX_STRIDE, STAGE_BYTES = LY::STAGE_BYTES;
     constexpr int OFF_SLOTS = LY::OFF_SLOTS, OFF_DIAG = LY::OFF_DIAG, OFF_TAPS = LY::OFF_TAPS, OFF_W3S = LY::OFF_W3S;
@@ -215,6 +222,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         // featurizer taps of item t: staged in shared memory by the epilogue warps together with the item's Toeplitz
         // operand (a_ready); [feature][tap][channel] fp32, this lane's two channels as one 8-byte load
         auto load_w3 = [&](int t) {
+            if (!FEAT) return true;
             if (!mbar_wait(a_ready(t & 1), (uint32_t)((t >> 1) & 1), 17)) return false;
             const uint32_t base = sm_u + OFF_W3S + (uint32_t)((t & 1) * W3S_BYTES) + 8u * (uint32_t)p;
 #pragma unroll
@@ -269,16 +277,24 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             for (int i = 0; i < RB; ++i) {
                 f32x2 x0[3], z[3];
                 unpack(raw[i + 2], x0);
-#pragma unroll
-                for (int x = 0; x < 3; ++x) {
-                    z[x] = fma2(w3[x][0], x2[x], fma2(w3[x][1], x1[x], mul2(w3[x][2], x0[x])));
-                    x2[x] = x1[x];
-                    x1[x] = x0[x];
-                }
-                // (the staged taps of v carry the 2^-6 of the k*v tile; rows before the sequence start are zeros)
                 float kv0, kv1, q0, q1;
-                up2(mul2(SWAP ? z[0] : z[1], z[2]), kv0, kv1);
-                up2(SWAP ? z[1] : z[0], q0, q1);
+                if (FEAT) {
+#pragma unroll
+                    for (int x = 0; x < 3; ++x) {
+                        z[x] = fma2(w3[x][0], x2[x], fma2(w3[x][1], x1[x], mul2(w3[x][2], x0[x])));
+                        x2[x] = x1[x];
+                        x1[x] = x0[x];
+                    }
+                    // (the staged taps of v carry the 2^-6 of the k*v tile; rows before the sequence start are zeros)
+                    up2(mul2(SWAP ? z[0] : z[1], z[2]), kv0, kv1);
+                    up2(SWAP ? z[1] : z[0], q0, q1);
+                } else {
+                    // k*v rounded to bf16 as the reference materialises it, then scaled: exact in fp16
+                    up2(mul2(x0[1], x0[2]), kv0, kv1);
+                    const uint32_t r = pack_bf16(kv0, kv1);
+                    kv0 = bf_lo(r) * KV_SCALE; kv1 = bf_hi(r) * KV_SCALE;
+                    up2(x0[0], q0, q1);
+                }
                 // row0 is a multiple of 8, so the swizzle phase of row row0 + i is i & 7
                 const uint32_t kaddr = kv_a0 ^ (uint32_t)((i & 7) << 4);
                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + i * 128), "r"(pack_f16(kv0, kv1)));
@@ -332,11 +348,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
             for (int m = r; m < 384; m += 128) {
                 const int l = m - 128;
                 float v = 0.f;
-                if (l >= 0 && l < K) v = KV_UNSCALE * ld_param(a.h, a.h_dtype, (int64_t)g * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
+                if (l >= 0 && l < K) v = KV_UNSCALE * ld_param(a.h, a.h_dtype, ((int64_t)g * CH / a.dg) * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
                 tp[m] = f16_bits(v);
             }
             if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? KV_UNSCALE * ld_param(a.bias, a.bias_dtype, (int64_t)g * CH + r) : 0.f;
-            {   // featurizer taps of the group's 16 channels (the front end picks them up at the item's first chunk)
+            if (FEAT) {   // featurizer taps of the group's 16 channels (the front end picks them up at the item's first chunk)
                 QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
                 float* w3s = reinterpret_cast<float*>(smp(OFF_W3S + ab * W3S_BYTES));
                 for (int m = r; m < 3 * 3 * CH; m += 128) {
@@ -424,14 +440,28 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                         f32x2 y[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) y[j] = pk2(__uint_as_float(acc[8 * hf + 2 * j]), __uint_as_float(acc[8 * hf + 2 * j + 1]));
+                        // rounds a pair to bf16 and back (the operator-only variant materialises what the reference does)
+                        auto rnd = [](f32x2 v) {
+                            float v0, v1;
+                            up2(v, v0, v1);
+                            const uint32_t r = pack_bf16(v0, v1);
+                            return pk2(bf_lo(r), bf_hi(r));
+                        };
                         if (has_skip) {
                             // skip term D[c] * kv[t, c] from this row of the k*v tile (both carry their power of two)
                             const uint4 k4 = *reinterpret_cast<const uint4*>(kv_p + off);
+                            const uint32_t kw[4] = {k4.x, k4.y, k4.z, k4.w};
                             const float4 d0 = dsk[2 * hf], d1 = dsk[2 * hf + 1];
-                            y[0] = fma2(pk2(d0.x, d0.y), unpack_f16(k4.x), y[0]);
-                            y[1] = fma2(pk2(d0.z, d0.w), unpack_f16(k4.y), y[1]);
-                            y[2] = fma2(pk2(d1.x, d1.y), unpack_f16(k4.z), y[2]);
-                            y[3] = fma2(pk2(d1.z, d1.w), unpack_f16(k4.w), y[3]);
+                            const f32x2 dd[4] = {pk2(d0.x, d0.y), pk2(d0.z, d0.w), pk2(d1.x, d1.y), pk2(d1.z, d1.w)};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (FEAT || a.taps == VTX_TAPS_CONV) y[j] = fma2(dd[j], unpack_f16(kw[j]), y[j]);     // fp32 sum, one rounding
+                                else y[j] = add2(rnd(y[j]), rnd(mul2(dd[j], unpack_f16(kw[j]))));     // filter output and skip rounded apart
+                            }
+                        }
+                        if (!FEAT) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) y[j] = rnd(y[j]);
                         }
                         const uint4 q4 = *reinterpret_cast<const uint4*>(kv_p + Q_OFF + off);
                         const uint32_t qw[4] = {q4.x, q4.y, q4.z, q4.w};
@@ -522,6 +552,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         if (lane == 0) {
             // ======== TMA issue ======================================================================
             tma_prefetch_desc(&tmap);
+            if (!FEAT) { tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v); }
             uint32_t nh = 2 * cc;                    // staged half chunks so far
             bool ok = true;
             for (int t = 0; t < nmine && ok; ++t) {
@@ -530,6 +561,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 int col[3] = {0, 0, 0};
                 if (INTERLEAVED) {
                     col[0] = 3 * g * CH;
+                } else if (!FEAT) {
+                    col[0] = col[1] = col[2] = g * CH;          // the same channels of three tensors
                 } else {
                     const int64_t d0 = (int64_t)g * CH;
                     if (a.layout == VTX_QKV_COLUMN_SPLIT) {
@@ -562,7 +595,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                         } else {
 #pragma unroll
                             for (int pl = 0; pl < 3; ++pl)
-                                tma_load_3d(dst + pl * IN_PLANE, &tmap, bar, col[pl], row, bidx[s]);
+                                tma_load_3d(dst + pl * IN_PLANE, FEAT || pl == 0 ? &tmap : pl == 1 ? &tmap_k : &tmap_v, bar, col[pl], row, bidx[s]);
                         }
                     }
                 }
@@ -678,6 +711,64 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
 
 }  // namespace mr
 
+namespace mr {
+
+// Time segments: a sequence is cut into nseg segments of whole chunks, a work item is one group x four streams
+// (batch element x segment), the items are dealt round-robin to one persistent CTA per SM.  Every item pays one
+// halo chunk, and the launch lasts as long as the CTA with the most chunks: pick the segment length that makes
+// that CTA's chunk count smallest (ties: fewer items).
+static int plan_items(Args& a) {
+    const int64_t nchunks_total = ceil_div<int64_t>(a.L, CHUNK);
+    int64_t nseg = 1, best_cost = INT64_MAX;
+    for (int64_t seg_chunks = nchunks_total; seg_chunks >= 1; --seg_chunks) {
+        const int64_t ns_ = ceil_div<int64_t>(nchunks_total, seg_chunks);
+        if (ceil_div<int64_t>(nchunks_total, ns_) != seg_chunks) continue;       // same plan as a shorter segment
+        const int64_t items = a.G * ceil_div<int64_t>(a.B * ns_, NS);
+        const int64_t cost = ceil_div<int64_t>(items, kNumSMs) * (seg_chunks + 1) * 64 + ns_;   // (+ a little per segment)
+        if (cost < best_cost) { best_cost = cost; nseg = ns_; }
+        if (seg_chunks <= 2 || items > (int64_t)kNumSMs * 64) break;            // shorter segments only add halo chunks
+    }
+    a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
+    a.nseg = ceil_div<int64_t>(a.L, a.seg_len);
+    a.nstream = a.B * a.nseg;
+    a.nquad = ceil_div<int64_t>(a.nstream, NS);
+    VTX_REQUIRE(a.G * a.nquad < (int64_t)1 << 31, VTX_ERR_UNSUPPORTED, "fused_fir: too many work items");
+    a.nitems = a.G * a.nquad;
+    return VTX_OK;
+}
+
+// One persistent CTA per SM (the shared-memory footprint allows no more), each walking the items blockIdx,
+// blockIdx + gridDim, ...  The CTA count must not exceed what is resident at once: a second round would double the time.
+template <typename Kern>
+static int launch(Kern kern, int variant, int smem_bytes, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                  const Args& a, cudaStream_t stream) {
+    // the opt-in is a per-device property of the function: remember it per device
+    static bool attr_set[64][4] = {};
+    static int resident[64][4] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const bool known = dev >= 0 && dev < 64;
+    if (!known || !attr_set[dev][variant]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
+        if (known) attr_set[dev][variant] = true;
+    }
+    int nres = known ? resident[dev][variant] : 0;
+    if (nres == 0) {
+        int sms = 0, per_sm = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem_bytes);
+        nres = sms * per_sm;
+        if (nres <= 0) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): the kernel does not fit an SM (%d SMs, %d blocks each)", sms, per_sm);
+        if (known) resident[dev][variant] = nres;
+    }
+    const int64_t ncta = a.nitems < nres ? a.nitems : nres;
+    kern<<<(unsigned)ncta, THREADS, smem_bytes, stream>>>(tq, tk, tv, a);
+    return check_launch("fused_fir(mr)");
+}
+
+}  // namespace mr
+
 int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     using namespace mr;
     VTX_REQUIRE(p->io_dtype == VTX_BF16, VTX_ERR_UNSUPPORTED, "fused_fir: the tensor-core path takes bf16 I/O");
@@ -693,7 +784,7 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     a.u = static_cast<const __nv_bfloat16*>(p->u); a.u_stride_b = p->u_stride_b; a.u_stride_l = p->u_stride_l;
     a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
     a.fir_state = static_cast<__nv_bfloat16*>(p->fir_state); a.inner_state = static_cast<__nv_bfloat16*>(p->inner_state);
-    a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K;
+    a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->G; a.K = p->K; a.dg = CH;
     a.layout = (int)p->layout; a.flip = p->flip_x1x2 != 0; a.taps = (int)p->taps;
     a.hd = p->D;
     a.hist = (int)p->u_hist_rows;
@@ -704,28 +795,7 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     }
     VTX_REQUIRE(p->layout == VTX_QKV_INTERLEAVED || (p->D * 2) % 16 == 0, VTX_ERR_ALIGNMENT,
                 "fused_fir: D*itemsize must be a multiple of 16 bytes for this q/k/v layout");
-    // Time segments: a sequence is cut into nseg segments of whole chunks, a work item is one group x four streams
-    // (batch element x segment), the items are dealt round-robin to one persistent CTA per SM.  Every item pays one
-    // halo chunk, and the launch lasts as long as the CTA with the most chunks: pick the segment length that makes
-    // that CTA's chunk count smallest (ties: fewer items).
-    const int64_t nchunks_total = ceil_div<int64_t>(p->L, CHUNK);
-    int64_t nseg = 1, best_cost = INT64_MAX;
-    for (int64_t seg_chunks = nchunks_total; seg_chunks >= 1; --seg_chunks) {
-        const int64_t ns_ = ceil_div<int64_t>(nchunks_total, seg_chunks);
-        if (ceil_div<int64_t>(nchunks_total, ns_) != seg_chunks) continue;       // same plan as a shorter segment
-        const int64_t items = p->G * ceil_div<int64_t>(p->B * ns_, NS);
-        const int64_t cost = ceil_div<int64_t>(items, kNumSMs) * (seg_chunks + 1) * 64 + ns_;   // (+ a little per segment)
-        if (cost < best_cost) { best_cost = cost; nseg = ns_; }
-        if (seg_chunks <= 2 || items > (int64_t)kNumSMs * 64) break;            // shorter segments only add halo chunks
-    }
-    a.seg_len = ceil_div<int64_t>(nchunks_total, nseg) * CHUNK;
-    a.nseg = ceil_div<int64_t>(p->L, a.seg_len);
-    a.nstream = p->B * a.nseg;
-    const int64_t nquad = ceil_div<int64_t>(a.nstream, NS);
-    VTX_REQUIRE(p->G * nquad < (int64_t)1 << 31, VTX_ERR_UNSUPPORTED, "fused_fir: too many work items");
-    a.nquad = nquad;
-    a.nitems = p->G * nquad;
-
+    if (int rc = plan_items(a)) return rc;
     const bool inter = p->layout == VTX_QKV_INTERLEAVED;
     CUtensorMap tmap;
     // the tensor map starts at the first history row (chunked prefill), else at u
@@ -733,33 +803,64 @@ int fused_mr_tc_fwd(const vtx_fused_fir_params* p, cudaStream_t stream) {
     if (int rc = make_tmap_3d(&tmap, u_first, VTX_BF16, 3 * p->D, p->L + p->u_hist_rows, p->B, p->u_stride_l, p->u_stride_b,
                               inter ? 3 * CH : CH, BOX_ROWS, 0, "fused_fir(mr)"))
         return rc;
-    const int variant = !inter ? 0 : (a.flip ? 2 : 1);
-    auto kern = variant == 0 ? fused_mr_kernel<false, false> : variant == 1 ? fused_mr_kernel<true, false> : fused_mr_kernel<true, true>;
-    const int smem_bytes = inter ? Lay<true>::SMEM_BYTES : Lay<false>::SMEM_BYTES;
-    // the opt-in is a per-device property of the function: remember it per device
-    static bool attr_set[64][3] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev][variant]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-        if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): shared memory opt-in: %s", cudaGetErrorString(e));
-        if (dev >= 0 && dev < 64) attr_set[dev][variant] = true;
-    }
-    // One persistent CTA per SM (the shared-memory footprint allows no more), each walking the items blockIdx,
-    // blockIdx + gridDim, ...  The CTA count must not exceed what is resident at once: a second round would double the time.
-    static int resident[64][3] = {};
-    int nres = (dev >= 0 && dev < 64) ? resident[dev][variant] : 0;
-    if (nres == 0) {
-        int sms = 0, per_sm = 0;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem_bytes);
-        nres = sms * per_sm;
-        if (nres <= 0) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): the kernel does not fit an SM (%d SMs, %d blocks each)", sms, per_sm);
-        if (dev >= 0 && dev < 64) resident[dev][variant] = nres;
-    }
-    const int64_t ncta = a.nitems < nres ? a.nitems : nres;
-    kern<<<(unsigned)ncta, THREADS, smem_bytes, stream>>>(tmap, a);
-    return check_launch("fused_fir(mr)");
+    if (!inter) return launch(fused_mr_kernel<false, false, true>, 0, Lay<false>::SMEM_BYTES, tmap, tmap, tmap, a, stream);
+    if (!a.flip) return launch(fused_mr_kernel<true, false, true>, 1, Lay<true>::SMEM_BYTES, tmap, tmap, tmap, a, stream);
+    return launch(fused_mr_kernel<true, true, true>, 2, Lay<true>::SMEM_BYTES, tmap, tmap, tmap, a, stream);
 }
 
 }  // namespace vtx
+
+namespace vtx {
+// Inner FIR cache of the operator-only call: state[b, d, j] = bf16(k * v)[b, L - ns + j, d], ns = min(L, K - 1).  A copy
+// of products of the inputs, so it is made from them directly (the k*v tiles of the main kernel are fp16 and scaled:
+// exact for the contraction's purposes, but not bit for bit for products below 2^-11).
+__global__ void gcg_cl_state_kernel(const __nv_bfloat16* k, int64_t k_stride_b, int64_t k_stride_l, const __nv_bfloat16* v,
+                                    int64_t v_stride_b, int64_t v_stride_l, __nv_bfloat16* state, int64_t B, int64_t L,
+                                    int64_t D, int64_t ns) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B * ns * D) return;
+    const int64_t d = i % D, j = (i / D) % ns, b = i / (D * ns), t = L - ns + j;
+    const float p = __bfloat162float(k[b * k_stride_b + t * k_stride_l + d]) * __bfloat162float(v[b * v_stride_b + t * v_stride_l + d]);
+    state[(b * D + d) * ns + j] = __float2bfloat16_rn(p);
+}
+}  // namespace vtx
+
+// Gate -> grouped causal FIR -> gate on three channel-last operands (no featurizer): the tensor-core kernel in its
+// operator-only form.
+extern "C" int vtx_gcg_cl_fwd(const vtx_gcg_cl_params* p, void* stream) {
+    using namespace vtx;
+    using namespace vtx::mr;
+    VTX_REQUIRE(p && p->q && p->k && p->v && p->h && p->y, VTX_ERR_BAD_ARG, "gcg_cl: null pointer");
+    VTX_REQUIRE(p->B > 0 && p->L > 0 && p->D > 0 && p->G > 0 && p->K > 0, VTX_ERR_BAD_ARG, "gcg_cl: sizes must be positive");
+    VTX_REQUIRE(p->D % p->G == 0, VTX_ERR_BAD_ARG, "gcg_cl: D not a multiple of G");
+    VTX_REQUIRE(p->io_dtype == VTX_BF16 && p->h_dtype == VTX_BF16, VTX_ERR_UNSUPPORTED, "gcg_cl: bf16 operands and filters only");
+    VTX_REQUIRE(p->K <= CHUNK, VTX_ERR_UNSUPPORTED, "gcg_cl: filter length %lld > %d", (long long)p->K, CHUNK);
+    VTX_REQUIRE((p->D / p->G) % CH == 0, VTX_ERR_UNSUPPORTED, "gcg_cl: filters must be shared by multiples of %d channels", CH);
+    VTX_REQUIRE(p->bias_mode == VTX_BIAS_NONE || (p->bias_mode == VTX_BIAS_GATED && p->bias), VTX_ERR_UNSUPPORTED,
+                "gcg_cl: bias mode must be none or gated");
+    VTX_REQUIRE(p->B <= 65535 && p->L < ((int64_t)1 << 30), VTX_ERR_UNSUPPORTED, "gcg_cl: problem too large");
+    VTX_REQUIRE((reinterpret_cast<uintptr_t>(p->y) % 32) == 0 && (p->y_stride_l % 16) == 0 && (p->y_stride_b % 16) == 0,
+                VTX_ERR_ALIGNMENT, "gcg_cl: y rows must be 32-byte aligned");
+    Args a{};
+    a.h = p->h; a.h_dtype = p->h_dtype; a.bias = p->bias; a.bias_dtype = p->bias_dtype; a.has_bias = p->bias_mode == VTX_BIAS_GATED;
+    a.y = static_cast<__nv_bfloat16*>(p->y); a.y_stride_b = p->y_stride_b; a.y_stride_l = p->y_stride_l;
+    a.B = p->B; a.L = p->L; a.D = p->D; a.G = p->D / CH; a.K = p->K; a.dg = p->D / p->G;
+    a.layout = VTX_QKV_SPLIT; a.taps = (int)p->taps; a.hd = p->D;
+    if (int rc = plan_items(a)) return rc;
+    CUtensorMap tm[3];
+    const void* ptrs[3] = {p->q, p->k, p->v};
+    const int64_t sl[3] = {p->q_stride_l, p->k_stride_l, p->v_stride_l}, sb[3] = {p->q_stride_b, p->k_stride_b, p->v_stride_b};
+    for (int i = 0; i < 3; ++i)
+        if (int rc = make_tmap_3d(&tm[i], ptrs[i], VTX_BF16, p->D, p->L, p->B, sl[i], sb[i], CH, BOX_ROWS, 0, "gcg_cl")) return rc;
+    if (int rc = launch(fused_mr_kernel<false, false, false>, 3, Lay<false>::SMEM_BYTES, tm[0], tm[1], tm[2], a, (cudaStream_t)stream))
+        return rc;
+    const int64_t ns = p->L < p->K - 1 ? p->L : p->K - 1;
+    if (p->state && ns > 0) {
+        const int64_t n = p->B * ns * p->D;
+        gcg_cl_state_kernel<<<(unsigned)ceil_div<int64_t>(n, 256), 256, 0, (cudaStream_t)stream>>>(
+            static_cast<const __nv_bfloat16*>(p->k), p->k_stride_b, p->k_stride_l, static_cast<const __nv_bfloat16*>(p->v),
+            p->v_stride_b, p->v_stride_l, static_cast<__nv_bfloat16*>(p->state), p->B, p->L, p->D, ns);
+        return check_launch("gcg_cl state");
+    }
+    return VTX_OK;
+}

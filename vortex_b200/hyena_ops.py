@@ -181,6 +181,13 @@ def _li_tensor_core_ok(u, w3, b3, residues, layout, num_heads):
 def gcg_fwd(x, B, C, h, bias=None, gated_bias=False):
     """y = C * xcorr(h_g, B * x) for (bs, l, g, dg) tensors, h (g, 1, hl); returns (bs, l, g, dg)."""
     bs, l, g, dg = x.shape
+    mode = BIAS_NONE if bias is None else (BIAS_GATED if gated_bias else BIAS_ADD)
+    if x.is_contiguous() and B.is_contiguous() and C.is_contiguous():
+        # (bs, l, g, dg) contiguous IS channel-last [bs, l, d]: bf16 operands go to the tensor-core kernel as they are
+        q3, k3, v3 = (t.view(bs, l, g * dg) for t in (C, B, x))
+        if ops.gcg_cl_ok(q3, k3, v3, h, mode):
+            y, _ = ops.gcg_cl_fwd(q3, k3, v3, h, bias, taps=TAPS_XCORR, bias_mode=mode)
+            return y.view(bs, l, g, dg)
     to_bdl = lambda t: t.reshape(bs, l, g * dg).permute(0, 2, 1).contiguous()  # noqa: E731
     y, _ = ops.gcg_fwd_bdl(to_bdl(C), to_bdl(B), to_bdl(x), h, bias, taps=TAPS_XCORR,
                            bias_mode=BIAS_NONE if bias is None else (BIAS_GATED if gated_bias else BIAS_ADD),

@@ -172,6 +172,45 @@ def gcg_fwd_bdl(q, k, v, h, bias=None, *, taps=TAPS_XCORR, bias_mode=BIAS_NONE, 
                     want_state=want_state, round_kv=round_kv, channel_last_out=False)
 
 
+def gcg_cl_ok(q, k, v, h, bias_mode=BIAS_NONE) -> bool:
+    """Shapes ``vtx_gcg_cl_fwd`` takes: bf16 channel-last operands [B, L, D] with unit channel stride and 16-byte
+    aligned rows, bf16 filters of up to 128 taps shared by a multiple of 16 channels."""
+    if not (q.dtype == k.dtype == v.dtype == h.dtype == torch.bfloat16) or q.dim() != 3 or bias_mode == BIAS_ADD:
+        return False
+    D, G, K = q.shape[-1], h.shape[0], h.shape[-1]
+    if K > 128 or D % G or (D // G) % 16:
+        return False
+    for t in (q, k, v):
+        if t.shape != q.shape or t.stride(2) != 1 or t.data_ptr() % 16 or (t.stride(1) * 2) % 16 or (t.stride(0) * 2) % 16:
+            return False
+    return True
+
+
+def gcg_cl_fwd(q, k, v, h, bias=None, *, taps=TAPS_XCORR, bias_mode=BIAS_NONE, want_state=False):
+    """Gate -> grouped FIR -> gate on channel-last operands q, k, v [B, L, D] (the hyena_ops layout with the group
+    axes merged): one launch of the tensor-core kernel.  Returns y [B, L, D] and the inner cache [B, D, min(L, K-1)]
+    or None."""
+    _need_cuda(q, k, v, h, bias)
+    B, L, D = q.shape
+    h = _param(h, q)
+    G = h.shape[0]
+    h = h.reshape(G, -1)
+    K = h.shape[1]
+    bias = _param(bias, q)
+    y = torch.empty(B, L, D, device=q.device, dtype=q.dtype)
+    ns = min(L, K - 1)
+    state = torch.empty(B, D, ns, device=q.device, dtype=q.dtype) if want_state else None
+    p = _lib.GcgClParams(
+        q=_ptr(q), q_stride_b=q.stride(0), q_stride_l=q.stride(1), k=_ptr(k), k_stride_b=k.stride(0), k_stride_l=k.stride(1),
+        v=_ptr(v), v_stride_b=v.stride(0), v_stride_l=v.stride(1), h=_ptr(h), h_dtype=_code(h),
+        bias=_ptr(bias), bias_dtype=_code(bias) if bias is not None else 0, y=_ptr(y), y_stride_b=L * D, y_stride_l=D,
+        state=_ptr(state) if (state is not None and ns > 0) else None, B=B, L=L, D=D, G=G, K=K, taps=taps,
+        bias_mode=bias_mode if bias is not None else BIAS_NONE, io_dtype=_code(q))
+    with _on(q):
+        _lib.check(_lib.lib().vtx_gcg_cl_fwd(C.byref(p), _stream(q)))
+    return y, state
+
+
 def fused_fir_fwd(u: torch.Tensor, w3, b3, h, bias, D: int, *, taps: int, bias_mode: int, layout="interleaved",
                   num_heads=1, flip=False, want_state=True, hist_rows=0):
     """Channel-last fused block: u [B, L, 3D] -> y [B, L, D], fir_state [B, 3D, min(L,2)], inner [B, D, min(L,K-1)].
