@@ -213,11 +213,12 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
             const int i = lane + 32 * j;
             s[r][j] = i < c ? sin_[r * c + i] : 0.f;
         }
-    float tap[4], tap_u = 0.f;
+    // Per row: the lane's partial dot product over its (up to) four samples, and the shifted samples on their way out.
+    float tap[4], tap_u[RW], part[RW], tap_u_cur = 0.f;
     int64_t g_have = -1;
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
-        const int64_t d = d0 + r, g = d / cpg;
+        const int64_t g = (d0 + r) / cpg;
         if (g != g_have) {          // taps of the row's group (usually the same for the whole tile)
             g_have = g;
 #pragma unroll
@@ -225,9 +226,9 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
                 const int i = lane + 32 * j;
                 tap[j] = i < c ? ld_param(p.h, p.h_dtype, g * K + (flip ? c - i : i)) : 0.f;
             }
-            tap_u = ld_param(p.h, p.h_dtype, g * K + (flip ? 0 : c));
+            tap_u_cur = ld_param(p.h, p.h_dtype, g * K + (flip ? 0 : c));
         }
-        const float kv = __shfl_sync(0xffffffffu, kv_own, r), q = __shfl_sync(0xffffffffu, q_own, r);
+        tap_u[r] = tap_u_cur;
         float acc = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -235,11 +236,43 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
             acc = fmaf(s[r][j], tap[j], acc);
             if (i >= 1 && i < c) sout[r * c + i - 1] = s[r][j];
         }
+        part[r] = acc;
+    }
+    // Sum every row's partials over the 32 lanes with a folding exchange: each step halves the number of rows a lane
+    // still carries (RW / 2 + RW / 4 + ... shuffles) instead of a five-step butterfly per row; lane l ends up with the
+    // total of row l % RW (for RW == 8: after three folds over lane bits 4, 3, 2, then two plain steps over bits 1, 0).
+    static_assert(RW == 8, "the fold below is written for eight rows per warp");
+    {
+        const bool hi4 = lane & 16, hi3 = lane & 8, hi2 = lane & 4;
+        float q4[4], q2[2], q1;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) {
+        for (int r = 0; r < 4; ++r) {       // fold lane bit 4: lower half keeps rows 0..3, upper half rows 4..7
+            const float give = hi4 ? part[r] : part[r + 4], keep = hi4 ? part[r + 4] : part[r];
+            q4[r] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {       // fold lane bit 3
+            const float give = hi3 ? q4[r] : q4[r + 2], keep = hi3 ? q4[r + 2] : q4[r];
+            q2[r] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+        }
+        {                                   // fold lane bit 2
+            const float give = hi2 ? q2[0] : q2[1], keep = hi2 ? q2[1] : q2[0];
+            q1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+        }
+        q1 += __shfl_xor_sync(0xffffffffu, q1, 2);
+        q1 += __shfl_xor_sync(0xffffffffu, q1, 1);
+        // row held by this lane: bit 4 -> +4, bit 3 -> +2, bit 2 -> +1
+        const int r = (hi4 ? 4 : 0) + (hi3 ? 2 : 0) + (hi2 ? 1 : 0);
+        // the row's new sample and gate sit on lane r (featurizer step above)
+        const float kv = __shfl_sync(0xffffffffu, kv_own, r), q = __shfl_sync(0xffffffffu, q_own, r);
+        float tu = tap_u[0];
+#pragma unroll
+        for (int x = 1; x < RW; ++x)
+            if (r == x) tu = tap_u[x];
+        if ((lane & 3) == 0) {              // one lane per row finishes it
+            const int64_t d = d0 + r;
             sout[r * c + c - 1] = kv;
-            float f = fmaf(tap_u, kv, acc);
+            float f = fmaf(tu, kv, q1);
             if (p.bias_mode != VTX_BIAS_NONE) {
                 const float bias = ld_param(p.bias, p.bias_dtype, d);
                 f = p.bias_mode == VTX_BIAS_GATED ? fmaf(bias, kv, f) : f + bias;
