@@ -623,8 +623,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 sb[s] = (int)st.b;
                 tr1[s] = (st.active && st.te == L) ? (int)(L - st.ts) : -(1 << 29);
             }
-            // the input words of fir_state are requested now (volatile: issued where they stand) and stored after the
-            // item's first hand-over, so that the round trip to memory never holds up a slot
+            // the input words of fir_state are requested now (volatile: issued where they stand) and stored at the end
+            // of the item, so that the round trip to memory never holds up a slot
             uint16_t fsv[NS][3];
             auto fs_col = [&](int m) {      // m-th of the group's 3 x 16 packed columns times n3 rows -> packed column
                 const QkvMap map{a.layout, 0, a.D, a.hd};
@@ -682,7 +682,9 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(slot_free(slot));
-                if (k == 0 && a.fir_state && n3 > 0) {
+                // (stored at the item's last chunk: by then the words requested at its start have long arrived, and
+                // this warp never sits on a memory round trip while slots wait for its hand-over)
+                if (k == nchunk - 1 && a.fir_state && n3 > 0) {
 #pragma unroll
                     for (int s = 0; s < NS; ++s) {
                         if (tr1[s] <= 0) continue;
