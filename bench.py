@@ -82,6 +82,14 @@ WORKLOADS = {
                           name="Evo 2 7B-shaped Hyena stack (9 SE + 9 MR + 9 LI with 16 real poles per channel): prefill of "
                                "64 x 8192 tokens through engine.fused_prefill, then decode steps through engine.fused_decode "
                                "on the caches the prefill left"),
+    # configuration 5's Hyena share: the 42 Hyena layers of an Evo 2 40B-shaped stack (14 SE + 14 MR + 14 LI, hidden size
+    # 8192, `configs/evo2-40b-1m.yml`) prefill ONE sequence of 1,048,576 tokens through engine.fused_prefill, the hidden
+    # channels cut into N shards of whole filter groups (no collective: projections, attention and MLPs are not part of
+    # the path).  One "step" is one prefill of the whole stack.
+    "evo2_40b_hyena": dict(B=1, L=1048576, D=8192, G=512, K=-1, io="bf16", seed=4, stack=True, harness=True, n_each=14,
+                           prefill_only=True,
+                           name="Evo 2 40B-shaped Hyena stack (14 SE + 14 MR + 14 LI with 16 real poles per channel, hidden 8192): "
+                                "prefill of one sequence of 1,048,576 tokens through engine.fused_prefill, channel-sharded"),
 }
 
 
@@ -178,7 +186,8 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
     gc = torch.Generator().manual_seed(w["seed"])
     dims = (D, 1, D, 16, G)
     layers = []
-    for i, kind in enumerate(STACK_KINDS):
+    kinds = ["se", "mr", "li"] * w.get("n_each", 9)
+    for i, kind in enumerate(kinds):
         c = {"kind": kind, "eng": HyenaInferenceEngine(layer_idx=i),
              "w3": (torch.randn(3 * D, 1, 3, generator=gc) / 3 ** 0.5).bfloat16().to(dev)}
         if kind == "li":
@@ -192,8 +201,9 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
     fir_cache, iir_cache = HyenaCascadeFIRInferenceParams(), HyenaCascadeIIRInferenceParams()
     # one projection output stands for every layer's (values do not matter to the kernels' speed)
     u = torch.empty(B, L, 3 * D, device=dev, dtype=torch.bfloat16)
-    for b0 in range(0, B, 4):
-        u[b0:b0 + 4] = torch.randn(min(4, B - b0), L, 3 * D, device=dev, generator=g).bfloat16()
+    for b0 in range(B):
+        for t0 in range(0, L, 8192):
+            u[b0, t0:t0 + 8192] = torch.randn(min(8192, L - t0), 3 * D, device=dev, generator=g).bfloat16()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def prefill():
@@ -204,16 +214,34 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
 
     prefill()
     ops.device_status()
-    barrier()
-    ev0.record()
-    y = prefill()
-    ev1.record()
-    barrier()
-    ms_prefill = max_over_ranks(ev0.elapsed_time(ev1))
-    assert bool(torch.isfinite(y.float()).all())
-    pre_bytes = sum(8 * B * D * L + B * 3 * D * 4 + (B * D * 16 * 4 if k == "li" else B * D * ((7 if k == "se" else 128) - 1) * 2)
-                    for k in STACK_KINDS)
+    n_pre = max(1, min(a.steps, 3)) if w.get("prefill_only") else 1
+    with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as cs_pre:
+        barrier()
+        ev0.record()
+        for _ in range(n_pre):
+            y = prefill()
+        ev1.record()
+        barrier()
+    ms_prefill = max_over_ranks(ev0.elapsed_time(ev1)) / n_pre
+    assert bool(torch.isfinite(y[:, -4096:].float()).all())
+    pre_bytes = algorithmic_bytes(dict(w, decode=False, prefill_only=True, n_each=w.get("n_each", 9)))
     del y
+    if w.get("prefill_only"):
+        if rank != 0:
+            return None
+        peak, peak_kind = _peaks()
+        return {
+            "metric": "hyena_prefill_throughput", "value": full["B"] * L / (ms_prefill * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": n_pre, "warmup": 1, "ms_per_step": ms_prefill, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs_pre.summary(),
+            "gpu_launches": sum(3 if k == "li" else 1 for k in kinds) * n_pre,
+            "roofline": {"bound": "hbm", "achieved": pre_bytes / (ms_prefill * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": pre_bytes / (ms_prefill * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": pre_bytes,
+                         "note": "per rank and prefill of the whole stack (one fused launch per FIR layer, three per "
+                                 "per-channel long-filter layer): 8 bytes per hidden channel and token plus the caches"},
+            "collective": None, "e2e": None,
+        }
     tok = torch.randn(B, 3 * D, device=dev, generator=g).bfloat16()
 
     def decode_step():
@@ -221,6 +249,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
             ip = iir_cache if c["kind"] == "li" else fir_cache
             yd = c["eng"].fused_decode(tok, c["w3"], None, dims, ip, **c["kw"])
         return yd
+
 
     for _ in range(max(a.warmup, 3)):
         decode_step()                       # (the first step turns the prefill's bf16 caches into fp32 ones)
@@ -240,11 +269,12 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
     ms_step = ms / a.steps
     step_bytes = decode_bytes(dict(w, stack=True))
     tokens = full["B"]
+    kinds = None
     return {
         "metric": "hyena_decode_throughput", "value": tokens / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
-        "gpu_launches": len(STACK_KINDS) * a.steps,
+        "gpu_launches": 27 * a.steps,
         "roofline": {"bound": "hbm", "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": step_bytes,
@@ -274,6 +304,9 @@ def algorithmic_bytes(w):
     if w.get("decode"):
         return decode_bytes(w)
     B, L, D, K = w["B"], w["L"], w["D"], w["K"]
+    if w.get("prefill_only"):
+        return sum(8 * B * D * L + B * 3 * D * 4 + (B * D * 16 * 4 if k == "li" else B * D * ((7 if k == "se" else 128) - 1) * 2)
+                   for k in ["se", "mr", "li"] * w["n_each"])
     if w.get("cc1d"):
         return 12 * B * D * L
     if w.get("dropin"):
@@ -725,7 +758,7 @@ def main():
 
 
 # kernel launches of ours per step of each workload
-LAUNCHES = {"evo2_7b_hyena": len(STACK_KINDS), "mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
+LAUNCHES = {"evo2_40b_hyena": 70, "evo2_7b_hyena": len(STACK_KINDS), "mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.026e9, "se": 1.024e9, "mr_dropin": 2.407e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch

@@ -14,7 +14,8 @@
 // wide (4 x 16 channels, bf16 head | bf16 remainder of k*v).  The states at the four chunk starts follow from the
 // four increments by a short recurrence in registers (one warp owning lanes 96..127), are written back to shared
 // memory as bf16 head + remainder, and a second, short MMA sequence adds C S.  All operands that come from fp32 math
-// (taps, pole powers, states, k*v) are carried as bf16 head + remainder, which keeps ~16 bits.
+// (taps, pole powers, states, k*v) are carried as bf16 head + remainder, which keeps ~16 bits; the gate q crosses
+// shared memory as fp16 (11 bits: 2.8e-4, beside the 1.7e-3 of the output's own rounding; saturating at +-65504).
 //
 // The walk is aligned to the END of the sequence: the first step is padded in front with rows before the sequence start
 // (zeros, like the featurizer's own history), so the state after the last step is the state after the last token.
@@ -48,13 +49,12 @@ constexpr int BOX_ROWS = HROWS + 2 + (NS - 1);         // featurizer halo + stre
 constexpr int BOX_BYTES = BOX_ROWS * 3 * CH * 2;
 constexpr int IN_PLANE = (BOX_ROWS * 32 + 127) / 128 * 128;
 constexpr int BOX_STRIDE = 3 * IN_PLANE;
-constexpr int IN_STAGES = 3;
+constexpr int IN_STAGES = 4;
 constexpr int STAGE_BYTES = NS * BOX_STRIDE;
 constexpr int KV_TILE = CHUNK * 128;       // [96 rows][64 channels] bf16, 128-byte swizzle
-constexpr int QH_TILE = KV_TILE, QM_TILE = CHUNK * 64;
+constexpr int QH_TILE = KV_TILE;          // q as fp16 (11 significant bits: 2.8e-4, against 1.7e-3 of the output's own rounding)
 constexpr int S_TILE = 2 * NPOLE * 128;    // [32 state rows][64 channels] bf16, 128-byte swizzle
-constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE, QM_OFF = QH_OFF + QH_TILE, SH_OFF = QM_OFF + QM_TILE,
-              SL_OFF = SH_OFF + S_TILE;
+constexpr int HI_OFF = 0, LO_OFF = KV_TILE, QH_OFF = 2 * KV_TILE, SH_OFF = QH_OFF + QH_TILE, SL_OFF = SH_OFF + S_TILE;
 constexpr int SLOT_BYTES = SL_OFF + S_TILE;
 constexpr int NPW = CHUNK + 4;             // pole powers p^0 .. p^96 (padded)
 constexpr int NSLOT = 3;                   // a slot lives from the front end's stores to the end of its epilogue, i.e.
@@ -69,7 +69,7 @@ constexpr int OFF_DIAG = OFF_SLOTS + NSLOT * SLOT_BYTES;     // float [16]: skip
 constexpr int OFF_BARS = OFF_DIAG + 64;
 constexpr int NBARS = IN_STAGES * 2 + NSLOT * 3 + 2 * 3 + 1;
 constexpr int SMEM_BYTES = OFF_BARS + NBARS * 8 + 16 + 1024;
-static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0 && QH_OFF % 1024 == 0 && QM_OFF % 1024 == 0 &&
+static_assert(OFF_SLOTS % 1024 == 0 && SLOT_BYTES % 1024 == 0 && QH_OFF % 1024 == 0 &&
               SH_OFF % 1024 == 0 && SL_OFF % 1024 == 0, "tiles must be 1024-byte aligned");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 // TMEM columns: stacked [T; Bm] head and remainder (96 K elements = 48 columns each), [C; 0] head and remainder
@@ -247,7 +247,6 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                     w3[x][j] = pk2(ld_param(a.w3, a.w3_dtype, pc[0][x] * 3 + j), ld_param(a.w3, a.w3_dtype, pc[1][x] * 3 + j));
         }
         const uint32_t kv_chunk = (uint32_t)(s * 2 + p / 4), kv_in = (uint32_t)((p % 4) * 4);   // 16-byte chunk and offset of this lane's bf16 pair in a k*v row
-        const uint32_t qm_in = (uint32_t)(2 * p);                                          // this lane's two third-bytes in the 16-byte chunk s of a q row
         constexpr int ROWB = INTERLEAVED ? 96 : 32;             // bytes per staged row (per plane in the planar layouts)
         auto box_addr = [&](int k, int hb) {
             const int nh = 2 * k + w / (NFE / 2), stg = nh % IN_STAGES;
@@ -280,7 +279,6 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             // 4 (w & 1) resp. 2 (w & 1), is folded into the lane's chunk index once, the rest, (6 hb + i) & 7 resp.
             // ((6 hb + i) >> 1) & 3, is a compile-time constant of each store.
             const uint32_t kv_a0 = slot_u + ((kv_chunk ^ (uint32_t)((w & 1) * 4)) << 4) + kv_in + row0 * 128;
-            const uint32_t qm_a0 = slot_u + QM_OFF + (((uint32_t)s ^ (uint32_t)((w & 1) * 2)) << 4) + qm_in + row0 * 64;
             f32x2 x1[3], x2[3];
             unpack(raw[0], x2);
             unpack(raw[1], x1);
@@ -307,10 +305,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                 asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + LO_OFF), "r"(lo));
                 float q0, q1;
                 up2(q, q0, q1);
-                const uint32_t qh = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x7632);   // upper halves
-                const uint32_t qm = __byte_perm(__float_as_uint(q0), __float_as_uint(q1), 0x5151);   // third bytes
-                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + QH_OFF), "r"(qh));
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"((qm_a0 ^ (uint32_t)((((RB * hb + i) >> 1) & 3) << 4)) + i * 64), "h"((unsigned short)qm));
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(kaddr + QH_OFF), "r"(pack_f16(q0, q1)));
             }
         };
         auto stage_of = [&](int k) { return (2 * k + w / (NFE / 2)) % IN_STAGES; };
@@ -363,7 +358,6 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
             const uint32_t taddr = tmem + ((uint32_t)(e * 32) << 16) + D_COL + dbuf * 128;
             const uint8_t* slot_p = sm + OFF_SLOTS + slot * SLOT_BYTES;
             const uint8_t* qh_p = slot_p + QH_OFF + r * 128;
-            const uint8_t* qm_p = slot_p + QM_OFF + r * 64;
             const int64_t yoff = (int64_t)(kbase + k) * step_pitch;
             // (rolled over the four chunks: the unrolled form of this loop, with the skip term, does not fit the
             // instruction cache next to the other roles' loops)
@@ -399,19 +393,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_li_kernel(const __grid_const
                     }
                 }
                 uint32_t o[8];
-                const uint4 qm4 = *reinterpret_cast<const uint4*>(qm_p + ((s ^ ((r >> 1) & 3)) << 4));
-                const uint32_t qm[4] = {qm4.x, qm4.y, qm4.z, qm4.w};
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const uint4 qh4 = *reinterpret_cast<const uint4*>(qh_p + (((2 * s + hf) ^ (r & 7)) << 4));
                     const uint32_t qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {          // channels 8 hf + 2 j, + 1: third bytes 2 (j % 2), + 1 of word 2 hf + j / 2
-                        const uint32_t mw = qm[2 * hf + j / 2];
-                        const uint32_t qa = __byte_perm(qh[j], mw, (j % 2) ? 0x1066 : 0x1044);
-                        const uint32_t qb = __byte_perm(qh[j], mw, (j % 2) ? 0x3277 : 0x3255);
+                    for (int j = 0; j < 4; ++j) {          // channels 8 hf + 2 j, + 1
                         float o0, o1;
-                        up2(mul2(y[4 * hf + j], pk2(__uint_as_float(qa), __uint_as_float(qb))), o0, o1);
+                        up2(mul2(y[4 * hf + j], unpack_f16(qh[j])), o0, o1);
                         o[4 * hf + j] = pack_bf16(o0, o1);
                     }
                 }

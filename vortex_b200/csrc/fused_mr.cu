@@ -125,18 +125,6 @@ __device__ __forceinline__ Stream stream_of(const Args& a, int64_t quad, int s) 
     return st;
 }
 
-// two fp32 -> packed fp16 (lo in bits [15:0]), saturating at +-65504
-__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-// packed fp16 pair -> packed fp32 pair
-__device__ __forceinline__ f32x2 unpack_f16(uint32_t w) {
-    float lo, hi;
-    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w));
-    return pk2(lo, hi);
-}
 // instruction descriptor: f32 accumulate, A fp16 (K-major, from TMEM), B fp16 (N-major).  Both operands have the same
 // format: a descriptor that asked for bf16 x fp16 raised "illegal instruction" on this part.
 __device__ __forceinline__ uint32_t instr_desc_f16(int M, int N) {

@@ -106,5 +106,18 @@ __device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
     return d;
 }
 
+// two fp32 -> packed fp16 (lo in bits [15:0]), saturating at +-65504
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// packed fp16 pair -> packed fp32 pair
+__device__ __forceinline__ f32x2 unpack_f16(uint32_t w) {
+    float lo, hi;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w));
+    return pk2(lo, hi);
+}
+
 }  // namespace umma
 }  // namespace vtx
