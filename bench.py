@@ -226,6 +226,17 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
     assert bool(torch.isfinite(y[:, -4096:].float()).all())
     pre_bytes = algorithmic_bytes(dict(w, decode=False, prefill_only=True, n_each=w.get("n_each", 9)))
     del y
+    # the share of each kind of layer: its layers alone, timed the same way
+    per_kind = {}
+    for kind in ("se", "mr", "li"):
+        mine = [c for c in layers if c["kind"] == kind]
+        barrier()
+        ev0.record()
+        for c in mine:
+            c["eng"].fused_prefill(u, c["w3"], None, dims, inference_params=iir_cache if kind == "li" else fir_cache, **c["kw"])
+        ev1.record()
+        barrier()
+        per_kind[kind] = max_over_ranks(ev0.elapsed_time(ev1)) / len(mine)
     if w.get("prefill_only"):
         if rank != 0:
             return None
@@ -240,7 +251,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
                          "algorithmic_bytes_per_launch": pre_bytes,
                          "note": "per rank and prefill of the whole stack (one fused launch per FIR layer, three per "
                                  "per-channel long-filter layer): 8 bytes per hidden channel and token plus the caches"},
-            "collective": None, "e2e": None,
+            "ms_per_layer": per_kind, "collective": None, "e2e": None,
         }
     tok = torch.randn(B, 3 * D, device=dev, generator=g).bfloat16()
 
@@ -280,7 +291,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
                      "algorithmic_bytes_per_launch": step_bytes,
                      "note": "per rank and decode step (27 launches from Python, no CUDA graph): every cache read and "
                              "written once; host launch time is inside the figure"},
-        "prefill": {"ms": ms_prefill, "tokens_per_s": full["B"] * L / (ms_prefill * 1e-3),
+        "prefill": {"ms": ms_prefill, "ms_per_layer": per_kind, "tokens_per_s": full["B"] * L / (ms_prefill * 1e-3),
                     "frac_of_hbm_peak_per_rank": pre_bytes / (ms_prefill * 1e-3) / 1e9 / peak,
                     "note": "27 layers, one fused launch each (three for the per-channel long filter), caches written"},
         "collective": None, "e2e": None,

@@ -295,6 +295,12 @@ LI_CC_CASES = [
     (3, 1, 256, 256, 16, False, "f32", "interleaved", 1, False, False),     # single token
     (1, 70003, 32, 32, 16, False, "f32", "interleaved", 1, False, False),   # ~1100 time segments, ragged end
     (2, 777, 40, 40, 12, True, "f16", "interleaved", 1, False, False),      # fp16, channels not a multiple of 32
+    # rows staged by TMA (16-bit I/O, real poles, interleaved q/k/v, channels a multiple of 128)
+    (2, 1000, 128, 128, 16, False, "bf16", "interleaved", 1, False, False),
+    (1, 4099, 256, 256, 16, False, "bf16", "interleaved", 1, True, True),   # ragged end, q and k swapped, featurizer bias
+    (3, 5, 128, 128, 16, False, "bf16", "interleaved", 1, False, False),    # shorter than one stage
+    (1, 20011, 384, 48, 12, False, "f16", "interleaved", 1, False, False),  # fp16, systems shared by 8 channels, 12 poles
+    (2, 1, 128, 128, 16, False, "bf16", "interleaved", 1, True, False),     # single token
 ]
 
 
@@ -345,13 +351,15 @@ def test_fused_li_recurrence_vs_oracle(B, L, D, G, S, cplx, io, layout, heads, f
 
 
 @pytest.mark.parametrize("io,cplx,cuts", [("f32", False, (0, 300, 301, 1000)), ("bf16", True, (0, 2, 3, 640, 1000)),
-                                          ("bf16", False, (0, 512, 1000))])
+                                          ("bf16", False, (0, 512, 1000)), ("bf16", False, (0, 3, 700, 701, 2500))])
 def test_fused_li_chunked_prefill_carries_state(io, cplx, cuts):
     """Prefill in chunks, every call starting from the caches the previous one returned (featurizer rows and modal
     state), gives the output and the final caches of one call over the whole sequence."""
     from vortex_b200 import hyena_ops, ops
     B, D, G, S = 2, 64, (8 if cplx else 64), 16
     L = cuts[-1]
+    if L == 2500:
+        D = G = 128       # the kernels that stage rows by TMA
     p = make_block(53, B, L, D, G, 0, io, modal=True, S=S, complex_poles=cplx)
     pc = cuda(p)
     kw = dict(theta=pc.get("theta"), res_im=pc.get("res_im"), want_state=True)

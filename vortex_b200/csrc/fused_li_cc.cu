@@ -17,15 +17,21 @@
 // A call can continue an earlier one (chunked prefill): state_in is the modal state and fir_state_in the two
 // projection rows the earlier call ended with.
 #include "common.cuh"
+#include "tma.cuh"
 #include "umma.cuh"
 
 namespace vtx {
+
+VTX_DEFINE_STATUS_READER()
+
 namespace licc {
 
 using umma::f32x2;
 using umma::fma2;
 using umma::pk2;
 using umma::up2;
+using umma::add2;
+using umma::mul2;
 
 constexpr int NS = 16;         // states per thread (shorter systems are padded with p = R = 0)
 constexpr int THREADS = 128;
@@ -473,8 +479,330 @@ __global__ void __launch_bounds__(THREADS, VTX_LICC_MINB) licc_output_kernel(Arg
     }
 }
 
+
+// ---- phases A and C with rows staged by TMA (16-bit I/O, real poles, interleaved q/k/v, D a multiple of 128) ------
+// A CTA owns 128 neighbouring channels of one segment of one sequence.  The segment's rows (768 bytes per row: 128
+// channels x q,k,v) stream through a ring of shared-memory stages as two TMA boxes of 64 channels; the four warps read
+// their samples from the stage with constant offsets, so the arithmetic never waits on a global load and carries no
+// load buffers in registers.  There is no producer warp: the warp that is LAST to finish a stage (an arrival counter
+// in shared memory) re-arms the stage's barrier and issues the boxes that refill it, so no warp ever waits for a stage
+// to drain.  A warp takes the EVEN or the ODD channels of 64: a channel's three
+// 16-bit values (6 bytes) then sit in one aligned 32-bit word and one 16-bit half at the same place for every lane
+// (word first for even channels, half first for odd ones), which makes two conflict-free shared loads per sample.
+// ROLE names what the word's low half, its high half and the single half hold (flip_x1x2 swaps q and k):
+//   0: q k | v     1: k q | v     2: q | k v  (half first)     3: k | q v  (half first)
+constexpr int TC = 128;                     // channels per CTA
+constexpr int RS = 8;                       // rows per stage (every segment but the last is a multiple of it)
+constexpr int NST = 6;                      // stages in flight
+constexpr int HALF_ROW = 64 * 3 * 2;        // bytes of a row of one 64-channel box
+constexpr int HALF_BYTES = RS * HALF_ROW;
+constexpr int STAGE_BYTES = 2 * HALF_BYTES;
+constexpr int TTHREADS = 128;
+constexpr int MINB_A = 5, MINB_C = 4;      // resident CTAs per SM asked of the compiler: phase A, phase C
+
+template <typename T> __device__ __forceinline__ float lo_f32(uint32_t w);
+template <typename T> __device__ __forceinline__ float hi_f32(uint32_t w);
+template <> __device__ __forceinline__ float lo_f32<__nv_bfloat16>(uint32_t w) { return __uint_as_float(w << 16); }
+template <> __device__ __forceinline__ float hi_f32<__nv_bfloat16>(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+template <> __device__ __forceinline__ float lo_f32<__half>(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
+template <> __device__ __forceinline__ float hi_f32<__half>(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// arrival at a stage's counter; release / acquire so that the warp that sees the last arrival may overwrite the stage
+__device__ __forceinline__ uint32_t arrive_count(uint32_t addr) {
+    uint32_t old;
+    asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(addr) : "memory");
+    return old;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+// Raw bits of parameter i (run-time dtype) and their value: kept apart so that a thread can issue every load of its
+// set-up before it uses the first result (one memory round trip instead of one per parameter).
+__device__ __forceinline__ uint32_t ld_raw(const void* p, bool wide, int64_t i) {
+    return wide ? static_cast<const uint32_t*>(p)[i] : (uint32_t) static_cast<const unsigned short*>(p)[i];
+}
+__device__ __forceinline__ float cvt_raw(uint32_t raw, int64_t dtype) {
+    return dtype == VTX_F32 ? __uint_as_float(raw)
+           : dtype == VTX_BF16 ? __uint_as_float(raw << 16) : __half2float(__ushort_as_half((unsigned short)raw));
+}
+
+// Per-thread state of the staged kernels: the modal system as packed pairs, the featurizer of k and v as one packed
+// stream, the featurizer of q as a scalar one.  The output of a sample uses the state BEFORE the sample,
+//   y[t] = q[t] (sum_s (R_s p_s) sigma_s[t-1] + (sum_s R_s + bias) kv[t]),
+// so that its 8 packed FMAs do not wait for the 8 that advance the state.
+template <bool OUT>
+struct Lane {
+    f32x2 p2[NS / 2], c2[NS / 2], s2[NS / 2];      // poles, R p (OUT), states
+    f32x2 W0, W1, W2, WB, U1, U2;                  // featurizer of (k, v): taps, bias, the two samples before
+    float q0, q1, q2, qb, qu1, qu2;                // featurizer of q (OUT)
+    float direct;                                  // sum of residues + skip (OUT)
+};
+
+template <typename T, bool OUT, int ROLE>
+__device__ __forceinline__ void tma_segment(const CUtensorMap* tmu, const Args& a, Lane<OUT>& ln, int64_t b, int64_t d,
+                                            int64_t t0, int64_t t1, int x0, int lane, int par, int half, uint32_t stage0,
+                                            uint32_t full0, uint32_t cnt0) {
+    // position of q and of k in the channel's three packed values (v is the third)
+    constexpr int PQ = (ROLE & 1) ? 1 : 0, PK = 1 - PQ;
+    T* yp = OUT ? static_cast<T*>(a.y) + b * a.ysb + t0 * a.ysl + d : nullptr;
+    const int64_t ysl = a.ysl;
+    // byte offsets of the lane's word and half inside a row of its box
+    const uint32_t off_w = 12 * lane + (par ? 8 : 0), off_s = 12 * lane + (par ? 6 : 4);
+
+    // featurizer of one row: k*v and (OUT) q of the sample, from the lane's word and half
+    auto front = [&](uint32_t wd, uint32_t hs, float& x, float& q) {
+        const float fl = lo_f32<T>(wd), fh = hi_f32<T>(wd), fs = lo_f32<T>(hs);
+        // par 0: positions 0, 1 in the word, 2 in the half;  par 1: position 0 in the half, 1, 2 in the word
+        const float u_pos0 = (ROLE < 2) ? fl : fs, u_pos1 = (ROLE < 2) ? fh : fl, u_pos2 = (ROLE < 2) ? fs : fh;
+        const float uk = PK == 0 ? u_pos0 : u_pos1, uq = PQ == 0 ? u_pos0 : u_pos1;
+        const f32x2 u0 = pk2(uk, u_pos2);
+        const f32x2 z = fma2(ln.W2, u0, fma2(ln.W1, ln.U1, fma2(ln.W0, ln.U2, ln.WB)));
+        ln.U2 = ln.U1; ln.U1 = u0;
+        float zk, zv;
+        up2(z, zk, zv);
+        x = zk * zv;
+        if (OUT) {
+            q = fmaf(ln.q2, uq, fmaf(ln.q1, ln.qu1, fmaf(ln.q0, ln.qu2, ln.qb)));
+            ln.qu2 = ln.qu1; ln.qu1 = uq;
+        }
+    };
+    // the recurrence of one sample; returns the gated output (OUT)
+    auto back = [&](float x, float q) -> float {
+        const f32x2 x2 = pk2(x, x);
+        float y = 0.f;
+        if (OUT) {
+            f32x2 a0 = mul2(ln.c2[0], ln.s2[0]), a1 = mul2(ln.c2[1], ln.s2[1]);
+#pragma unroll
+            for (int j = 2; j < NS / 2; j += 2) {
+                a0 = fma2(ln.c2[j], ln.s2[j], a0);
+                a1 = fma2(ln.c2[j + 1], ln.s2[j + 1], a1);
+            }
+            float e0, e1;
+            up2(add2(a0, a1), e0, e1);
+            y = fmaf(ln.direct, x, e0 + e1) * q;
+        }
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) ln.s2[j] = fma2(ln.p2[j], ln.s2[j], x2);
+        return y;
+    };
+    // A stage in three sweeps over its rows: every shared load, every featurizer (independent between rows), then the
+    // recurrence with the stores.  Written out this way the loads of a row never sit behind the store of the row before.
+    auto stage_full = [&](uint32_t base) {
+        uint32_t wd[RS], hs[RS];
+        float x[RS], q[RS];
+#pragma unroll
+        for (int r = 0; r < RS; ++r) { wd[r] = lds32(base + r * HALF_ROW + off_w); hs[r] = lds16(base + r * HALF_ROW + off_s); }
+#pragma unroll
+        for (int r = 0; r < RS; ++r) front(wd[r], hs[r], x[r], q[r]);
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            const float y = back(x[r], q[r]);
+            if (OUT) { *yp = from_f32<T>(y); yp += ysl; }
+        }
+    };
+    auto sample = [&](uint32_t row) {
+        float x, q = 0.f;
+        front(lds32(row + off_w), lds16(row + off_s), x, q);
+        const float y = back(x, q);
+        if (OUT) { *yp = from_f32<T>(y); yp += ysl; }
+    };
+
+    const int nrows = (int)(t1 - t0), nfull = nrows / RS, rem = nrows - nfull * RS;
+    const int nstage = nfull + (rem ? 1 : 0);
+    for (int k = 0; k < nstage; ++k) {
+        const int st = k % NST;
+        if (!mbar_wait(full0 + 8 * st, (k / NST) & 1, 61)) return;
+        const uint32_t base = stage0 + st * STAGE_BYTES + half * HALF_BYTES;
+        if (k < nfull) {
+            stage_full(base);
+        } else {
+            for (int r = 0; r < rem; ++r) sample(base + r * HALF_ROW);
+        }
+        __syncwarp();
+        // the counter only grows: the fourth arrival of round k / NST finds 4 (k / NST) + 3
+        if (lane == 0 && arrive_count(cnt0 + 4 * st) == 4u * (uint32_t)(k / NST) + 3u && k + NST < nstage) {
+            mbar_expect_tx(full0 + 8 * st, STAGE_BYTES);
+            const uint32_t dst = stage0 + st * STAGE_BYTES;
+            const int y = (int)(t0 + (int64_t)(k + NST) * RS);
+            tma_load_3d(dst, tmu, full0 + 8 * st, x0, y, (int)b);
+            tma_load_3d(dst + HALF_BYTES, tmu, full0 + 8 * st, x0 + 3 * 64, y, (int)b);
+        }
+    }
+}
+
+template <typename T, bool OUT, int MINB>
+__global__ void __launch_bounds__(TTHREADS, MINB) licc_tma_kernel(const __grid_constant__ CUtensorMap tmu, Args a) {
+    __shared__ __align__(128) uint8_t stages[NST * STAGE_BYTES];
+    __shared__ __align__(8) uint64_t bars[NST];
+    __shared__ uint32_t counts[NST];
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t stage0 = smem_u32(stages), full0 = smem_u32(&bars[0]), cnt0 = smem_u32(&counts[0]);
+    // blockIdx = (segment, sequence, channel tile), channel tile fastest: neighbouring CTAs read neighbouring pieces of a row
+    const int64_t ntile = a.D / TC;
+    const int64_t tile = blockIdx.x % ntile, b = (blockIdx.x / ntile) % a.B, seg = blockIdx.x / (ntile * a.B);
+    const int64_t t0 = seg * a.pl.seg_len, t1 = t0 + a.pl.seg_len < a.L ? t0 + a.pl.seg_len : a.L;
+    const int half = (warp >> 1) & 1, par = warp & 1;
+    const int64_t d = tile * TC + half * 64 + 2 * lane + par, row = b * a.D + d, rows = a.B * a.D;
+    const int S = (int)a.m.S;
+
+    // ---- the first boxes, then every global load of the set-up, before anything waits
+    const int x0 = (int)(tile * 3 * TC);
+    if (tid == 0) {
+        for (int s = 0; s < NST; ++s) { mbar_init(full0 + 8 * s, 1); counts[s] = 0; }
+        fence_mbar_init();
+        const int nstage = (int)((t1 - t0 + RS - 1) / RS);
+        for (int k = 0; k < NST && k < nstage; ++k) {
+            mbar_expect_tx(full0 + 8 * k, STAGE_BYTES);
+            const uint32_t dst = stage0 + k * STAGE_BYTES;
+            tma_load_3d(dst, &tmu, full0 + 8 * k, x0, (int)(t0 + (int64_t)k * RS), (int)b);
+            tma_load_3d(dst + HALF_BYTES, &tmu, full0 + 8 * k, x0 + 3 * 64, (int)(t0 + (int64_t)k * RS), (int)b);
+        }
+    }
+    float lp[NS], rr[NS], st[NS];
+    uint32_t wraw[9], braw[3] = {0, 0, 0}, hraw[6] = {0, 0, 0, 0, 0, 0}, draw = 0;
+    const bool slow_hist = t0 < 2 && a.hist_rows < 2;       // the sequence starts here: rows of an earlier call, or zeros
+    {
+        const int64_t g = d / (a.D / a.m.G);
+        const float* lpp = static_cast<const float*>(a.m.log_poles) + g * S;
+        const float* rrp = static_cast<const float*>(a.m.res_re) + g * S;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            lp[s] = s < S ? lpp[s] : 0.f;
+            rr[s] = s < S ? rrp[s] : 0.f;
+            st[s] = 0.f;
+        }
+        if (OUT) {
+            if (seg > 0) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) if (s < S) st[s] = a.scratch[(seg * S + s) * rows + row];
+            } else if (a.state_in) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) if (s < S) st[s] = a.state_in[row * S + s];
+            }
+        }
+        const bool w_wide = a.w3_dtype == VTX_F32;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) wraw[i] = ld_raw(a.w3, w_wide, 9 * d + i);
+        if (a.b3) {
+            const bool b_wide = a.b3_dtype == VTX_F32;
+#pragma unroll
+            for (int i = 0; i < 3; ++i) braw[i] = ld_raw(a.b3, b_wide, 3 * d + i);
+        }
+        if (OUT && a.bias) draw = ld_raw(a.bias, a.bias_dtype == VTX_F32, d);
+        if (!slow_hist) {
+            const unsigned short* up = reinterpret_cast<const unsigned short*>(a.u) + b * a.sb + (t0 - 2) * a.sl + 3 * d;
+#pragma unroll
+            for (int i = 0; i < 3; ++i) { hraw[i] = up[i]; hraw[3 + i] = up[a.sl + i]; }      // rows t0-2 and t0-1
+        }
+    }
+    __syncthreads();
+
+    // ---- values
+    Lane<OUT> ln;
+    const int PQ = a.map.flip ? 1 : 0, PK = 1 - PQ;
+    float wv[9], bv[3], hv[6];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) wv[i] = cvt_raw(wraw[i], a.w3_dtype);
+#pragma unroll
+    for (int i = 0; i < 3; ++i) bv[i] = a.b3 ? cvt_raw(braw[i], a.b3_dtype) : 0.f;
+    if (slow_hist) {
+        // sample at time t < 0: this call's rows in front of u, else the rows the previous call ended with, else zero
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+            const int64_t c = 3 * d + i % 3, t = t0 - 2 + i / 3;
+            float v = 0.f;
+            if (t >= -a.hist_rows) v = to_f32<T>(static_cast<const T*>(a.u)[b * a.sb + t * a.sl + c]);
+            else if (a.fs_in) v = ld_param(a.fs_in, a.fs_dtype, (b * 3 * a.D + c) * 2 + (2 + t));
+            hv[i] = v;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 6; ++i) hv[i] = lo_f32<T>(hraw[i]);
+    }
+    // packed channel pos: taps wv[3 pos + tap], bias bv[pos], history hv[pos] (t0-2), hv[3 + pos] (t0-1)
+    ln.W0 = pk2(wv[3 * PK + 0], wv[6]); ln.W1 = pk2(wv[3 * PK + 1], wv[7]); ln.W2 = pk2(wv[3 * PK + 2], wv[8]);
+    ln.WB = pk2(bv[PK], bv[2]);
+    ln.U2 = pk2(hv[PK], hv[2]); ln.U1 = pk2(hv[3 + PK], hv[5]);
+    ln.q0 = wv[3 * PQ + 0]; ln.q1 = wv[3 * PQ + 1]; ln.q2 = wv[3 * PQ + 2]; ln.qb = bv[PQ];
+    ln.qu2 = hv[PQ]; ln.qu1 = hv[3 + PQ];
+    float rsum = 0.f;
+    {
+        float pm[NS], cm[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            pm[s] = s < S ? expf(lp[s]) : 0.f;
+            cm[s] = rr[s] * pm[s];
+            rsum += rr[s];
+        }
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) {
+            ln.p2[j] = pk2(pm[2 * j], pm[2 * j + 1]);
+            ln.c2[j] = pk2(cm[2 * j], cm[2 * j + 1]);
+            ln.s2[j] = pk2(st[2 * j], st[2 * j + 1]);
+        }
+    }
+    ln.direct = rsum + (OUT && a.bias ? cvt_raw(draw, a.bias_dtype) : 0.f);
+
+    switch (par * 2 + PQ) {
+        case 0: tma_segment<T, OUT, 0>(&tmu, a, ln, b, d, t0, t1, x0, lane, par, half, stage0, full0, cnt0); break;
+        case 1: tma_segment<T, OUT, 1>(&tmu, a, ln, b, d, t0, t1, x0, lane, par, half, stage0, full0, cnt0); break;
+        case 2: tma_segment<T, OUT, 2>(&tmu, a, ln, b, d, t0, t1, x0, lane, par, half, stage0, full0, cnt0); break;
+        default: tma_segment<T, OUT, 3>(&tmu, a, ln, b, d, t0, t1, x0, lane, par, half, stage0, full0, cnt0); break;
+    }
+    float* out = OUT ? (a.state && seg == a.pl.nseg - 1 ? a.state + row * S : nullptr) : a.scratch + (seg * S) * rows + row;
+    const int64_t stride = OUT ? 1 : rows;
+    if (out) {
+#pragma unroll
+        for (int j = 0; j < NS / 2; ++j) {
+            float lo, hi;
+            up2(ln.s2[j], lo, hi);
+            if (2 * j < S) out[(2 * j) * stride] = lo;
+            if (2 * j + 1 < S) out[(2 * j + 1) * stride] = hi;
+        }
+    }
+}
+
+// the staged kernels take bf16 / fp16 rows whose q, k, v are neighbours, 128 channels at a time
+static bool tma_path(const vtx_fused_iir_params* p) {
+    return (p->io_dtype == VTX_BF16 || p->io_dtype == VTX_F16) && !p->modal.theta && p->layout == VTX_QKV_INTERLEAVED &&
+           p->D % TC == 0 && reinterpret_cast<uintptr_t>(p->u) % 16 == 0 && (p->u_stride_l * 2) % 16 == 0 &&
+           (p->u_stride_b * 2) % 16 == 0 && p->L < ((int64_t)1 << 31) && p->B < 65536;
+}
+
+// Segments for the staged kernels.  A CTA is 128 channels of one segment; CTAs of a launch take the same time and run
+// in waves of (SMs x resident CTAs), so the cost of a plan is counted in waves: phase C over all segments, phase A
+// (about half the arithmetic per sample) over all but the last, each CTA paying a fixed set-up worth ~32 samples.
+// One segment means no phase A and no carries at all.
+static Plan plan_staged(int64_t B, int64_t L, int64_t D, bool have_scratch) {
+    Plan best{1, L};
+    if (!have_scratch) return best;
+    const int64_t base = B * (D / TC), slots_c = (int64_t)kNumSMs * MINB_C, slots_a = (int64_t)kNumSMs * MINB_A;
+    double best_cost = 0;
+    const int64_t max_seg = L / 64 < 1 ? 1 : (L / 64 > 4096 ? 4096 : L / 64);
+    for (int64_t n = 1; n <= max_seg; ++n) {
+        const int64_t seg = ceil_div<int64_t>(ceil_div<int64_t>(L, n), (int64_t)RS) * RS;
+        const int64_t nseg = ceil_div<int64_t>(L, seg);
+        if (nseg != n) continue;
+        const double cost = (double)ceil_div<int64_t>(base * nseg, slots_c) * (double)(seg + 32) +
+                            (nseg > 1 ? (double)ceil_div<int64_t>(base * (nseg - 1), slots_a) * (0.47 * (double)seg + 24.0) +
+                                            4.0 * (double)nseg        /* carry scan */
+                                      : 0.0);
+        if (best_cost == 0 || cost < best_cost) { best_cost = cost; best.nseg = nseg; best.seg_len = seg; }
+    }
+    return best;
+}
+
+static bool tma_path(const vtx_fused_iir_params* p);
+
 int64_t scratch_bytes(const vtx_fused_iir_params* p) {
-    const Plan pl = plan(p->B, p->L, p->D, true);
+    const Plan pl = tma_path(p) ? plan_staged(p->B, p->L, p->D, true) : plan(p->B, p->L, p->D, true);
     if (pl.nseg <= 1) return 0;
     return p->B * p->D * pl.nseg * p->modal.S * (p->modal.theta ? 2 : 1) * (int64_t)sizeof(float);
 }
@@ -502,11 +830,37 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_iir: bad num_heads");
         a.map.hd = p->D / p->num_heads;
     }
-    a.pl = plan(p->B, p->L, p->D, p->scratch != nullptr);
+    a.pl = tma_path(p) ? plan_staged(p->B, p->L, p->D, p->scratch != nullptr) : plan(p->B, p->L, p->D, p->scratch != nullptr);
     const bool cplx = p->modal.theta != nullptr;
     const int64_t n = p->B * p->D * a.pl.nseg;
     VTX_REQUIRE(ceil_div<int64_t>(n, THREADS) < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "fused_iir: problem too large");
     const unsigned blocks = (unsigned)ceil_div<int64_t>(n, THREADS);
+    if (tma_path(p)) {
+        CUtensorMap tmu;
+        if (int rc = make_tmap_3d(&tmu, p->u, p->io_dtype, 3 * p->D, p->L, p->B, p->u_stride_l, p->u_stride_b, 3 * 64, RS, 0,
+                                  "fused_iir"))
+            return rc;
+        const int64_t per_seg = p->B * (p->D / TC);
+        VTX_REQUIRE(per_seg * a.pl.nseg < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "fused_iir: problem too large");
+        if (p->io_dtype == VTX_BF16) {
+            using T = __nv_bfloat16;
+            if (a.pl.nseg > 1) {
+                licc_tma_kernel<T, false, MINB_A><<<(unsigned)(per_seg * (a.pl.nseg - 1)), TTHREADS, 0, stream>>>(tmu, a);
+                const int64_t nc = p->B * p->D * p->modal.S;
+                licc_carry_kernel<false><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);
+            }
+            licc_tma_kernel<T, true, MINB_C><<<(unsigned)(per_seg * a.pl.nseg), TTHREADS, 0, stream>>>(tmu, a);
+        } else {
+            using T = __half;
+            if (a.pl.nseg > 1) {
+                licc_tma_kernel<T, false, MINB_A><<<(unsigned)(per_seg * (a.pl.nseg - 1)), TTHREADS, 0, stream>>>(tmu, a);
+                const int64_t nc = p->B * p->D * p->modal.S;
+                licc_carry_kernel<false><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);
+            }
+            licc_tma_kernel<T, true, MINB_C><<<(unsigned)(per_seg * a.pl.nseg), TTHREADS, 0, stream>>>(tmu, a);
+        }
+        return check_launch("fused_iir");
+    }
     VTX_DISPATCH_IO(p->io_dtype, T, {
         if (a.pl.nseg > 1) {
             const unsigned ablocks = (unsigned)ceil_div<int64_t>(p->B * p->D * (a.pl.nseg - 1), THREADS);
