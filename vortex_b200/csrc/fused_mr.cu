@@ -103,7 +103,8 @@ struct Args {
     __nv_bfloat16* fir_state; __nv_bfloat16* inner_state;    // prefill caches, or null
     int64_t B, L, D, G, K;
     int64_t nseg, seg_len, nstream;        // streams per group = B * nseg
-    int64_t nquad, nitems;                 // stream quads per group; work items (group x quad) of the launch
+    int64_t nquad, nitems;                 // stream quads per group; work items (group x quad) of the call
+    int64_t item0, item1;                  // the items of this launch
     int layout, flip, taps, has_bias;
     int64_t hd;
     int hist;        // rows before u[b][0] that hold the sequence's earlier samples (the tensor map starts there)
@@ -174,11 +175,11 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
     // of the NEXT item into the other half of a double buffer while the current item streams, so the roles run
     // through the items without draining.  Per-role running counters give the barrier phases.
     const int ncta = (int)gridDim.x;
-    const int nmine = (int)((a.nitems - (int64_t)blockIdx.x + ncta - 1) / ncta);      // items blockIdx, blockIdx + ncta, ...
+    const int nmine = (int)((a.item1 - a.item0 - (int64_t)blockIdx.x + ncta - 1) / ncta);      // items item0 + blockIdx, + ncta, ...
     const int K = (int)a.K;
     const int nchunk = (int)(a.seg_len / CHUNK) + 1;     // chunk 0 of an item is its halo chunk (front end only)
-    auto item_group = [&](int t) { return (int)(((int64_t)blockIdx.x + (int64_t)t * ncta) % a.G); };
-    auto item_quad = [&](int t) { return (int)(((int64_t)blockIdx.x + (int64_t)t * ncta) / a.G); };
+    auto item_group = [&](int t) { return (int)((a.item0 + (int64_t)blockIdx.x + (int64_t)t * ncta) % a.G); };
+    auto item_quad = [&](int t) { return (int)((a.item0 + (int64_t)blockIdx.x + (int64_t)t * ncta) / a.G); };
 
     // ---------------- setup -------------------------------------------------------------------
     if (tid == 0) {
@@ -752,8 +753,25 @@ static int launch(Kern kern, int variant, int smem_bytes, const CUtensorMap& tq,
         if (nres <= 0) return fail(VTX_ERR_LAUNCH, "fused_fir(mr): the kernel does not fit an SM (%d SMs, %d blocks each)", sms, per_sm);
         if (known) resident[dev][variant] = nres;
     }
-    const int64_t ncta = a.nitems < nres ? a.nitems : nres;
-    kern<<<(unsigned)ncta, THREADS, smem_bytes, stream>>>(tq, tk, tv, a);
+    // The CTAs of a launch start side by side on neighbouring groups of the same rows: their 96-byte pieces of a row
+    // share 128-byte lines and DRAM pages.  Nothing holds them together afterwards, and over a few milliseconds they
+    // drift apart; measured on a 1 M-token sequence of 8192 channels, one launch of 66 items per CTA ran at half the
+    // speed of the same items in launches of a few milliseconds each.  So a call is cut into launches of about
+    // 500 chunks per CTA (250 and 500 measured alike, 1000 a little slower on the short filter, 2000 clearly slower);
+    // each starts its CTAs side by side again.
+    const int64_t nchunk = a.seg_len / CHUNK + 1;
+#ifndef VTX_MR_LAUNCH_CHUNKS
+#define VTX_MR_LAUNCH_CHUNKS 500
+#endif
+    int64_t rounds = VTX_MR_LAUNCH_CHUNKS / nchunk;
+    if (rounds < 1) rounds = 1;
+    Args b = a;
+    for (int64_t i0 = 0; i0 < a.nitems; i0 += rounds * nres) {
+        b.item0 = i0;
+        b.item1 = i0 + rounds * nres < a.nitems ? i0 + rounds * nres : a.nitems;
+        const int64_t n = b.item1 - b.item0, ncta = n < nres ? n : nres;
+        kern<<<(unsigned)ncta, THREADS, smem_bytes, stream>>>(tq, tk, tv, b);
+    }
     return check_launch("fused_fir(mr)");
 }
 
