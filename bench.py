@@ -215,6 +215,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
     prefill()
     ops.device_status()
     n_pre = max(1, min(a.steps, 3)) if w.get("prefill_only") else 1
+    c0 = ops.launch_count()
     with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as cs_pre:
         barrier()
         ev0.record()
@@ -222,6 +223,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
             y = prefill()
         ev1.record()
         barrier()
+    launches_pre = ops.launch_count() - c0
     ms_prefill = max_over_ranks(ev0.elapsed_time(ev1)) / n_pre
     assert bool(torch.isfinite(y[:, -4096:].float()).all())
     pre_bytes = algorithmic_bytes(dict(w, decode=False, prefill_only=True, n_each=w.get("n_each", 9)))
@@ -245,7 +247,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
             "metric": "hyena_prefill_throughput", "value": full["B"] * L / (ms_prefill * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": n_pre, "warmup": 1, "ms_per_step": ms_prefill, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs_pre.summary(),
-            "gpu_launches": sum(3 if k == "li" else 1 for k in kinds) * n_pre,
+            "gpu_launches": launches_pre,
             "roofline": {"bound": "hbm", "achieved": pre_bytes / (ms_prefill * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": pre_bytes / (ms_prefill * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                          "algorithmic_bytes_per_launch": pre_bytes,
@@ -265,6 +267,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
     for _ in range(max(a.warmup, 3)):
         decode_step()                       # (the first step turns the prefill's bf16 caches into fp32 ones)
     ops.device_status()
+    c0 = ops.launch_count()
     with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as cs:
         barrier()
         ev0.record()
@@ -272,6 +275,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
             yd = decode_step()
         ev1.record()
         barrier()
+    launches = ops.launch_count() - c0
     ms = max_over_ranks(ev0.elapsed_time(ev1))
     assert bool(torch.isfinite(yd.float()).all())
     if rank != 0:
@@ -285,7 +289,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
         "metric": "hyena_decode_throughput", "value": tokens / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": cs.summary(),
-        "gpu_launches": 27 * a.steps,
+        "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": step_bytes,
@@ -623,6 +627,9 @@ def main():
     for _ in range(a.warmup):
         y = step()
     ops.device_status()
+    c0 = ops.launch_count()
+    y = step()
+    launches_per_step = ops.launch_count() - c0      # the library's own count of the kernels one step launches
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     graph = None
@@ -742,7 +749,6 @@ def main():
             dist.destroy_process_group()
         return
     peak, peak_kind = _peaks()
-    launches_per_step = LAUNCHES.get(a.workload, 1)
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
     traffic = NCU_TRAFFIC.get(a.workload)
     if traffic is not None:
@@ -769,7 +775,6 @@ def main():
 
 
 # kernel launches of ours per step of each workload
-LAUNCHES = {"evo2_40b_hyena": 70, "evo2_7b_hyena": len(STACK_KINDS), "mr_dropin": 2, "se_cfg1": 1, "mr": 1, "se": 1, "li": 1, "li_pc": 3, "cc1d": 1, "decode_mr": 1, "decode_se": 1, "decode_li": 1, "decode_stack": len(STACK_KINDS)}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"mr": 1.026e9, "se": 1.024e9, "mr_dropin": 2.407e9, "li": 4.13e9, "cc1d": 1.44e9}   # small-case captures scaled by the units of a bench launch

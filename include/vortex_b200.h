@@ -60,7 +60,7 @@ enum { VTX_BIAS_NONE = 0, VTX_BIAS_ADD = 1, VTX_BIAS_GATED = 2 /* + bias[d] * kv
 size_t vtx_last_error(char* buf, size_t len);
 /* ABI version of this header: major * 1000 + minor.  vtx_abi_version() returns the value the library was
  * built with; a binding compares the two (same major, library minor >= the minor it was written for). */
-#define VTX_ABI_VERSION 1003
+#define VTX_ABI_VERSION 1004
 int64_t vtx_abi_version(void);
 /* sizeof() of the parameter structs in declaration order (0 = vtx_featurizer_params, ...),
  * -1 past the end; lets a binding verify that its mirror of a struct has the same size. */
@@ -69,6 +69,9 @@ int64_t vtx_struct_size(int64_t which);
  * (mbarrier / TMA completion) ran out.  Synchronous (a small device-to-host copy); meant to be
  * called after the stream was synchronised.  Returns VTX_OK or VTX_ERR_DEVICE. */
 int vtx_device_status(void);
+/* Kernels launched by this library since it was loaded (all entry points, all threads).  A caller that wants the
+ * launches of a region reads it before and after.  No counterpart in the reference. */
+int64_t vtx_launch_count(void);
 /* Diagnostics: how often a kernel polls a global-memory flag written by another block (the hand-over between the
  * time slices of one long-filter walk) before it gives up, sets the status word and carries on with what it has.
  * 0 restores the default (2^21 polls with a short sleep each, far beyond any real wait).  A tiny value makes the

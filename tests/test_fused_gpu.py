@@ -617,3 +617,22 @@ def test_device_status_reports_a_wait_that_ran_out():
     ops.device_status()                      # the word was cleared by the read above
     assert torch.equal(run(), good)
     ops.device_status()
+
+
+@pytest.mark.gpu
+def test_launch_count_follows_the_kernels_a_call_launches():
+    """vtx_launch_count: one launch for a short-filter block, three (segment states, carries, outputs) for a long-filter
+    block whose sequence is cut into segments, one when a single segment covers it."""
+    from vortex_b200 import hyena_ops, ops
+    p = cuda(make_block(3, 2, 4096, 128, 8, 7, "bf16"))
+    c0 = ops.launch_count()
+    hyena_ops.hyena_se_fwd(p["u"], p["w3"], None, p["h"], want_state=False)
+    assert ops.launch_count() - c0 == 1
+    q = cuda(make_block(4, 1, 8192, 128, 128, 0, "bf16", modal=True, S=16, complex_poles=False))
+    c0 = ops.launch_count()
+    hyena_ops.hyena_li_fwd(q["u"], q["w3"], None, q["log_poles"], q["residues"], q["Dp"], want_state=False)
+    assert ops.launch_count() - c0 == 3
+    c0 = ops.launch_count()
+    hyena_ops.hyena_li_fwd(q["u"][:, :64], q["w3"], None, q["log_poles"], q["residues"], q["Dp"], want_state=False)
+    assert ops.launch_count() - c0 == 1
+    ops.device_status()

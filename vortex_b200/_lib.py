@@ -132,6 +132,7 @@ SYMBOLS = {
     "vtx_struct_size": (_i, [_i]),
     "vtx_device_status": (C.c_int, []),
     "vtx_debug_set_flag_poll_limit": (C.c_int, [_i]),
+    "vtx_launch_count": (C.c_int64, []),
     "vtx_featurizer_fwd": (C.c_int, [C.POINTER(FeaturizerParams), _p]),
     "vtx_gcg_fwd": (C.c_int, [C.POINTER(GcgParams), _p]),
     "vtx_gcg_cl_fwd": (C.c_int, [C.POINTER(GcgClParams), _p]),

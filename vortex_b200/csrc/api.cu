@@ -1,4 +1,5 @@
 // Error plumbing and ABI version of the vortex_b200 C ABI.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -16,7 +17,9 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-int check_launch(const char* what) {
+static std::atomic<long long> g_launches{0};
+int check_launch(const char* what, long long launches) {
+    g_launches.fetch_add(launches, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(VTX_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
     return VTX_OK;
@@ -111,6 +114,8 @@ extern "C" int vtx_device_status(void) {
     if (worst) vtx::fail(VTX_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", worst);
     return worst ? VTX_ERR_DEVICE : VTX_OK;
 }
+
+extern "C" int64_t vtx_launch_count(void) { return (int64_t)vtx::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int vtx_debug_set_flag_poll_limit(int64_t polls) {
     if (polls < 0 || polls > (1 << 30)) return vtx::fail(VTX_ERR_BAD_ARG, "flag poll limit out of range");

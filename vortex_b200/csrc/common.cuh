@@ -15,7 +15,8 @@ namespace vtx {
 
 // ---- error plumbing -------------------------------------------------------
 int fail(int code, const char* fmt, ...);   // records the message for vtx_last_error, returns code
-int check_launch(const char* what);         // cudaGetLastError -> VTX_ERR_LAUNCH
+// cudaGetLastError -> VTX_ERR_LAUNCH; adds the kernels the caller just launched to the count vtx_launch_count() reports
+int check_launch(const char* what, long long launches = 1);
 
 #define VTX_REQUIRE(cond, code, ...)            \
     do {                                        \

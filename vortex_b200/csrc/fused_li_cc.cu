@@ -859,7 +859,7 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
             }
             licc_tma_kernel<T, true, MINB_C><<<(unsigned)(per_seg * a.pl.nseg), TTHREADS, 0, stream>>>(tmu, a);
         }
-        return check_launch("fused_iir");
+        return check_launch("fused_iir", a.pl.nseg > 1 ? 3 : 1);
     }
     VTX_DISPATCH_IO(p->io_dtype, T, {
         if (a.pl.nseg > 1) {
@@ -876,7 +876,7 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
         else if (inter) licc_output_kernel<T, false, true><<<blocks, THREADS, 0, stream>>>(a);
         else licc_output_kernel<T, false, false><<<blocks, THREADS, 0, stream>>>(a);
     });
-    return check_launch("fused_iir");
+    return check_launch("fused_iir", a.pl.nseg > 1 ? 3 : 1);
 }
 
 }  // namespace licc

@@ -766,13 +766,14 @@ static int launch(Kern kern, int variant, int smem_bytes, const CUtensorMap& tq,
     int64_t rounds = VTX_MR_LAUNCH_CHUNKS / nchunk;
     if (rounds < 1) rounds = 1;
     Args b = a;
-    for (int64_t i0 = 0; i0 < a.nitems; i0 += rounds * nres) {
+    long long launches = 0;
+    for (int64_t i0 = 0; i0 < a.nitems; i0 += rounds * nres, ++launches) {
         b.item0 = i0;
         b.item1 = i0 + rounds * nres < a.nitems ? i0 + rounds * nres : a.nitems;
         const int64_t n = b.item1 - b.item0, ncta = n < nres ? n : nres;
         kern<<<(unsigned)ncta, THREADS, smem_bytes, stream>>>(tq, tk, tv, b);
     }
-    return check_launch("fused_fir(mr)");
+    return check_launch("fused_fir(mr)", launches);
 }
 
 }  // namespace mr

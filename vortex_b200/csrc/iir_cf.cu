@@ -377,7 +377,7 @@ extern "C" int vtx_iir_fwd(const vtx_iir_params* p, void* stream) {
         if (cplx) iir_output_kernel<T, true><<<blocks, ITHREADS, 0, s>>>(*p, pl);
         else iir_output_kernel<T, false><<<blocks, ITHREADS, 0, s>>>(*p, pl);
     });
-    return check_launch("iir");
+    return check_launch("iir", pl.nseg > 1 ? 3 : 1);
 }
 
 extern "C" int vtx_iir_recurrence_fwd(const vtx_iir_params* p, void* stream) {

@@ -71,6 +71,11 @@ def device_status() -> None:
     _lib.check(_lib.lib().vtx_device_status())
 
 
+def launch_count() -> int:
+    """Kernels this library has launched since it was loaded (read it before and after a region to count its launches)."""
+    return int(_lib.lib().vtx_launch_count())
+
+
 # ----------------------------------------------------------------------------------------------
 def featurizer_fwd(u_blc: torch.Tensor, w: torch.Tensor, bias=None, mask=None, want_state=True):
     """u_blc: logical [B, L, C] (any strides).  Returns z [B, C, L] and state [B, C, min(L,K-1)] or None."""
