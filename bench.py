@@ -214,7 +214,7 @@ def run_harness(a, w, full, dev, rank, world, config, max_over_ranks, barrier):
 
     prefill()
     ops.device_status()
-    n_pre = max(1, min(a.steps, 3)) if w.get("prefill_only") else 1
+    n_pre = max(1, min(a.steps, 3))
     c0 = ops.launch_count()
     with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as cs_pre:
         barrier()

@@ -301,6 +301,10 @@ LI_CC_CASES = [
     (3, 5, 128, 128, 16, False, "bf16", "interleaved", 1, False, False),    # shorter than one stage
     (1, 20011, 384, 48, 12, False, "f16", "interleaved", 1, False, False),  # fp16, systems shared by 8 channels, 12 poles
     (2, 1, 128, 128, 16, False, "bf16", "interleaved", 1, True, False),     # single token
+    # two channels per thread (channels a multiple of 256, no featurizer bias)
+    (2, 3001, 256, 256, 16, False, "bf16", "interleaved", 1, False, False),
+    (1, 9000, 512, 64, 12, False, "f16", "interleaved", 1, True, False),    # fp16, q and k swapped, shared systems, 12 poles
+    (3, 2, 256, 256, 16, False, "bf16", "interleaved", 1, False, False),    # two tokens
 ]
 
 
@@ -351,7 +355,8 @@ def test_fused_li_recurrence_vs_oracle(B, L, D, G, S, cplx, io, layout, heads, f
 
 
 @pytest.mark.parametrize("io,cplx,cuts", [("f32", False, (0, 300, 301, 1000)), ("bf16", True, (0, 2, 3, 640, 1000)),
-                                          ("bf16", False, (0, 512, 1000)), ("bf16", False, (0, 3, 700, 701, 2500))])
+                                          ("bf16", False, (0, 512, 1000)), ("bf16", False, (0, 3, 700, 701, 2500)),
+                                          ("bf16", False, (0, 2, 900, 2501))])
 def test_fused_li_chunked_prefill_carries_state(io, cplx, cuts):
     """Prefill in chunks, every call starting from the caches the previous one returned (featurizer rows and modal
     state), gives the output and the final caches of one call over the whole sequence."""
@@ -360,6 +365,8 @@ def test_fused_li_chunked_prefill_carries_state(io, cplx, cuts):
     L = cuts[-1]
     if L == 2500:
         D = G = 128       # the kernels that stage rows by TMA
+    if L == 2501:
+        D = G = 256       # ... with two channels per thread
     p = make_block(53, B, L, D, G, 0, io, modal=True, S=S, complex_poles=cplx)
     pc = cuda(p)
     kw = dict(theta=pc.get("theta"), res_im=pc.get("res_im"), want_state=True)

@@ -45,11 +45,12 @@ constexpr int TB = VTX_LICC_TB;   // samples per software-pipeline block
 
 struct Plan {
     int64_t nseg, seg_len;
+    int pairs_a, pairs_c;      // staged kernels only: phase A / phase C run two channels per thread
 };
 
 // Segments per channel: about four rounds of resident threads over the SMs, segments of at least 64 samples.
 static Plan plan(int64_t B, int64_t L, int64_t D, bool have_scratch) {
-    Plan pl{1, L};
+    Plan pl{1, L, 0, 0};
     if (!have_scratch) return pl;
     const int64_t rows = B * D, want = (int64_t)kNumSMs * 640 * 4;
     int64_t nseg = ceil_div<int64_t>(want, rows);
@@ -769,40 +770,243 @@ __global__ void __launch_bounds__(TTHREADS, MINB) licc_tma_kernel(const __grid_c
     }
 }
 
+// ---- the same two phases with TWO channels per thread, packed ACROSS the channels ------------------------------
+// A lane owns a channel pair (12 bytes of a row: three aligned words); every value of the recurrence is an f32x2 of
+// the two channels, so the k*v product is born packed (no broadcast move), the q featurizer is packed too, a sample
+// costs three shared loads, six conversions and one 4-byte store per PAIR, and the two outputs leave as one bf16x2.
+// Per sample and channel that is 52 issue cycles in C and 27 in A against 67 and 33 of the kernel above, at twice the
+// registers (three resident CTAs per SM in C, four in A).  A warp streams its own 64 channels through its own ring of
+// stages: no barrier is shared between warps.  Needs D a multiple of 256 and no featurizer bias.
+// Measured (B=1, L=131072, D=4096): 1.67 ms with both phases this way, 1.86 ms with phase A only, 1.93 ms with
+// neither.  The segment plan picks the form of each phase (both read the same plan and the same scratch).
+constexpr int TC2 = 256;                    // channels per CTA
+constexpr int NST2 = 3;                     // stages in flight per warp
+constexpr int BOX2_BYTES = RS * HALF_ROW;   // one stage of one warp: RS rows of 64 channels
+constexpr int MINB2_A = 4, MINB2_C = 3;
+
+template <typename T> __device__ __forceinline__ uint32_t pack_io(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_io<__nv_bfloat16>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+template <> __device__ __forceinline__ uint32_t pack_io<__half>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <typename T, bool OUT, bool FLIP, int MINB>
+__global__ void __launch_bounds__(TTHREADS, MINB) licc_tma2_kernel(const __grid_constant__ CUtensorMap tmu, Args a) {
+    __shared__ __align__(128) uint8_t stages[4 * NST2 * BOX2_BYTES];
+    __shared__ __align__(8) uint64_t bars[4 * NST2];
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t stage0 = smem_u32(stages) + warp * NST2 * BOX2_BYTES, full0 = smem_u32(&bars[warp * NST2]);
+    const int64_t ntile = a.D / TC2;
+    const int64_t tile = blockIdx.x % ntile, b = (blockIdx.x / ntile) % a.B, seg = blockIdx.x / (ntile * a.B);
+    const int64_t t0 = seg * a.pl.seg_len, t1 = t0 + a.pl.seg_len < a.L ? t0 + a.pl.seg_len : a.L;
+    const int64_t d0 = tile * TC2 + warp * 64 + 2 * lane, row0 = b * a.D + d0, rows = a.B * a.D;
+    const int S = (int)a.m.S;
+    const int nrows = (int)(t1 - t0), nfull = nrows / RS, rem = nrows - nfull * RS, nstage = nfull + (rem ? 1 : 0);
+    const int x0 = (int)(tile * 3 * TC2 + warp * 3 * 64);
+
+    // ---- the warp's first boxes, then every global load of the set-up, before anything waits
+    if (lane == 0) {
+        for (int k = 0; k < NST2; ++k) mbar_init(full0 + 8 * k, 1);
+        fence_mbar_init();
+        for (int k = 0; k < NST2 && k < nstage; ++k) {
+            mbar_expect_tx(full0 + 8 * k, BOX2_BYTES);
+            tma_load_3d(stage0 + k * BOX2_BYTES, &tmu, full0 + 8 * k, x0, (int)(t0 + (int64_t)k * RS), (int)b);
+        }
+    }
+    float lp[2][NS], rr[2][NS], st[2][NS];
+    uint32_t wraw[18], hraw[12], draw[2] = {0, 0};
+    const bool slow_hist = t0 < 2 && a.hist_rows < 2;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int64_t g = (d0 + c) / (a.D / a.m.G);
+        const float* lpp = static_cast<const float*>(a.m.log_poles) + g * S;
+        const float* rrp = static_cast<const float*>(a.m.res_re) + g * S;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            lp[c][s] = s < S ? lpp[s] : 0.f;
+            rr[c][s] = s < S ? rrp[s] : 0.f;
+            st[c][s] = 0.f;
+        }
+        if (OUT) {
+            if (seg > 0) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) if (s < S) st[c][s] = a.scratch[(seg * S + s) * rows + row0 + c];
+            } else if (a.state_in) {
+#pragma unroll
+                for (int s = 0; s < NS; ++s) if (s < S) st[c][s] = a.state_in[(row0 + c) * S + s];
+            }
+        }
+        if (OUT && a.bias) draw[c] = ld_raw(a.bias, a.bias_dtype == VTX_F32, d0 + c);
+    }
+    {
+        const bool w_wide = a.w3_dtype == VTX_F32;
+#pragma unroll
+        for (int i = 0; i < 18; ++i) wraw[i] = ld_raw(a.w3, w_wide, 9 * d0 + i);
+        if (!slow_hist) {
+            const unsigned short* up = reinterpret_cast<const unsigned short*>(a.u) + b * a.sb + (t0 - 2) * a.sl + 3 * d0;
+#pragma unroll
+            for (int i = 0; i < 6; ++i) { hraw[i] = up[i]; hraw[6 + i] = up[a.sl + i]; }      // rows t0-2 and t0-1
+        }
+    }
+    __syncwarp();
+
+    // ---- values: everything as pairs (channel d0, channel d0 + 1)
+    constexpr int PQ = FLIP ? 1 : 0, PK = 1 - PQ;
+    float hv[12];
+    if (slow_hist) {
+#pragma unroll
+        for (int i = 0; i < 12; ++i) {
+            const int64_t c = 3 * d0 + i % 6, t = t0 - 2 + i / 6;
+            float v = 0.f;
+            if (t >= -a.hist_rows) v = to_f32<T>(static_cast<const T*>(a.u)[b * a.sb + t * a.sl + c]);
+            else if (a.fs_in) v = ld_param(a.fs_in, a.fs_dtype, (b * 3 * a.D + c) * 2 + (2 + t));
+            hv[i] = v;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 12; ++i) hv[i] = lo_f32<T>(hraw[i]);
+    }
+    // packed position pos of channel c: taps wraw[9 c + 3 pos + tap], history hv[3 c + pos] (t0-2), hv[6 + 3 c + pos] (t0-1)
+    auto tap2 = [&](int pos, int tap) {
+        return pk2(cvt_raw(wraw[3 * pos + tap], a.w3_dtype), cvt_raw(wraw[9 + 3 * pos + tap], a.w3_dtype));
+    };
+    f32x2 Wk[3], Wv[3], Wq[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) { Wk[j] = tap2(PK, j); Wv[j] = tap2(2, j); Wq[j] = tap2(PQ, j); }
+    f32x2 Uk2 = pk2(hv[PK], hv[3 + PK]), Uk1 = pk2(hv[6 + PK], hv[9 + PK]);
+    f32x2 Uv2 = pk2(hv[2], hv[5]), Uv1 = pk2(hv[8], hv[11]);
+    f32x2 Uq2 = pk2(hv[PQ], hv[3 + PQ]), Uq1 = pk2(hv[6 + PQ], hv[9 + PQ]);
+    f32x2 p2[NS], c2[OUT ? NS : 1], s2[NS];
+    float rsum0 = 0.f, rsum1 = 0.f;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        const float pa = s < S ? expf(lp[0][s]) : 0.f, pb = s < S ? expf(lp[1][s]) : 0.f;
+        p2[s] = pk2(pa, pb);
+        if (OUT) c2[s] = pk2(rr[0][s] * pa, rr[1][s] * pb);
+        s2[s] = pk2(st[0][s], st[1][s]);
+        rsum0 += rr[0][s]; rsum1 += rr[1][s];
+    }
+    const f32x2 direct = pk2(rsum0 + (OUT && a.bias ? cvt_raw(draw[0], a.bias_dtype) : 0.f),
+                             rsum1 + (OUT && a.bias ? cvt_raw(draw[1], a.bias_dtype) : 0.f));
+    uint32_t* yp = OUT ? reinterpret_cast<uint32_t*>(static_cast<T*>(a.y) + b * a.ysb + t0 * a.ysl + d0) : nullptr;
+    const int64_t ysl2 = a.ysl / 2;                 // row pitch in 4-byte words (rows are 4-byte aligned: checked by the host)
+    const uint32_t off = 12 * lane;
+
+    auto sample = [&](uint32_t rowaddr) {
+        const uint32_t w0 = lds32(rowaddr + off), w1 = lds32(rowaddr + off + 4), w2 = lds32(rowaddr + off + 8);
+        // channel d0: positions 0, 1 in w0, 2 in the low half of w1; channel d0 + 1: 0 in the high half of w1, 1, 2 in w2
+        const f32x2 P0 = pk2(lo_f32<T>(w0), hi_f32<T>(w1)), P1 = pk2(hi_f32<T>(w0), lo_f32<T>(w2)),
+                    P2 = pk2(lo_f32<T>(w1), hi_f32<T>(w2));
+        const f32x2 uk = PK == 0 ? P0 : P1, uq = PQ == 0 ? P0 : P1;
+        const f32x2 zk = fma2(Wk[2], uk, fma2(Wk[1], Uk1, mul2(Wk[0], Uk2)));
+        const f32x2 zv = fma2(Wv[2], P2, fma2(Wv[1], Uv1, mul2(Wv[0], Uv2)));
+        Uk2 = Uk1; Uk1 = uk; Uv2 = Uv1; Uv1 = P2;
+        const f32x2 x2 = mul2(zk, zv);
+        if (OUT) {
+            const f32x2 zq = fma2(Wq[2], uq, fma2(Wq[1], Uq1, mul2(Wq[0], Uq2)));
+            Uq2 = Uq1; Uq1 = uq;
+            f32x2 a0 = mul2(c2[0], s2[0]), a1 = mul2(c2[1], s2[1]);
+#pragma unroll
+            for (int j = 2; j < NS; j += 2) {
+                a0 = fma2(c2[j], s2[j], a0);
+                a1 = fma2(c2[j + 1], s2[j + 1], a1);
+            }
+#pragma unroll
+            for (int j = 0; j < NS; ++j) s2[j] = fma2(p2[j], s2[j], x2);
+            float y0, y1;
+            up2(mul2(fma2(direct, x2, add2(a0, a1)), zq), y0, y1);
+            *yp = pack_io<T>(y0, y1);
+            yp += ysl2;
+        } else {
+#pragma unroll
+            for (int j = 0; j < NS; ++j) s2[j] = fma2(p2[j], s2[j], x2);
+        }
+    };
+
+    for (int k = 0; k < nstage; ++k) {
+        const int sl = k % NST2;
+        if (!mbar_wait(full0 + 8 * sl, (k / NST2) & 1, 63)) return;
+        const uint32_t base = stage0 + sl * BOX2_BYTES;
+        if (k < nfull) {
+#pragma unroll
+            for (int r = 0; r < RS; ++r) sample(base + r * HALF_ROW);
+        } else {
+            for (int r = 0; r < rem; ++r) sample(base + r * HALF_ROW);
+        }
+        __syncwarp();
+        if (lane == 0 && k + NST2 < nstage) {
+            mbar_expect_tx(full0 + 8 * sl, BOX2_BYTES);
+            tma_load_3d(base, &tmu, full0 + 8 * sl, x0, (int)(t0 + (int64_t)(k + NST2) * RS), (int)b);
+        }
+    }
+    float* out = OUT ? (a.state && seg == a.pl.nseg - 1 ? a.state + row0 * S : nullptr) : a.scratch + (seg * S) * rows + row0;
+    if (out) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            float lo, hi;
+            up2(s2[s], lo, hi);
+            if (s < S) {
+                if (OUT) { out[s] = lo; out[S + s] = hi; }
+                else { out[s * rows] = lo; out[s * rows + 1] = hi; }
+            }
+        }
+    }
+}
+
 // the staged kernels take bf16 / fp16 rows whose q, k, v are neighbours, 128 channels at a time
 static bool tma_path(const vtx_fused_iir_params* p) {
     return (p->io_dtype == VTX_BF16 || p->io_dtype == VTX_F16) && !p->modal.theta && p->layout == VTX_QKV_INTERLEAVED &&
            p->D % TC == 0 && reinterpret_cast<uintptr_t>(p->u) % 16 == 0 && (p->u_stride_l * 2) % 16 == 0 &&
            (p->u_stride_b * 2) % 16 == 0 && p->L < ((int64_t)1 << 31) && p->B < 65536;
 }
+// ... two channels per thread: 256 channels at a time, no featurizer bias, output rows on 4-byte boundaries
+static bool tma2_path(const vtx_fused_iir_params* p) {
+    return tma_path(p) && p->D % TC2 == 0 && !p->b3 && reinterpret_cast<uintptr_t>(p->y) % 4 == 0 && p->y_stride_l % 2 == 0 &&
+           p->y_stride_b % 2 == 0;
+}
 
-// Segments for the staged kernels.  A CTA is 128 channels of one segment; CTAs of a launch take the same time and run
-// in waves of (SMs x resident CTAs), so the cost of a plan is counted in waves: phase C over all segments, phase A
-// (about half the arithmetic per sample) over all but the last, each CTA paying a fixed set-up worth ~32 samples.
-// One segment means no phase A and no carries at all.
-static Plan plan_staged(int64_t B, int64_t L, int64_t D, bool have_scratch) {
-    Plan best{1, L};
-    if (!have_scratch) return best;
-    const int64_t base = B * (D / TC), slots_c = (int64_t)kNumSMs * MINB_C, slots_a = (int64_t)kNumSMs * MINB_A;
+// Segments for the staged kernels.  CTAs of a launch take the same time and run in waves of (SMs x resident CTAs), so
+// the cost of a plan is counted in waves: phase C over all segments, phase A over all but the last, each CTA paying
+// a fixed set-up worth ~30 samples.  One segment means no phase A and no carries at all.  Either phase can run one
+// channel per thread (128 channels per CTA) or two (256 per CTA, fewer resident CTAs): per sample a CTA then takes
+// (issue cycles per warp x warps per scheduler) = C 67 x 4, A 33 x 5, C pairs 103 x 3, A pairs 53 x 4, i.e. 1, 0.62,
+// 1.15 and 0.79 in units of the first.  Pairs move more channels per cycle when their CTAs fill the machine, fewer when
+// they leave it half empty (B=16, L=8192, D=4096 as one segment: 256 CTAs on 444 places), so the plan tries both.
+static Plan plan_staged(int64_t B, int64_t L, int64_t D, bool have_scratch, bool pairs_ok) {
+    Plan best{1, L, 0, 0};
     double best_cost = 0;
-    const int64_t max_seg = L / 64 < 1 ? 1 : (L / 64 > 4096 ? 4096 : L / 64);
-    for (int64_t n = 1; n <= max_seg; ++n) {
-        const int64_t seg = ceil_div<int64_t>(ceil_div<int64_t>(L, n), (int64_t)RS) * RS;
-        const int64_t nseg = ceil_div<int64_t>(L, seg);
-        if (nseg != n) continue;
-        const double cost = (double)ceil_div<int64_t>(base * nseg, slots_c) * (double)(seg + 32) +
-                            (nseg > 1 ? (double)ceil_div<int64_t>(base * (nseg - 1), slots_a) * (0.47 * (double)seg + 24.0) +
-                                            4.0 * (double)nseg        /* carry scan */
-                                      : 0.0);
-        if (best_cost == 0 || cost < best_cost) { best_cost = cost; best.nseg = nseg; best.seg_len = seg; }
+    const int64_t max_seg = !have_scratch ? 1 : (L / 64 < 1 ? 1 : (L / 64 > 4096 ? 4096 : L / 64));
+    for (int pc = 0; pc <= (pairs_ok ? 1 : 0); ++pc) {
+        for (int pa = 0; pa <= (pairs_ok ? 1 : 0); ++pa) {
+            const int64_t base_c = B * (D / (pc ? TC2 : TC)), base_a = B * (D / (pa ? TC2 : TC));
+            const int64_t slots_c = (int64_t)kNumSMs * (pc ? MINB2_C : MINB_C), slots_a = (int64_t)kNumSMs * (pa ? MINB2_A : MINB_A);
+            const double tc = pc ? 1.15 : 1.0, ta = pa ? 0.79 : 0.62;
+            for (int64_t n = 1; n <= max_seg; ++n) {
+                const int64_t seg = ceil_div<int64_t>(ceil_div<int64_t>(L, n), (int64_t)RS) * RS;
+                const int64_t nseg = ceil_div<int64_t>(L, seg);
+                if (nseg != n) continue;
+                const double cost = (double)ceil_div<int64_t>(base_c * nseg, slots_c) * tc * (double)(seg + 32) +
+                                    (nseg > 1 ? (double)ceil_div<int64_t>(base_a * (nseg - 1), slots_a) * ta * (double)(seg + 32) +
+                                                    4.0 * (double)nseg        /* carry scan */
+                                              : 0.0);
+                if (best_cost == 0 || cost < best_cost) { best_cost = cost; best = Plan{nseg, seg, pa, pc}; }
+            }
+        }
     }
     return best;
 }
 
 static bool tma_path(const vtx_fused_iir_params* p);
+static bool tma2_path(const vtx_fused_iir_params* p);
 
 int64_t scratch_bytes(const vtx_fused_iir_params* p) {
-    const Plan pl = tma_path(p) ? plan_staged(p->B, p->L, p->D, true) : plan(p->B, p->L, p->D, true);
+    const Plan pl = tma_path(p) ? plan_staged(p->B, p->L, p->D, true, tma2_path(p)) : plan(p->B, p->L, p->D, true);
     if (pl.nseg <= 1) return 0;
     return p->B * p->D * pl.nseg * p->modal.S * (p->modal.theta ? 2 : 1) * (int64_t)sizeof(float);
 }
@@ -830,7 +1034,8 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
         VTX_REQUIRE(p->num_heads > 0 && p->D % p->num_heads == 0, VTX_ERR_BAD_ARG, "fused_iir: bad num_heads");
         a.map.hd = p->D / p->num_heads;
     }
-    a.pl = tma_path(p) ? plan_staged(p->B, p->L, p->D, p->scratch != nullptr) : plan(p->B, p->L, p->D, p->scratch != nullptr);
+    a.pl = tma_path(p) ? plan_staged(p->B, p->L, p->D, p->scratch != nullptr, tma2_path(p))
+                       : plan(p->B, p->L, p->D, p->scratch != nullptr);
     const bool cplx = p->modal.theta != nullptr;
     const int64_t n = p->B * p->D * a.pl.nseg;
     VTX_REQUIRE(ceil_div<int64_t>(n, THREADS) < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "fused_iir: problem too large");
@@ -842,23 +1047,25 @@ int fwd(const vtx_fused_iir_params* p, cudaStream_t stream) {
             return rc;
         const int64_t per_seg = p->B * (p->D / TC);
         VTX_REQUIRE(per_seg * a.pl.nseg < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "fused_iir: problem too large");
-        if (p->io_dtype == VTX_BF16) {
-            using T = __nv_bfloat16;
-            if (a.pl.nseg > 1) {
-                licc_tma_kernel<T, false, MINB_A><<<(unsigned)(per_seg * (a.pl.nseg - 1)), TTHREADS, 0, stream>>>(tmu, a);
-                const int64_t nc = p->B * p->D * p->modal.S;
-                licc_carry_kernel<false><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);
-            }
-            licc_tma_kernel<T, true, MINB_C><<<(unsigned)(per_seg * a.pl.nseg), TTHREADS, 0, stream>>>(tmu, a);
-        } else {
-            using T = __half;
-            if (a.pl.nseg > 1) {
-                licc_tma_kernel<T, false, MINB_A><<<(unsigned)(per_seg * (a.pl.nseg - 1)), TTHREADS, 0, stream>>>(tmu, a);
-                const int64_t nc = p->B * p->D * p->modal.S;
-                licc_carry_kernel<false><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);
-            }
-            licc_tma_kernel<T, true, MINB_C><<<(unsigned)(per_seg * a.pl.nseg), TTHREADS, 0, stream>>>(tmu, a);
-        }
+        const bool flip = a.map.flip != 0;
+        const unsigned ga1 = (unsigned)(per_seg * (a.pl.nseg - 1)), gc1 = (unsigned)(per_seg * a.pl.nseg);
+        const unsigned ga2 = (unsigned)(p->B * (p->D / TC2) * (a.pl.nseg - 1)), gc2 = (unsigned)(p->B * (p->D / TC2) * a.pl.nseg);
+#define VTX_LICC_STAGED(T)                                                                                       \
+    do {                                                                                                         \
+        if (a.pl.nseg > 1) {                                                                                     \
+            if (a.pl.pairs_a && flip) licc_tma2_kernel<T, false, true, MINB2_A><<<ga2, TTHREADS, 0, stream>>>(tmu, a);       \
+            else if (a.pl.pairs_a) licc_tma2_kernel<T, false, false, MINB2_A><<<ga2, TTHREADS, 0, stream>>>(tmu, a);         \
+            else licc_tma_kernel<T, false, MINB_A><<<ga1, TTHREADS, 0, stream>>>(tmu, a);                        \
+            const int64_t nc = p->B * p->D * p->modal.S;                                                         \
+            licc_carry_kernel<false><<<(unsigned)ceil_div<int64_t>(nc, 128), 128, 0, stream>>>(a);               \
+        }                                                                                                        \
+        if (a.pl.pairs_c && flip) licc_tma2_kernel<T, true, true, MINB2_C><<<gc2, TTHREADS, 0, stream>>>(tmu, a);            \
+        else if (a.pl.pairs_c) licc_tma2_kernel<T, true, false, MINB2_C><<<gc2, TTHREADS, 0, stream>>>(tmu, a);              \
+        else licc_tma_kernel<T, true, MINB_C><<<gc1, TTHREADS, 0, stream>>>(tmu, a);                             \
+    } while (0)
+        if (p->io_dtype == VTX_BF16) VTX_LICC_STAGED(__nv_bfloat16);
+        else VTX_LICC_STAGED(__half);
+#undef VTX_LICC_STAGED
         return check_launch("fused_iir", a.pl.nseg > 1 ? 3 : 1);
     }
     VTX_DISPATCH_IO(p->io_dtype, T, {
