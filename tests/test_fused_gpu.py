@@ -643,3 +643,33 @@ def test_launch_count_follows_the_kernels_a_call_launches():
     hyena_ops.hyena_li_fwd(q["u"][:, :64], q["w3"], None, q["log_poles"], q["residues"], q["Dp"], want_state=False)
     assert ops.launch_count() - c0 == 1
     ops.device_status()
+
+
+@pytest.mark.gpu
+def test_fused_mr_call_cut_into_launches():
+    """A call large enough to be cut into several launches (24 sequences of 8192 tokens, 4096 channels: 6.4 GB moved)
+    gives, bit for bit, what single-launch calls on slices of the batch give, caches included; the oracle agrees on a
+    slice of channels of one sequence."""
+    from vortex_b200 import hyena_ops, ops
+    B, L, D, G, K = 24, 8192, 4096, 256, 128
+    g = torch.Generator(device="cuda").manual_seed(11)
+    u = torch.empty(B, L, 3 * D, device="cuda", dtype=torch.bfloat16)
+    for b in range(B):
+        u[b] = torch.randn(L, 3 * D, device="cuda", generator=g).bfloat16()
+    w3 = (torch.randn(3 * D, 1, 3, device="cuda", generator=g) / 3 ** 0.5).bfloat16()
+    h = (torch.randn(G, 1, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    Dp = torch.randn(D, device="cuda", generator=g).bfloat16()
+    c0 = ops.launch_count()
+    y, fs, st = hyena_ops.hyena_mr_fwd(u, w3, None, h, Dp, want_state=True)
+    assert ops.launch_count() - c0 >= 2
+    for b0 in range(0, B, 4):
+        c0 = ops.launch_count()
+        ys, fss, sts = hyena_ops.hyena_mr_fwd(u[b0:b0 + 4], w3, None, h, Dp, want_state=True)
+        assert ops.launch_count() - c0 == 1
+        assert torch.equal(ys, y[b0:b0 + 4]) and torch.equal(fss, fs[b0:b0 + 4]) and torch.equal(sts, st[b0:b0 + 4])
+    ops.device_status()
+    d0, d1, b = 3008, 3040, 17
+    sub = {"u": u[b:b + 1, :, 3 * d0:3 * d1].cpu(), "w3": w3[3 * d0:3 * d1].cpu(), "h": h[d0 // 16:d1 // 16].cpu(),
+           "Dp": Dp[d0:d1].cpu()}
+    ref, _, _ = _oracle(sub, d1 - d0, K, "bf16", "interleaved")
+    check("call cut into launches: y[b, :, d0:d1], ref", rel_l2(y[b:b + 1, :, d0:d1], ref), TOL["bf16"])
