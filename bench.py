@@ -60,6 +60,10 @@ WORKLOADS = {
                        "channel + skip, state after the last token)"),
     # the featurizer as the conv extension's operator runs it (causal_conv1d_fn on the channel-last view [B,3D,L] of
     # the projection rows, width 3, no activation): 2 bytes in + 2 bytes out per packed channel and token
+    # backward of the gate-conv-gate operator at configuration 2's operator-only size: (bs, l, g, dg) = (4, 8192, 256, 16)
+    # operands x, B, C (the three thirds of one [B, L, 3D] tensor), dy and the saved filter output y2 in, dx, dB, dC, dh out
+    "gcg_bwd": dict(B=4, L=8192, D=4096, G=256, K=128, io="bf16", seed=1, cc1d=True, bwd=True,
+                    name="hyena_ops gate-conv-gate BACKWARD (two_pass_bwd_grouped) B=4 L=8192 D=4096 bf16, 128 taps, groups of 16"),
     "cc1d": dict(B=4, L=8192, D=4096, G=256, K=3, io="bf16", seed=1, cc1d=True,
                  name="causal_conv1d_fwd B=4 L=8192 channels=12288 bf16 channel-last (width-3 depthwise causal conv)"),
     # one-token decode of one Hyena layer (one launch): a step = B tokens; fp32 caches as after the first decode step
@@ -345,6 +349,8 @@ def algorithmic_bytes(w):
     if w.get("prefill_only"):
         return sum(8 * B * D * L + B * 3 * D * 4 + (B * D * 16 * 4 if k == "li" else B * D * ((7 if k == "se" else 128) - 1) * 2)
                    for k in ["se", "mr", "li"] * w["n_each"])
+    if w.get("bwd"):
+        return 16 * B * D * L            # dy, x, B, C, y2 in; dx, dB, dC out (2 bytes each)
     if w.get("cc1d"):
         return 12 * B * D * L
     if w.get("dropin"):
@@ -380,6 +386,16 @@ def run_block(name, pc, u=None):
                                     res_im=pc["res_im"], bias=pc["Dp"])[0]
         return ops.decode_layer(un, pc["w3"], None, c["fir_state"], pc["D"], h=pc["h"], inner_state=c["inner_state"],
                                 bias=pc["Dp"], flip_filter=name == "decode_mr", gated_bias=name == "decode_mr")[0]
+    if name == "gcg_bwd":
+        B, L, D3 = u.shape
+        D, G = D3 // 3, pc["h"].shape[0]
+        if "dy" not in pc:
+            g = torch.Generator(device=u.device).manual_seed(5)
+            pc["dy"] = torch.randn(B, L, D, device=u.device, generator=g).to(u.dtype)
+            pc["y2"] = torch.randn(B, L, D, device=u.device, generator=g).to(u.dtype)
+        v4 = lambda t: t.unflatten(2, (G, D // G))  # noqa: E731
+        return hyena_ops.two_pass_bwd_grouped(v4(pc["dy"]), v4(u[..., :D]), v4(u[..., D:2 * D]), v4(u[..., 2 * D:]), pc["h"],
+                                              v4(pc["y2"]))[0].flatten(2)
     if name == "cc1d":
         return hyena_ops.causal_conv1d_fn(u.transpose(1, 2), pc["w3"].reshape(-1, 3))
     caches = bool(pc.get("caches"))
@@ -451,13 +467,22 @@ def cpu_baseline(name, w, steps=1, warmup=1, cap_s=25.0):
     except (AttributeError, RuntimeError):
         pass
     torch.manual_seed(0)
-    Ds = min(w["D"], {"mr": 256, "se": 256, "li": 64, "li_pc": 64, "cc1d": 256, "mr_dropin": 256, "se_cfg1": 768}[name])
+    Ds = min(w["D"], {"mr": 256, "se": 256, "li": 64, "li_pc": 64, "cc1d": 256, "mr_dropin": 256, "se_cfg1": 768, "gcg_bwd": 256}[name])
     B, L, D, G, K = w["B"], w["L"], w["D"], w["G"], w["K"]
     Gs = max(1, G * Ds // D)
     dt = torch.float32 if w.get("io") == "f32" else torch.bfloat16
     u = torch.randn(B, L, 3 * Ds).to(dt)
     w3 = (torch.randn(3 * Ds, 1, 3) / 3 ** 0.5).to(dt)
-    if w.get("cc1d"):
+    if w.get("bwd"):
+        # autograd through the reference's forward math (F.conv1d on the gated product, ref_fwd.py:80-127)
+        hb = (torch.randn(Gs, 1, K) / K ** 0.5).to(dt).repeat_interleave(Ds // Gs, 0).float()
+        xs, Bs, Cs = (u[..., i * Ds:(i + 1) * Ds].float().transpose(1, 2).contiguous().requires_grad_(True) for i in range(3))
+        dy = torch.randn(B, Ds, L)
+
+        def step():
+            y = Cs * torch.nn.functional.conv1d(Bs * xs, hb, groups=Ds, padding=K - 1)[..., :L]
+            return torch.autograd.grad(y, (xs, Bs, Cs), dy)[0]
+    elif w.get("cc1d"):
         def step():
             return TP.featurizer(u, w3)[0]
     elif K > 0:

@@ -60,7 +60,7 @@ enum { VTX_BIAS_NONE = 0, VTX_BIAS_ADD = 1, VTX_BIAS_GATED = 2 /* + bias[d] * kv
 size_t vtx_last_error(char* buf, size_t len);
 /* ABI version of this header: major * 1000 + minor.  vtx_abi_version() returns the value the library was
  * built with; a binding compares the two (same major, library minor >= the minor it was written for). */
-#define VTX_ABI_VERSION 1004
+#define VTX_ABI_VERSION 1005
 int64_t vtx_abi_version(void);
 /* sizeof() of the parameter structs in declaration order (0 = vtx_featurizer_params, ...),
  * -1 past the end; lets a binding verify that its mirror of a struct has the same size. */
@@ -158,6 +158,28 @@ typedef struct vtx_gcg_cl_params {
     int64_t io_dtype;
 } vtx_gcg_cl_params;
 int vtx_gcg_cl_fwd(const vtx_gcg_cl_params* p, void* stream);
+
+/* Backward of the same operator on channel-last tensors [B,L,D] (channel stride 1): replaces two_pass_bwd_grouped
+ * (vortex/ops/hyena_se/bwd.py:11-330, kernels bwd_kernels.py:239,468; restated by gcg_two_pass_chunked_bwd,
+ * ref_bwd.py:31-115).  With z = Bg * x, y2 = xcorr(h_g, z) (saved by the forward) and y = C * y2:
+ *   dC = dy * y2,   dz = h_g run against time over dy * C,   dx = dz * Bg,   dB = dz * x,
+ *   dh32[g,k] += sum over batch, time and the group's channels of (dy * C)[t] z[t - (K-1) + k].
+ * dx, dB, dC are contiguous [B,L,D] in the I/O dtype; dh32 is an fp32 [G,K] accumulator the caller zeroes (partial
+ * sums are added with atomics: the order, hence the last bits, can differ between runs).  K <= 128; any I/O dtype;
+ * fp32 accumulation on the CUDA cores. */
+typedef struct vtx_gcg_bwd_params {
+    const void* dy;  int64_t dy_stride_b, dy_stride_l;
+    const void* x;   int64_t x_stride_b, x_stride_l;
+    const void* Bg;  int64_t b_stride_b, b_stride_l;
+    const void* C;   int64_t c_stride_b, c_stride_l;
+    const void* y2;  int64_t y2_stride_b, y2_stride_l;
+    const void* h;   int64_t h_dtype;           /* [G,K] contiguous */
+    void* dx; void* dB; void* dC;               /* [B,L,D] contiguous */
+    float* dh32;                                /* [G,K] fp32, zeroed by the caller */
+    int64_t B, L, D, G, K;
+    int64_t io_dtype;
+} vtx_gcg_bwd_params;
+int vtx_gcg_bwd(const vtx_gcg_bwd_params* p, void* stream);
 
 /* ------------------------------------------------------------------------
  * Fused Hyena FIR block on the projection output, channel-last in and out:

@@ -491,6 +491,30 @@ def gcg_blgdg(x, Bg, Cg, h):
     return np.asarray(Cg, dtype=np.float64) * y.transpose(0, 2, 1).reshape(bs, l, g, dg)
 
 
+def gcg_blgdg_bwd(dy, x, Bg, Cg, h):
+    """hyena_se/ref_bwd.py:31-115 (gcg_two_pass_chunked_bwd), un-chunked: gradients of y = C * xcorr(h_g, B*x) with
+    tensors (bs, l, g, dg), h (g, 1, hl).  Returns dx, dB, dC (bs, l, g, dg) and dh (g, 1, hl).
+    With z = B*x and y2[t] = sum_k h[k] z[t-(hl-1)+k]:  dC = dy*y2;  dz[t] = sum_k h[k] (dy*C)[t+(hl-1)-k];
+    dx = dz*B;  dB = dz*x;  dh[k] = sum_{b,t,dg} (dy*C)[t] z[t-(hl-1)+k]."""
+    dy, x, Bg, Cg = (np.asarray(t, dtype=np.float64) for t in (dy, x, Bg, Cg))
+    h = np.asarray(h, dtype=np.float64)
+    bs, l, g, dg = x.shape
+    hl = h.shape[-1]
+    z = Bg * x
+    y2 = gcg_blgdg(x, Bg, np.ones_like(Cg), h)
+    g2 = dy * Cg
+    dz = np.zeros_like(z)
+    dh = np.zeros((g, 1, hl))
+    for k in range(hl):
+        s = hl - 1 - k                      # y2[t] takes h[k] z[t - s]
+        if s >= l:
+            continue
+        hk = h[:, 0, k][None, None, :, None]
+        dz[:, :l - s] += hk * g2[:, s:]
+        dh[:, 0, k] = np.einsum("blgd,blgd->g", g2[:, s:], z[:, :l - s])
+    return dz * Bg, dz * x, dy * y2, dh
+
+
 def toeplitz_pair(hf, size):
     """hyena_se/utils.py:5-51: T[i,j] = hf[i-j] (0 <= i-j < hl) and the
     correction T_hat[i,j] = hf[i+size-j] (j >= i, i+size-j < hl), hf = h.flip."""

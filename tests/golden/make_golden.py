@@ -221,6 +221,20 @@ def main(ref_root):
         hf = h.flip(-1)[:, 0]
         out[k + "_T"], out[k + "_That"] = np32(toeplitz(hf, 128)), np32(correction_toeplitz(hf, 128))
 
+    # ---- hyena_ops backward (ref_bwd.py: gcg_two_pass_chunked_bwd), fp32 on CPU ------------------
+    from hyena_ops.ref_bwd import gcg_two_pass_chunked_bwd
+    for hl, gg, dg, l in ((4, 2, 16, 256), (32, 3, 8, 384), (128, 2, 16, 512)):
+        g = torch.Generator().manual_seed(6500 + hl)
+        bs = 2
+        x, Bm, Cm, dy = (torch.randn(bs, l, gg, dg, generator=g) for _ in range(4))
+        h = torch.randn(gg, 1, hl, generator=g) / hl ** 0.5
+        y2 = gcg_fwd_ref_corrected(x, Bm, torch.ones_like(Cm), h)
+        dx, dB, dC, dh = gcg_two_pass_chunked_bwd(dy, x, y2, Bm, Cm, h, gl=128)
+        k = f"opsbwd_hl{hl}"
+        out[k + "_x"], out[k + "_B"], out[k + "_C"], out[k + "_h"] = np32(x), np32(Bm), np32(Cm), np32(h)
+        out[k + "_dy"], out[k + "_y2"] = np32(dy), np32(y2)
+        out[k + "_dx"], out[k + "_dB"], out[k + "_dC"], out[k + "_dh"] = np32(dx), np32(dB), np32(dC), np32(dh)
+
     # ---- Hyena-X reference (depthwise FIR on q, k, v, three-way gate) -----------------
     from vortex.ops.hyena_x.triton_indirect_fwd import hyena_x_fwd_ref
     for io, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):

@@ -179,6 +179,47 @@ def test_golden_hyena_ops_layout(golden, hl):
     check("test_engine_gpu.py:176 y, golden[k + '_y_chunked']", rel_l2(y, golden[k + "_y_chunked"]), 1e-5)
 
 
+@pytest.mark.parametrize("hl", [4, 32, 128])
+def test_golden_hyena_ops_backward(golden, hl):
+    """two_pass_bwd_grouped against the reference's own backward (fp32 vectors of ref_bwd.py), and through autograd."""
+    from vortex_b200 import hyena_ops
+
+    k = f"opsbwd_hl{hl}"
+    t = {n: T(golden[f"{k}_{n}"], "f32") for n in ("dy", "x", "B", "C", "h", "y2")}
+    grads = hyena_ops.two_pass_bwd_grouped(t["dy"], t["x"], t["B"], t["C"], t["h"], t["y2"], version="v2", CHUNK_SIZE=128)
+    for name, got in zip(("dx", "dB", "dC", "dh"), grads):
+        assert got.shape == golden[f"{k}_{name}"].shape
+        check(f"hyena_ops backward hl={hl} {name} vs the reference's", rel_l2(got, golden[f"{k}_{name}"]), 1e-5)
+    # without the saved filter output, and through the autograd function of the interface
+    grads2 = hyena_ops.gcg_bwd(t["dy"], t["x"], t["B"], t["C"], t["h"])
+    leaves = [t[n].clone().requires_grad_(True) for n in ("x", "B", "C", "h")]
+    y = hyena_ops.two_pass_chunked_gate_conv_gate(*leaves)
+    y.backward(t["dy"])
+    for name, a, b in zip(("dx", "dB", "dC", "dh"), grads2, leaves):
+        check(f"hyena_ops backward hl={hl} {name}, recomputed y2", rel_l2(a, golden[f"{k}_{name}"]), 1e-5)
+        check(f"hyena_ops backward hl={hl} {name}, autograd", rel_l2(b.grad, golden[f"{k}_{name}"]), 1e-5)
+
+
+@pytest.mark.parametrize("io,bs,l,g,dg,hl", [("bf16", 2, 1000, 4, 16, 7), ("bf16", 1, 777, 3, 24, 128), ("f16", 2, 300, 5, 1, 33),
+                                             ("f32", 1, 4099, 2, 64, 128), ("bf16", 3, 5, 2, 16, 128)])
+def test_hyena_ops_backward_vs_oracle(io, bs, l, g, dg, hl):
+    """Seeded shapes the golden vectors do not cover: ragged lengths, groups of 1 / 24 / 64 channels, 16-bit I/O,
+    sequences shorter than the filter."""
+    from vortex_b200 import hyena_ops
+
+    gen = torch.Generator().manual_seed(77)
+    x, Bm, Cm, dy = (torch.randn(bs, l, g, dg, generator=gen).to(DT[io]) for _ in range(4))
+    h = (torch.randn(g, 1, hl, generator=gen) / hl ** 0.5).to(DT[io])
+    ref = O.gcg_blgdg_bwd(to_np(dy), to_np(x), to_np(Bm), to_np(Cm), to_np(h))
+    got = hyena_ops.gcg_bwd(dy.cuda(), x.cuda(), Bm.cuda(), Cm.cuda(), h.cuda())
+    tol = 1e-4 if io == "f32" else TOL["bf16"] if io == "bf16" else 5e-4
+    for name, a, b in zip(("dx", "dB", "dC", "dh"), got, ref):
+        assert a.shape == b.shape and a.dtype == DT[io]
+        # dC = dy * y2, where the forward that recomputes y2 rounds B * x and y2 to the I/O dtype as the reference
+        # materialises them: three independent roundings (sqrt(3) x one) on as few as 480 values
+        check(f"hyena_ops backward {io} {name} vs oracle", rel_l2(a, b), tol * (2.5 if name == "dC" else 1.0))
+
+
 # ------------------------------------------------------------------ seeded parity against the oracle
 def _engine_block(eng, p, D, G, K, layout, ip=None, heads=1):
     """The reference's two-call sequence (model.py:233-291) on the drop-in engine."""

@@ -138,6 +138,18 @@ def test_hyena_ops_layout(golden, hl):
         assert np.array_equal(Th.astype(np.float32), golden[k + "_That"][g])
 
 
+@pytest.mark.parametrize("hl", [4, 32, 128])
+def test_hyena_ops_backward(golden, hl):
+    """The oracle's backward against the reference's own (ref_bwd.py: gcg_two_pass_chunked_bwd, fp32 on CPU)."""
+    k = f"opsbwd_hl{hl}"
+    y2 = O.gcg_blgdg(golden[k + "_x"], golden[k + "_B"], np.ones_like(golden[k + "_C"]), golden[k + "_h"])
+    assert O.rel_l2(y2, golden[k + "_y2"]) < 2e-6
+    grads = O.gcg_blgdg_bwd(golden[k + "_dy"], golden[k + "_x"], golden[k + "_B"], golden[k + "_C"], golden[k + "_h"])
+    for name, got in zip(("dx", "dB", "dC", "dh"), grads):
+        assert got.shape == golden[f"{k}_{name}"].shape
+        assert O.rel_l2(got, golden[f"{k}_{name}"]) < 2e-6, name
+
+
 @pytest.mark.parametrize("io", ["f32", "bf16"])
 @pytest.mark.parametrize("Lh", [4, 16])
 def test_hyena_x(golden, io, Lh):

@@ -59,6 +59,11 @@ GcgClParams = _struct("GcgClParams", """
     p:h i:h_dtype p:bias i:bias_dtype p:y i:y_stride_b i:y_stride_l p:state
     i:B i:L i:D i:G i:K i:taps i:bias_mode i:io_dtype""")
 
+GcgBwdParams = _struct("GcgBwdParams", """
+    p:dy i:dy_stride_b i:dy_stride_l p:x i:x_stride_b i:x_stride_l p:Bg i:b_stride_b i:b_stride_l
+    p:C i:c_stride_b i:c_stride_l p:y2 i:y2_stride_b i:y2_stride_l p:h i:h_dtype p:dx p:dB p:dC p:dh32
+    i:B i:L i:D i:G i:K i:io_dtype""")
+
 ModalParams = _struct("ModalParams", "p:log_poles p:theta p:res_re p:res_im i:G i:S")
 
 
@@ -123,7 +128,7 @@ class DecodeLayerParams(C.Structure):
 
 STRUCTS = [FeaturizerParams, GcgParams, FusedFirParams, ModalParams, IirParams, StepFirParams, StepIirParams,
            DecodeLayerParams, FusedIirParams, HyenaXParams, CausalConv1dParams, CausalConv1dUpdateParams,
-           VarlenStatesParams, GcgClParams]
+           VarlenStatesParams, GcgClParams, GcgBwdParams]
 
 # name -> (restype, argtypes); every symbol include/vortex_b200.h declares
 SYMBOLS = {
@@ -136,6 +141,7 @@ SYMBOLS = {
     "vtx_featurizer_fwd": (C.c_int, [C.POINTER(FeaturizerParams), _p]),
     "vtx_gcg_fwd": (C.c_int, [C.POINTER(GcgParams), _p]),
     "vtx_gcg_cl_fwd": (C.c_int, [C.POINTER(GcgClParams), _p]),
+    "vtx_gcg_bwd": (C.c_int, [C.POINTER(GcgBwdParams), _p]),
     "vtx_fused_fir_fwd": (C.c_int, [C.POINTER(FusedFirParams), _p]),
     "vtx_modal_filter": (C.c_int, [C.POINTER(ModalParams), _p, _i, _p]),
     "vtx_iir_scratch_bytes": (_i, [_i, _i, _i, _i, _i]),

@@ -151,6 +151,7 @@ extern "C" int64_t vtx_struct_size(int64_t which) {
         case 11: return sizeof(vtx_causal_conv1d_update_params);
         case 12: return sizeof(vtx_varlen_states_params);
         case 13: return sizeof(vtx_gcg_cl_params);
+        case 14: return sizeof(vtx_gcg_bwd_params);
         default: return -1;
     }
 }

@@ -249,12 +249,49 @@ def inner_hyena_se(x, k, q, h, bias=None, input_layout="bdl", output_layout="bdl
     raise NotImplementedError("output_layout must be bdl, bld, blgdg or bgdgl")
 
 
+def gcg_bwd(dy, x, B, C, h, y2=None):
+    """Gradients of ``gcg_fwd``: (dx, dB, dC, dh) for (bs, l, g, dg) tensors and h (g, 1, hl) -- the reference's
+    ``two_pass_bwd_grouped`` (``vortex/ops/hyena_se/bwd.py:11``; math ``ref_bwd.py:31-115``).  ``y2`` is the filter
+    output xcorr(h_g, B * x) the reference's forward saves; without it, it is recomputed by one more forward pass."""
+    bs, l, g, dg = x.shape
+    if y2 is None:
+        y2 = gcg_fwd(x, B, torch.ones_like(C), h)
+    f = lambda t: t.reshape(bs, l, g * dg)  # noqa: E731
+    dx, dB, dC, dh = ops.gcg_bwd(f(dy), f(x), f(B), f(C), f(y2), h)
+    return dx.view(bs, l, g, dg), dB.view(bs, l, g, dg), dC.view(bs, l, g, dg), dh.view(g, 1, -1).to(h.dtype)
+
+
+def two_pass_bwd_grouped(dy, x, B, C, h, y2, **kernel_options):
+    """The reference's backward entry point by name (``vortex/ops/hyena_se/bwd.py:11-60``): (dx, dB, dC, dh).  The
+    saved Toeplitz matrices, the lagged product and the scheduling arguments are accepted and ignored."""
+    return gcg_bwd(dy, x, B, C, h, y2)
+
+
+class TwoPassChunkedGateConvGate(torch.autograd.Function):
+    """y = C * xcorr(h_g, B * x) with its backward (``vortex/ops/hyena_se/interface.py:47-167``): the forward keeps
+    the filter output y2, the backward is ``gcg_bwd``."""
+
+    @staticmethod
+    def forward(ctx, x, B, C, h):
+        y2 = gcg_fwd(x, B, torch.ones_like(C), h)
+        ctx.save_for_backward(x, B, C, h, y2)
+        return C * y2
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, B, C, h, y2 = ctx.saved_tensors
+        return gcg_bwd(dy.contiguous(), x, B, C, h, y2)
+
+
 def two_pass_chunked_gate_conv_gate(x, B, C, h, return_toeplitz=False, **kernel_options):
-    """Forward of the reference's ``two_pass_chunked_gate_conv_gate`` (``vortex/ops/hyena_se/interface.py:170-204``;
-    kernel ``two_pass_fwd_grouped``, ``fwd.py:17``): y = C * xcorr(h_g, B * x) on (bs, l, g, dg) tensors.  The chunking
-    and autotuning arguments are accepted and ignored; no Toeplitz matrices are returned (there is no backward)."""
+    """The reference's ``two_pass_chunked_gate_conv_gate`` (``vortex/ops/hyena_se/interface.py:170-204``; kernel
+    ``two_pass_fwd_grouped``, ``fwd.py:17``): y = C * xcorr(h_g, B * x) on (bs, l, g, dg) tensors, differentiable in
+    x, B, C and h.  The chunking and autotuning arguments are accepted and ignored; no Toeplitz matrices are returned
+    (the backward here does not use them)."""
     if return_toeplitz:
-        raise NotImplementedError("return_toeplitz serves the backward pass, which is not built")
+        raise NotImplementedError("Toeplitz matrices are not materialised: the backward does not use them")
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (x, B, C, h)):
+        return TwoPassChunkedGateConvGate.apply(x, B, C, h)
     return gcg_fwd(x, B, C, h)
 
 

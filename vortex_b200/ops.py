@@ -216,6 +216,33 @@ def gcg_cl_fwd(q, k, v, h, bias=None, *, taps=TAPS_XCORR, bias_mode=BIAS_NONE, w
     return y, state
 
 
+def gcg_bwd(dy, x, Bg, Cg, y2, h):
+    """Backward of y = Cg * xcorr(h_g, Bg * x) on channel-last tensors [B, L, D] (unit channel stride), y2 the filter
+    output the forward saved.  Returns dx, dB, dC [B, L, D] in the I/O dtype and dh [G, K] in fp32."""
+    _need_cuda(dy, x, Bg, Cg, y2, h)
+    B, L, D = x.shape
+    ts = []
+    for t in (dy, x, Bg, Cg, y2):
+        if tuple(t.shape) != (B, L, D) or t.dtype != x.dtype:
+            raise ValueError("dy, x, B, C and y2 must have the same shape and dtype")
+        ts.append(t if t.stride(2) == 1 else t.contiguous())
+    dy, x, Bg, Cg, y2 = ts
+    h = _param(h, x)
+    G = h.shape[0]
+    h = h.reshape(G, -1)
+    K = h.shape[1]
+    dx, dB, dC = (torch.empty(B, L, D, device=x.device, dtype=x.dtype) for _ in range(3))
+    dh = torch.zeros(G, K, device=x.device, dtype=torch.float32)
+    p = _lib.GcgBwdParams(
+        dy=_ptr(dy), dy_stride_b=dy.stride(0), dy_stride_l=dy.stride(1), x=_ptr(x), x_stride_b=x.stride(0), x_stride_l=x.stride(1),
+        Bg=_ptr(Bg), b_stride_b=Bg.stride(0), b_stride_l=Bg.stride(1), C=_ptr(Cg), c_stride_b=Cg.stride(0), c_stride_l=Cg.stride(1),
+        y2=_ptr(y2), y2_stride_b=y2.stride(0), y2_stride_l=y2.stride(1), h=_ptr(h), h_dtype=_code(h),
+        dx=_ptr(dx), dB=_ptr(dB), dC=_ptr(dC), dh32=_ptr(dh), B=B, L=L, D=D, G=G, K=K, io_dtype=_code(x))
+    with _on(x):
+        _lib.check(_lib.lib().vtx_gcg_bwd(C.byref(p), _stream(x)))
+    return dx, dB, dC, dh
+
+
 def fused_fir_fwd(u: torch.Tensor, w3, b3, h, bias, D: int, *, taps: int, bias_mode: int, layout="interleaved",
                   num_heads=1, flip=False, want_state=True, hist_rows=0):
     """Channel-last fused block: u [B, L, 3D] -> y [B, L, D], fir_state [B, 3D, min(L,2)], inner [B, D, min(L,K-1)].
