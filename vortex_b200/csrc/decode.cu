@@ -7,6 +7,14 @@
 
 namespace vtx {
 
+// Row and channel indices fit 32 bits (checked by the host): their quotients are taken as 32-bit divisions, which cost
+// a tenth of the 64-bit ones -- the one-token kernels are short enough for a few 64-bit divisions per thread to be most
+// of their instructions (the 128-tap tile kernel executed 1385 instructions per tile with them, eight per tile).
+__device__ __forceinline__ int div32(int64_t a, int64_t b) { return (int)((unsigned)a / (unsigned)b); }
+__device__ __forceinline__ QkvMap qkv_map(const vtx_decode_layer_params& p) {
+    return QkvMap{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? (int64_t)div32(p.D, p.num_heads) : p.D};
+}
+
 // Sum over the LPR lanes of a row.  The mask names only the lanes of this row's group, so the
 // groups of a warp may diverge from one another (e.g. when the last rows of a launch are absent).
 template <int LPR>
@@ -48,12 +56,12 @@ __global__ void __launch_bounds__(256) step_fir_kernel(vtx_step_fir_params p) {
     const int lane = threadIdx.x % LPR;
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
     if (row >= p.B * p.C) return;   // whole groups leave together (blockDim % LPR == 0)
-    const int64_t ch = row % p.C;
+    const int64_t ch = row - (int64_t)div32(row, p.C) * p.C;
     const int c = (int)p.c, K = (int)p.K;
     const int c_out = c < K - 1 ? c + 1 : c;
     const float u = to_f32<T>(static_cast<const T*>(p.u)[row]);
     float y = fir_row_step<LPR>(p.state_in, p.state_dtype, row * c, c, K, p.w, p.w_dtype,
-                                (ch / (p.C / p.Gw)) * K, p.flip_filter != 0, u, p.state_out + row * c_out, lane);
+                                (int64_t)div32(ch, div32(p.C, p.Gw)) * K, p.flip_filter != 0, u, p.state_out + row * c_out, lane);
     if (lane == 0) {
         if (p.bias_mode != VTX_BIAS_NONE) {
             float b = ld_param(p.bias, p.bias_dtype, ch);
@@ -95,11 +103,11 @@ __global__ void __launch_bounds__(256) step_iir_kernel(vtx_step_iir_params p) {
     const int lane = threadIdx.x % 16;
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 16;
     if (row >= p.B * p.D) return;
-    const int64_t d = row % p.D;
+    const int64_t d = row - (int64_t)div32(row, p.D) * p.D;
     const int64_t ss = p.modal.S * (p.modal.theta ? 2 : 1);
     float q = to_f32<T>(static_cast<const T*>(p.q)[row]);
     float kv = round_io<T>(to_f32<T>(static_cast<const T*>(p.k)[row]) * to_f32<T>(static_cast<const T*>(p.v)[row]));
-    float res = iir_row_step(p.modal, d / (p.D / p.modal.G), p.state_in + row * ss, p.state_out + row * ss, kv, lane);
+    float res = iir_row_step(p.modal, div32(d, div32(p.D, p.modal.G)), p.state_in + row * ss, p.state_out + row * ss, kv, lane);
     if (lane == 0) {
         // D * x1v is a product of two I/O-dtype tensors in the reference (rounded there) unless D is fp32
         float skip = p.bias ? ld_param(p.bias, p.bias_dtype, d) * kv : 0.f;
@@ -114,8 +122,8 @@ __global__ void __launch_bounds__(256) decode_layer_kernel(vtx_decode_layer_para
     const int lane = threadIdx.x % LPR;
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
     if (row >= p.B * p.D) return;
-    const int64_t b = row / p.D, d = row % p.D;
-    QkvMap map{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? p.D / p.num_heads : p.D};
+    const int64_t b = div32(row, p.D), d = row - b * p.D;
+    const QkvMap map = qkv_map(p);
     int64_t ch[3];
     map.get(d, ch[0], ch[1], ch[2]);
     const int K3 = (int)p.K3, c3 = K3 - 1;
@@ -143,13 +151,13 @@ __global__ void __launch_bounds__(256) decode_layer_kernel(vtx_decode_layer_para
     if (MODE == 0) {
         const int K = (int)p.K, c = K - 1;
         float f = fir_row_step<LPR>(p.inner_state_in, p.inner_state_dtype, row * c, c, K, p.h, p.h_dtype,
-                                    (d / (p.D / p.G)) * K, p.flip_filter != 0, kv, p.inner_state_out + row * c, lane);
+                                    (int64_t)div32(d, div32(p.D, p.G)) * K, p.flip_filter != 0, kv, p.inner_state_out + row * c, lane);
         if (p.bias_mode == VTX_BIAS_GATED) f = fmaf(bias, kv, f);
         else if (p.bias_mode == VTX_BIAS_ADD) f += bias;
         y = round_io<T>(f) * q;
     } else {
         const int64_t ss = p.modal.S * (p.modal.theta ? 2 : 1);
-        float res = iir_row_step(p.modal, d / (p.D / p.modal.G), p.iir_state_in + row * ss,
+        float res = iir_row_step(p.modal, div32(d, div32(p.D, p.modal.G)), p.iir_state_in + row * ss,
                                  p.iir_state_out + row * ss, kv, lane);
         float skip = bias * kv;
         if (p.bias && p.bias_dtype != VTX_F32) skip = round_io<T>(skip);
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(256) decode_layer_kernel(vtx_decode_layer_para
 // featurizer step of hidden channel d of batch element b: new q and k*v, featurizer cache shifted (K3 == 3)
 template <typename T>
 __device__ __forceinline__ void featurizer_step3(const vtx_decode_layer_params& p, int64_t b, int64_t d, float& q, float& kv) {
-    QkvMap map{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? p.D / p.num_heads : p.D};
+    const QkvMap map = qkv_map(p);
     int64_t ch[3];
     map.get(d, ch[0], ch[1], ch[2]);
     const T* u = static_cast<const T*>(p.u) + b * 3 * p.D;
@@ -196,12 +204,13 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
     const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
     const int64_t row0 = tile * RW;
     if (row0 >= p.B * p.D) return;
-    const int64_t b = row0 / p.D, d0 = row0 % p.D;
+    const int64_t b = div32(row0, p.D), d0 = row0 - b * p.D;
     float q_own = 0.f, kv_own = 0.f;
     if (lane < RW) featurizer_step3<T>(p, b, d0 + lane, q_own, kv_own);
     const int K = (int)p.K, c = K - 1;
     const bool flip = p.flip_filter != 0;
-    const int64_t cpg = p.D / p.G;
+    const int cpg = div32(p.D, p.G);
+    int g_row = div32(d0, cpg), g_rem = (int)d0 - g_row * cpg;      // group of row r, and the row's place in it
     const float* sin_ = static_cast<const float*>(p.inner_state_in) + row0 * c;
     float* sout = p.inner_state_out + row0 * c;
     // all cache loads of the tile first
@@ -218,7 +227,8 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
     int64_t g_have = -1;
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
-        const int64_t g = (d0 + r) / cpg;
+        const int64_t g = g_row;
+        if (++g_rem == cpg) { g_rem = 0; ++g_row; }
         if (g != g_have) {          // taps of the row's group (usually the same for the whole tile)
             g_have = g;
 #pragma unroll
@@ -282,6 +292,101 @@ __global__ void __launch_bounds__(256) decode_fir_tile_kernel(vtx_decode_layer_p
     }
 }
 
+// The 128-tap layer (Evo 2's medium filter: 127 cached samples per row) with everything the general tile kernel works
+// out at run time fixed at compile time: the row pitch (load and store offsets become immediates), which lanes have a
+// fourth sample, one filter for the whole tile (groups are whole tiles).  The featurizer step of the tile's 24 packed
+// channels is done by 24 lanes, one channel each (the general kernel lets 8 lanes do three channels in turn).
+// An instruction count a quarter of the general kernel's 1385 per tile, which had the kernel bound by issue.
+template <typename T>
+__global__ void __launch_bounds__(256) decode_fir127_kernel(vtx_decode_layer_params p) {
+    constexpr int RW = 8, C = 127, K = 128;
+    const int lane = threadIdx.x % 32;
+    const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int64_t row0 = tile * RW;
+    if (row0 >= p.B * p.D) return;
+    const int64_t b = div32(row0, p.D), d0 = row0 - b * p.D;
+    const float* sin_ = static_cast<const float*>(p.inner_state_in) + row0 * C + lane;
+    float* sout = p.inner_state_out + row0 * C + lane;
+    // all cache loads of the tile first
+    float s[RW][4];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+#pragma unroll
+        for (int j = 0; j < 3; ++j) s[r][j] = sin_[r * C + 32 * j];
+        s[r][3] = lane < 31 ? sin_[r * C + 96] : 0.f;
+    }
+    // featurizer step: lane < 24 takes packed channel (lane % 3) of row (lane / 3)
+    float z = 0.f;
+    if (lane < 3 * RW) {
+        const QkvMap map = qkv_map(p);
+        int64_t ch[3];
+        map.get(d0 + lane / 3, ch[0], ch[1], ch[2]);
+        const int part = lane % 3;
+        const int64_t c = part == 0 ? ch[0] : part == 1 ? ch[1] : ch[2], so = (b * 3 * p.D + c) * 2;
+        const float2 st = *reinterpret_cast<const float2*>(static_cast<const float*>(p.fir_state_in) + so);
+        const float x = to_f32<T>(static_cast<const T*>(p.u)[b * 3 * p.D + c]);
+        float acc = ld_param(p.w3, p.w3_dtype, c * 3 + 2) * x;
+        acc = fmaf(st.x, ld_param(p.w3, p.w3_dtype, c * 3), acc);
+        acc = fmaf(st.y, ld_param(p.w3, p.w3_dtype, c * 3 + 1), acc);
+        *reinterpret_cast<float2*>(p.fir_state_out + so) = make_float2(st.y, x);
+        if (p.b3) acc += ld_param(p.b3, p.b3_dtype, c);
+        z = round_io<T>(acc);
+    }
+    // the tile's filter: sample i of a row meets tap i (or c - i when the taps are stored flipped)
+    const bool flip = p.flip_filter != 0;
+    const int64_t hb = (int64_t)div32(d0, div32(p.D, p.G)) * K;
+    float tap[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = lane + 32 * j;
+        tap[j] = i < C ? ld_param(p.h, p.h_dtype, hb + (flip ? C - i : i)) : 0.f;
+    }
+    const float tu = ld_param(p.h, p.h_dtype, hb + (flip ? 0 : C));
+    float part[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        part[r] = fmaf(s[r][3], tap[3], fmaf(s[r][2], tap[2], fmaf(s[r][1], tap[1], s[r][0] * tap[0])));
+        if (lane >= 1) sout[r * C - 1] = s[r][0];
+        sout[r * C + 31] = s[r][1];
+        sout[r * C + 63] = s[r][2];
+        if (lane < 31) sout[r * C + 95] = s[r][3];
+    }
+    // fold the eight rows' partial sums over the 32 lanes (as in the general kernel): lane l ends with the total of
+    // row (bit 4 -> +4, bit 3 -> +2, bit 2 -> +1)
+    const bool hi4 = lane & 16, hi3 = lane & 8, hi2 = lane & 4;
+    float q4[4], q2[2], q1;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float give = hi4 ? part[r] : part[r + 4], keep = hi4 ? part[r + 4] : part[r];
+        q4[r] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const float give = hi3 ? q4[r] : q4[r + 2], keep = hi3 ? q4[r + 2] : q4[r];
+        q2[r] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    }
+    {
+        const float give = hi2 ? q2[0] : q2[1], keep = hi2 ? q2[1] : q2[0];
+        q1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+    }
+    q1 += __shfl_xor_sync(0xffffffffu, q1, 2);
+    q1 += __shfl_xor_sync(0xffffffffu, q1, 1);
+    const int r = (hi4 ? 4 : 0) + (hi3 ? 2 : 0) + (hi2 ? 1 : 0);
+    // the row's featurizer outputs sit on lanes 3 r (q), 3 r + 1 (k), 3 r + 2 (v)
+    const float q = __shfl_sync(0xffffffffu, z, 3 * r), kk = __shfl_sync(0xffffffffu, z, 3 * r + 1),
+                v = __shfl_sync(0xffffffffu, z, 3 * r + 2);
+    if ((lane & 3) == 0) {
+        const float kv = round_io<T>(kk * v);
+        (p.inner_state_out + row0 * C)[r * C + C - 1] = kv;
+        float f = fmaf(tu, kv, q1);
+        if (p.bias_mode != VTX_BIAS_NONE) {
+            const float bias = ld_param(p.bias, p.bias_dtype, d0 + r);
+            f = p.bias_mode == VTX_BIAS_GATED ? fmaf(bias, kv, f) : f + bias;
+        }
+        static_cast<T*>(p.y)[row0 + r] = from_f32<T>(round_io<T>(f) * q);
+    }
+}
+
 // Short FIR layer (K == 7: six cached samples per row), four consecutive rows per thread: the thread's 24 cache
 // values are contiguous and 16-byte aligned, so they move as six 16-byte loads and six 16-byte stores.
 template <typename T>
@@ -289,7 +394,7 @@ __global__ void __launch_bounds__(256) decode_fir7_kernel(vtx_decode_layer_param
     constexpr int K = 7, c = 6, RT = 4;
     const int64_t row0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * RT;
     if (row0 >= p.B * p.D) return;
-    const int64_t b = row0 / p.D, d0 = row0 % p.D;
+    const int64_t b = div32(row0, p.D), d0 = row0 - b * p.D;
     const float4* sin4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.inner_state_in) + row0 * c);
     float4 v[6];
 #pragma unroll
@@ -298,11 +403,13 @@ __global__ void __launch_bounds__(256) decode_fir7_kernel(vtx_decode_layer_param
 #pragma unroll
     for (int j = 0; j < 6; ++j) { s[4 * j] = v[j].x; s[4 * j + 1] = v[j].y; s[4 * j + 2] = v[j].z; s[4 * j + 3] = v[j].w; }
     const bool flip = p.flip_filter != 0;
-    const int64_t cpg = p.D / p.G;
+    const int cpg = div32(p.D, p.G);
+    int g_row = div32(d0, cpg), g_rem = (int)d0 - g_row * cpg;
     float o[RT * c];
 #pragma unroll
     for (int r = 0; r < RT; ++r) {
-        const int64_t d = d0 + r, g = d / cpg;
+        const int64_t d = d0 + r, g = g_row;
+        if (++g_rem == cpg) { g_rem = 0; ++g_row; }
         float q, kv;
         featurizer_step3<T>(p, b, d, q, kv);
         float acc = 0.f;
@@ -333,9 +440,9 @@ __global__ void __launch_bounds__(256) decode_iir_tile_kernel(vtx_decode_layer_p
     const int lane = threadIdx.x % 16, hw = threadIdx.x / 16;
     const unsigned mask = 0xffffu << (threadIdx.x % 32 - lane);
     const int S = (int)p.modal.S;
-    const int64_t cpg = p.D / p.modal.G;
+    const int64_t cpg = div32(p.D, p.modal.G);
     // block -> (batch slab, first group): blockIdx.x = slab * (G / gpb) + group block
-    const int64_t gblocks = p.modal.G / gpb, g0 = (blockIdx.x % gblocks) * gpb, slab = blockIdx.x / gblocks;
+    const int64_t gblocks = div32(p.modal.G, gpb), slab = div32(blockIdx.x, gblocks), g0 = ((int64_t)blockIdx.x - slab * gblocks) * gpb;
     for (int i = threadIdx.x; i < gpb * 16; i += blockDim.x) {
         const int gl = i / 16, sp = i % 16;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -415,14 +522,14 @@ __global__ void __launch_bounds__(256) decode_iir_quad_kernel(vtx_decode_layer_p
     const int part = (int)(tid & 3);
     if (row >= p.B * p.D) return;                  // rows are whole quads: a quad leaves together
     const unsigned mask = 0xfu << ((threadIdx.x & 31) & ~3);
-    const int64_t b = row / p.D, d = row % p.D, g = d / (p.D / p.modal.G);
+    const int64_t b = div32(row, p.D), d = row - b * p.D, g = div32(d, div32(p.D, p.modal.G));
     // state and parameters first: the longest latencies
     const float4 s = reinterpret_cast<const float4*>(p.iir_state_in + row * 16)[part];
     const float4 lp = reinterpret_cast<const float4*>(static_cast<const float*>(p.modal.log_poles) + g * 16)[part];
     const float4 rr = reinterpret_cast<const float4*>(static_cast<const float*>(p.modal.res_re) + g * 16)[part];
     float z = 0.f;
     if (part < 3) {
-        QkvMap map{(int)p.layout, (int)p.flip_x1x2, p.D, p.num_heads > 0 ? p.D / p.num_heads : p.D};
+        const QkvMap map = qkv_map(p);
         int64_t ch[3];
         map.get(d, ch[0], ch[1], ch[2]);
         const int64_t c = part == 0 ? ch[0] : part == 1 ? ch[1] : ch[2], so = (b * 3 * p.D + c) * 2;
@@ -460,6 +567,7 @@ extern "C" int vtx_step_fir(const vtx_step_fir_params* p, void* stream) {
     using namespace vtx;
     VTX_REQUIRE(p && p->u && p->w && p->y, VTX_ERR_BAD_ARG, "step_fir: null pointer");
     VTX_REQUIRE(p->B > 0 && p->C > 0 && p->K > 0 && p->Gw > 0, VTX_ERR_BAD_ARG, "step_fir: sizes must be positive");
+    VTX_REQUIRE(p->B * p->C < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "step_fir: more than 2^31 rows");
     VTX_REQUIRE(p->C % p->Gw == 0, VTX_ERR_BAD_ARG, "step_fir: C not a multiple of the filter count");
     VTX_REQUIRE(p->c >= 0 && p->c <= p->K - 1, VTX_ERR_BAD_ARG, "step_fir: cache length %lld outside [0, K-1]",
                 (long long)p->c);
@@ -482,6 +590,7 @@ extern "C" int vtx_step_iir(const vtx_step_iir_params* p, void* stream) {
     VTX_REQUIRE(p && p->q && p->k && p->v && p->y && p->state_in && p->state_out, VTX_ERR_BAD_ARG,
                 "step_iir: null pointer");
     VTX_REQUIRE(p->B > 0 && p->D > 0, VTX_ERR_BAD_ARG, "step_iir: sizes must be positive");
+    VTX_REQUIRE(p->B * p->D < ((int64_t)1 << 31), VTX_ERR_UNSUPPORTED, "step_iir: more than 2^31 rows");
     VTX_REQUIRE(p->modal.log_poles && p->modal.res_re && p->modal.G > 0 && p->modal.S > 0, VTX_ERR_BAD_ARG,
                 "step_iir: bad modal parameters");
     VTX_REQUIRE(p->D % p->modal.G == 0, VTX_ERR_BAD_ARG, "step_iir: D not a multiple of the number of modal systems");
@@ -497,6 +606,7 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
     VTX_REQUIRE(p && p->u && p->w3 && p->y, VTX_ERR_BAD_ARG, "decode_layer: null pointer");
     VTX_REQUIRE(p->B > 0 && p->D > 0 && p->K3 >= 1 && p->K3 <= 8 && p->K >= 0, VTX_ERR_BAD_ARG,
                 "decode_layer: bad sizes");
+    VTX_REQUIRE(p->B * p->D < ((int64_t)1 << 29), VTX_ERR_UNSUPPORTED, "decode_layer: more than 2^29 rows");
     VTX_REQUIRE(p->K3 == 1 || (p->fir_state_in && p->fir_state_out), VTX_ERR_BAD_ARG, "decode_layer: null fir state");
     VTX_REQUIRE((const void*)p->fir_state_out != p->fir_state_in, VTX_ERR_BAD_ARG,
                 "decode_layer: fir_state_out aliases fir_state_in");
@@ -519,6 +629,8 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
                             reinterpret_cast<uintptr_t>(p->inner_state_out) % 16 == 0;
         VTX_DISPATCH_IO(p->io_dtype, T, {
             if (short7) decode_fir7_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 4, 256), 256, 0, s>>>(*p);
+            else if (tiled && p->K == 128 && (p->D / p->G) % 8 == 0)
+                decode_fir127_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);
             else if (tiled) decode_fir_tile_kernel<T, 8><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);
             else if (p->K > 17) decode_layer_kernel<T, 32, 0><<<(unsigned)ceil_div<int64_t>(rows * 32, 256), 256, 0, s>>>(*p);
             else decode_layer_kernel<T, 1, 0><<<(unsigned)ceil_div<int64_t>(rows, 256), 256, 0, s>>>(*p);
