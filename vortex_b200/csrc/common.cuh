@@ -57,6 +57,17 @@ __device__ __forceinline__ float ld_param(const void* p, int64_t dtype, int64_t 
     return __half2float(static_cast<const __half*>(p)[i]);
 }
 
+// Raw bits of parameter i and their value, kept apart so that a thread can issue every load of its set-up before it
+// uses the first result (one memory round trip instead of one per parameter: ld_param's dtype branches end a basic
+// block at every call).
+__device__ __forceinline__ uint32_t ld_raw(const void* p, bool wide, int64_t i) {
+    return wide ? static_cast<const uint32_t*>(p)[i] : (uint32_t) static_cast<const unsigned short*>(p)[i];
+}
+__device__ __forceinline__ float cvt_raw(uint32_t raw, int64_t dtype) {
+    return dtype == VTX_F32 ? __uint_as_float(raw)
+           : dtype == VTX_BF16 ? __uint_as_float(raw << 16) : __half2float(__ushort_as_half((unsigned short)raw));
+}
+
 // ---- q / k / v channel map -------------------------------------------------
 struct QkvMap {
     int layout;

@@ -431,6 +431,86 @@ __global__ void __launch_bounds__(256) decode_fir7_kernel(vtx_decode_layer_param
     for (int j = 0; j < 6; ++j) sout4[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
 }
 
+// The same layer for interleaved q/k/v (Evo 2's layout): the 12 packed channels of the thread's four hidden channels are
+// neighbours, so their featurizer caches are six 16-byte vectors in and out, and every load of the thread (caches,
+// tokens, raw parameter bits) is issued before the first use: one memory round trip, a few hundred instructions less
+// than four calls of the general featurizer step.  Needs groups that are whole quads of channels.
+template <typename T>
+__global__ void __launch_bounds__(64) decode_fir7i_kernel(vtx_decode_layer_params p) {
+    constexpr int K = 7, c = 6, RT = 4;
+    const int64_t row0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * RT;
+    if (row0 >= p.B * p.D) return;
+    const int64_t b = div32(row0, p.D), d0 = row0 - b * p.D, c0 = b * 3 * p.D + 3 * d0;      // first packed channel
+    const float4* sin4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.inner_state_in) + row0 * c);
+    const float4* fin4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.fir_state_in) + c0 * 2);
+    float4 v[6], f[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) { v[j] = sin4[j]; f[j] = fin4[j]; }
+    T ur[12];
+#pragma unroll
+    for (int i = 0; i < 12; ++i) ur[i] = static_cast<const T*>(p.u)[c0 + i];
+    const bool w_wide = p.w3_dtype == VTX_F32, h_wide = p.h_dtype == VTX_F32;
+    uint32_t wr[36], hr[K], br[12], dr[RT];
+    const int64_t w0 = (3 * d0) * 3, hb = (int64_t)div32(d0, div32(p.D, p.G)) * K;
+#pragma unroll
+    for (int i = 0; i < 36; ++i) wr[i] = ld_raw(p.w3, w_wide, w0 + i);
+#pragma unroll
+    for (int i = 0; i < K; ++i) hr[i] = ld_raw(p.h, h_wide, hb + i);
+#pragma unroll
+    for (int i = 0; i < 12; ++i) br[i] = p.b3 ? ld_raw(p.b3, p.b3_dtype == VTX_F32, 3 * d0 + i) : 0u;
+#pragma unroll
+    for (int r = 0; r < RT; ++r) dr[r] = p.bias_mode != VTX_BIAS_NONE ? ld_raw(p.bias, p.bias_dtype == VTX_F32, d0 + r) : 0u;
+
+    const float fs[24] = {f[0].x, f[0].y, f[0].z, f[0].w, f[1].x, f[1].y, f[1].z, f[1].w, f[2].x, f[2].y, f[2].z, f[2].w,
+                          f[3].x, f[3].y, f[3].z, f[3].w, f[4].x, f[4].y, f[4].z, f[4].w, f[5].x, f[5].y, f[5].z, f[5].w};
+    float z[12], fo[24];
+#pragma unroll
+    for (int i = 0; i < 12; ++i) {
+        const float x = to_f32<T>(ur[i]);
+        float acc = cvt_raw(wr[3 * i + 2], p.w3_dtype) * x;
+        acc = fmaf(fs[2 * i], cvt_raw(wr[3 * i], p.w3_dtype), acc);
+        acc = fmaf(fs[2 * i + 1], cvt_raw(wr[3 * i + 1], p.w3_dtype), acc);
+        if (p.b3) acc += cvt_raw(br[i], p.b3_dtype);
+        z[i] = round_io<T>(acc);
+        fo[2 * i] = fs[2 * i + 1];
+        fo[2 * i + 1] = x;
+    }
+    float4* fout4 = reinterpret_cast<float4*>(p.fir_state_out + c0 * 2);
+#pragma unroll
+    for (int j = 0; j < 6; ++j) fout4[j] = make_float4(fo[4 * j], fo[4 * j + 1], fo[4 * j + 2], fo[4 * j + 3]);
+
+    const float s[RT * c] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w, v[2].x, v[2].y, v[2].z, v[2].w,
+                             v[3].x, v[3].y, v[3].z, v[3].w, v[4].x, v[4].y, v[4].z, v[4].w, v[5].x, v[5].y, v[5].z, v[5].w};
+    const bool flip = p.flip_filter != 0, swap = p.flip_x1x2 != 0;
+    float tap[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) tap[i] = cvt_raw(hr[i], p.h_dtype);
+    float o[RT * c], y[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+        const float q = swap ? z[3 * r + 1] : z[3 * r], k = swap ? z[3 * r] : z[3 * r + 1];
+        const float kv = round_io<T>(k * z[3 * r + 2]);
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < c; ++i) {
+            acc = fmaf(s[r * c + i], flip ? tap[c - i] : tap[i], acc);
+            if (i >= 1) o[r * c + i - 1] = s[r * c + i];
+        }
+        o[r * c + c - 1] = kv;
+        float fv = fmaf(flip ? tap[0] : tap[c], kv, acc);
+        if (p.bias_mode != VTX_BIAS_NONE) {
+            const float bias = cvt_raw(dr[r], p.bias_dtype);
+            fv = p.bias_mode == VTX_BIAS_GATED ? fmaf(bias, kv, fv) : fv + bias;
+        }
+        y[r] = round_io<T>(fv) * q;
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r) static_cast<T*>(p.y)[row0 + r] = from_f32<T>(y[r]);
+    float4* sout4 = reinterpret_cast<float4*>(p.inner_state_out + row0 * c);
+#pragma unroll
+    for (int j = 0; j < 6; ++j) sout4[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+}
+
 // Modal layer, RW rows per half-warp (lane = pole).  A block of 16 half-warps covers GPB channel groups of BPB batch
 // elements; the groups' pole and residue parameters (expf, sincosf) are evaluated once per block into shared memory
 // instead of once per tile.
@@ -528,18 +608,24 @@ __global__ void __launch_bounds__(256) decode_iir_quad_kernel(vtx_decode_layer_p
     const float4 lp = reinterpret_cast<const float4*>(static_cast<const float*>(p.modal.log_poles) + g * 16)[part];
     const float4 rr = reinterpret_cast<const float4*>(static_cast<const float*>(p.modal.res_re) + g * 16)[part];
     float z = 0.f;
+    const uint32_t draw = (part == 0 && p.bias) ? ld_raw(p.bias, p.bias_dtype == VTX_F32, d) : 0u;
     if (part < 3) {
         const QkvMap map = qkv_map(p);
         int64_t ch[3];
         map.get(d, ch[0], ch[1], ch[2]);
         const int64_t c = part == 0 ? ch[0] : part == 1 ? ch[1] : ch[2], so = (b * 3 * p.D + c) * 2;
+        // every load of the featurizer step before the first use (raw parameter bits: no dtype branch in between)
         const float2 st = *reinterpret_cast<const float2*>(static_cast<const float*>(p.fir_state_in) + so);
-        const float x = to_f32<T>(static_cast<const T*>(p.u)[b * 3 * p.D + c]);
-        float acc = ld_param(p.w3, p.w3_dtype, c * 3 + 2) * x;
-        acc = fmaf(st.x, ld_param(p.w3, p.w3_dtype, c * 3), acc);
-        acc = fmaf(st.y, ld_param(p.w3, p.w3_dtype, c * 3 + 1), acc);
+        const T xr = static_cast<const T*>(p.u)[b * 3 * p.D + c];
+        const bool wide = p.w3_dtype == VTX_F32;
+        const uint32_t w0 = ld_raw(p.w3, wide, c * 3), w1 = ld_raw(p.w3, wide, c * 3 + 1), w2 = ld_raw(p.w3, wide, c * 3 + 2);
+        const uint32_t b3r = p.b3 ? ld_raw(p.b3, p.b3_dtype == VTX_F32, c) : 0u;
+        const float x = to_f32<T>(xr);
+        float acc = cvt_raw(w2, p.w3_dtype) * x;
+        acc = fmaf(st.x, cvt_raw(w0, p.w3_dtype), acc);
+        acc = fmaf(st.y, cvt_raw(w1, p.w3_dtype), acc);
         *reinterpret_cast<float2*>(p.fir_state_out + so) = make_float2(st.y, x);
-        if (p.b3) acc += ld_param(p.b3, p.b3_dtype, c);
+        if (p.b3) acc += cvt_raw(b3r, p.b3_dtype);
         z = round_io<T>(acc);
     }
     const float q = __shfl_sync(mask, z, 0, 4), k = __shfl_sync(mask, z, 1, 4), v = __shfl_sync(mask, z, 2, 4);
@@ -554,7 +640,7 @@ __global__ void __launch_bounds__(256) decode_iir_quad_kernel(vtx_decode_layer_p
     sum += __shfl_xor_sync(mask, sum, 1, 4);
     sum += __shfl_xor_sync(mask, sum, 2, 4);
     if (part == 0) {
-        const float bias = p.bias ? ld_param(p.bias, p.bias_dtype, d) : 0.f;
+        const float bias = p.bias ? cvt_raw(draw, p.bias_dtype) : 0.f;
         float skip = bias * kv;
         if (p.bias && p.bias_dtype != VTX_F32) skip = round_io<T>(skip);
         static_cast<T*>(p.y)[row] = from_f32<T>(q * (sum + skip));
@@ -628,7 +714,12 @@ extern "C" int vtx_decode_layer(const vtx_decode_layer_params* p, void* stream) 
                             p->inner_state_dtype == VTX_F32 && reinterpret_cast<uintptr_t>(p->inner_state_in) % 16 == 0 &&
                             reinterpret_cast<uintptr_t>(p->inner_state_out) % 16 == 0;
         VTX_DISPATCH_IO(p->io_dtype, T, {
-            if (short7) decode_fir7_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 4, 256), 256, 0, s>>>(*p);
+            const bool inter7 = short7 && p->layout == VTX_QKV_INTERLEAVED && (p->D / p->G) % 4 == 0 &&
+                                reinterpret_cast<uintptr_t>(p->fir_state_in) % 16 == 0 &&
+                                reinterpret_cast<uintptr_t>(p->fir_state_out) % 16 == 0;
+            // (64-thread blocks: at ~140 registers per thread that is what lets B=64 x 4096 channels be resident at once)
+            if (inter7) decode_fir7i_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 4, 64), 64, 0, s>>>(*p);
+            else if (short7) decode_fir7_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 4, 256), 256, 0, s>>>(*p);
             else if (tiled && p->K == 128 && (p->D / p->G) % 8 == 0)
                 decode_fir127_kernel<T><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);
             else if (tiled) decode_fir_tile_kernel<T, 8><<<(unsigned)ceil_div<int64_t>(rows / 8 * 32, 256), 256, 0, s>>>(*p);

@@ -524,16 +524,6 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     return v;
 }
 
-// Raw bits of parameter i (run-time dtype) and their value: kept apart so that a thread can issue every load of its
-// set-up before it uses the first result (one memory round trip instead of one per parameter).
-__device__ __forceinline__ uint32_t ld_raw(const void* p, bool wide, int64_t i) {
-    return wide ? static_cast<const uint32_t*>(p)[i] : (uint32_t) static_cast<const unsigned short*>(p)[i];
-}
-__device__ __forceinline__ float cvt_raw(uint32_t raw, int64_t dtype) {
-    return dtype == VTX_F32 ? __uint_as_float(raw)
-           : dtype == VTX_BF16 ? __uint_as_float(raw << 16) : __half2float(__ushort_as_half((unsigned short)raw));
-}
-
 // Per-thread state of the staged kernels: the modal system as packed pairs, the featurizer of k and v as one packed
 // stream, the featurizer of q as a scalar one.  The output of a sample uses the state BEFORE the sample,
 //   y[t] = q[t] (sum_s (R_s p_s) sigma_s[t-1] + (sum_s R_s + bias) kv[t]),
