@@ -208,11 +208,12 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         // (item-agnostic: the rows arrive staged; only the featurizer taps depend on the group)
         const int w = warp, p = lane % 8, s = lane / 8;
         f32x2 w3[3][3];     // [q|k|v][tap], each the pair of this lane's two channels (of the current item's group)
-        // featurizer taps of item t: staged in shared memory by the epilogue warps together with the item's Toeplitz
-        // operand (a_ready); [feature][tap][channel] fp32, this lane's two channels as one 8-byte load
+        // featurizer taps of item t: staged in shared memory by the epilogue warps before they expand the item's Toeplitz
+        // operand (taps_ready: the front end of a launch's first item starts while that expansion still runs);
+        // [feature][tap][channel] fp32, this lane's two channels as one 8-byte load
         auto load_w3 = [&](int t) {
             if (!FEAT) return true;
-            if (!mbar_wait(a_ready(t & 1), (uint32_t)((t >> 1) & 1), 17)) return false;
+            if (!mbar_wait(taps_ready(t & 1), (uint32_t)((t >> 1) & 1), 17)) return false;
             const uint32_t base = sm_u + OFF_W3S + (uint32_t)((t & 1) * W3S_BYTES) + 8u * (uint32_t)p;
 #pragma unroll
             for (int x = 0; x < 3; ++x)
