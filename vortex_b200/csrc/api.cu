@@ -72,8 +72,10 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int64_t dtype, int64_t cols
                             : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                             : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
                                                   : CU_TENSOR_MAP_SWIZZLE_NONE;
+    // 256-byte L2 promotion: the row pieces of neighbouring CTAs are neighbours in memory (measured on the fused FIR
+    // kernel against none / 64 / 128 bytes: 1 % faster than 128, 2 % faster than 64)
     CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(VTX_ERR_BAD_ARG, "%s: cuTensorMapEncodeTiled failed with CUresult %d", who, (int)r);
     return VTX_OK;
 }

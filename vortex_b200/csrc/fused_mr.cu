@@ -335,21 +335,42 @@ __global__ void __launch_bounds__(THREADS, 1) fused_mr_kernel(const __grid_const
         auto expand = [&](int t) {
             const int g = item_group(t), ab = t & 1;
             uint16_t* tp = reinterpret_cast<uint16_t*>(smp(OFF_TAPS + ab * 768));
-            for (int m = r; m < 384; m += 128) {
-                const int l = m - 128;
-                float v = 0.f;
-                if (l >= 0 && l < K) v = KV_UNSCALE * ld_param(a.h, a.h_dtype, ((int64_t)g * CH / a.dg) * K + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l));
-                tp[m] = f16_bits(v);
+            // every global load of the staging first (raw bits, no dtype branch in between): one memory round trip
+            // instead of five, which at the start of a launch is what the front end waits for
+            const bool h_wide = a.h_dtype == VTX_F32, w_wide = a.w3_dtype == VTX_F32;
+            const int64_t hrow = (int64_t)((unsigned)(g * CH) / (unsigned)a.dg) * K;      // the group's filter row
+            uint32_t traw[3], braw = 0, wraw[2] = {0, 0};
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const int l = r + 128 * i - 128;
+                traw[i] = (l >= 0 && l < K) ? ld_raw(a.h, h_wide, hrow + (a.taps == VTX_TAPS_CONV ? l : K - 1 - l)) : 0u;
             }
-            if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? KV_UNSCALE * ld_param(a.bias, a.bias_dtype, (int64_t)g * CH + r) : 0.f;
+            if (r < CH && a.has_bias) braw = ld_raw(a.bias, a.bias_dtype == VTX_F32, (int64_t)g * CH + r);
             if (FEAT) {   // featurizer taps of the group's 16 channels (the front end picks them up at the item's first chunk)
                 QkvMap map{a.layout, INTERLEAVED ? 0 : a.flip, a.D, a.hd};
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int m = r + 128 * i;
+                    if (m < 3 * 3 * CH) {
+                        const int c = m % CH, j = (m / CH) % 3, x = m / (3 * CH);
+                        int64_t pc[3];
+                        map.get((int64_t)g * CH + c, pc[0], pc[1], pc[2]);
+                        wraw[i] = ld_raw(a.w3, w_wide, (x == 0 ? pc[0] : x == 1 ? pc[1] : pc[2]) * 3 + j);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const int l = r + 128 * i - 128;
+                tp[r + 128 * i] = f16_bits((l >= 0 && l < K) ? KV_UNSCALE * cvt_raw(traw[i], a.h_dtype) : 0.f);
+            }
+            if (r < CH) reinterpret_cast<float*>(smp(OFF_DIAG + ab * 64))[r] = a.has_bias ? KV_UNSCALE * cvt_raw(braw, a.bias_dtype) : 0.f;
+            if (FEAT) {
                 float* w3s = reinterpret_cast<float*>(smp(OFF_W3S + ab * W3S_BYTES));
-                for (int m = r; m < 3 * 3 * CH; m += 128) {
-                    const int c = m % CH, j = (m / CH) % 3, x = m / (3 * CH);
-                    int64_t pc[3];
-                    map.get((int64_t)g * CH + c, pc[0], pc[1], pc[2]);
-                    w3s[m] = ld_param(a.w3, a.w3_dtype, pc[x] * 3 + j) * (x == 2 ? KV_SCALE : 1.f);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int m = r + 128 * i;
+                    if (m < 3 * 3 * CH) w3s[m] = cvt_raw(wraw[i], a.w3_dtype) * (m / (3 * CH) == 2 ? KV_SCALE : 1.f);
                 }
             }
             __syncwarp();
