@@ -370,8 +370,9 @@ __global__ void licc_carry_kernel(Args a) {
         cr = a.state_in[row * SS + (CPLX ? 2 * s : s)];
         if (CPLX) ci = a.state_in[row * SS + 2 * s + 1];
     }
-    // the end states of CB segments are read together (independent loads), then scanned and overwritten
-    constexpr int CB = 8;
+    // the end states of CB segments are read together (independent loads: the kernel is bound by memory latency),
+    // then scanned and overwritten
+    constexpr int CB = CPLX ? 8 : 24;       // (real systems: half the registers per segment, three times the loads in flight)
     const int64_t nseg = a.pl.nseg, seg_stride = (int64_t)SS * rows;
     float* e0 = a.scratch + (int64_t)(CPLX ? 2 * s : s) * rows + row;
     for (int64_t sb = 0; sb < nseg; sb += CB) {
