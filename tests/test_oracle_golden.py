@@ -227,3 +227,23 @@ def test_long_fir_threshold(golden, io, thr):
     k = f"iirfir_{io}_thr{thr}"
     y = O.long_fir_gate(golden[k + "_z"], golden[k + "_h"], golden[k + "_D"], 16, thr, io=io)
     close(y, golden[k + "_y"], io)
+
+
+def test_hyena_ops_backward_matches_autograd():
+    """The oracle's backward against torch autograd through a plain float64 forward (F.conv1d on the gated product),
+    on a shape the golden vectors do not hold: ragged length, three groups of four channels, seven taps."""
+    import torch
+    import torch.nn.functional as F
+
+    g = torch.Generator().manual_seed(0)
+    bs, l, G, dg, hl = 2, 53, 3, 4, 7
+    x, B, C = (torch.randn(bs, l, G, dg, generator=g, dtype=torch.float64, requires_grad=True) for _ in range(3))
+    h = torch.randn(G, 1, hl, generator=g, dtype=torch.float64, requires_grad=True)
+    y2 = F.conv1d((B * x).reshape(bs, l, G * dg).permute(0, 2, 1), h.repeat_interleave(dg, 0), groups=G * dg,
+                  padding=hl - 1)[..., :l]
+    y = C * y2.permute(0, 2, 1).reshape(bs, l, G, dg)
+    dy = torch.randn(bs, l, G, dg, generator=g, dtype=torch.float64)
+    y.backward(dy)
+    got = O.gcg_blgdg_bwd(dy.numpy(), x.detach().numpy(), B.detach().numpy(), C.detach().numpy(), h.detach().numpy())
+    for a, b in zip(got, (x.grad, B.grad, C.grad, h.grad)):
+        assert np.abs(a - b.numpy()).max() < 1e-12
