@@ -673,3 +673,65 @@ def test_fused_mr_call_cut_into_launches():
            "Dp": Dp[d0:d1].cpu()}
     ref, _, _ = _oracle(sub, d1 - d0, K, "bf16", "interleaved")
     check("call cut into launches: y[b, :, d0:d1], ref", rel_l2(y[b:b + 1, :, d0:d1], ref), TOL["bf16"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,layout,heads,flip,flip_filter,with_b3,G", [
+    ("mr", "split", 1, True, False, True, 12),            # taps not flipped, q and k swapped, featurizer bias, groups of 8
+    ("mr", "column_split", 4, False, True, False, 6),
+    ("se", "interleaved", 1, True, True, True, 24),       # q and k swapped on the interleaved fast path, groups of 4
+    ("se", "split", 1, False, False, False, 6),
+    ("li", "column_split", 2, True, False, True, 96),
+])
+def test_decode_layer_variants_match_step_sequence(kind, layout, heads, flip, flip_filter, with_b3, G):
+    """The specialised one-token kernels under the other channel maps, tap orders and with a featurizer bias, against
+    the step sequence of the drop-in engine (bf16 I/O, fp32 caches from the second step on)."""
+    from vortex_b200 import HyenaInferenceEngine, ops
+    eng = HyenaInferenceEngine()
+    B, D = 2, 96
+    K = {"se": 7, "mr": 128, "li": 0}[kind]
+    g = torch.Generator().manual_seed(23)
+    dt = torch.bfloat16
+    w3 = (torch.randn(3 * D, 1, 3, generator=g) / 3 ** 0.5).to(dt).cuda()
+    b3 = (0.1 * torch.randn(3 * D, generator=g)).to(dt).cuda() if with_b3 else None
+    fs = torch.randn(B, 3 * D, 2, generator=g).to(dt).cuda()
+    Dp = torch.randn(D, generator=g).to(dt).cuda()
+    if kind == "li":
+        lp = torch.log(0.9 + 0.099 * torch.rand(G, 16, 1, generator=g)).cuda()
+        R = torch.randn(G, 16, generator=g).cuda()
+        st = torch.randn(B, D, 16, generator=g).cuda()
+    else:
+        h = (torch.randn(G, 1, K, generator=g) / K ** 0.5).to(dt).cuda()
+        st = torch.randn(B, D, K - 1, generator=g).to(dt).cuda()
+
+    def qkv(z):
+        if layout == "interleaved":
+            q, k, v = z[:, 0::3], z[:, 1::3], z[:, 2::3]
+        elif layout == "split":
+            q, k, v = z[:, :D], z[:, D:2 * D], z[:, 2 * D:]
+        else:
+            z4 = z.reshape(B, heads, 3, D // heads)
+            q, k, v = (z4[:, :, i].reshape(B, D) for i in range(3))
+        return (k, q, v) if flip else (q, k, v)
+
+    fs_a, st_a, fs_b, st_b = fs, st, fs, st
+    for step in range(3):
+        u = torch.randn(B, 3 * D, generator=g).to(dt).cuda()
+        z, fs_a = eng.step_fir(u, fs_a, w3, bias=b3)
+        q, k, v = qkv(z)
+        if kind == "li":
+            ya, st_a = eng.step_iir(q, k, v, Dp, R.repeat_interleave(D // G, 0), lp.repeat_interleave(D // G, 0), st_a)
+            ya = ya.to(dt)
+            yb, fs_b, st_b = ops.decode_layer(u, w3, b3, fs_b, D, log_poles=lp, residues=R, bias=Dp, iir_state=st_b,
+                                              layout=layout, num_heads=heads, flip=flip)
+        else:
+            ya, st_a = eng.step_fir(k * v, st_a, h.repeat_interleave(D // G, 0), bias=Dp if K >= 128 else None,
+                                    flip_filter=flip_filter, gated_bias=K >= 128)
+            ya = ya * q
+            yb, fs_b, st_b = ops.decode_layer(u, w3, b3, fs_b, D, h=h, inner_state=st_b, bias=Dp if K >= 128 else None,
+                                              flip_filter=flip_filter, gated_bias=K >= 128, layout=layout, num_heads=heads,
+                                              flip=flip)
+        assert torch.equal(fs_a, fs_b)
+        check(f"decode variants {kind}/{layout} step {step}: y", rel_l2(yb, ya), 2e-3)
+        check(f"decode variants {kind}/{layout} step {step}: state", rel_l2(st_b, st_a), 1e-6)
+    ops.device_status()
